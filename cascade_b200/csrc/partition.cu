@@ -1,0 +1,260 @@
+// K-gram sampling, splitter selection, partition ids and the scatter of suffix positions into partitions.
+// A partition is the set of suffixes whose K-gram (first CSA_K symbols, zero-padded past the text's end) lies
+// between two splitters, so it owns a fixed, contiguous range of the final suffix array.
+//
+// Reference behaviour followed: GPU_SACA::select_pivots (src/GPU_SACA.cu:290-364), compute_partition_IDs_kernel
+// (include/GPU_SACA.cuh:23-73) and the host scatter of GPU_SACA::partition (src/GPU_SACA.cu:795-826).
+#include "common.cuh"
+#include "part.cuh"
+
+#include <algorithm>
+#include <utility>
+#include <vector>
+
+namespace
+{
+
+__host__ __device__ __forceinline__ u64 mix64(u64 x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__global__ void sample_kgrams_kernel(const u16* __restrict__ T, const u64 n, const u64 n_samples, const u64 seed, u64* __restrict__ out)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= n_samples) return;
+    const u64 pos = mix64(seed * 0x100000001B3ull + i) % n;
+    out[2 * i] = pack4(T, pos);             // the zero padding after the text makes short suffixes pad with zeros
+    out[2 * i + 1] = pack4(T, pos + 4);
+}
+
+constexpr u32 BULK_WAIT_LIMIT = 1u << 16;   // each try may itself block for a while
+
+__device__ __forceinline__ u32 smem_addr(const void* p) { return u32(__cvta_generic_to_shared(p)); }
+
+// Copies `bytes` bytes (a multiple of 16, from a 16-byte aligned global address to a 16-byte aligned shared address)
+// with one bulk asynchronous copy that signals `bar`. Called by one thread.
+__device__ __forceinline__ void bulk_copy_to_shared(void* dst, const void* src, u32 bytes, u64* bar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_addr(bar)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+
+// Waits, with a bound, for phase `parity` of `bar`. Returns false if the bound ran out.
+__device__ __forceinline__ bool bulk_wait(u64* bar, u32 parity)
+{
+    for(u32 spin = 0; spin < BULK_WAIT_LIMIT; ++spin)
+    {
+        u32 done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+        if(done) return true;
+    }
+    return false;
+}
+
+// Partition ids of the positions [first, first + count). A block takes a tile of BLOCK * ITEMS consecutive positions:
+// the text window of the tile (tile + K - 1 symbols) arrives in shared memory by one bulk copy, a thread slides a
+// K-gram over its ITEMS positions and searches the splitters, kept in shared memory too.
+template <int BLOCK, int ITEMS>
+__global__ void __launch_bounds__(BLOCK) partition_ids_kernel(const u16* __restrict__ T, const u64 n, const u64 first, const u64 count,
+                                                             const u64* __restrict__ pivots, const u32 p, u16* __restrict__ pid_out,
+                                                             u64* __restrict__ hist, u64* __restrict__ dev_status)
+{
+    constexpr int TILE = BLOCK * ITEMS;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    u16* const win = reinterpret_cast<u16*>(smem_raw);                               // TILE + 8 symbols
+    u64* const bar = reinterpret_cast<u64*>(smem_raw + (TILE + 8) * 2);               // one mbarrier
+    u64* const piv = reinterpret_cast<u64*>(smem_raw + (TILE + 8) * 2 + 16);          // 2 (p-1) words
+    u32* const cnt = reinterpret_cast<u32*>(piv + 2 * (p > 1 ? p - 1 : 1));           // p counters
+
+    const u32 tid = threadIdx.x;
+    const u64 tile_first = first + u64(blockIdx.x) * TILE;          // `first` is a multiple of 8: the copy starts 16-byte aligned
+    const u64 tile_count = (first + count - tile_first < u64(TILE)) ? first + count - tile_first : u64(TILE);
+
+    if(tid == 0)
+    {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_addr(bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if(tid == 0)
+    {
+        // Readable symbols from the tile's start: the text and its zero padding, rounded down to whole 16-byte pieces.
+        const u64 readable = ((n + CSA_TEXT_PAD - tile_first) / 8) * 8;
+        const u64 want = TILE + 8;
+        bulk_copy_to_shared(win, T + tile_first, u32((readable < want ? readable : want) * 2), bar);
+    }
+    for(u32 i = tid; i < 2 * (p - 1); i += BLOCK) piv[i] = pivots[i];
+    for(u32 i = tid; i < p; i += BLOCK) cnt[i] = 0;
+    __syncthreads();
+    if(!bulk_wait(bar, 0))
+    {
+        atomicOr(dev_status, (u64)CSA_ST_BULK_TIMEOUT);
+        bulk_wait(bar, 0);      // a second bounded wait for the copy still in flight before the block leaves
+        return;
+    }
+
+    const u32 local = tid * ITEMS;
+    if(local < tile_count)
+    {
+        u64 hi = (u64(win[local]) << 48) | (u64(win[local + 1]) << 32) | (u64(win[local + 2]) << 16) | u64(win[local + 3]);
+        u64 lo = (u64(win[local + 4]) << 48) | (u64(win[local + 5]) << 32) | (u64(win[local + 6]) << 16) | u64(win[local + 7]);
+        u16 ids[ITEMS];
+        #pragma unroll
+        for(int k = 0; k < ITEMS; ++k)
+        {
+            // lower bound: the first splitter that is not smaller than the K-gram
+            u32 a = 0, b = p - 1;
+            while(a < b)
+            {
+                const u32 mid = (a + b) >> 1;
+                const u64 ph = piv[2 * mid], pl = piv[2 * mid + 1];
+                const bool le = (hi < ph) || (hi == ph && lo <= pl);
+                if(le) b = mid; else a = mid + 1;
+            }
+            ids[k] = u16(a);
+            if(local + k < tile_count) atomicAdd(&cnt[a], 1u);
+            hi = (hi << 16) | (lo >> 48);
+            lo = (lo << 16) | u64(win[local + k + 8]);
+        }
+        if(local + ITEMS <= tile_count)
+        {
+            if constexpr(ITEMS % 8 == 0)
+            {
+                uint4* dst = reinterpret_cast<uint4*>(pid_out + (tile_first - first) + local);
+                #pragma unroll
+                for(int k = 0; k < ITEMS; k += 8)
+                    dst[k / 8] = make_uint4(u32(ids[k]) | (u32(ids[k + 1]) << 16), u32(ids[k + 2]) | (u32(ids[k + 3]) << 16),
+                                            u32(ids[k + 4]) | (u32(ids[k + 5]) << 16), u32(ids[k + 6]) | (u32(ids[k + 7]) << 16));
+            }
+            else
+            {
+                #pragma unroll
+                for(int k = 0; k < ITEMS; ++k) pid_out[(tile_first - first) + local + k] = ids[k];
+            }
+        }
+        else
+        {
+            for(int k = 0; k < ITEMS; ++k)
+                if(local + k < tile_count) pid_out[(tile_first - first) + local + k] = ids[k];
+        }
+    }
+    __syncthreads();
+    for(u32 i = tid; i < p; i += BLOCK)
+        if(cnt[i]) atomicAdd(&hist[i], u64(cnt[i]));
+}
+
+// Scatter of positions by partition id. A block takes BLOCK * ITEMS positions: counts them by partition in shared
+// memory, reserves one run per partition with a single atomic on the partition's cursor, and writes every position
+// into its run. Runs of a partition from different blocks follow one another in the order the blocks reserve them.
+template <int BLOCK, int ITEMS>
+__global__ void __launch_bounds__(BLOCK) scatter_by_pid_kernel(const u16* __restrict__ pid, const u64 first, const u64 count, const u32 p,
+                                                              u32* const* __restrict__ part_base, u64* __restrict__ cursor)
+{
+    constexpr int TILE = BLOCK * ITEMS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    u64* const base = reinterpret_cast<u64*>(smem_raw);        // p
+    u32* const cnt = reinterpret_cast<u32*>(base + p);          // p
+    const u32 tid = threadIdx.x;
+    const u64 tile_first = u64(blockIdx.x) * TILE;
+    for(u32 i = tid; i < p; i += BLOCK) cnt[i] = 0;
+    __syncthreads();
+    u16 id[ITEMS];
+    u32 r[ITEMS];
+    #pragma unroll
+    for(int k = 0; k < ITEMS; ++k)
+    {
+        const u64 idx = tile_first + tid + u64(k) * BLOCK;
+        if(idx < count)
+        {
+            id[k] = pid[idx];
+            r[k] = atomicAdd(&cnt[id[k]], 1u);
+        }
+    }
+    __syncthreads();
+    for(u32 i = tid; i < p; i += BLOCK)
+        if(cnt[i]) base[i] = atomicAdd(&cursor[i], u64(cnt[i]));
+    __syncthreads();
+    #pragma unroll
+    for(int k = 0; k < ITEMS; ++k)
+    {
+        const u64 idx = tile_first + tid + u64(k) * BLOCK;
+        if(idx < count) part_base[id[k]][base[id[k]] + r[k]] = u32(first + idx);
+    }
+}
+
+}   // namespace
+
+extern "C" int csa_sample_kgrams(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t n_samples, uint64_t seed, uint64_t* samples)
+{
+    if(!ctx || !text || !samples || n == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_sample_kgrams: bad argument");
+    if(n_samples == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    sample_kgrams_kernel<<<unsigned(div_up(n_samples, 256)), 256, 0, ctx->stream>>>(text, n, n_samples, seed, reinterpret_cast<u64*>(samples));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_select_pivots(const uint64_t* samples, uint64_t n_samples, uint32_t p, uint64_t* pivots, uint32_t* p_out)
+{
+    if(!samples || !p_out || p == 0 || (p > 1 && !pivots)) return CSA_E_INVALID;
+    if(p > CSA_MAX_PARTITIONS) return CSA_E_LIMIT;
+    std::vector<std::pair<u64, u64>> s(n_samples);
+    for(u64 i = 0; i < n_samples; ++i) s[i] = {samples[2 * i], samples[2 * i + 1]};
+    std::sort(s.begin(), s.end());
+    u32 made = 0;
+    for(u32 j = 1; j < p && n_samples > 0; ++j)
+    {
+        const u64 at = (u64(j) * n_samples) / p;
+        const auto& c = s[at == 0 ? 0 : at - 1];
+        if(made > 0 && pivots[2 * (made - 1)] == c.first && pivots[2 * (made - 1) + 1] == c.second) continue;    // equal K-grams never split
+        pivots[2 * made] = c.first;
+        pivots[2 * made + 1] = c.second;
+        ++made;
+    }
+    *p_out = made + 1;
+    return CSA_OK;
+}
+
+constexpr int PID_BLOCK = 256, PID_ITEMS = 16;
+
+extern "C" int csa_partition_ids(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t first, uint64_t count, const uint64_t* pivots,
+                                 uint32_t p, uint16_t* pid, uint64_t* hist)
+{
+    if(!ctx || !text || !pid || !hist || p == 0 || (p > 1 && !pivots) || first + count > n) return csa_fail(ctx, CSA_E_INVALID, "csa_partition_ids: bad argument");
+    if(p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "csa_partition_ids: too many partitions");
+    if((reinterpret_cast<uintptr_t>(text) & 15) || (first & 7) || (reinterpret_cast<uintptr_t>(pid) & 15))
+        return csa_fail(ctx, CSA_E_INVALID, "csa_partition_ids: text and pid must be 16-byte aligned and `first` a multiple of 8");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    constexpr int TILE = PID_BLOCK * PID_ITEMS;
+    const size_t smem = (TILE + 8) * 2 + 16 + size_t(2) * (p > 1 ? p - 1 : 1) * 8 + size_t(p) * 4;
+    auto kern = partition_ids_kernel<PID_BLOCK, PID_ITEMS>;
+    CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(text, n, first, count, reinterpret_cast<const u64*>(pivots), p, pid,
+                                                                          reinterpret_cast<u64*>(hist), ctx->d_status);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_scatter_by_pid(csa_ctx* ctx, const uint16_t* pid, uint64_t first, uint64_t count, uint32_t p, uint32_t* const* part_base,
+                                  uint64_t* cursor)
+{
+    if(!ctx || !pid || !part_base || !cursor || p == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_by_pid: bad argument");
+    if(p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "csa_scatter_by_pid: too many partitions");
+    if(first + count > 0xFFFFFFFFull) return csa_fail(ctx, CSA_E_LIMIT, "csa_scatter_by_pid: positions must fit 32 bits");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    constexpr int TILE = PID_BLOCK * PID_ITEMS;
+    const size_t smem = size_t(p) * 12;
+    auto kern = scatter_by_pid_kernel<PID_BLOCK, PID_ITEMS>;
+    CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(pid, first, count, p, part_base, reinterpret_cast<u64*>(cursor));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}

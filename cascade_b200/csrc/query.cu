@@ -1,0 +1,358 @@
+// Batched count / locate queries over a suffix-array index: a sample table of packed K-grams (every stride-th
+// suffix) brackets each boundary of a query's interval, and a binary search of the suffix array inside the bracket
+// finds it exactly. Results equal ref::find_one's (include/CPU_Reference.hpp:42-73).
+//
+// Reference behaviour followed: Sample_Table build_kernel (src/Sample_Table.cu:26-31), the bracket rules of
+// table_kernel (src/Query_Engine.cu:205-279), search_kernel (:369-418) and certify_kernel (:665-686). Locate has no
+// counterpart there; it lists SA[lo + k] in rank order.
+#include "common.cuh"
+
+namespace
+{
+
+__global__ void table_build_kernel(const u16* __restrict__ T, const u8* __restrict__ sa40, const u64 n, const u64 stride, const u64 entries,
+                                   u64* __restrict__ table)
+{
+    const u64 j = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(j >= entries) return;
+    const u64 pos = sa40_load(sa40, j * stride);
+    if(pos >= n) { table[2 * j] = 0; table[2 * j + 1] = 0; return; }
+    table[2 * j] = pack4(T, pos);          // the text's zero padding pads short suffixes
+    table[2 * j + 1] = pack4(T, pos + 4);
+}
+
+// Order of the suffix at `pos`, truncated to m symbols, against the pattern: -1, 0 or 1; a suffix that ends before
+// m symbols while still matching is smaller (ref::cmp_suffix_pattern, include/CPU_Reference.hpp:26-36).
+__device__ __forceinline__ int cmp_suffix_pattern(const u16* __restrict__ T, const u64 n, const u64 pos, const u16* __restrict__ P, const u64 m)
+{
+    const u64 len = (n - pos < m) ? n - pos : m;
+    for(u64 i = 0; i < len; ++i)
+    {
+        const u16 a = T[pos + i], b = P[i];
+        if(a != b) return a < b ? -1 : 1;
+    }
+    return len < m ? -1 : 0;
+}
+
+__global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, const u16* __restrict__ sym, const u64 q, u64* __restrict__ itv)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= q) return;
+    const u64 n = idx.n, stride = idx.stride;
+    const u64 m = off[i + 1] - off[i];
+    const u16* const P = sym + (off[i] - off[0]);
+    if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = n; return; }
+
+    // The pattern's first min(m, K) symbols, packed like a table key, and the mask of those symbols.
+    const u32 mm = m < CSA_K ? u32(m) : u32(CSA_K);
+    u64 qh = 0, ql = 0;
+    for(u32 k = 0; k < mm; ++k)
+    {
+        if(k < 4) qh |= u64(P[k]) << (48 - 16 * k);
+        else ql |= u64(P[k]) << (48 - 16 * (k - 4));
+    }
+    const u64 mask_h = mm >= 4 ? ~0ull : ~0ull << (64 - 16 * mm);
+    const u64 mask_l = mm <= 4 ? 0ull : (mm == 8 ? ~0ull : ~0ull << (64 - 16 * (mm - 4)));
+
+    const u64 J = (n + stride - 1) / stride;
+    const ulonglong2* const tab = reinterpret_cast<const ulonglong2*>(idx.table);
+    // a = table keys (masked) smaller than the pattern's; b = those not greater.
+    u64 a, b;
+    {
+        u64 x = 0, y = J;
+        while(x < y)
+        {
+            const u64 mid = x + ((y - x) >> 1);
+            const ulonglong2 t = tab[mid];
+            const u64 th = t.x & mask_h, tl = t.y & mask_l;
+            if(th < qh || (th == qh && tl < ql)) x = mid + 1; else y = mid;
+        }
+        a = x;
+        y = J;
+        while(x < y)
+        {
+            const u64 mid = x + ((y - x) >> 1);
+            const ulonglong2 t = tab[mid];
+            const u64 th = t.x & mask_h, tl = t.y & mask_l;
+            if(th < qh || (th == qh && tl <= ql)) x = mid + 1; else y = mid;
+        }
+        b = x;
+    }
+
+    // Sampled rank j * stride carries table key j. Ranks up to (a-1) stride are smaller than the pattern; ranks from
+    // b stride on are greater.
+    const u64 L = (a == 0) ? 0 : (a - 1) * stride + 1;
+    const u64 R = (b >= J) ? n : b * stride;
+    u64 lo_last = R, hi_first = L;
+    if(m <= CSA_K)
+    {
+        // Every suffix whose masked key equals the pattern's matches it, except suffixes that end inside the pattern and
+        // owe the equality to zero padding; there are fewer than m of them and they need the pattern to end in a zero.
+        const u64 e = (P[m - 1] == 0) ? m - 1 : 0;
+        const u64 cap = a * stride + e;
+        if(cap < lo_last) lo_last = cap;
+        if(b > 0 && (b - 1) * stride + 1 > hi_first) hi_first = (b - 1) * stride + 1;
+    }
+
+    const u8* const SA = idx.sa40;
+    const u16* const T = idx.text;
+    u64 x = L, y = lo_last;
+    while(x < y)
+    {
+        const u64 mid = x + ((y - x) >> 1);
+        if(cmp_suffix_pattern(T, n, sa40_load(SA, mid), P, m) < 0) x = mid + 1; else y = mid;
+    }
+    const u64 lo = x;
+    x = (hi_first > lo) ? hi_first : lo;
+    y = R;
+    if(x > y) x = y;
+    while(x < y)
+    {
+        const u64 mid = x + ((y - x) >> 1);
+        if(cmp_suffix_pattern(T, n, sa40_load(SA, mid), P, m) <= 0) x = mid + 1; else y = mid;
+    }
+    itv[2 * i] = lo;
+    itv[2 * i + 1] = x;
+}
+
+// One warp per query: row i of pos receives SA[lo + k], k < min(max_pos, hi - lo).
+__global__ void locate_rows_kernel(const u8* __restrict__ sa40, const u64* __restrict__ itv, const u64 q, const u32 max_pos, u64* __restrict__ pos,
+                                   u32* __restrict__ cnt)
+{
+    const u64 w = (u64(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if(w >= q) return;
+    const u64 lo = itv[2 * w], hi = itv[2 * w + 1];
+    const u64 c = (hi - lo < max_pos) ? hi - lo : max_pos;
+    if(lane_id() == 0) cnt[w] = u32(c);
+    for(u64 k = lane_id(); k < c; k += 32) pos[w * max_pos + k] = sa40_load(sa40, lo + k);
+}
+
+// The same into one packed array: query i's positions start at pos_off[i].
+__global__ void locate_packed_kernel(const u8* __restrict__ sa40, const u64* __restrict__ itv, const u64 q, const u32 max_pos,
+                                     const u64* __restrict__ pos_off, u64* __restrict__ pos)
+{
+    const u64 w = (u64(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if(w >= q) return;
+    const u64 lo = itv[2 * w], hi = itv[2 * w + 1];
+    const u64 c = (hi - lo < max_pos) ? hi - lo : max_pos;
+    const u64 o = pos_off[w];
+    for(u64 k = lane_id(); k < c; k += 32) pos[o + k] = sa40_load(sa40, lo + k);
+}
+
+__global__ void counts_kernel(const u64* __restrict__ itv, const u64 q, const u32 max_pos, u32* __restrict__ cnt)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= q) return;
+    const u64 d = itv[2 * i + 1] - itv[2 * i];
+    cnt[i] = u32(d < max_pos ? d : max_pos);
+}
+
+// Exclusive prefix sums of 32-bit counts into 64-bit offsets (off[count] = total), in three steps without waits:
+// block sums, a one-block scan of them, and the per-block scans.
+constexpr int SCAN_BLOCK = 256, SCAN_ITEMS = 8, SCAN_TILE = SCAN_BLOCK * SCAN_ITEMS;
+
+__global__ void __launch_bounds__(SCAN_BLOCK) scan_sums_kernel(const u32* __restrict__ in, const u64 count, u64* __restrict__ sums)
+{
+    __shared__ u64 s[SCAN_BLOCK / 32];
+    u64 v = 0;
+    const u64 first = u64(blockIdx.x) * SCAN_TILE + u64(threadIdx.x) * SCAN_ITEMS;
+    for(int i = 0; i < SCAN_ITEMS; ++i) if(first + i < count) v += in[first + i];
+    for(int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    if(lane_id() == 0) s[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if(threadIdx.x == 0) { u64 t = 0; for(int w = 0; w < SCAN_BLOCK / 32; ++w) t += s[w]; sums[blockIdx.x] = t; }
+}
+
+__global__ void __launch_bounds__(1024) scan_carry_kernel(u64* __restrict__ sums, const u64 tiles, u64* __restrict__ total)
+{
+    __shared__ u64 s[32];
+    __shared__ u64 carry;
+    if(threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for(u64 base = 0; base < tiles; base += 1024)
+    {
+        const u64 t = base + threadIdx.x;
+        const u64 v = (t < tiles) ? sums[t] : 0;
+        u64 inc = v;
+        for(int o = 1; o < 32; o <<= 1) { const u64 u = __shfl_up_sync(0xFFFFFFFFu, inc, o); if(int(lane_id()) >= o) inc += u; }
+        if(lane_id() == 31) s[threadIdx.x >> 5] = inc;
+        __syncthreads();
+        u64 pre = carry;
+        for(u32 w = 0; w < (threadIdx.x >> 5); ++w) pre += s[w];
+        __syncthreads();
+        if(t < tiles) sums[t] = pre + inc - v;
+        if(threadIdx.x == 1023) carry = pre + inc;
+        __syncthreads();
+    }
+    if(threadIdx.x == 0) *total = carry;
+}
+
+__global__ void __launch_bounds__(SCAN_BLOCK) scan_apply_kernel(const u32* __restrict__ in, const u64 count, const u64* __restrict__ sums,
+                                                               const u64* __restrict__ total, u64* __restrict__ out)
+{
+    __shared__ u64 s[SCAN_BLOCK / 32];
+    const u64 first = u64(blockIdx.x) * SCAN_TILE + u64(threadIdx.x) * SCAN_ITEMS;
+    u32 v[SCAN_ITEMS];
+    u64 mine = 0;
+    for(int i = 0; i < SCAN_ITEMS; ++i) { v[i] = (first + i < count) ? in[first + i] : 0; mine += v[i]; }
+    u64 inc = mine;
+    for(int o = 1; o < 32; o <<= 1) { const u64 u = __shfl_up_sync(0xFFFFFFFFu, inc, o); if(int(lane_id()) >= o) inc += u; }
+    if(lane_id() == 31) s[threadIdx.x >> 5] = inc;
+    __syncthreads();
+    u64 run = sums[blockIdx.x] + inc - mine;
+    for(u32 w = 0; w < (threadIdx.x >> 5); ++w) run += s[w];
+    for(int i = 0; i < SCAN_ITEMS; ++i)
+    {
+        if(first + i < count) out[first + i] = run;
+        run += v[i];
+    }
+    if(blockIdx.x == 0 && threadIdx.x == 0) out[count] = *total;
+}
+
+__global__ void certify_kernel(const csa_index idx, const u64* __restrict__ off, const u16* __restrict__ sym, const u64 q, const u64* __restrict__ itv,
+                               u64* __restrict__ result)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= q) return;
+    const u64 n = idx.n, m = off[i + 1] - off[i], lo = itv[2 * i], hi = itv[2 * i + 1];
+    const u16* const P = sym + (off[i] - off[0]);
+    bool ok = true;
+    if(lo > hi || hi > n) ok = false;
+    else if(m == 0) ok = (lo == 0 && hi == n);
+    else
+    {
+        if(lo > 0 && cmp_suffix_pattern(idx.text, n, sa40_load(idx.sa40, lo - 1), P, m) >= 0) ok = false;
+        if(ok && lo < hi && (cmp_suffix_pattern(idx.text, n, sa40_load(idx.sa40, lo), P, m) != 0
+                             || cmp_suffix_pattern(idx.text, n, sa40_load(idx.sa40, hi - 1), P, m) != 0)) ok = false;
+        if(ok && hi < n && cmp_suffix_pattern(idx.text, n, sa40_load(idx.sa40, hi), P, m) <= 0) ok = false;
+    }
+    if(!ok)
+    {
+        atomicAdd(&result[0], 1ull);
+        atomicMin(&result[1], i);
+    }
+}
+
+int check_index(csa_ctx* ctx, const csa_index* index)
+{
+    if(!ctx || !index || !index->text || !index->sa40 || !index->table || index->n == 0 || index->stride == 0)
+        return csa_fail(ctx, CSA_E_INVALID, "query: incomplete index");
+    if(reinterpret_cast<uintptr_t>(index->sa40) & 3) return csa_fail(ctx, CSA_E_INVALID, "query: the suffix array must be 4-byte aligned");
+    if(reinterpret_cast<uintptr_t>(index->table) & 15) return csa_fail(ctx, CSA_E_INVALID, "query: the sample table must be 16-byte aligned");
+    return CSA_OK;
+}
+
+int exclusive_sum(csa_ctx* ctx, const u32* in, u64 count, u64* out, u64* sums_scratch, u64* total_dev)
+{
+    const u64 tiles = div_up(count, SCAN_TILE);
+    if(tiles == 0) { CSA_CUDA(ctx, cudaMemsetAsync(out, 0, 8, ctx->stream)); CSA_CUDA(ctx, cudaMemsetAsync(total_dev, 0, 8, ctx->stream)); return CSA_OK; }
+    scan_sums_kernel<<<unsigned(tiles), SCAN_BLOCK, 0, ctx->stream>>>(in, count, sums_scratch);
+    CSA_LAUNCH_CHECK(ctx);
+    scan_carry_kernel<<<1, 1024, 0, ctx->stream>>>(sums_scratch, tiles, total_dev);
+    CSA_LAUNCH_CHECK(ctx);
+    scan_apply_kernel<<<unsigned(tiles), SCAN_BLOCK, 0, ctx->stream>>>(in, count, sums_scratch, total_dev, out);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+}   // namespace
+
+extern "C" int csa_table_build(csa_ctx* ctx, const uint16_t* text, uint64_t n, const uint8_t* sa40, uint64_t stride, uint64_t* table)
+{
+    if(!ctx || !text || !sa40 || !table || n == 0 || stride == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_table_build: bad argument");
+    if(reinterpret_cast<uintptr_t>(sa40) & 3) return csa_fail(ctx, CSA_E_INVALID, "csa_table_build: the suffix array must be 4-byte aligned");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const u64 entries = div_up(n, stride);
+    table_build_kernel<<<unsigned(div_up(entries, 256)), 256, 0, ctx->stream>>>(text, sa40, n, stride, entries, reinterpret_cast<u64*>(table));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_find(csa_ctx* ctx, const csa_index* index, const uint64_t* off, const uint16_t* sym, uint64_t q, uint64_t* itv)
+{
+    CSA_TRY(check_index(ctx, index));
+    if(q == 0) return CSA_OK;
+    if(!off || !itv) return csa_fail(ctx, CSA_E_INVALID, "csa_find: null buffer");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    find_kernel<<<unsigned(div_up(q, 128)), 128, 0, ctx->stream>>>(*index, reinterpret_cast<const u64*>(off), sym, q, reinterpret_cast<u64*>(itv));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_locate(csa_ctx* ctx, const csa_index* index, const uint64_t* itv, uint64_t q, uint32_t max_pos, uint64_t* pos, uint32_t* cnt)
+{
+    CSA_TRY(check_index(ctx, index));
+    if(q == 0) return CSA_OK;
+    if(!itv || !pos || !cnt || max_pos == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_locate: bad argument");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    locate_rows_kernel<<<unsigned(div_up(q * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, reinterpret_cast<const u64*>(itv), q, max_pos,
+                                                                               reinterpret_cast<u64*>(pos), cnt);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_certify(csa_ctx* ctx, const csa_index* index, const uint64_t* off, const uint16_t* sym, uint64_t q, const uint64_t* itv,
+                           uint64_t* result)
+{
+    CSA_TRY(check_index(ctx, index));
+    if(!result) return csa_fail(ctx, CSA_E_INVALID, "csa_certify: null result");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const u64 init[2] = {0, ~0ull};
+    CSA_CUDA(ctx, cudaMemcpyAsync(result, init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if(q == 0) return CSA_OK;
+    if(!off || !itv) return csa_fail(ctx, CSA_E_INVALID, "csa_certify: null buffer");
+    certify_kernel<<<unsigned(div_up(q, 128)), 128, 0, ctx->stream>>>(*index, reinterpret_cast<const u64*>(off), sym, q,
+                                                                      reinterpret_cast<const u64*>(itv), reinterpret_cast<u64*>(result));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_query_host(csa_ctx* ctx, const csa_index* index, const uint64_t* off_host, const uint16_t* sym_host, uint64_t q, uint32_t max_pos,
+                              uint64_t* itv_host, uint32_t* cnt_host, uint64_t* pos_off_host, uint64_t* pos_host, uint64_t pos_capacity,
+                              uint64_t* pos_total)
+{
+    CSA_TRY(check_index(ctx, index));
+    if(pos_total) *pos_total = 0;
+    if(q == 0) return CSA_OK;
+    if(!off_host || !itv_host) return csa_fail(ctx, CSA_E_INVALID, "csa_query_host: null buffer");
+    const bool want_pos = max_pos > 0 && pos_host && cnt_host && pos_off_host;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const u64 sym_c = off_host[q] - off_host[0];
+    const size_t b_off = align_up256((q + 1) * 8), b_sym = align_up256(sym_c * 2 + 16), b_itv = align_up256(q * 16), b_cnt = align_up256(q * 4),
+                 b_poff = align_up256((q + 1) * 8), b_sums = align_up256((div_up(q, SCAN_TILE) + 1) * 8),
+                 b_pos = want_pos ? align_up256(size_t(q) * max_pos * 8) : 0;
+    void* ws = nullptr;
+    CSA_TRY(csa_arena(ctx, b_off + b_sym + b_itv + b_cnt + b_poff + b_sums + b_pos + 4096, &ws));
+    u8* p = static_cast<u8*>(ws);
+    u64* off_d = reinterpret_cast<u64*>(p); p += b_off;
+    u16* sym_d = reinterpret_cast<u16*>(p); p += b_sym;
+    u64* itv_d = reinterpret_cast<u64*>(p); p += b_itv;
+    u32* cnt_d = reinterpret_cast<u32*>(p); p += b_cnt;
+    u64* poff_d = reinterpret_cast<u64*>(p); p += b_poff;
+    u64* sums_d = reinterpret_cast<u64*>(p); p += b_sums;
+    u64* pos_d = reinterpret_cast<u64*>(p);
+    CSA_CUDA(ctx, cudaMemcpyAsync(off_d, off_host, (q + 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
+    if(sym_c) CSA_CUDA(ctx, cudaMemcpyAsync(sym_d, sym_host, sym_c * 2, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_TRY(csa_find(ctx, index, reinterpret_cast<uint64_t*>(off_d), sym_d, q, reinterpret_cast<uint64_t*>(itv_d)));
+    CSA_CUDA(ctx, cudaMemcpyAsync(itv_host, itv_d, q * 16, cudaMemcpyDeviceToHost, ctx->stream));
+    if(want_pos)
+    {
+        counts_kernel<<<unsigned(div_up(q, 256)), 256, 0, ctx->stream>>>(itv_d, q, max_pos, cnt_d);
+        CSA_LAUNCH_CHECK(ctx);
+        u64* total_d = ctx->d_scalars + 8;
+        CSA_TRY(exclusive_sum(ctx, cnt_d, q, poff_d, sums_d, total_d));
+        locate_packed_kernel<<<unsigned(div_up(q * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, itv_d, q, max_pos, poff_d, pos_d);
+        CSA_LAUNCH_CHECK(ctx);
+        CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 8, total_d, 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaMemcpyAsync(cnt_host, cnt_d, q * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaMemcpyAsync(pos_off_host, poff_d, (q + 1) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        const u64 total = ctx->h_scalars[8];
+        if(pos_total) *pos_total = total;
+        if(total > pos_capacity) return csa_fail(ctx, CSA_E_NOMEM, "csa_query_host: the positions buffer is too small");
+        if(total) CSA_CUDA(ctx, cudaMemcpyAsync(pos_host, pos_d, total * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    u64 bits = 0;
+    return csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits));
+}

@@ -1,0 +1,202 @@
+/* C ABI of the B200 (sm_100a) suffix-array builder and batched query engine.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status (CSA_OK = 0) and never exits,
+ * traps or throws. Device work is queued on the context's stream; csa_sync waits for it and reports the
+ * device status word. Pointers named *_dev are device addresses on the context's device (or, where
+ * stated, host memory that the device can address); pointers named *_host are ordinary host memory.
+ *
+ * The reference has no FFI layer: its host classes launch kernels directly. Each entry point below names
+ * the reference call site (path within the reference project) whose device work it replaces.
+ */
+#ifndef CASCADE_B200_H
+#define CASCADE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. */
+enum
+{
+    CSA_OK = 0,
+    CSA_E_INVALID = 1,      /* a bad argument */
+    CSA_E_CUDA = 2,         /* a CUDA call failed; csa_last_error has its text */
+    CSA_E_NOMEM = 3,        /* device or host memory ran out, or a workspace was too small */
+    CSA_E_LIMIT = 4,        /* a size beyond what the build supports (n, partition size, key bits) */
+    CSA_E_DEVICE = 5,       /* the device status word is non-zero (csa_sync gives its bits) */
+    CSA_E_COMM = 6          /* the multi-GPU exchange callback failed */
+};
+
+/* Symbols of zero padding that must follow the text in device memory (the reference keeps 64 bytes,
+ * include/sa40.hpp:27; the tiled text-window copies here want 64 symbols). */
+#define CSA_TEXT_PAD 64
+/* Bytes of padding that must follow a 5-byte suffix array in memory (include/sa40.hpp:32). */
+#define CSA_SA_PAD_BYTES 128
+/* Symbols of a pivot / sample-table key (two 64-bit words of four u16 symbols; include/Packed_Prefix.hpp:20-34). */
+#define CSA_K 8
+/* Most partitions of a build (the splitters of a partition-id search are kept in shared memory). */
+#define CSA_MAX_PARTITIONS 4096
+/* Most GPUs of one build. */
+#define CSA_MAX_GPUS 8
+
+typedef struct csa_ctx csa_ctx;
+
+/* ---- context ---------------------------------------------------------------------------------------- */
+
+/* One context per (device, host thread): a stream, a status word and scratch. Replaces the per-dispatcher
+ * stream and buffer set of src/GPU_SACA.cu:48-86,534-590. */
+int csa_ctx_create(int device, csa_ctx** out);
+void csa_ctx_destroy(csa_ctx* ctx);
+/* Waits for the context's stream. If status_bits is non-null it receives the device status word; a non-zero
+ * word makes the call return CSA_E_DEVICE and clears the word. Replaces synchronize_or_abort (src/utility.cpp:20-30). */
+int csa_sync(csa_ctx* ctx, uint64_t* status_bits);
+/* Text of the last error of this context ("" if none). The pointer stays valid until the next call on ctx. */
+const char* csa_last_error(const csa_ctx* ctx);
+/* The context's cudaStream_t, for callers that order their own work against it. */
+void* csa_ctx_stream(csa_ctx* ctx);
+/* Launches of this library's kernels on ctx since the last reset, and a reset. */
+uint64_t csa_kernel_launches(const csa_ctx* ctx);
+void csa_reset_counters(csa_ctx* ctx);
+/* Library version string. */
+const char* csa_version(void);
+
+/* ---- LSD radix sort (replaces the cub::DeviceRadixSort::SortPairs calls of src/GPU_SACA.cu:1175,1203,1783,1849) */
+
+/* Bytes of workspace that csa_sort_pairs needs for n records. */
+size_t csa_sort_workspace_bytes(uint64_t n);
+/* Stable least-significant-digit radix sort of n (64-bit key, value) records on key bits [begin_bit, end_bit),
+ * 8 bits per pass, each pass one sweep over the records. val_bytes is 4 or 8. The records ping-pong between
+ * (keys, vals) and (keys_alt, vals_alt); *in_alt is set to 1 if the sorted records end in the alt buffers, else 0.
+ * Passes whose digit is the same for every key are skipped. */
+int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, void* vals_dev, void* vals_alt_dev,
+                   uint32_t val_bytes, uint64_t n, int begin_bit, int end_bit, void* workspace_dev, size_t workspace_bytes,
+                   int* in_alt);
+/* Average device time of the digit passes of the sorts run on ctx since the last csa_reset_counters, measured
+ * with CUDA events on the context's stream when pass timing is on (csa_set_pass_timing): total milliseconds,
+ * the passes timed and the records they moved. */
+int csa_set_pass_timing(csa_ctx* ctx, int on);
+int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64_t* records);
+
+/* ---- build: sampling and partitioning ---------------------------------------------------------------- */
+
+/* Packs the K-gram (CSA_K symbols, two big-endian-packed 64-bit words, zero-padded past the text's end) at
+ * n_samples pseudo-random positions drawn from seed into samples_dev (2 words each, unsorted).
+ * Replaces the sampling loop of GPU_SACA::select_pivots (src/GPU_SACA.cu:290-312). */
+int csa_sample_kgrams(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint64_t n_samples, uint64_t seed,
+                      uint64_t* samples_dev);
+/* Host side of select_pivots (src/GPU_SACA.cu:313-364): sorts the samples and picks up to p-1 distinct pivots
+ * (inclusive upper bounds) at equal strides, so that equal K-grams never split. pivots_host holds 2 (p-1)
+ * words; *p_out receives the partition count actually formed (<= p). */
+int csa_select_pivots(const uint64_t* samples_host, uint64_t n_samples, uint32_t p, uint64_t* pivots_host, uint32_t* p_out);
+/* For the positions [first, first + count) of the text: partition id = min{q : kgram(i) <= pivot[q]}, written to
+ * pid_dev[i - first], and the partitions' sizes added into hist_dev[p]. Replaces compute_partition_IDs_kernel
+ * (include/GPU_SACA.cuh:23-73, launched at src/GPU_SACA.cu:939). pivots_dev holds 2 (p-1) words. */
+int csa_partition_ids(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint64_t first, uint64_t count,
+                      const uint64_t* pivots_dev, uint32_t p, uint16_t* pid_dev, uint64_t* hist_dev);
+/* Scatters the positions [first, first + count) into their partitions: position i goes to
+ * part_base_dev[pid] [ cursor_dev[pid]++ ], 4 bytes each. part_base_dev holds p device pointers (they may
+ * point into another GPU's memory); cursor_dev holds p running offsets. Replaces the host scatter of
+ * GPU_SACA::partition (src/GPU_SACA.cu:795-826). */
+int csa_scatter_by_pid(csa_ctx* ctx, const uint16_t* pid_dev, uint64_t first, uint64_t count, uint32_t p,
+                       uint32_t* const* part_base_dev, uint64_t* cursor_dev);
+
+/* ---- build: whole suffix array ------------------------------------------------------------------------ */
+
+typedef struct csa_build_stats
+{
+    uint64_t n;                 /* suffixes */
+    uint32_t partitions;        /* partitions formed */
+    uint32_t generations;       /* doubling generations run after the initial sort */
+    uint64_t max_partition;     /* largest partition, in suffixes */
+    uint64_t active_after_gen0; /* suffixes still tied after the initial sort */
+    uint64_t sort_passes;       /* radix digit passes run */
+    uint64_t sort_records;      /* records moved by those passes */
+    uint64_t kernel_launches;   /* kernels of this library launched by the build */
+    uint64_t peer_bytes;        /* bytes read from or written to other GPUs' memory (multi-GPU builds) */
+    double ms_partition;        /* device milliseconds by phase, from CUDA events */
+    double ms_gen0;
+    double ms_doubling;
+    double ms_output;
+    double ms_total;
+    double ms_sort_passes;      /* total of the digit passes, when pass timing is on */
+    uint64_t active_per_gen[48];
+} csa_build_stats;
+
+/* Device bytes that csa_build_sa allocates for a text of n symbols in p partitions (beyond text and output). */
+size_t csa_build_device_bytes(uint64_t n, uint32_t p);
+/* Builds the suffix array of text_dev[0, n) (n < 2^32 - 2^26; CSA_TEXT_PAD zero symbols must follow the text)
+ * into sa40_dev as 5-byte little-endian entries in numeric symbol order with shorter suffixes first
+ * (5 n bytes are written; the buffer must hold 5 n + CSA_SA_PAD_BYTES). p is the number of partitions asked for
+ * (K-gram splitters, CSA_K symbols); seed drives the sampling only (the suffix array does not depend on it).
+ * Replaces GPU_SACA::build_SA (src/GPU_SACA.cu:124-216) for a text resident in device memory. */
+int csa_build_sa(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_dev,
+                 csa_build_stats* stats);
+/* The same from host buffers: copies text_host[0, n) to the device, builds, and copies the 5 n output bytes to
+ * sa40_host. Pinned host buffers make the copies asynchronous and fast; pageable ones work. This is the call that
+ * stands for `cascade <text> <sa>` (src/main.cu:12-46) once the files are in memory. */
+int csa_build_sa_host(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
+                      csa_build_stats* stats);
+
+/* ---- query engine ------------------------------------------------------------------------------------- */
+
+typedef struct csa_index
+{
+    const uint16_t* text;   /* n symbols + CSA_TEXT_PAD zero symbols, device memory */
+    const uint8_t* sa40;    /* 5 n bytes + CSA_SA_PAD_BYTES; device memory, or pinned host memory mapped for the device */
+    const uint64_t* table;  /* sample table: 2 words per sampled suffix, ceil(n / stride) entries; device memory */
+    uint64_t n;
+    uint64_t stride;
+} csa_index;
+
+/* table_dev[j] = the K-gram of suffix SA[j * stride], zero-padded past the text's end, for j < ceil(n / stride).
+ * Replaces Sample_Table::build / build_kernel (src/Sample_Table.cu:26-31,218-288). */
+int csa_table_build(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint8_t* sa40_dev, uint64_t stride,
+                    uint64_t* table_dev);
+/* SA intervals of q queries: query i is sym_dev[off_dev[i] - off_dev[0], ...) of length off_dev[i+1] - off_dev[i];
+ * itv_dev receives {lo, hi} pairs. Semantics of ref::find_one (include/CPU_Reference.hpp:42-73). Replaces
+ * Query_Engine::find_async (src/Query_Engine.cu:1314) with its rank and search kernels (:176-279, :369-418). */
+int csa_find(csa_ctx* ctx, const csa_index* index, const uint64_t* off_dev, const uint16_t* sym_dev, uint64_t q,
+             uint64_t* itv_dev);
+/* Positions of each query: SA[lo + k] for k < min(max_pos, hi - lo), in rank order, written to row i of
+ * pos_dev (q rows of max_pos words); cnt_dev[i] = the number written. The reference has no locate output
+ * (include/query-file.hpp:18-19); this is the definition its intervals imply. */
+int csa_locate(csa_ctx* ctx, const csa_index* index, const uint64_t* itv_dev, uint64_t q, uint32_t max_pos,
+               uint64_t* pos_dev, uint32_t* cnt_dev);
+/* Interval certificate of ref::certify (include/CPU_Reference.hpp:79-101) for every query: result_dev[0] = number
+ * of failing queries, result_dev[1] = first failing query (or ~0). Replaces certify_kernel (src/Query_Engine.cu:665-686). */
+int csa_certify(csa_ctx* ctx, const csa_index* index, const uint64_t* off_dev, const uint16_t* sym_dev, uint64_t q,
+                const uint64_t* itv_dev, uint64_t* result_dev);
+/* Count + locate from host buffers: copies the batch to the device, finds the intervals, lists up to max_pos
+ * positions per query and copies the results back: itv_host {lo, hi} pairs, cnt_host[i] = positions listed for query i,
+ * pos_off_host[q + 1] = their offsets into pos_host (packed, rank order), *pos_total = their number. pos_host must hold
+ * pos_capacity words; CSA_E_NOMEM if that is too few (then *pos_total says how many are needed). Pass max_pos = 0 (or
+ * null position buffers) for counts only. Stands for Query_Engine::find (src/Query_Engine.cu:1355). */
+int csa_query_host(csa_ctx* ctx, const csa_index* index, const uint64_t* off_host, const uint16_t* sym_host, uint64_t q,
+                   uint32_t max_pos, uint64_t* itv_host, uint32_t* cnt_host, uint64_t* pos_off_host, uint64_t* pos_host,
+                   uint64_t pos_capacity, uint64_t* pos_total);
+
+/* ---- synthetic workloads (seeded; the same integers on host and device) -------------------------------- */
+
+/* Fills text[0, n) with the Zipf corpus: separators 0xFFFF before documents of geometric length (mean mean_doc),
+ * tokens drawn by inverse CDF from cdf[vocab] (64-bit thresholds). The device and host forms give the same symbols. */
+int csa_gen_corpus_dev(csa_ctx* ctx, uint16_t* text_dev, uint64_t n, uint64_t seed, uint32_t mean_doc,
+                       const uint64_t* cdf_dev, uint32_t vocab);
+int csa_gen_corpus_host(uint16_t* text_host, uint64_t first, uint64_t count, uint64_t seed, uint32_t mean_doc,
+                        const uint64_t* cdf_host, uint32_t vocab);
+
+/* A query batch with the semantics of the reference's `query gen` (src/query.cu:826-882): std::mt19937_64(seed);
+ * kind 0 = substrings of text_host (length lens[rng() % len_c], place rng() % (n - len + 1)); kind 1 = random symbols
+ * rng() % vocab. off_out holds q + 1 offsets, sym_out up to sym_capacity symbols (CSA_E_NOMEM if too few). Host only. */
+int csa_gen_queries_host(int kind, const uint16_t* text_host, uint64_t n, uint64_t q, const uint32_t* lens, uint32_t len_c,
+                         uint64_t vocab, uint64_t seed, uint64_t* off_out, uint16_t* sym_out, uint64_t sym_capacity);
+/* FNV-1a-64 over the little-endian counts hi - lo of q {lo, hi} pairs: `counts_hash` of include/query-file.hpp:228-263. */
+uint64_t csa_counts_hash(const uint64_t* itv_host, uint64_t q);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

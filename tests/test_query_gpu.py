@@ -1,0 +1,121 @@
+"""The batched count / locate engine on the GPU (through the C ABI) against the oracle's intervals and positions and
+against the golden intervals made by the reference's host search."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import conftest
+from conftest import GOLDEN, sa40_to_u64
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from cascade_b200 import api
+    c = api.Context(0)
+    yield c
+    c.close()
+
+
+def _index(ctx, T, sa40, stride):
+    from cascade_b200 import api
+    n = len(T)
+    Tp = np.concatenate([np.ascontiguousarray(T, np.uint16), np.zeros(api.TEXT_PAD, np.uint16)])
+    td = torch.from_numpy(Tp.view(np.int16)).cuda().view(torch.uint16)
+    sd = torch.from_numpy(np.ascontiguousarray(sa40)).cuda()
+    return api.SuffixIndex(ctx, td, sd, n, stride)
+
+
+def _dev(off, sym):
+    o = torch.from_numpy(off.view(np.int64)).cuda()
+    s = torch.from_numpy(np.concatenate([sym, np.zeros(8, np.uint16)]).view(np.int16)).cuda()
+    return o, s
+
+
+def test_known_answer_table(ctx, oracle):
+    with open(os.path.join(GOLDEN, "known_answers.json")) as f:
+        cases = json.load(f)
+    for stride in (1, 2, 32):
+        for c in cases:
+            T, P = np.array(c["text"], np.uint16), np.array(c["pattern"], np.uint16)
+            sa = oracle.build_sa40(T)
+            idx = _index(ctx, T, sa, stride)
+            off = np.array([0, len(P)], np.uint64)
+            o, s = _dev(off, P)
+            itv = idx.find(o, s, 1).cpu().numpy().view(np.uint64)
+            assert (int(itv[0]), int(itv[1])) == (c["lo"], c["hi"]), (c, stride)
+
+
+@pytest.mark.parametrize("stride", [1, 2, 3, 16, 64, 100000])
+def test_golden_query_fixtures(ctx, oracle, stride):
+    g = np.load(os.path.join(GOLDEN, "query_fixtures.npz"))
+    s = np.load(os.path.join(GOLDEN, "sa_fixtures.npz"))
+    for name in [k[4:] for k in g.files if k.startswith("off_")]:
+        T = s["T_" + name]
+        sa = oracle.build_sa40(T)
+        idx = _index(ctx, T, sa, stride)
+        off, sym, want = g["off_" + name], g["sym_" + name], g["itv_" + name]
+        q = len(off) - 1
+        o, sy = _dev(off, sym)
+        itv = idx.find(o, sy, q)
+        got = itv.cpu().numpy().view(np.uint64)
+        bad = np.flatnonzero(got != want)
+        assert bad.size == 0, (name, stride, bad[:4] // 2, got[bad[:4]], want[bad[:4]])
+        fails, first = idx.certify(o, sy, q, itv)
+        assert fails == 0
+        pos, cnt = idx.locate(itv, q, 100)
+        wp, wc = oracle.locate_batch(sa, got, 100)
+        assert np.array_equal(cnt.cpu().numpy().view(np.uint32), wc)
+        pn = pos.cpu().numpy().view(np.uint64)
+        for i in range(q):
+            assert np.array_equal(pn[i, :wc[i]], wp[i, :wc[i]]), (name, i)
+
+
+def test_certificate_rejects_wrong_intervals(ctx, oracle):
+    rng = np.random.default_rng(1)
+    T = rng.integers(0, 3, 5000).astype(np.uint16)
+    sa = oracle.build_sa40(T)
+    idx = _index(ctx, T, sa, 8)
+    off, sym, _ = conftest.fixture_queries(T, rng, 64)
+    o, s = _dev(off, sym)
+    itv = idx.find(o, s, 64)
+    assert idx.certify(o, s, 64, itv) == (0, 2**64 - 1)
+    bad = itv.clone()
+    k = next(i for i in range(64) if int(bad[2 * i + 1]) - int(bad[2 * i]) >= 2)
+    bad[2 * k] += 1
+    fails, first = idx.certify(o, s, 64, bad)
+    assert fails == 1 and first == k
+
+
+def test_zipf_index_batch_and_host_entry_point(ctx, oracle):
+    """A 2 Mi-token Zipf corpus built on the GPU, queried with the two halves of BASELINE config 5 (substrings and random
+    strings of 1-16 tokens): intervals, counts hash and positions equal the oracle's; the host-buffer entry point agrees."""
+    from cascade_b200 import api
+    n = 1 << 21
+    Td = api.gen_corpus_device(ctx, n, 0, 1024)
+    sa, _ = api.build_sa(ctx, Td, n, 8)
+    Th = Td.cpu().view(torch.int16).numpy().view(np.uint16)
+    sa_h = sa.cpu().numpy()
+    idx = api.SuffixIndex(ctx, Td, sa, n, 32)
+    oa, sa_ = api.gen_queries("substring", Th, n, 20000, seed=1)
+    ob, sb = api.gen_queries("random", None, 0, 20000, seed=2)
+    off = np.concatenate([oa, ob[1:] + oa[-1]])
+    sym = np.concatenate([sa_, sb])
+    q = len(off) - 1
+    o, s = _dev(off, sym)
+    itv = idx.find(o, s, q)
+    got = itv.cpu().numpy().view(np.uint64)
+    want = oracle.find_batch(Th[:n], sa_h, off, sym)
+    assert np.array_equal(got, want)
+    assert api.counts_hash(got) == oracle.counts_hash(want)
+    assert idx.certify(o, s, q, itv)[0] == 0
+    itv_h, cnt_h, poff_h, pos_h, total = idx.query_host(off, sym, 100)
+    assert np.array_equal(itv_h, want)
+    wp, wc = oracle.locate_batch(sa_h, want, 100)
+    assert np.array_equal(cnt_h, wc) and total == int(wc.sum()) and int(poff_h[-1]) == total
+    for i in list(range(0, q, 997)) + [q - 1]:
+        assert np.array_equal(pos_h[int(poff_h[i]):int(poff_h[i + 1])], wp[i, :wc[i]])

@@ -1,0 +1,66 @@
+"""The hand-written radix sort (through the C ABI) against a stable comparison sort of the same records."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from cascade_b200 import api
+    c = api.Context(0)
+    yield c
+    c.close()
+
+
+def _check(ctx, keys, vals, b0, b1):
+    from cascade_b200 import api
+    k0 = keys.clone()
+    ko, vo = api.sort_pairs(ctx, keys, vals, b0, b1)
+    width = b1 - b0
+    if width >= 64:
+        mk = k0 ^ (-(1 << 63))          # unsigned order on int64 storage
+    else:
+        mk = (k0 >> b0) & ((1 << width) - 1)
+    order = torch.sort(mk, stable=True).indices
+    assert torch.equal(k0[order], ko)
+    assert torch.equal(order.to(vo.dtype), vo)
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 31, 255, 4095, 4096, 4097, 100003, 1 << 20])
+def test_sort_random_full_keys(ctx, n):
+    g = torch.Generator(device="cuda").manual_seed(n)
+    keys = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g) * 2 + (torch.arange(n, device="cuda") & 1)
+    _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 64)
+
+
+@pytest.mark.parametrize("bits", [(0, 8), (3, 40), (16, 17), (0, 56), (40, 64)])
+def test_sort_bit_ranges_are_stable(ctx, bits):
+    n = 300007
+    g = torch.Generator(device="cuda").manual_seed(7)
+    keys = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g)
+    _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), *bits)
+
+
+def test_sort_skewed_digits_and_skipped_passes(ctx):
+    n = 1 << 21
+    g = torch.Generator(device="cuda").manual_seed(1)
+    keys = (torch.randint(0, 7, (n,), device="cuda", dtype=torch.int64, generator=g) << 20) | 5     # most digits are constant
+    _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 64)
+    keys = torch.zeros(n, device="cuda", dtype=torch.int64)                                         # every pass is skipped
+    _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 64)
+
+
+def test_sort_64_bit_values(ctx):
+    n = 1 << 20
+    g = torch.Generator(device="cuda").manual_seed(2)
+    keys = torch.randint(0, 1 << 40, (n,), device="cuda", dtype=torch.int64, generator=g)
+    _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int64) * 3, 0, 40)
+
+
+def test_sort_many_tiles(ctx):
+    n = 20_000_003
+    g = torch.Generator(device="cuda").manual_seed(3)
+    keys = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g)
+    _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 64)
