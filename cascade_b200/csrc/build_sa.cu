@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include "part.cuh"
 
+#include <cstdlib>
 #include <vector>
 
 namespace
@@ -138,6 +139,8 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     u64 active = ctx->h_scalars[0];
     st.active_after_gen0 = active;
+    const bool debug = std::getenv("CSA_DEBUG") != nullptr;
+    if(debug) std::fprintf(stderr, "[csa] n=%llu partitions=%u largest=%llu active after generation 0: %llu\n", n, p_eff, max_part, active);
 
     // ---- doubling generations -------------------------------------------------------------------------------
     u32* pos_cur = posA; u32* pos_other = posB;
@@ -159,7 +162,10 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
         CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
         CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, 0, sa, head, pn, act_count, scratch));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if(ctx->h_scalars[1] != 0) { u64 b = 0; return csa_sync(ctx, reinterpret_cast<uint64_t*>(&b)); }
+        if(debug) std::fprintf(stderr, "[csa] generation %u: h=%llu active %llu -> %llu (key bits %d)\n", gen + 1, h, active, ctx->h_scalars[0], sec_bits + prim_bits);
         active = ctx->h_scalars[0];
         pos_cur = pn; pos_other = ps;
         ++gen;

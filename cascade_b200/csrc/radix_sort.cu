@@ -19,13 +19,21 @@ constexpr u32 FLAG_SHIFT = 30;
 constexpr u32 COUNT_MASK = (1u << FLAG_SHIFT) - 1;
 constexpr u32 FLAG_AGGREGATE = 1u << FLAG_SHIFT;
 constexpr u32 FLAG_PREFIX = 2u << FLAG_SHIFT;
-constexpr u64 PORTION = 1ull << 29;         // records per launch of a pass: tile counts stay below 2^30
+u64 PORTION = 1ull << 29;                   // records per launch of a pass: tile counts stay below 2^30 (tests may lower it)
 constexpr u32 LOOKBACK_SPIN_LIMIT = 1u << 22;
+constexpr int LOOKBACK_BATCH = 8;
 
-// Digit histograms of every pass in one read of the keys. hist holds [passes][RADIX] 32-bit counts for this portion.
+// The digit of a pass that starts at bit `shift` holds min(8, end_bit - shift) bits.
+__host__ __device__ __forceinline__ u32 digit_mask(int shift, int end_bit)
+{
+    const int w = end_bit - shift;
+    return w >= RADIX_BITS ? u32(RADIX - 1) : ((1u << w) - 1);
+}
+
+// Digit histograms of every pass in one read of the keys. hist holds [passes][RADIX] 64-bit counts of the whole array.
 template <int BLOCK>
-__global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict__ keys, const u64 n, const int begin_bit, const int passes,
-                                                         u32* __restrict__ hist)
+__global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict__ keys, const u64 n, const int begin_bit, const int end_bit, const int passes,
+                                                         u64* __restrict__ hist)
 {
     __shared__ u32 h[8 * RADIX];
     for(int i = threadIdx.x; i < passes * RADIX; i += BLOCK) h[i] = 0;
@@ -46,8 +54,9 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
         for(int p = 0; p < passes; ++p)
         {
             const int sh = begin_bit + p * RADIX_BITS;
-            const u32 d0 = live ? u32(v.x >> sh) & (RADIX - 1) : RADIX;       // RADIX = "no record"
-            const u32 d1 = live ? u32(v.y >> sh) & (RADIX - 1) : RADIX;
+            const u32 dm = digit_mask(sh, end_bit);
+            const u32 d0 = live ? u32(v.x >> sh) & dm : RADIX;       // RADIX = "no record"
+            const u32 d1 = live ? u32(v.y >> sh) & dm : RADIX;
             const u32 m0 = __match_any_sync(0xFFFFFFFFu, d0);
             const u32 m1 = __match_any_sync(0xFFFFFFFFu, d1);
             if(live)
@@ -60,17 +69,19 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
     if((n & 1) && blockIdx.x == 0 && threadIdx.x == 0)
     {
         const u64 k = keys[n - 1];
-        for(int p = 0; p < passes; ++p) atomicAdd(&h[p * RADIX + (u32(k >> (begin_bit + p * RADIX_BITS)) & (RADIX - 1))], 1u);
+        for(int p = 0; p < passes; ++p)
+            atomicAdd(&h[p * RADIX + (u32(k >> (begin_bit + p * RADIX_BITS)) & digit_mask(begin_bit + p * RADIX_BITS, end_bit))], 1u);
     }
     __syncthreads();
     for(int i2 = threadIdx.x; i2 < passes * RADIX; i2 += BLOCK)
-        if(h[i2] != 0) atomicAdd(&hist[i2], h[i2]);
+        if(h[i2] != 0) atomicAdd(&hist[i2], u64(h[i2]));
 }
 
-// From the portions' histograms: the global base offset of every (portion, pass, digit), and for every pass
-// whether a single digit holds all n records (such a pass moves nothing and is skipped).
-// hist: [portions][passes][RADIX] u32. base: same shape, u64. skip: [passes] u64.
-__global__ void __launch_bounds__(RADIX) digit_base_kernel(const u32* __restrict__ hist, const int portions, const int passes, const u64 n,
+// From the histograms: for every pass the global offset of each digit's first record (what the first launch of the pass
+// starts from; a later launch starts from the offsets that the launch before it leaves behind), and whether a single
+// digit holds all n records (such a pass moves nothing and is skipped).
+// hist: [passes][RADIX]. base: [passes][launches + 1][RADIX], of which slot 0 is written here. skip: [passes].
+__global__ void __launch_bounds__(RADIX) digit_base_kernel(const u64* __restrict__ hist, const int launches, const u64 n,
                                                           u64* __restrict__ base, u64* __restrict__ skip)
 {
     __shared__ u64 warp_tot[RADIX / 32];
@@ -78,10 +89,8 @@ __global__ void __launch_bounds__(RADIX) digit_base_kernel(const u32* __restrict
     const int p = blockIdx.x, d = threadIdx.x;
     if(d == 0) s_skip = 0;
     __syncthreads();
-    u64 total = 0;
-    for(int P = 0; P < portions; ++P) total += hist[(u64(P) * passes + p) * RADIX + d];
+    const u64 total = hist[u64(p) * RADIX + d];
     if(total == n) s_skip = 1;
-    // exclusive scan of `total` over the 256 digits
     u64 inc = total;
     for(int o = 1; o < 32; o <<= 1)
     {
@@ -92,13 +101,7 @@ __global__ void __launch_bounds__(RADIX) digit_base_kernel(const u32* __restrict
     __syncthreads();
     u64 pre = 0;
     for(int w = 0; w < (d >> 5); ++w) pre += warp_tot[w];
-    u64 run = pre + inc - total;
-    for(int P = 0; P < portions; ++P)
-    {
-        const u64 idx = (u64(P) * passes + p) * RADIX + d;
-        base[idx] = run;
-        run += hist[idx];
-    }
+    base[(u64(p) * (launches + 1)) * RADIX + d] = pre + inc - total;
     if(d == 0) skip[p] = u64(s_skip);
 }
 
@@ -107,16 +110,17 @@ struct Pass_Smem
 {
     static constexpr int TILE = BLOCK * ITEMS;
     static constexpr int WARPS = BLOCK / 32;
-    static constexpr size_t bytes = size_t(TILE) * 8 + size_t(TILE) * sizeof(V) + size_t(WARPS) * RADIX * 4 + RADIX * 4 + RADIX * 8 + 64;
+    static constexpr size_t bytes = size_t(TILE) * 8 + size_t(TILE) * sizeof(V) + size_t(WARPS) * RADIX * 4 + RADIX * 4 + RADIX * 8 + 256;
 };
 
-// One digit pass over one portion of the records. status: [tiles][RADIX] words, zeroed before the launch;
-// tile_counter: one zeroed word. digit_base: [RADIX] global offsets of this portion and pass.
-template <int BLOCK, int ITEMS, typename V>
-__global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const V* __restrict__ vals_in,
-                                                             V* __restrict__ vals_out, const u64 n, const int shift,
-                                                             const u64* __restrict__ digit_base, u32* __restrict__ status, u32* __restrict__ tile_counter,
-                                                             u64* __restrict__ dev_status)
+// One digit pass over one launch's share of the records. status: [tiles][RADIX] words, zeroed before the launch;
+// tile_counter: one zeroed word. digit_base: [RADIX] global offsets at which this launch's records of each digit start;
+// the launch's last tile leaves in next_base the offsets at which the next launch's start.
+template <int BLOCK, int ITEMS, typename V, int MATCH_BITS, bool FULL>
+__device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const V* __restrict__ vals_in,
+                                              V* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
+                                              const u64* __restrict__ digit_base, u64* __restrict__ next_base, u32* __restrict__ status,
+                                              u64* __restrict__ dev_status, const u32 tile, const u32 valid_records)
 {
     constexpr int TILE = BLOCK * ITEMS;
     constexpr int WARPS = BLOCK / 32;
@@ -126,65 +130,78 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
     u32* const warp_hist = reinterpret_cast<u32*>(smem_raw + size_t(TILE) * 8 + size_t(TILE) * sizeof(V));
     u32* const tile_excl = warp_hist + WARPS * RADIX;
     u64* const g_off = reinterpret_cast<u64*>(tile_excl + RADIX);
-    u32* const misc = reinterpret_cast<u32*>(g_off + RADIX);   // [0] tile id, [1..8] warp totals of the digit scan
+    u32* const misc = reinterpret_cast<u32*>(g_off + RADIX);   // [0] tile id, [1..] warp totals of the digit scan
 
     const u32 tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-    // Tiles are taken in launch order of the blocks that run, so that every tile a block waits on is already running.
-    if(tid == 0) misc[0] = atomicAdd(tile_counter, 1u);
-    for(int i = tid; i < WARPS * RADIX; i += BLOCK) warp_hist[i] = 0;
-    __syncthreads();
-    const u32 tile = misc[0];
     const u64 tile_base = u64(tile) * TILE;
-    if(tile_base >= n) return;
-    const u32 valid = (n - tile_base < u64(TILE)) ? u32(n - tile_base) : u32(TILE);
+    const u32 valid = FULL ? u32(TILE) : valid_records;     // a full tile needs no bounds checks
 
     // Warp-striped load: a warp owns 32 * ITEMS consecutive records; item i of lane l is record i * 32 + l of them.
+    // Keys and values are requested together so that one memory round trip covers both.
     u64 key[ITEMS];
+    V val[ITEMS];
     const u32 warp_first = warp * 32 * ITEMS;
     #pragma unroll
     for(int i = 0; i < ITEMS; ++i)
     {
         const u32 idx = warp_first + i * 32 + lane;
-        key[i] = (idx < valid) ? keys_in[tile_base + idx] : ~0ull;
+        key[i] = (FULL || idx < valid) ? keys_in[tile_base + idx] : ~0ull;
     }
-
-    // Rank of every record among the records of its digit within the warp, and the warp's digit counts.
-    u16 rank[ITEMS];
-    u32* const wh = warp_hist + warp * RADIX;
     #pragma unroll
     for(int i = 0; i < ITEMS; ++i)
     {
-        const u32 d = u32(key[i] >> shift) & (RADIX - 1);
-        const u32 peers = __match_any_sync(0xFFFFFFFFu, d);
-        const u32 leader = __ffs(peers) - 1;
-        u32 old = 0;
-        if(lane == leader) { old = wh[d]; wh[d] = old + __popc(peers); }
-        old = __shfl_sync(0xFFFFFFFFu, old, leader);
-        rank[i] = u16(old + __popc(peers & lanemask_lt()));
-        __syncwarp();
+        const u32 idx = warp_first + i * 32 + lane;
+        if(FULL || idx < valid) val[i] = vals_in[tile_base + idx];
+    }
+
+    // Rank of every record among the records of its digit within the warp, and the warp's digit counts. The lanes that
+    // hold a digit find one another (warp-level multisplit): the high bits of the digit by one match.any, whose cost grows
+    // with the number of distinct values, and the low bits by one ballot each; the lowest lane of a group adds the group's
+    // size to the warp's counter of the digit and hands the old value round. The steps run as separate sweeps over the
+    // items so that their latencies overlap; shared-memory atomics of one warp take effect in program order, which keeps
+    // the ranks stable.
+    u32 dig[ITEMS], rank[ITEMS];
+    u32* const wh = warp_hist + warp * RADIX;
+    {
+        u32 peers[ITEMS], old[ITEMS];
+        #pragma unroll
+        for(int i = 0; i < ITEMS; ++i)
+        {
+            dig[i] = u32(key[i] >> shift) & dmask;
+            u32 m = (MATCH_BITS > 0) ? __match_any_sync(0xFFFFFFFFu, dig[i] >> (RADIX_BITS - MATCH_BITS)) : 0xFFFFFFFFu;
+            #pragma unroll
+            for(int b = 0; b < RADIX_BITS - MATCH_BITS; ++b)
+            {
+                const u32 sel = 0u - ((dig[i] >> b) & 1u);                  // all ones if the bit is set
+                const u32 v = __ballot_sync(0xFFFFFFFFu, sel != 0);
+                m &= ~(v ^ sel);                                            // lanes whose bit equals this lane's
+            }
+            peers[i] = m;
+        }
+        #pragma unroll
+        for(int i = 0; i < ITEMS; ++i)
+        {
+            old[i] = 0;
+            if((peers[i] & lanemask_lt()) == 0) old[i] = atomicAdd(&wh[dig[i]], u32(__popc(peers[i])));    // lowest lane of the group
+        }
+        #pragma unroll
+        for(int i = 0; i < ITEMS; ++i)
+            rank[i] = __shfl_sync(0xFFFFFFFFu, old[i], __ffs(peers[i]) - 1) + __popc(peers[i] & lanemask_lt());
     }
     __syncthreads();
 
-    // Per digit: exclusive offsets of the warps, and the tile's count. Records past the end carry digit 255 and
-    // rank last, so they only have to leave the count.
+    // Per digit: the tile's count, then (after a scan of the counts over the digits) the offset within the tile at which
+    // each warp's records of the digit start. Records past the end carry the largest digit and rank last, so they only
+    // have to leave the count.
     u32 count = 0;
+    u32 wcount[WARPS];
     if(tid < RADIX)
     {
-        u32 sum = 0;
         #pragma unroll
-        for(int w = 0; w < WARPS; ++w)
-        {
-            const u32 t = warp_hist[w * RADIX + tid];
-            warp_hist[w * RADIX + tid] = sum;
-            sum += t;
-        }
-        if(tid == RADIX - 1) sum -= (u32(TILE) - valid);
-        count = sum;
+        for(int w = 0; w < WARPS; ++w) { wcount[w] = warp_hist[w * RADIX + tid]; count += wcount[w]; }
+        if(!FULL && tid == dmask) count -= (u32(TILE) - valid);      // dmask is the digit of the all-ones filler key
         st_relaxed_u32(status + u64(tile) * RADIX + tid, (tile == 0 ? FLAG_PREFIX : FLAG_AGGREGATE) | count);
     }
-
-    // Exclusive scan of the tile's digit counts.
     {
         u32 inc = count;
         if(tid < RADIX)
@@ -202,9 +219,14 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
         {
             u32 pre = 0;
             for(u32 w = 0; w < warp; ++w) pre += misc[1 + w];
-            tile_excl[tid] = pre + inc - count;
+            u32 run = pre + inc - count;
+            tile_excl[tid] = run;
+            #pragma unroll
+            for(int w = 0; w < WARPS; ++w) { warp_hist[w * RADIX + tid] = run; run += wcount[w]; }
         }
     }
+
+    __syncthreads();
 
     // Look back over the tiles before this one for the records of this digit that precede the tile.
     if(tid < RADIX)
@@ -212,30 +234,44 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
         u32 before = 0;
         if(tile > 0)
         {
-            bool gave_up = false;
-            for(long long t = (long long)tile - 1; t >= 0; --t)
+            // The status words of LOOKBACK_BATCH earlier tiles are requested at once, so that a long walk costs one memory
+            // round trip per batch instead of one per tile; a word that is still empty is polled (with a bound) in place.
+            bool gave_up = false, done = false;
+            long long t = (long long)tile - 1;
+            while(t >= 0 && !done && !gave_up)
             {
-                const u32* const slot = status + u64(t) * RADIX + tid;
-                u32 s = ld_relaxed_u32(slot);
-                u32 spins = 0;
-                while((s >> FLAG_SHIFT) == 0)
+                u32 s[LOOKBACK_BATCH];
+                #pragma unroll
+                for(int j = 0; j < LOOKBACK_BATCH; ++j)
+                    s[j] = (t - j >= 0) ? ld_relaxed_u32(status + u64(t - j) * RADIX + tid) : FLAG_PREFIX;
+                #pragma unroll
+                for(int j = 0; j < LOOKBACK_BATCH; ++j)
                 {
-                    if(++spins > LOOKBACK_SPIN_LIMIT || ((spins & 255u) == 0 && (ld_relaxed_u64(dev_status) & CSA_ST_LOOKBACK_TIMEOUT)))
+                    if(done || gave_up || t - j < 0) break;
+                    u32 v = s[j];
+                    u32 spins = 0;
+                    while((v >> FLAG_SHIFT) == 0)
                     {
-                        gave_up = true;
-                        break;
+                        if(++spins > LOOKBACK_SPIN_LIMIT || ((spins & 255u) == 0 && (ld_relaxed_u64(dev_status) & CSA_ST_LOOKBACK_TIMEOUT)))
+                        {
+                            gave_up = true;
+                            break;
+                        }
+                        __nanosleep(20);
+                        v = ld_relaxed_u32(status + u64(t - j) * RADIX + tid);
                     }
-                    __nanosleep(40);
-                    s = ld_relaxed_u32(slot);
+                    if(gave_up) break;
+                    before += v & COUNT_MASK;
+                    if((v >> FLAG_SHIFT) == 2) done = true;
                 }
-                if(gave_up) break;
-                before += s & COUNT_MASK;
-                if((s >> FLAG_SHIFT) == 2) break;
+                t -= LOOKBACK_BATCH;
             }
             if(gave_up) atomicOr(dev_status, (u64)CSA_ST_LOOKBACK_TIMEOUT);
             st_relaxed_u32(status + u64(tile) * RADIX + tid, FLAG_PREFIX | ((before + count) & COUNT_MASK));
         }
-        g_off[tid] = digit_base[tid] + before - tile_excl[tid];
+        const u64 db = digit_base[tid];
+        if(tile_base + TILE >= n) next_base[tid] = db + before + count;     // the last tile has seen every record of the launch
+        g_off[tid] = db + before - tile_excl[tid];
     }
     __syncthreads();
 
@@ -243,17 +279,15 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
     #pragma unroll
     for(int i = 0; i < ITEMS; ++i)
     {
-        const u32 d = u32(key[i] >> shift) & (RADIX - 1);
-        const u32 pos = tile_excl[d] + wh[d] + rank[i];
         const u32 idx = warp_first + i * 32 + lane;
-        rank[i] = u16(pos);
-        if(idx < valid) stage_keys[pos] = key[i];
+        rank[i] += wh[dig[i]];
+        if(FULL || idx < valid) stage_keys[rank[i]] = key[i];
     }
     #pragma unroll
     for(int i = 0; i < ITEMS; ++i)
     {
         const u32 idx = warp_first + i * 32 + lane;
-        if(idx < valid) stage_vals[rank[i]] = vals_in[tile_base + idx];
+        if(FULL || idx < valid) stage_vals[rank[i]] = val[i];
     }
     __syncthreads();
 
@@ -262,22 +296,48 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
     for(int k = 0; k < ITEMS; ++k)
     {
         const u32 p = tid + k * BLOCK;
-        if(p < valid)
+        if(FULL || p < valid)
         {
             const u64 kk = stage_keys[p];
-            const u64 dst = g_off[u32(kk >> shift) & (RADIX - 1)] + p;
+            const u64 dst = g_off[u32(kk >> shift) & dmask] + p;
             keys_out[dst] = kk;
             vals_out[dst] = stage_vals[p];
         }
     }
 }
 
-template <int BLOCK, int ITEMS, typename V>
-int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, u64 n, int shift, const u64* digit_base, u32* status, u32* counter)
+template <int BLOCK, int ITEMS, typename V, int MATCH_BITS>
+__global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const V* __restrict__ vals_in,
+                                                             V* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
+                                                             const u64* __restrict__ digit_base, u64* __restrict__ next_base, u32* __restrict__ status,
+                                                             u32* __restrict__ tile_counter, u64* __restrict__ dev_status)
+{
+    constexpr int TILE = BLOCK * ITEMS;
+    constexpr int WARPS = BLOCK / 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    u32* const warp_hist = reinterpret_cast<u32*>(smem_raw + size_t(TILE) * 8 + size_t(TILE) * sizeof(V));
+    u32* const misc = reinterpret_cast<u32*>(smem_raw + size_t(TILE) * 8 + size_t(TILE) * sizeof(V) + size_t(WARPS) * RADIX * 4 + RADIX * 4 + RADIX * 8);
+
+    // Tiles are taken in launch order of the blocks that run, so that every tile a block waits on is already running.
+    if(threadIdx.x == 0) misc[0] = atomicAdd(tile_counter, 1u);
+    for(int i = threadIdx.x; i < WARPS * RADIX; i += BLOCK) warp_hist[i] = 0;
+    __syncthreads();
+    const u32 tile = misc[0];
+    const u64 tile_base = u64(tile) * TILE;
+    if(tile_base >= n) return;
+    if(n - tile_base >= u64(TILE))
+        onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, true>(keys_in, keys_out, vals_in, vals_out, n, shift, dmask, digit_base, next_base, status, dev_status, tile, u32(TILE));
+    else
+        onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, false>(keys_in, keys_out, vals_in, vals_out, n, shift, dmask, digit_base, next_base, status, dev_status, tile,
+                                                          u32(n - tile_base));
+}
+
+template <int BLOCK, int ITEMS, typename V, int MATCH_BITS>
+int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, u64 n, int shift, u32 dmask, const u64* digit_base, u64* next_base, u32* status, u32* counter)
 {
     using S = Pass_Smem<BLOCK, ITEMS, V>;
     static bool configured[64] = {false};
-    auto kern = onesweep_pass_kernel<BLOCK, ITEMS, V>;
+    auto kern = onesweep_pass_kernel<BLOCK, ITEMS, V, MATCH_BITS>;
     if(!configured[ctx->device & 63])
     {
         CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::bytes)));
@@ -286,14 +346,29 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
     const u64 tiles = div_up(n, S::TILE);
     CSA_CUDA(ctx, cudaMemsetAsync(status, 0, tiles * RADIX * sizeof(u32), ctx->stream));
     CSA_CUDA(ctx, cudaMemsetAsync(counter, 0, sizeof(u32), ctx->stream));
-    kern<<<unsigned(tiles), BLOCK, S::bytes, ctx->stream>>>(kin, kout, vin, vout, n, shift, digit_base, status, counter, ctx->d_status);
+    kern<<<unsigned(tiles), BLOCK, S::bytes, ctx->stream>>>(kin, kout, vin, vout, n, shift, dmask, digit_base, next_base, status, counter, ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
 
-constexpr int PASS_BLOCK = 256;
-constexpr int PASS_ITEMS = 16;
-constexpr int PASS_TILE = PASS_BLOCK * PASS_ITEMS;
+// Shapes of the pass kernel to choose from (block size x items per thread); the smallest tile sizes the workspace.
+int g_variant = 0;
+constexpr int PASS_TILE = 2048;     // smallest tile among the variants
+
+template <typename V>
+int launch_pass_variant(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, u64 n, int shift, u32 dmask, const u64* db, u64* nb, u32* status,
+                        u32* counter)
+{
+    switch(g_variant)
+    {
+    case 1: return launch_pass<256, 8, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 2: return launch_pass<512, 4, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 3: return launch_pass<256, 12, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 4: return launch_pass<1024, 4, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 5: return launch_pass<512, 8, V, 4>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    default: return launch_pass<512, 8, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    }
+}
 
 struct Pass_Timer
 {
@@ -305,14 +380,21 @@ Pass_Timer g_timer[64];
 
 }   // namespace
 
+extern "C" int csa_debug_set(int key, uint64_t value)
+{
+    if(key == 0 && value >= 12 && value <= 29) { PORTION = 1ull << value; return CSA_OK; }
+    if(key == 1 && value <= 5) { g_variant = int(value); return CSA_OK; }
+    return CSA_E_INVALID;
+}
+
 size_t csa_sort_workspace_bytes(uint64_t n)
 {
     const u64 portions = n == 0 ? 1 : div_up(n, PORTION);
     const u64 tiles = div_up(n < PORTION ? n : PORTION, PASS_TILE) + 1;
     return size_t(tiles) * RADIX * 4 + 256            // tile status
          + 256                                         // tile counter
-         + size_t(portions) * 8 * RADIX * 4 + 256      // histograms
-         + size_t(portions) * 8 * RADIX * 8 + 256      // digit bases
+         + size_t(8) * RADIX * 8 + 256                 // histograms
+         + size_t(portions + 1) * 8 * RADIX * 8 + 256  // digit bases of every launch
          + 4096;
 }
 
@@ -366,20 +448,20 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     const u64 tiles_max = div_up(n < PORTION ? n : PORTION, PASS_TILE) + 1;
     u32* status = cv.take<u32>(tiles_max * RADIX);
     u32* counter = cv.take<u32>(64);
-    u32* hist = cv.take<u32>(u64(portions) * 8 * RADIX);
-    u64* base = cv.take<u64>(u64(portions) * 8 * RADIX);
+    u64* hist = cv.take<u64>(u64(8) * RADIX);
+    u64* base = cv.take<u64>(u64(portions + 1) * 8 * RADIX);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "csa_sort_pairs: workspace too small");
 
-    CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, u64(portions) * passes * RADIX * sizeof(u32), ctx->stream));
+    CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, u64(passes) * RADIX * sizeof(u64), ctx->stream));
     for(int P = 0; P < portions; ++P)
     {
         const u64 first = u64(P) * PORTION, cnt = (n - first < PORTION ? n - first : PORTION);
         const unsigned blocks = unsigned(cnt / (2 * 256 * 8) < 1 ? 1 : (cnt / (2 * 256 * 8) > 148 * 8 ? 148 * 8 : cnt / (2 * 256 * 8)));
-        histogram_kernel<256><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const u64*>(keys) + first, cnt, begin_bit, passes, hist + u64(P) * passes * RADIX);
+        histogram_kernel<256><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const u64*>(keys) + first, cnt, begin_bit, end_bit, passes, hist);
         CSA_LAUNCH_CHECK(ctx);
     }
     u64* d_skip = ctx->d_scalars + 32;
-    digit_base_kernel<<<passes, RADIX, 0, ctx->stream>>>(hist, portions, passes, n, base, d_skip);
+    digit_base_kernel<<<passes, RADIX, 0, ctx->stream>>>(hist, portions, n, base, d_skip);
     CSA_LAUNCH_CHECK(ctx);
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 32, d_skip, passes * sizeof(u64), cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -404,11 +486,11 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
         for(int P = 0; P < portions; ++P)
         {
             const u64 first = u64(P) * PORTION, cnt = (n - first < PORTION ? n - first : PORTION);
-            const u64* db = base + (u64(P) * passes + p) * RADIX;
+            u64* db = base + (u64(p) * (portions + 1) + P) * RADIX;
             if(val_bytes == 4)
-                CSA_TRY((launch_pass<PASS_BLOCK, PASS_ITEMS, u32>(ctx, kin + first, kout, static_cast<const u32*>(vin) + first, static_cast<u32*>(vout), cnt, shift, db, status, counter)));
+                CSA_TRY(launch_pass_variant<u32>(ctx, kin + first, kout, static_cast<const u32*>(vin) + first, static_cast<u32*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
             else
-                CSA_TRY((launch_pass<PASS_BLOCK, PASS_ITEMS, u64>(ctx, kin + first, kout, static_cast<const u64*>(vin) + first, static_cast<u64*>(vout), cnt, shift, db, status, counter)));
+                CSA_TRY(launch_pass_variant<u64>(ctx, kin + first, kout, static_cast<const u64*>(vin) + first, static_cast<u64*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
         }
         if(timer.on)
         {

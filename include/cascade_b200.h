@@ -74,6 +74,9 @@ size_t csa_sort_workspace_bytes(uint64_t n);
 int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, void* vals_dev, void* vals_alt_dev,
                    uint32_t val_bytes, uint64_t n, int begin_bit, int end_bit, void* workspace_dev, size_t workspace_bytes,
                    int* in_alt);
+/* Test hook. key 0: log2 of the most records one launch of a digit pass takes (12..29, default 29); larger sorts run
+ * as several launches per pass. */
+int csa_debug_set(int key, uint64_t value);
 /* Average device time of the digit passes of the sorts run on ctx since the last csa_reset_counters, measured
  * with CUDA events on the context's stream when pass timing is on (csa_set_pass_timing): total milliseconds,
  * the passes timed and the records they moved. */

@@ -16,7 +16,7 @@ def ctx():
 
 def _check(ctx, keys, vals, b0, b1):
     from cascade_b200 import api
-    k0 = keys.clone()
+    k0, v0 = keys.clone(), vals.clone()
     ko, vo = api.sort_pairs(ctx, keys, vals, b0, b1)
     width = b1 - b0
     if width >= 64:
@@ -25,7 +25,7 @@ def _check(ctx, keys, vals, b0, b1):
         mk = (k0 >> b0) & ((1 << width) - 1)
     order = torch.sort(mk, stable=True).indices
     assert torch.equal(k0[order], ko)
-    assert torch.equal(order.to(vo.dtype), vo)
+    assert torch.equal(v0[order], vo)
 
 
 @pytest.mark.parametrize("n", [1, 2, 3, 31, 255, 4095, 4096, 4097, 100003, 1 << 20])
@@ -64,3 +64,18 @@ def test_sort_many_tiles(ctx):
     g = torch.Generator(device="cuda").manual_seed(3)
     keys = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g)
     _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 64)
+
+
+def test_sort_in_several_launches_per_pass(ctx):
+    """Sorts larger than one launch's share run as several launches per pass whose digit offsets chain up."""
+    from cascade_b200._lib import lib
+    assert lib().csa_debug_set(0, 16) == 0
+    try:
+        n = 1_000_003
+        g = torch.Generator(device="cuda").manual_seed(9)
+        keys = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g)
+        _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 64)
+        keys = torch.randint(0, 1 << 20, (n,), device="cuda", dtype=torch.int64, generator=g)
+        _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 20)
+    finally:
+        assert lib().csa_debug_set(0, 29) == 0
