@@ -35,34 +35,42 @@ template <int BLOCK>
 __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict__ keys, const u64 n, const int begin_bit, const int end_bit, const int passes,
                                                          u64* __restrict__ hist)
 {
-    __shared__ u32 h[8 * RADIX];
-    for(int i = threadIdx.x; i < passes * RADIX; i += BLOCK) h[i] = 0;
+    // One private histogram per warp keeps the shared-memory atomics of different warps apart; lanes of a warp that
+    // hold the same digit still meet, and when all 32 do (a digit that is constant over long stretches, as the high bytes
+    // of token ids are) one lane counts for the warp.
+    constexpr int WARPS = BLOCK / 32;
+    extern __shared__ u32 h[];                       // [WARPS][passes][RADIX]
+    const int per_warp = passes * RADIX;
+    for(int i = threadIdx.x; i < WARPS * per_warp; i += BLOCK) h[i] = 0;
     __syncthreads();
+    u32* const mine = h + (threadIdx.x >> 5) * per_warp;
 
     const u64 pairs = n >> 1;   // 128-bit loads of two keys
     const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(keys);
     const u64 stride = u64(gridDim.x) * BLOCK;
-    // Whole warps take part in every round so that the match instruction sees a full mask.
-    const u64 rounds = (pairs + stride - 1) / stride;
+    const u64 rounds = (pairs + stride - 1) / stride;       // whole warps take part in every round: the votes see a full mask
     u64 i = u64(blockIdx.x) * BLOCK + threadIdx.x;
     for(u64 r = 0; r < rounds; ++r, i += stride)
     {
         const bool live = i < pairs;
         ulonglong2 v = make_ulonglong2(0, 0);
         if(live) v = k2[i];
+        const bool all_live = __all_sync(0xFFFFFFFFu, live);
         #pragma unroll 1
         for(int p = 0; p < passes; ++p)
         {
             const int sh = begin_bit + p * RADIX_BITS;
             const u32 dm = digit_mask(sh, end_bit);
-            const u32 d0 = live ? u32(v.x >> sh) & dm : RADIX;       // RADIX = "no record"
-            const u32 d1 = live ? u32(v.y >> sh) & dm : RADIX;
-            const u32 m0 = __match_any_sync(0xFFFFFFFFu, d0);
-            const u32 m1 = __match_any_sync(0xFFFFFFFFu, d1);
-            if(live)
+            const u32 d0 = u32(v.x >> sh) & dm, d1 = u32(v.y >> sh) & dm;
+            const u32 lead = __shfl_sync(0xFFFFFFFFu, d0, 0);
+            if(all_live && __all_sync(0xFFFFFFFFu, d0 == lead && d1 == lead))
             {
-                if(lane_id() == u32(__ffs(m0) - 1)) atomicAdd(&h[p * RADIX + d0], __popc(m0));
-                if(lane_id() == u32(__ffs(m1) - 1)) atomicAdd(&h[p * RADIX + d1], __popc(m1));
+                if(lane_id() == 0) atomicAdd(&mine[p * RADIX + lead], 64u);
+            }
+            else if(live)
+            {
+                atomicAdd(&mine[p * RADIX + d0], 1u);
+                atomicAdd(&mine[p * RADIX + d1], 1u);
             }
         }
     }
@@ -70,11 +78,16 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
     {
         const u64 k = keys[n - 1];
         for(int p = 0; p < passes; ++p)
-            atomicAdd(&h[p * RADIX + (u32(k >> (begin_bit + p * RADIX_BITS)) & digit_mask(begin_bit + p * RADIX_BITS, end_bit))], 1u);
+            atomicAdd(&mine[p * RADIX + (u32(k >> (begin_bit + p * RADIX_BITS)) & digit_mask(begin_bit + p * RADIX_BITS, end_bit))], 1u);
     }
     __syncthreads();
-    for(int i2 = threadIdx.x; i2 < passes * RADIX; i2 += BLOCK)
-        if(h[i2] != 0) atomicAdd(&hist[i2], u64(h[i2]));
+    for(int i2 = threadIdx.x; i2 < per_warp; i2 += BLOCK)
+    {
+        u32 t = 0;
+        #pragma unroll
+        for(int w = 0; w < WARPS; ++w) t += h[w * per_warp + i2];
+        if(t != 0) atomicAdd(&hist[i2], u64(t));
+    }
 }
 
 // From the histograms: for every pass the global offset of each digit's first record (what the first launch of the pass
@@ -452,12 +465,20 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     u64* base = cv.take<u64>(u64(portions + 1) * 8 * RADIX);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "csa_sort_pairs: workspace too small");
 
+    {
+        static bool hist_configured[64] = {false};
+        if(!hist_configured[ctx->device & 63])
+        {
+            CSA_CUDA(ctx, cudaFuncSetAttribute(histogram_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8 * RADIX * 4));
+            hist_configured[ctx->device & 63] = true;
+        }
+    }
     CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, u64(passes) * RADIX * sizeof(u64), ctx->stream));
     for(int P = 0; P < portions; ++P)
     {
         const u64 first = u64(P) * PORTION, cnt = (n - first < PORTION ? n - first : PORTION);
         const unsigned blocks = unsigned(cnt / (2 * 256 * 8) < 1 ? 1 : (cnt / (2 * 256 * 8) > 148 * 8 ? 148 * 8 : cnt / (2 * 256 * 8)));
-        histogram_kernel<256><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const u64*>(keys) + first, cnt, begin_bit, end_bit, passes, hist);
+        histogram_kernel<256><<<blocks, 256, size_t(8) * passes * RADIX * 4, ctx->stream>>>(reinterpret_cast<const u64*>(keys) + first, cnt, begin_bit, end_bit, passes, hist);
         CSA_LAUNCH_CHECK(ctx);
     }
     u64* d_skip = ctx->d_scalars + 32;
