@@ -528,3 +528,96 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     *in_alt = flips & 1;
     return CSA_OK;
 }
+
+// ---- the sort for callers that must not allocate ---------------------------------------------------------------------
+//
+// Some hosts of this library run where device allocation is off the table: a plugin called in the middle of another
+// runtime's step, whose memory pool owns the whole device and treats a foreign cudaMalloc as an error (or would stall on
+// it, since cudaMalloc synchronises the device), or a service that has been told to stay inside a fixed memory budget
+// after start-up. csa_sort_pairs needs a context (which allocates) and a workspace. The entry point below needs neither:
+// its scratch (tile status words, digit histograms and offsets, a status word) is a fixed array in the library's device
+// image, which every GPU that loads the library holds from load to exit.
+
+namespace
+{
+
+constexpr u64 STATIC_SORT_MAX = CSA_STATIC_SORT_MAX_RECORDS;
+constexpr int ST_BLOCK = 512, ST_ITEMS = 8, ST_MATCH = 3, ST_TILE = ST_BLOCK * ST_ITEMS;
+constexpr size_t ST_OFF_STATUS = 0;                                                        // [tiles][RADIX] u32
+constexpr size_t ST_OFF_COUNTER = ST_OFF_STATUS + (STATIC_SORT_MAX / ST_TILE + 1) * RADIX * 4; // tile counter
+constexpr size_t ST_OFF_HIST = ST_OFF_COUNTER + 256;                                       // [8][RADIX] u64
+constexpr size_t ST_OFF_BASE = ST_OFF_HIST + size_t(8) * RADIX * 8;                        // [8][2][RADIX] u64
+constexpr size_t ST_OFF_SKIP = ST_OFF_BASE + size_t(8) * 2 * RADIX * 8;                    // [8] u64 (written, not read)
+constexpr size_t ST_OFF_DEVSTATUS = ST_OFF_SKIP + 256;                                     // one u64
+constexpr size_t ST_BYTES = ST_OFF_DEVSTATUS + 256;
+
+// Device code could name this array directly; host code must not pass its name to a kernel (on the host the name is only
+// a stand-in for the symbol), so the host asks the runtime for the array's device address once per device.
+static __device__ __align__(256) unsigned char g_static_scratch[ST_BYTES];
+unsigned char* g_static_scratch_addr[64] = {nullptr};
+
+}   // namespace
+
+extern "C" int csa_sort_pairs_static(void* stream_, uint64_t* keys, uint64_t* keys_alt, uint32_t* vals, uint32_t* vals_alt, uint64_t n,
+                                     int begin_bit, int end_bit, int* in_alt)
+{
+    if(!in_alt) return CSA_E_INVALID;
+    *in_alt = 0;
+    if(begin_bit < 0 || end_bit > 64 || begin_bit > end_bit) return CSA_E_INVALID;
+    if(n > STATIC_SORT_MAX)
+    {
+        std::fprintf(stderr, "csa_sort_pairs_static: %llu records exceed the fixed scratch's maximum of %llu; use csa_sort_pairs\n",
+                     (unsigned long long)n, (unsigned long long)STATIC_SORT_MAX);
+        return CSA_E_LIMIT;
+    }
+    if(n <= 1 || begin_bit == end_bit) return CSA_OK;
+    if(!keys || !keys_alt || !vals || !vals_alt) return CSA_E_INVALID;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    int dev = 0;
+    if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CSA_E_CUDA;
+    auto kern = onesweep_pass_kernel<ST_BLOCK, ST_ITEMS, u32, ST_MATCH>;
+    using S = Pass_Smem<ST_BLOCK, ST_ITEMS, u32>;
+    if(!g_static_scratch_addr[dev])
+    {
+        // Set-up, once per device, with that device current: the array's device address, and the kernel's shared-memory size.
+        void* p = nullptr;
+        if(cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) { cudaGetLastError(); return CSA_E_CUDA; }
+        if(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::bytes)) != cudaSuccess) { cudaGetLastError(); return CSA_E_CUDA; }
+        if(cudaFuncSetAttribute(histogram_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8 * RADIX * 4) != cudaSuccess) { cudaGetLastError(); return CSA_E_CUDA; }
+        g_static_scratch_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* const base_addr = g_static_scratch_addr[dev];
+    u32* const status = reinterpret_cast<u32*>(base_addr + ST_OFF_STATUS);
+    u32* const counter = reinterpret_cast<u32*>(base_addr + ST_OFF_COUNTER);
+    u64* const hist = reinterpret_cast<u64*>(base_addr + ST_OFF_HIST);
+    u64* const base = reinterpret_cast<u64*>(base_addr + ST_OFF_BASE);
+    u64* const skip = reinterpret_cast<u64*>(base_addr + ST_OFF_SKIP);
+    u64* const dev_status = reinterpret_cast<u64*>(base_addr + ST_OFF_DEVSTATUS);
+
+    const int passes = (end_bit - begin_bit + RADIX_BITS - 1) / RADIX_BITS;
+    const u64 tiles = div_up(n, ST_TILE);
+    // The array keeps the last call's contents: everything that must start at zero is cleared here.
+    if(cudaMemsetAsync(base_addr + ST_OFF_COUNTER, 0, ST_BYTES - ST_OFF_COUNTER, stream) != cudaSuccess) return CSA_E_CUDA;
+    const unsigned hblocks = unsigned(n / (2 * 256 * 8) < 1 ? 1 : (n / (2 * 256 * 8) > 148 * 8 ? 148 * 8 : n / (2 * 256 * 8)));
+    histogram_kernel<256><<<hblocks, 256, size_t(8) * passes * RADIX * 4, stream>>>(reinterpret_cast<const u64*>(keys), n, begin_bit, end_bit, passes, hist);
+    digit_base_kernel<<<passes, RADIX, 0, stream>>>(hist, 1, n, base, skip);
+    u64* kin = reinterpret_cast<u64*>(keys); u64* kout = reinterpret_cast<u64*>(keys_alt);
+    u32* vin = vals; u32* vout = vals_alt;
+    for(int p = 0; p < passes; ++p)     // every pass runs (no read-back decides about skipping), so the result's place is known
+    {
+        const int shift = begin_bit + p * RADIX_BITS;
+        if(cudaMemsetAsync(status, 0, tiles * RADIX * sizeof(u32), stream) != cudaSuccess) return CSA_E_CUDA;
+        if(cudaMemsetAsync(counter, 0, sizeof(u32), stream) != cudaSuccess) return CSA_E_CUDA;
+        u64* db = base + u64(p) * 2 * RADIX;
+        kern<<<unsigned(tiles), ST_BLOCK, S::bytes, stream>>>(kin, kout, vin, vout, n, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter, dev_status);
+        u64* tk = kin; kin = kout; kout = tk;
+        u32* tv = vin; vin = vout; vout = tv;
+    }
+    if(cudaGetLastError() != cudaSuccess) return CSA_E_CUDA;
+    u64 bits = 0;
+    if(cudaMemcpyAsync(&bits, dev_status, sizeof(bits), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return CSA_E_CUDA;
+    if(cudaStreamSynchronize(stream) != cudaSuccess) return CSA_E_CUDA;
+    *in_alt = passes & 1;
+    return bits == 0 ? CSA_OK : CSA_E_DEVICE;
+}

@@ -74,6 +74,19 @@ size_t csa_sort_workspace_bytes(uint64_t n);
 int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, void* vals_dev, void* vals_alt_dev,
                    uint32_t val_bytes, uint64_t n, int begin_bit, int end_bit, void* workspace_dev, size_t workspace_bytes,
                    int* in_alt);
+/* Most records of one csa_sort_pairs_static call. */
+#define CSA_STATIC_SORT_MAX_RECORDS (1ull << 22)
+/* The same sort for callers that cannot allocate device memory (no counterpart in the reference). It takes no context
+ * and no workspace: its scratch is a fixed array of about 1.1 MB inside the library's device image, which each GPU that
+ * loads the library holds until the process exits, so n is limited to CSA_STATIC_SORT_MAX_RECORDS (CSA_E_LIMIT beyond,
+ * with a line on stderr). It calls no cudaMalloc, cudaFree or other allocating routine. Keys are 64-bit, values 32-bit;
+ * every pass runs, so *in_alt = number of passes & 1. The work is queued on `stream` (a cudaStream_t, or null) of the
+ * current device and the call returns after it has finished, with CSA_E_DEVICE if a bounded wait ran out.
+ * The first call on each device looks up the array's device address and sizes the kernel's shared memory; make that
+ * first call outside any stream capture. All calls share the one array: calls that overlap on the GPU (two streams, two
+ * threads) race on it, so keep them one after another per device. */
+int csa_sort_pairs_static(void* stream, uint64_t* keys_dev, uint64_t* keys_alt_dev, uint32_t* vals_dev, uint32_t* vals_alt_dev,
+                          uint64_t n, int begin_bit, int end_bit, int* in_alt);
 /* Test hook. key 0: log2 of the most records one launch of a digit pass takes (12..29, default 29); larger sorts run
  * as several launches per pass. */
 int csa_debug_set(int key, uint64_t value);
