@@ -22,6 +22,13 @@ class BuildStats(ctypes.Structure):
     ]
 
 
+ALLGATHER_FN = ctypes.CFUNCTYPE(c_int, c_vp, c_vp, c_vp, c_u64)
+
+
+class Comm(ctypes.Structure):
+    _fields_ = [("rank", c_u32), ("world", c_u32), ("allgather", ALLGATHER_FN), ("user", c_vp)]
+
+
 class Index(ctypes.Structure):
     _fields_ = [("text", c_vp), ("sa40", c_vp), ("table", c_vp), ("n", c_u64), ("stride", c_u64)]
 
@@ -48,6 +55,8 @@ _SIGS = {
     "csa_build_device_bytes": (ctypes.c_size_t, [c_u64, c_u32]),
     "csa_build_sa": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_build_sa_host": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
+    "csa_plan_shards": (c_int, [c_vp, c_u32, c_u32, c_vp, c_vp, c_vp, c_vp]),
+    "csa_build_sa_multi": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, ctypes.POINTER(c_u64), ctypes.POINTER(c_u64), ctypes.POINTER(BuildStats)]),
     "csa_table_build": (c_int, [c_vp, c_vp, c_u64, c_vp, c_u64, c_vp]),
     "csa_find": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp]),
     "csa_locate": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp, c_vp]),

@@ -1,0 +1,353 @@
+// The suffix-array build spread over the GPUs of one box, one process per GPU.
+//
+// Sharding: a partition (a fixed contiguous range of the suffix array) is owned by one GPU for the whole build; the
+// inverse array `isa` (rank of every text position) is cut into equal shards by position, one per GPU. A position
+// travels to the owner of its partition, and a rank to the owner of its text position, as plain stores into the peer's
+// memory (CUDA IPC mapping of the peer's arena, NVLink through NVSwitch); a suffix reads the rank of the suffix h
+// positions ahead with a plain peer load. That is the whole exchange: what the reference moves as messages through host
+// RAM or files between generations (src/Partition_Backend.cpp:516-553, include/message.hpp:22-61) and joins by search
+// (join_messages_kernel, include/GPU_SACA.cuh:362-389) is here one 4-byte peer write and one 4-byte peer read.
+// The ranks meet at host barriers (the caller's all-gather): after the scatter, after generation 0, and twice per later
+// generation (all reads of `isa` before any write; all writes before the next reads). No device-side waits on peers.
+#include "common.cuh"
+#include "part.cuh"
+
+#include <cstdlib>
+#include <vector>
+
+extern "C" int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t world, uint64_t* part_off, uint32_t* owner, uint64_t* slot_base,
+                               uint64_t* cursor_all)
+{
+    if(!hist_all || !part_off || !owner || !slot_base || !cursor_all || p == 0 || world == 0 || world > CSA_MAX_GPUS) return CSA_E_INVALID;
+    part_off[0] = 0;
+    for(uint32_t q = 0; q < p; ++q)
+    {
+        uint64_t size = 0;
+        for(uint32_t g = 0; g < world; ++g) { cursor_all[uint64_t(g) * p + q] = size; size += hist_all[uint64_t(g) * p + q]; }
+        part_off[q + 1] = part_off[q] + size;
+    }
+    const uint64_t n = part_off[p];
+    // A partition goes to the GPU in whose equal share of the suffix array its middle falls: owners are non-decreasing.
+    uint32_t last = 0;
+    for(uint32_t q = 0; q < p; ++q)
+    {
+        const uint64_t mid = part_off[q] + (part_off[q + 1] - part_off[q]) / 2;
+        uint32_t g = n == 0 ? 0 : uint32_t((static_cast<unsigned __int128>(mid) * world) / n);
+        if(g >= world) g = world - 1;
+        if(g < last) g = last;
+        owner[q] = g;
+        last = g;
+    }
+    // Owners are non-decreasing, so GPU g's slice starts at the first partition whose owner is g or later.
+    for(uint32_t g = 0; g <= world; ++g)
+    {
+        uint64_t start = n;
+        for(uint32_t q = 0; q < p; ++q)
+            if(g < world && owner[q] >= g) { start = part_off[q]; break; }
+        slot_base[g] = start;
+    }
+    return CSA_OK;
+}
+
+namespace
+{
+
+struct Multi_Layout
+{
+    size_t keys, pos, head, isa, sa, sort_ws, scratch, pid, small, total;
+    size_t off_isa, off_sa;
+};
+
+Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
+{
+    Multi_Layout L;
+    const u64 cap = n_local ? n_local : 1;
+    L.keys = align_up256(cap * 8);
+    L.pos = align_up256(cap * 4);
+    L.head = align_up256(cap * 4);
+    L.isa = align_up256(shard * 4 + 64);
+    L.sa = align_up256(cap * 4 + 64);
+    L.sort_ws = align_up256(csa_sort_workspace_bytes(cap));
+    L.scratch = align_up256(div_up(cap, RANK_TILE) * 3 * 4 + 256);
+    L.pid = align_up256(shard * 2 + 64);
+    L.small = align_up256(size_t(p) * 8) * 3 + align_up256(size_t(2) * p * 8) + 4096;
+    // isa and sa come first so that their offsets inside the arena are the same formula on every rank
+    L.off_isa = 0;
+    L.off_sa = L.isa;
+    L.total = L.isa + L.sa + 2 * L.keys + 2 * L.pos + L.head + L.sort_ws + L.scratch + L.pid + L.small + 4096;
+    return L;
+}
+
+struct Peer_Info
+{
+    unsigned char handle[64];
+    u64 off_isa, off_sa, arena_bytes;
+};
+
+int gather(csa_ctx* ctx, const csa_comm* comm, const void* send, void* recv, u64 bytes)
+{
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));      // a barrier: this rank's queued device work is done first
+    if(comm->allgather(comm->user, send, recv, bytes) != 0) return csa_fail(ctx, CSA_E_COMM, "the caller's all-gather failed");
+    return CSA_OK;
+}
+
+int barrier(csa_ctx* ctx, const csa_comm* comm)
+{
+    u64 token = comm->rank, all[CSA_MAX_GPUS];
+    return gather(ctx, comm, &token, all, sizeof(u64));
+}
+
+}   // namespace
+
+extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint16_t* T, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40,
+                                  uint64_t capacity_entries, uint64_t* slot_first, uint64_t* slot_count, csa_build_stats* stats)
+{
+    if(!ctx || !comm || !comm->allgather || !T || !sa40 || !slot_first || !slot_count) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: null argument");
+    const u32 G = comm->world, me = comm->rank;
+    if(G == 0 || G > CSA_MAX_GPUS || me >= G) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: bad rank or world size");
+    if(n == 0 || p == 0 || p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: n or partition count out of range");
+    if(n >= (u64(1) << 32) - (u64(1) << 26)) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: this build addresses fewer than 2^32 - 2^26 suffixes");
+    if((reinterpret_cast<uintptr_t>(T) & 15) || (reinterpret_cast<uintptr_t>(sa40) & 15)) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: text and output must be 16-byte aligned");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+
+    csa_build_stats local_stats;
+    csa_build_stats& st = stats ? *stats : local_stats;
+    std::memset(&st, 0, sizeof(st));
+    st.n = n;
+    const u64 launches_before = ctx->counters[0], passes_before = ctx->counters[1], records_before = ctx->counters[2];
+    const bool debug = std::getenv("CSA_DEBUG") != nullptr;
+
+    cudaEvent_t ev[5];
+    for(auto& e : ev) CSA_CUDA(ctx, cudaEventCreate(&e));
+    struct Ev_Guard { cudaEvent_t* e; ~Ev_Guard() { for(int i = 0; i < 5; ++i) cudaEventDestroy(e[i]); } } ev_guard{ev};
+    CSA_CUDA(ctx, cudaEventRecord(ev[0], ctx->stream));
+
+    // Position shards: equal, a multiple of 8 positions so that text windows start 16-byte aligned.
+    const u64 shard = ((div_up(n, G) + 7) / 8) * 8;
+    const u64 my_first = u64(me) * shard < n ? u64(me) * shard : n;
+    const u64 my_count = (my_first + shard <= n) ? shard : n - my_first;
+
+    // ---- splitters: every rank samples the same positions of the same text, so all get the same splitters ----------
+    constexpr u64 MAX_SAMPLES = 1u << 19;
+    void* ws = nullptr;
+    const size_t pre_bytes = align_up256(2 * MAX_SAMPLES * 8) + align_up256(size_t(2) * p * 8) + align_up256(size_t(p) * 8) + 4096;
+    CSA_TRY(csa_arena(ctx, pre_bytes, &ws));
+    u32 p_eff = 1;
+    std::vector<u64> pivots(2 * size_t(p));
+    std::vector<u64> my_hist(p, 0);
+    {
+        Carver cv(ws, ctx->arena_bytes);
+        u64* samples_dev = cv.take<u64>(2 * MAX_SAMPLES);
+        u64* pivots_dev = cv.take<u64>(2 * u64(p));
+        u64* hist = cv.take<u64>(p);
+        if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: arena too small");
+        if(p > 1)
+        {
+            u64 n_samples = u64(32) * p * u64(bits_for(n));
+            if(n_samples > MAX_SAMPLES) n_samples = MAX_SAMPLES;
+            if(n_samples < 1024) n_samples = 1024;
+            CSA_TRY(csa_sample_kgrams(ctx, T, n, n_samples, seed, reinterpret_cast<uint64_t*>(samples_dev)));
+            std::vector<u64> samples(2 * n_samples);
+            CSA_CUDA(ctx, cudaMemcpyAsync(samples.data(), samples_dev, samples.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            const int r = csa_select_pivots(reinterpret_cast<const uint64_t*>(samples.data()), n_samples, p, reinterpret_cast<uint64_t*>(pivots.data()), &p_eff);
+            if(r != CSA_OK) return csa_fail(ctx, r, "multi-GPU build: splitter selection failed");
+            if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
+        }
+        // sizes of the partitions over this rank's positions (ids are made again once the arena has its final size)
+        CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
+        if(my_count) CSA_TRY(csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, nullptr, reinterpret_cast<uint64_t*>(hist)));
+        CSA_CUDA(ctx, cudaMemcpyAsync(my_hist.data(), hist, size_t(p_eff) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    st.partitions = p_eff;
+
+    // ---- plan: the same on every rank ------------------------------------------------------------------------------
+    std::vector<u64> hist_all(size_t(G) * p_eff), send_hist(my_hist.begin(), my_hist.begin() + p_eff);
+    CSA_TRY(gather(ctx, comm, send_hist.data(), hist_all.data(), size_t(p_eff) * 8));
+    std::vector<u64> part_off(p_eff + 1), slot_base(G + 1), cursor_all(size_t(G) * p_eff);
+    std::vector<u32> owner(p_eff);
+    if(csa_plan_shards(reinterpret_cast<const uint64_t*>(hist_all.data()), p_eff, G, reinterpret_cast<uint64_t*>(part_off.data()), owner.data(),
+                       reinterpret_cast<uint64_t*>(slot_base.data()), reinterpret_cast<uint64_t*>(cursor_all.data())) != CSA_OK)
+        return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: shard plan failed");
+    if(part_off[p_eff] != n) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: partition sizes do not add up to n");
+    const u64 n_local = slot_base[me + 1] - slot_base[me];
+    u64 max_part = 0, n_local_max = 0;
+    for(u32 q = 0; q < p_eff; ++q) if(part_off[q + 1] - part_off[q] > max_part) max_part = part_off[q + 1] - part_off[q];
+    for(u32 g = 0; g < G; ++g) if(slot_base[g + 1] - slot_base[g] > n_local_max) n_local_max = slot_base[g + 1] - slot_base[g];
+    st.max_partition = max_part;
+    *slot_first = slot_base[me];
+    *slot_count = n_local;
+    if(n_local > capacity_entries) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: the output buffer holds fewer entries than this rank's slice");
+
+    // ---- arena of the final size; peers map one another's arenas ---------------------------------------------------
+    // Every rank sizes its arena for the largest slice, so the layout (and the offsets of isa and sa) is the same everywhere.
+    const Multi_Layout L = multi_layout(n_local_max, shard, p_eff);
+    CSA_TRY(csa_arena(ctx, L.total, &ws));
+    Carver cv(ws, ctx->arena_bytes);
+    u32* isa = cv.take<u32>(L.isa / 4);
+    u32* sa = cv.take<u32>(L.sa / 4);
+    u64* keysA = cv.take<u64>(L.keys / 8);
+    u64* keysB = cv.take<u64>(L.keys / 8);
+    u32* posA = cv.take<u32>(L.pos / 4);
+    u32* posB = cv.take<u32>(L.pos / 4);
+    u32* head = cv.take<u32>(L.head / 4);
+    void* sort_ws = cv.take<u8>(L.sort_ws);
+    u32* scratch = cv.take<u32>(L.scratch / 4);
+    u16* pid = cv.take<u16>(L.pid / 2);
+    u64* hist = cv.take<u64>(p_eff);
+    u64* cursor = cv.take<u64>(p_eff);
+    u32** part_base = cv.take<u32*>(p_eff);
+    u64* pivots_dev = cv.take<u64>(2 * u64(p_eff));
+    if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: arena too small");
+    if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
+
+    Peer_Info mine;
+    std::memset(&mine, 0, sizeof(mine));
+    if(G > 1)
+    {
+        cudaIpcMemHandle_t h;
+        CSA_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->arena));
+        static_assert(sizeof(h) == 64, "IPC handle size");
+        std::memcpy(mine.handle, &h, 64);
+    }
+    mine.off_isa = reinterpret_cast<u8*>(isa) - static_cast<u8*>(ctx->arena);
+    mine.off_sa = reinterpret_cast<u8*>(sa) - static_cast<u8*>(ctx->arena);
+    mine.arena_bytes = ctx->arena_bytes;
+    std::vector<Peer_Info> peers(G);
+    CSA_TRY(gather(ctx, comm, &mine, peers.data(), sizeof(Peer_Info)));
+    u8* peer_arena[CSA_MAX_GPUS];
+    for(u32 g = 0; g < G; ++g)
+    {
+        if(g == me) { peer_arena[g] = static_cast<u8*>(ctx->arena); continue; }
+        if(ctx->peer_open[g] && std::memcmp(ctx->peer_handle[g], peers[g].handle, 64) != 0)
+        {
+            cudaIpcCloseMemHandle(ctx->peer_base[g]);
+            ctx->peer_open[g] = false;
+        }
+        if(!ctx->peer_open[g])
+        {
+            cudaIpcMemHandle_t h;
+            std::memcpy(&h, peers[g].handle, 64);
+            void* base = nullptr;
+            CSA_CUDA(ctx, cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+            ctx->peer_base[g] = base;
+            std::memcpy(ctx->peer_handle[g], peers[g].handle, 64);
+            ctx->peer_open[g] = true;
+        }
+        peer_arena[g] = static_cast<u8*>(ctx->peer_base[g]);
+    }
+    Isa_View iv;
+    std::memset(&iv, 0, sizeof(iv));
+    iv.gpus = G; iv.shard_size = shard;
+    for(u32 g = 0; g < G; ++g) iv.shard[g] = reinterpret_cast<u32*>(peer_arena[g] + peers[g].off_isa);
+
+    // ---- partition ids of this rank's positions, then the scatter to the partitions' owners ------------------------
+    u64 peer_bytes = 0;
+    {
+        CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
+        if(my_count) CSA_TRY(csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist)));
+        std::vector<u32*> bases(p_eff);
+        for(u32 q = 0; q < p_eff; ++q)
+        {
+            const u32 o = owner[q];
+            bases[q] = reinterpret_cast<u32*>(peer_arena[o] + peers[o].off_sa) + (part_off[q] - slot_base[o]);
+            if(o != me) peer_bytes += hist_all[size_t(me) * p_eff + q] * 4;
+        }
+        CSA_CUDA(ctx, cudaMemcpyAsync(part_base, bases.data(), size_t(p_eff) * sizeof(u32*), cudaMemcpyHostToDevice, ctx->stream));
+        CSA_CUDA(ctx, cudaMemcpyAsync(cursor, cursor_all.data() + size_t(me) * p_eff, size_t(p_eff) * 8, cudaMemcpyHostToDevice, ctx->stream));
+        if(my_count) CSA_TRY(csa_scatter_by_pid(ctx, pid, my_first, my_count, p_eff, part_base, reinterpret_cast<uint64_t*>(cursor)));
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    CSA_CUDA(ctx, cudaEventRecord(ev[1], ctx->stream));
+    CSA_TRY(barrier(ctx, comm));        // every position has reached its owner
+
+    // ---- generation 0 over this rank's partitions -------------------------------------------------------------------
+    u64* act_count = ctx->d_scalars;
+    CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
+    const u64 base_slot = slot_base[me];
+    for(u32 q = 0; q < p_eff; ++q)
+    {
+        if(owner[q] != me) continue;
+        const u64 S = part_off[q + 1] - part_off[q], first = part_off[q] - base_slot;
+        if(S == 0) continue;
+        CSA_TRY(launch_keys_gen0(ctx, T, sa + first, S, keysA));
+        int in_alt = 0;
+        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), sa + first, posB, 4, S, 0, 64, sort_ws,
+                               L.sort_ws, &in_alt));
+        const u64* ks = in_alt ? keysB : keysA;
+        const u32* ps = in_alt ? posB : sa + first;
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, base_slot, sa, head, posA, act_count, scratch));
+    }
+    CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_CUDA(ctx, cudaEventRecord(ev[2], ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    u64 active = ctx->h_scalars[0];
+    peer_bytes += (n_local * 4 * (G - 1)) / G;     // ranks written to the position owners: (G-1)/G of them are remote
+    u64 counts[CSA_MAX_GPUS];
+    CSA_TRY(gather(ctx, comm, &active, counts, sizeof(u64)));     // also the barrier after generation 0's rank writes
+    u64 total_active = 0;
+    for(u32 g = 0; g < G; ++g) total_active += counts[g];
+    st.active_after_gen0 = total_active;
+    if(debug) std::fprintf(stderr, "[csa %u/%u] n=%llu local=%llu partitions=%u active after generation 0: %llu (all ranks %llu)\n", me, G, n, n_local,
+                           p_eff, active, total_active);
+
+    // ---- doubling generations: all ranks run the same number of them ------------------------------------------------
+    u32* pos_cur = posA; u32* pos_other = posB;
+    u64 h = 4;
+    u32 gen = 0;
+    const int prim_bits = bits_for(n_local_max ? n_local_max - 1 : 0) < 1 ? 1 : bits_for(n_local_max - 1);
+    while(total_active > 0)
+    {
+        if(gen < 48) st.active_per_gen[gen] = total_active;
+        const int sec_bits = bits_for(n - 1 + h);
+        if(sec_bits + prim_bits > 64) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: rank pair does not fit a 64-bit key");
+        CSA_TRY(launch_keys_gen(ctx, head, pos_cur, active, n, h, sec_bits, iv, keysA));
+        peer_bytes += (active * 8 * (G - 1)) / G;          // one rank read and one rank written per tied suffix
+        CSA_TRY(barrier(ctx, comm));                       // every rank has read the ranks of this generation
+        int in_alt = 0;
+        if(active) CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), pos_cur, pos_other, 4, active, 0,
+                                          sec_bits + prim_bits, sort_ws, L.sort_ws, &in_alt));
+        const u64* ks = in_alt ? keysB : keysA;
+        u32* ps = in_alt ? pos_other : pos_cur;
+        u32* pn = in_alt ? pos_cur : pos_other;
+        CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, base_slot, sa, head, pn, act_count, scratch));
+        CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        u64 mine2[2] = {ctx->h_scalars[0], ctx->h_scalars[1]}, all2[2 * CSA_MAX_GPUS];
+        CSA_TRY(gather(ctx, comm, mine2, all2, sizeof(mine2)));    // the barrier after this generation's rank writes
+        u64 next_total = 0, any_status = 0;
+        for(u32 g = 0; g < G; ++g) { next_total += all2[2 * g]; any_status |= all2[2 * g + 1]; }
+        if(any_status != 0) { u64 b = 0; csa_sync(ctx, reinterpret_cast<uint64_t*>(&b)); return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: a rank reported a device status"); }
+        if(debug) std::fprintf(stderr, "[csa %u/%u] generation %u: h=%llu active %llu -> %llu (all ranks %llu)\n", me, G, gen + 1, h, active, mine2[0], next_total);
+        active = mine2[0];
+        total_active = next_total;
+        pos_cur = pn; pos_other = ps;
+        ++gen;
+        if(h > (u64(1) << 40)) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: doubling did not terminate");
+        h *= 2;
+    }
+    st.generations = gen;
+    CSA_CUDA(ctx, cudaEventRecord(ev[3], ctx->stream));
+
+    // ---- this rank's slice of the output ------------------------------------------------------------------------------
+    CSA_TRY(launch_pack_sa40(ctx, sa, n_local, sa40));
+    CSA_CUDA(ctx, cudaEventRecord(ev[4], ctx->stream));
+    u64 bits = 0;
+    CSA_TRY(csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits)));
+    CSA_TRY(barrier(ctx, comm));        // no rank leaves (and reuses its arena) while another may still read it
+
+    float ms = 0;
+    cudaEventElapsedTime(&ms, ev[0], ev[1]); st.ms_partition = ms;
+    cudaEventElapsedTime(&ms, ev[1], ev[2]); st.ms_gen0 = ms;
+    cudaEventElapsedTime(&ms, ev[2], ev[3]); st.ms_doubling = ms;
+    cudaEventElapsedTime(&ms, ev[3], ev[4]); st.ms_output = ms;
+    cudaEventElapsedTime(&ms, ev[0], ev[4]); st.ms_total = ms;
+    st.kernel_launches = ctx->counters[0] - launches_before;
+    st.sort_passes = ctx->counters[1] - passes_before;
+    st.sort_records = ctx->counters[2] - records_before;
+    st.peer_bytes = peer_bytes;
+    return CSA_OK;
+}

@@ -38,6 +38,10 @@ struct csa_ctx
     size_t arena_bytes = 0;
     std::string err;
     u64 counters[16] = {0};        // launch and byte counters for the benchmark
+    // Mappings of other GPUs' arenas opened through CUDA IPC (multi-GPU builds), kept while the peers' handles stay the same.
+    void* peer_base[CSA_MAX_GPUS] = {nullptr};
+    unsigned char peer_handle[CSA_MAX_GPUS][64] = {{0}};
+    bool peer_open[CSA_MAX_GPUS] = {false};
 };
 
 #define CSA_CUDA(ctx, call)                                                                             \

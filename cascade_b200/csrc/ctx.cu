@@ -33,6 +33,7 @@ extern "C" void csa_ctx_destroy(csa_ctx* ctx)
     cudaSetDevice(ctx->device);
     if(ctx->stream) cudaStreamSynchronize(ctx->stream);
     sort_reset_timing(ctx);
+    for(int g = 0; g < CSA_MAX_GPUS; ++g) if(ctx->peer_open[g]) cudaIpcCloseMemHandle(ctx->peer_base[g]);
     if(ctx->arena) cudaFree(ctx->arena);
     if(ctx->d_status) cudaFree(ctx->d_status);
     if(ctx->d_scalars) cudaFree(ctx->d_scalars);

@@ -122,7 +122,8 @@ __global__ void __launch_bounds__(BLOCK) partition_ids_kernel(const u16* __restr
             hi = (hi << 16) | (lo >> 48);
             lo = (lo << 16) | u64(win[local + k + 8]);
         }
-        if(local + ITEMS <= tile_count)
+        if(pid_out == nullptr) { /* sizes only */ }
+        else if(local + ITEMS <= tile_count)
         {
             if constexpr(ITEMS % 8 == 0)
             {
@@ -226,7 +227,7 @@ constexpr int PID_BLOCK = 256, PID_ITEMS = 16;
 extern "C" int csa_partition_ids(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t first, uint64_t count, const uint64_t* pivots,
                                  uint32_t p, uint16_t* pid, uint64_t* hist)
 {
-    if(!ctx || !text || !pid || !hist || p == 0 || (p > 1 && !pivots) || first + count > n) return csa_fail(ctx, CSA_E_INVALID, "csa_partition_ids: bad argument");
+    if(!ctx || !text || !hist || p == 0 || (p > 1 && !pivots) || first + count > n) return csa_fail(ctx, CSA_E_INVALID, "csa_partition_ids: bad argument");
     if(p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "csa_partition_ids: too many partitions");
     if((reinterpret_cast<uintptr_t>(text) & 15) || (first & 7) || (reinterpret_cast<uintptr_t>(pid) & 15))
         return csa_fail(ctx, CSA_E_INVALID, "csa_partition_ids: text and pid must be 16-byte aligned and `first` a multiple of 8");

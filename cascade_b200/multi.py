@@ -1,0 +1,173 @@
+"""Multi-GPU build, one process per GPU: the host plumbing (torch.distributed) around csa_build_sa_multi.
+
+The library asks its caller for ONE collective, an all-gather of small host buffers (partition sizes, IPC handles,
+active counts; it also serves as the barrier between the steps). Here it is torch.distributed.all_gather, on CPU
+tensors under gloo and on device tensors under NCCL. All bulk data moves inside the library's kernels as peer loads
+and stores.
+"""
+import ctypes
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import api
+from ._lib import ALLGATHER_FN, BuildStats, Comm, c_u64
+
+
+def make_comm(rank, world, device=None):
+    """Returns (Comm, keepalive). `device` is the torch device for NCCL groups, None for gloo."""
+    def _allgather(user, send, recv, nbytes):
+        try:
+            n = int(nbytes)
+            src = np.ctypeslib.as_array(ctypes.cast(send, ctypes.POINTER(ctypes.c_uint8)), shape=(n,))
+            dst = np.ctypeslib.as_array(ctypes.cast(recv, ctypes.POINTER(ctypes.c_uint8)), shape=(n * world,))
+            if world == 1:
+                dst[:] = src
+                return 0
+            t = torch.from_numpy(src.copy())
+            if device is not None:
+                t = t.to(device)
+            out = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(out, t)
+            for r in range(world):
+                dst[r * n:(r + 1) * n] = out[r].cpu().numpy()
+            return 0
+        except Exception as e:  # the C side turns a non-zero return into CSA_E_COMM
+            print(f"[cascade_b200.multi] all-gather failed on rank {rank}: {e}", flush=True)
+            return 1
+
+    fn = ALLGATHER_FN(_allgather)
+    return Comm(rank, world, fn, None), fn
+
+
+def plan_shards(hist_all, world):
+    """Host-side shard plan (csa_plan_shards) from hist_all[world][p]. Returns (part_off, owner, slot_base, cursor_all)."""
+    from ._lib import lib
+    hist_all = np.ascontiguousarray(hist_all, dtype=np.uint64)
+    p = hist_all.shape[1]
+    part_off = np.zeros(p + 1, np.uint64)
+    owner = np.zeros(p, np.uint32)
+    slot_base = np.zeros(world + 1, np.uint64)
+    cursor = np.zeros((world, p), np.uint64)
+    rc = lib().csa_plan_shards(hist_all.ctypes.data, p, world, part_off.ctypes.data, owner.ctypes.data, slot_base.ctypes.data, cursor.ctypes.data)
+    if rc != 0:
+        raise api.CascadeError(rc, "csa_plan_shards")
+    return part_off, owner, slot_base, cursor
+
+
+def build_sa_multi(ctx, comm, text_dev, n, p, seed=0, out=None, capacity=None):
+    """This rank's slice of the suffix array of text_dev[0, n). Returns (sa40 slice tensor, first, count, stats)."""
+    world = comm.world
+    if capacity is None:
+        capacity = n if world == 1 else min(n, n // world + n // max(1, min(p, 8)) + 1024)
+    if out is None:
+        out = torch.zeros(5 * capacity + api.SA_PAD_BYTES, dtype=torch.uint8, device=text_dev.device)
+    st = BuildStats()
+    first, count = c_u64(0), c_u64(0)
+    torch.cuda.synchronize(text_dev.device)
+    ctx.check(ctx.L.csa_build_sa_multi(ctx.h, ctypes.byref(comm), text_dev.data_ptr(), n, p, seed, out.data_ptr(), capacity,
+                                       ctypes.byref(first), ctypes.byref(count), ctypes.byref(st)))
+    return out, int(first.value), int(count.value), st
+
+
+def _max_over_ranks(x, device):
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _sum_over_ranks(x, device):
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def bench(args, rank, world, local):
+    """The N > 1 arm of bench.py: the same corpus (strong scaling), partitions sharded over the ranks."""
+    import bench as B
+    dev = torch.device("cuda", local)
+    ctx = api.Context(local)
+    comm, keep = make_comm(rank, world, dev)
+    n, p = args.tokens, B.C2_PARTITIONS
+    peak, peak_kind = B.measured_peak_gbs()
+    T = api.gen_corpus_device(ctx, n, 0, B.C2_MEAN_DOC)          # every rank makes the same text in its own HBM
+    cap = min(n, n // world + n // 8 + 1024)
+    out = torch.zeros(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8, device=dev)
+    for _ in range(args.warmup):
+        build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+    ctx.L.csa_set_pass_timing(ctx.h, 1)
+    ctx.reset_counters()
+    dist.barrier()
+    torch.cuda.synchronize()
+    step_ms, launches, peer = [], 0, 0
+    with B.ClockSampler(local) as clocks:
+        for _ in range(args.steps):
+            _, first, count, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            step_ms.append(_max_over_ranks(st.ms_total, dev))
+            launches += st.kernel_launches
+            peer += st.peer_bytes
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms = sum(step_ms) / len(step_ms)
+    pm, pc, pr = ctypes.c_double(0), c_u64(0), c_u64(0)
+    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr))
+    ctx.L.csa_set_pass_timing(ctx.h, 0)
+    achieved = (pr.value * 24) / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
+
+    # cheap check of this rank's slice: sizes add up, and sampled neighbours are in order on their first 4 symbols
+    total = _sum_over_ranks(count, dev)
+    ok = 1.0
+    if count > 1:
+        g = torch.Generator(device=dev).manual_seed(rank)
+        r = torch.randint(0, count - 1, (min(count - 1, 1 << 20),), device=dev, generator=g)
+        b = out[:5 * count].view(count, 5).to(torch.int64)
+        posn = b[:, 0] | (b[:, 1] << 8) | (b[:, 2] << 16) | (b[:, 3] << 24) | (b[:, 4] << 32)
+        Tl = T.view(torch.int16).to(torch.int64) & 0xFFFF
+        def key4(ps):
+            return (Tl[ps] << 48) | (Tl[ps + 1] << 32) | (Tl[ps + 2] << 16) | Tl[ps + 3]
+        a, c = key4(posn[r]), key4(posn[r + 1])
+        ok = float(bool(((a >> 1) <= (c >> 1)).all()))      # compare as unsigned through a 63-bit view
+        del b, posn, Tl
+    ok_all = _sum_over_ranks(ok, dev) == world and total == n
+
+    # end to end: pinned host text in, this rank's slice of the 5-byte array out
+    e2e = None
+    if not args.no_e2e:
+        th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
+        th.copy_(T.cpu())
+        oh = torch.empty(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
+        ts = []
+        for it in range(1 + max(1, min(args.steps, 2))):
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            T.copy_(th, non_blocking=True)
+            _, first, count, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            oh[:5 * count].copy_(out[:5 * count], non_blocking=True)
+            torch.cuda.synchronize()
+            dt = _max_over_ranks(time.perf_counter() - t0, dev)
+            if it > 0:
+                ts.append(dt)
+        e_ms = 1e3 * sum(ts) / len(ts)
+        e2e = {"value": n / (e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": 2 * n * world, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms,
+               "api": "csa_build_sa_multi between a pinned host text copy in and a pinned copy of the rank's sa40 slice out"}
+    launches_all = _sum_over_ranks(launches, dev)
+    peer_all = _sum_over_ranks(peer, dev)
+    if rank == 0:
+        line = {"metric": B.METRIC, "value": n / (ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                "config": B.workload_config(args, world), "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches_all),
+                "roofline": {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort), rank 0", "achieved": achieved,
+                             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                             "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value},
+                "nvlink": {"peer_bytes_per_step_all_ranks": peer_all / args.steps, "generations": st.generations,
+                           "note": "positions to partition owners + ranks to and from position owners, 4 bytes each, (G-1)/G of them remote"},
+                "verified": {"slices_add_up_to_n": total == n, "sampled_neighbours_in_order": ok_all}}
+        print(json.dumps(line))
+    dist.barrier()
+    ctx.close()
+    dist.destroy_process_group()

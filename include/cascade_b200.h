@@ -156,6 +156,36 @@ int csa_build_sa(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint32_t p,
 int csa_build_sa_host(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
                       csa_build_stats* stats);
 
+/* ---- build on several GPUs of one box (one process per GPU) ------------------------------------------------ */
+
+/* All-gather of `bytes` bytes per rank between the ranks' HOST buffers: recv holds world * bytes, rank r's part at
+ * r * bytes. It also serves as a barrier. Returns 0 on success. The caller supplies it (torch.distributed, MPI, threads). */
+typedef int (*csa_allgather_fn)(void* user, const void* send, void* recv, uint64_t bytes);
+typedef struct csa_comm
+{
+    uint32_t rank, world;       /* world <= CSA_MAX_GPUS */
+    csa_allgather_fn allgather;
+    void* user;
+} csa_comm;
+
+/* Host-side plan of a sharded build, the same on every rank: from every rank's partition sizes over its share of the
+ * positions (hist_all[world][p]) the partitions' global offsets part_off[p + 1], their owners owner[p] (contiguous blocks
+ * of partitions balanced by size, so a GPU owns one contiguous slice of the suffix array), the slice starts
+ * slot_base[world + 1], and for every (rank, partition) the offset inside the partition at which that rank's positions
+ * go (cursor_all[world][p]). Stands where the reference keeps every partition on its one GPU (src/GPU_SACA.cu:982-985). */
+int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t world, uint64_t* part_off, uint32_t* owner,
+                    uint64_t* slot_base, uint64_t* cursor_all);
+/* The build of csa_build_sa spread over comm->world GPUs. Every rank passes the whole text in its own device memory
+ * (same n, p, seed everywhere). Whole partitions are owned by one GPU; positions travel to their partition's owner and
+ * ranks to the owner of their text position as plain stores into peer memory (CUDA IPC mappings, NVLink), and are read
+ * back by peer loads; the ranks meet at host barriers between the steps. Rank r receives its contiguous slice of the
+ * suffix array: entries [*slot_first, *slot_first + *slot_count) as 5-byte entries at sa40_dev, which must hold
+ * capacity_entries entries (n / world + the largest partition is always enough; CSA_E_NOMEM if too few).
+ * Replaces the host-mediated exchange of the reference (messages through RAM or files, src/Partition_Backend.cpp:516-553). */
+int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint16_t* text_dev, uint64_t n, uint32_t p, uint64_t seed,
+                       uint8_t* sa40_dev, uint64_t capacity_entries, uint64_t* slot_first, uint64_t* slot_count,
+                       csa_build_stats* stats);
+
 /* ---- query engine ------------------------------------------------------------------------------------- */
 
 typedef struct csa_index

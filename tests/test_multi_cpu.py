@@ -1,0 +1,88 @@
+"""Host side of the multi-GPU build, on CPU: the shard plan, and the caller-supplied all-gather between two gloo ranks."""
+import ctypes
+import os
+import socket
+import sys
+
+import numpy as np
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _check_plan(hist_all, world):
+    from cascade_b200 import multi
+    part_off, owner, slot_base, cursor = multi.plan_shards(hist_all, world)
+    p = hist_all.shape[1]
+    sizes = hist_all.sum(axis=0)
+    n = int(sizes.sum())
+    assert part_off[0] == 0 and np.array_equal(np.diff(part_off.astype(np.int64)), sizes.astype(np.int64))
+    assert np.all(np.diff(owner.astype(np.int64)) >= 0) and owner.max() < world          # contiguous blocks of partitions
+    assert slot_base[0] == 0 and slot_base[world] == n and np.all(np.diff(slot_base.astype(np.int64)) >= 0)
+    for q in range(p):
+        g = int(owner[q])
+        assert slot_base[g] <= part_off[q] and part_off[q + 1] <= slot_base[g + 1]      # a partition lies inside its owner's slice
+        # the ranks' runs inside a partition tile it exactly
+        assert cursor[0, q] == 0
+        for r in range(1, world):
+            assert cursor[r, q] == cursor[r - 1, q] + hist_all[r - 1, q]
+    return part_off, owner, slot_base
+
+
+def test_plan_is_balanced_and_consistent():
+    rng = np.random.default_rng(0)
+    for world in (1, 2, 4, 8):
+        for p in (1, 3, 64, 500):
+            h = rng.integers(0, 1000, size=(world, p)).astype(np.uint64)
+            part_off, owner, slot_base = _check_plan(h, world)
+            if p >= 64:
+                n = int(h.sum())
+                share = np.diff(slot_base.astype(np.int64))
+                assert share.max() <= n / world + 2 * int(h.sum(axis=0).max())
+    # degenerate: everything in one partition, more GPUs than partitions
+    h = np.zeros((4, 2), np.uint64)
+    h[:, 1] = 10
+    _check_plan(h, 4)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _gloo_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from cascade_b200 import multi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    comm, keep = multi.make_comm(rank, world, None)
+    p = 16
+    mine = (np.arange(p, dtype=np.uint64) + 1) * np.uint64(rank + 1)           # this rank's partition sizes
+    allh = np.zeros(world * p, np.uint64)
+    rc = comm.allgather(None, mine.ctypes.data, allh.ctypes.data, mine.nbytes)   # the call the library makes
+    assert rc == 0
+    part_off, owner, slot_base, cursor = multi.plan_shards(allh.reshape(world, p), world)
+    q.put((rank, allh.tolist(), part_off.tolist(), owner.tolist(), slot_base.tolist()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_allgather_callback_between_two_gloo_ranks():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, world, port, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    assert res[0][1:] == res[1][1:], "the ranks must see the same sizes and make the same plan"
+    want = [(i + 1) * (r + 1) for r in range(world) for i in range(16)]
+    assert res[0][1] == want
