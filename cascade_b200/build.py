@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcascade_b200.so")
-SOURCES = ["ctx.cu", "radix_sort.cu", "partition.cu", "doubling.cu", "build_sa.cu", "build_multi.cu", "query.cu", "corpus.cu", "host_tools.cu"]
+SOURCES = ["ctx.cu", "radix_sort.cu", "partition.cu", "doubling.cu", "build_sa.cu", "build_multi.cu", "exchange.cu", "query.cu", "corpus.cu", "host_tools.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-O3,-fopenmp", "--expt-relaxed-constexpr",
@@ -28,7 +28,8 @@ def needs_build():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "cascade_b200.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if os.path.isfile(os.path.join(CSRC, f))]
+    deps += [os.path.join(CSRC, "host", f) for f in os.listdir(os.path.join(CSRC, "host"))] + [os.path.join(HERE, "..", "include", "cascade_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
@@ -54,7 +55,18 @@ def build(force=False, verbose=False):
         objs.append(obj)
     cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart", "-Xcompiler", "-fopenmp", "-lgomp"]
     subprocess.check_call(cmd)
+    build_tools()
     return LIB
+
+
+def build_tools():
+    """The command lines of the drop-in surface: bin/cascade and bin/query, linked against the library."""
+    bindir = os.path.join(HERE, "bin")
+    os.makedirs(bindir, exist_ok=True)
+    for name, src in (("cascade", "cascade_main.cpp"), ("query", "query_main.cpp")):
+        cmd = [_nvcc(), "-O2", "-std=c++17", os.path.join(CSRC, "host", src), "-o", os.path.join(bindir, name), "-L" + HERE, "-lcascade_b200",
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/..", "-lcudart"]
+        subprocess.check_call(cmd)
 
 
 if __name__ == "__main__":

@@ -2,13 +2,15 @@
 //
 // Sharding: a partition (a fixed contiguous range of the suffix array) is owned by one GPU for the whole build; the
 // inverse array `isa` (rank of every text position) is cut into equal shards by position, one per GPU. A position
-// travels to the owner of its partition, and a rank to the owner of its text position, as plain stores into the peer's
-// memory (CUDA IPC mapping of the peer's arena, NVLink through NVSwitch); a suffix reads the rank of the suffix h
-// positions ahead with a plain peer load. That is the whole exchange: what the reference moves as messages through host
-// RAM or files between generations (src/Partition_Backend.cpp:516-553, include/message.hpp:22-61) and joins by search
-// (join_messages_kernel, include/GPU_SACA.cuh:362-389) is here one 4-byte peer write and one 4-byte peer read.
-// The ranks meet at host barriers (the caller's all-gather): after the scatter, after generation 0, and twice per later
-// generation (all reads of `isa` before any write; all writes before the next reads). No device-side waits on peers.
+// travels to the owner of its partition as a store into the peer's memory (CUDA IPC mapping of the peer's arena, NVLink
+// through NVSwitch), in runs of one partition. A rank travels to the owner of its text position as a message, as in the
+// reference (include/message.hpp:22-61), but over NVLink instead of host RAM or files (src/Partition_Backend.cpp:516-553):
+// every GPU buckets its (rank, position) updates by destination GPU, the buckets cross as contiguous copies into the
+// destinations' inboxes, and each GPU applies its inbox to its own shard; reads of ranks take a request and a response
+// leg of the same kind. Since a shard is addressed directly by position, no join by search is needed
+// (join_messages_kernel, include/GPU_SACA.cuh:362-389). Fine-grained peer loads and stores into a shard of several
+// gigabytes were measured to be far slower than these bulk copies, which is why ranks are not written in place.
+// The ranks meet at host barriers (the caller's all-gather) between the steps. No device-side waits on peers.
 #include "common.cuh"
 #include "part.cuh"
 
@@ -54,8 +56,7 @@ namespace
 
 struct Multi_Layout
 {
-    size_t keys, pos, head, isa, sa, sort_ws, scratch, pid, small, total;
-    size_t off_isa, off_sa;
+    size_t keys, pos, head, isa, sa, sort_ws, scratch, pid, small, xin, resp, upd, total;
 };
 
 Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
@@ -71,17 +72,17 @@ Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
     L.scratch = align_up256(div_up(cap, RANK_TILE) * 3 * 4 + 256);
     L.pid = align_up256(shard * 2 + 64);
     L.small = align_up256(size_t(p) * 8) * 3 + align_up256(size_t(2) * p * 8) + 4096;
-    // isa and sa come first so that their offsets inside the arena are the same formula on every rank
-    L.off_isa = 0;
-    L.off_sa = L.isa;
-    L.total = L.isa + L.sa + 2 * L.keys + 2 * L.pos + L.head + L.sort_ws + L.scratch + L.pid + L.small + 4096;
+    L.xin = align_up256(shard * 8 + 64);        // inbox of the bulk exchange: updates (8 bytes) or requests + responses (4 + 4)
+    L.resp = align_up256(cap * 4 + 64);         // responses to this GPU's requests
+    L.upd = align_up256(cap * 8 + 64);          // (rank, position) updates before they are bucketed
+    L.total = L.isa + L.sa + 2 * L.keys + 2 * L.pos + L.head + L.sort_ws + L.scratch + L.pid + L.small + L.xin + L.resp + L.upd + 4096;
     return L;
 }
 
 struct Peer_Info
 {
     unsigned char handle[64];
-    u64 off_isa, off_sa, arena_bytes;
+    u64 off_isa, off_sa, off_xin, off_resp, arena_bytes;
 };
 
 int gather(csa_ctx* ctx, const csa_comm* comm, const void* send, void* recv, u64 bytes)
@@ -199,6 +200,9 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     u64* cursor = cv.take<u64>(p_eff);
     u32** part_base = cv.take<u32*>(p_eff);
     u64* pivots_dev = cv.take<u64>(2 * u64(p_eff));
+    u8* xin = cv.take<u8>(L.xin);
+    u32* resp_in = cv.take<u32>(L.resp / 4);
+    u64* upd = cv.take<u64>(L.upd / 8);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: arena too small");
     if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
 
@@ -213,6 +217,8 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     }
     mine.off_isa = reinterpret_cast<u8*>(isa) - static_cast<u8*>(ctx->arena);
     mine.off_sa = reinterpret_cast<u8*>(sa) - static_cast<u8*>(ctx->arena);
+    mine.off_xin = xin - static_cast<u8*>(ctx->arena);
+    mine.off_resp = reinterpret_cast<u8*>(resp_in) - static_cast<u8*>(ctx->arena);
     mine.arena_bytes = ctx->arena_bytes;
     std::vector<Peer_Info> peers(G);
     CSA_TRY(gather(ctx, comm, &mine, peers.data(), sizeof(Peer_Info)));
@@ -241,6 +247,83 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     std::memset(&iv, 0, sizeof(iv));
     iv.gpus = G; iv.shard_size = shard;
     for(u32 g = 0; g < G; ++g) iv.shard[g] = reinterpret_cast<u32*>(peer_arena[g] + peers[g].off_isa);
+
+    // ---- bulk routes between the GPUs ---------------------------------------------------------------------------------
+    // counts_dev: G words on the device; C: the all-gathered matrix, C[s * G + d] = records that GPU s sends to GPU d.
+    u64* counts_dev = ctx->d_scalars + 16;
+    u64* cursor_dev = ctx->d_scalars + 24;
+    std::vector<u64> C(size_t(G) * G);
+    u64 route_bytes = 0;
+    auto exchange_counts = [&]() -> int
+    {
+        u64 mine_c[CSA_MAX_GPUS];
+        CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 16, counts_dev, G * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        for(u32 g = 0; g < G; ++g) mine_c[g] = ctx->h_scalars[16 + g];
+        CSA_TRY(gather(ctx, comm, mine_c, C.data(), G * 8));
+        u64 off = 0;
+        for(u32 d = 0; d < G; ++d) { ctx->h_scalars[24 + d] = off; off += C[size_t(me) * G + d]; }
+        CSA_CUDA(ctx, cudaMemcpyAsync(cursor_dev, ctx->h_scalars + 24, G * 8, cudaMemcpyHostToDevice, ctx->stream));
+        return CSA_OK;
+    };
+    auto out_off = [&](u32 s, u32 d) { u64 o = 0; for(u32 x = 0; x < d; ++x) o += C[size_t(s) * G + x]; return o; };    // in s's bucketed buffer
+    auto in_off = [&](u32 s, u32 d) { u64 o = 0; for(u32 x = 0; x < s; ++x) o += C[size_t(x) * G + d]; return o; };     // in d's inbox
+    auto inbox_total = [&]() { u64 o = 0; for(u32 x = 0; x < G; ++x) o += C[size_t(x) * G + me]; return o; };
+    // Routes `count` (rank << 32 | position) updates from `list` to the positions' owners and applies what arrives here.
+    auto route_updates = [&](const u64* list, u64 count, u64* bucketed) -> int
+    {
+        CSA_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, G * 8, ctx->stream));
+        CSA_TRY(launch_count_owners(ctx, nullptr, list, count, 0, ~0ull, shard, G, counts_dev));
+        CSA_TRY(exchange_counts());
+        if(inbox_total() > shard) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: more rank updates than positions in a shard");
+        CSA_TRY(launch_bucket_updates(ctx, list, count, shard, G, cursor_dev, bucketed));
+        for(u32 d = 0; d < G; ++d)
+        {
+            const u64 c = C[size_t(me) * G + d];
+            if(c == 0) continue;
+            u64* dst = reinterpret_cast<u64*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
+            CSA_CUDA(ctx, cudaMemcpyAsync(dst, bucketed + out_off(me, d), c * 8, cudaMemcpyDefault, ctx->stream));
+            if(d != me) route_bytes += c * 8;
+        }
+        CSA_TRY(barrier(ctx, comm));                                   // every inbox is complete
+        CSA_TRY(launch_apply_updates(ctx, isa, reinterpret_cast<const u64*>(xin), inbox_total()));
+        return CSA_OK;
+    };
+    // Builds keys[k] = head[k] << sec_bits | secondary(pos[k] + h) for the active list, fetching the ranks from their owners.
+    auto route_keys = [&](const u32* heads, const u32* poss, u64 count, u64 h, int sec_bits, u64* keys, u32* req_out, u32* perm) -> int
+    {
+        CSA_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, G * 8, ctx->stream));
+        CSA_TRY(launch_count_owners(ctx, poss, nullptr, count, h, n, shard, G, counts_dev));
+        CSA_TRY(exchange_counts());             // also: every GPU has applied the updates of the step before
+        if(inbox_total() > shard) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: more rank requests than positions in a shard");
+        CSA_TRY(launch_bucket_requests(ctx, poss, count, h, n, shard, G, cursor_dev, req_out, perm));
+        u32* const req_in = reinterpret_cast<u32*>(xin);
+        u32* const resp_out = req_in + shard;
+        for(u32 d = 0; d < G; ++d)
+        {
+            const u64 c = C[size_t(me) * G + d];
+            if(c == 0) continue;
+            u32* dst = reinterpret_cast<u32*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
+            CSA_CUDA(ctx, cudaMemcpyAsync(dst, req_out + out_off(me, d), c * 4, cudaMemcpyDefault, ctx->stream));
+            if(d != me) route_bytes += c * 4;
+        }
+        CSA_TRY(barrier(ctx, comm));                                   // every request has arrived
+        CSA_TRY(launch_serve_requests(ctx, isa, req_in, inbox_total(), resp_out));
+        for(u32 s2 = 0; s2 < G; ++s2)
+        {
+            const u64 c = C[size_t(s2) * G + me];
+            if(c == 0) continue;
+            u32* dst = reinterpret_cast<u32*>(peer_arena[s2] + peers[s2].off_resp) + out_off(s2, me);
+            CSA_CUDA(ctx, cudaMemcpyAsync(dst, resp_out + in_off(s2, me), c * 4, cudaMemcpyDefault, ctx->stream));
+            if(s2 != me) route_bytes += c * 4;
+        }
+        CSA_TRY(launch_keys_init(ctx, heads, poss, count, n, h, sec_bits, keys));
+        CSA_TRY(barrier(ctx, comm));                                   // every response has arrived
+        u64 asked = 0;
+        for(u32 d = 0; d < G; ++d) asked += C[size_t(me) * G + d];
+        CSA_TRY(launch_keys_add(ctx, perm, resp_in, asked, h, keys));
+        return CSA_OK;
+    };
 
     // ---- partition ids of this rank's positions, then the scatter to the partitions' owners ------------------------
     u64 peer_bytes = 0;
@@ -277,13 +360,13 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
                                L.sort_ws, &in_alt));
         const u64* ks = in_alt ? keysB : keysA;
         const u32* ps = in_alt ? posB : sa + first;
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, base_slot, sa, head, posA, act_count, scratch));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, base_slot, sa, head, posA, act_count, scratch, G > 1 ? upd + first : nullptr));
     }
+    if(G > 1) CSA_TRY(route_updates(upd, n_local, keysA));      // generation 0's ranks go to the owners of their positions
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaEventRecord(ev[2], ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     u64 active = ctx->h_scalars[0];
-    peer_bytes += (n_local * 4 * (G - 1)) / G;     // ranks written to the position owners: (G-1)/G of them are remote
     u64 counts[CSA_MAX_GPUS];
     CSA_TRY(gather(ctx, comm, &active, counts, sizeof(u64)));     // also the barrier after generation 0's rank writes
     u64 total_active = 0;
@@ -302,9 +385,8 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         if(gen < 48) st.active_per_gen[gen] = total_active;
         const int sec_bits = bits_for(n - 1 + h);
         if(sec_bits + prim_bits > 64) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: rank pair does not fit a 64-bit key");
-        CSA_TRY(launch_keys_gen(ctx, head, pos_cur, active, n, h, sec_bits, iv, keysA));
-        peer_bytes += (active * 8 * (G - 1)) / G;          // one rank read and one rank written per tied suffix
-        CSA_TRY(barrier(ctx, comm));                       // every rank has read the ranks of this generation
+        if(G > 1) CSA_TRY(route_keys(head, pos_cur, active, h, sec_bits, keysA, reinterpret_cast<u32*>(keysB), reinterpret_cast<u32*>(keysB) + n_local_max));
+        else CSA_TRY(launch_keys_gen(ctx, head, pos_cur, active, n, h, sec_bits, iv, keysA));
         int in_alt = 0;
         if(active) CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), pos_cur, pos_other, 4, active, 0,
                                           sec_bits + prim_bits, sort_ws, L.sort_ws, &in_alt));
@@ -312,7 +394,8 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         u32* ps = in_alt ? pos_other : pos_cur;
         u32* pn = in_alt ? pos_cur : pos_other;
         CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, base_slot, sa, head, pn, act_count, scratch));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, base_slot, sa, head, pn, act_count, scratch, G > 1 ? upd : nullptr));
+        if(G > 1) CSA_TRY(route_updates(upd, active, const_cast<u64*>(ks)));     // the sorted keys are spent: their buffer holds the buckets
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -348,6 +431,6 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     st.kernel_launches = ctx->counters[0] - launches_before;
     st.sort_passes = ctx->counters[1] - passes_before;
     st.sort_records = ctx->counters[2] - records_before;
-    st.peer_bytes = peer_bytes;
+    st.peer_bytes = peer_bytes + route_bytes;
     return CSA_OK;
 }

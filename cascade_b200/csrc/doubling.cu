@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(1024) rank_carry_kernel(u32* __restrict__ agg,
 __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __restrict__ keys, const u32* pos, const u64 count,
                                                                const int prim_shift, const u32 fixed_head, const Isa_View isa, const u64 slot_base,
                                                                u32* sa, u32* __restrict__ next_head, u32* __restrict__ next_pos,
-                                                               const u32* __restrict__ agg)
+                                                               const u32* __restrict__ agg, u64* __restrict__ updates)
 {
     __shared__ u32 s_prim[RANK_BLOCK / 32], s_full[RANK_BLOCK / 32], s_act[RANK_BLOCK / 32];
     const u64 first = u64(blockIdx.x) * RANK_TILE + u64(threadIdx.x) * RANK_ITEMS;
@@ -217,7 +217,10 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
         const u32 new_head = head + (sub_start - group_start);
         const u32 ps = pos[idx];
         if(sa + slot != pos + idx) sa[slot] = ps;
-        *isa_slot(isa, ps) = u32(slot_base + new_head);
+        // The new rank goes straight into the inverse array, or, when the array is spread over several GPUs, into a list
+        // of (rank, position) updates that is routed to the positions' owners in bulk.
+        if(updates) updates[idx] = (u64(u32(slot_base + new_head)) << 32) | ps;
+        else *isa_slot(isa, ps) = u32(slot_base + new_head);
         if(f.active & (1u << i))
         {
             next_head[out] = new_head;
@@ -283,7 +286,7 @@ int launch_keys_gen(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u6
 }
 
 int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 count, int prim_shift, u32 fixed_head, Isa_View isa,
-                            u64 slot_base, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch)
+                            u64 slot_base, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates)
 {
     if(count == 0) return CSA_OK;
     const u64 tiles = div_up(count, RANK_TILE);
@@ -292,7 +295,7 @@ int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 c
     rank_carry_kernel<<<1, 1024, 0, ctx->stream>>>(scratch, tiles, act_count);
     CSA_LAUNCH_CHECK(ctx);
     rank_apply_kernel<<<unsigned(tiles), RANK_BLOCK, 0, ctx->stream>>>(keys, pos, count, prim_shift, fixed_head, isa, slot_base, sa, next_head,
-                                                                       next_pos, scratch);
+                                                                       next_pos, scratch, updates);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }

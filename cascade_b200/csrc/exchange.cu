@@ -1,0 +1,178 @@
+// Bulk exchange of ranks between the GPUs of a sharded build. The inverse array is cut by text position into one shard
+// per GPU. Fine-grained loads and stores into a peer's shard are correct but slow once a shard spans gigabytes, so ranks
+// travel as the reference's messages do (one message = a position and a rank, include/message.hpp:22-61; collated by
+// destination, include/GPU_SACA.cuh:291-353), only over NVLink instead of host RAM: a GPU sorts its records into one
+// bucket per destination GPU, the buckets cross as plain contiguous copies into the destination's inbox, and the
+// destination applies them to its own shard. Reads work the same way with a request and a response leg.
+#include "common.cuh"
+#include "part.cuh"
+
+namespace
+{
+
+constexpr int EX_BLOCK = 256, EX_ITEMS = 8, EX_TILE = EX_BLOCK * EX_ITEMS;
+
+__device__ __forceinline__ u32 owner_of(u64 x, u64 shard) { return u32(x / shard); }
+
+template <bool PACKED>
+__global__ void __launch_bounds__(EX_BLOCK) count_owners_kernel(const u32* __restrict__ pos, const u64* __restrict__ packed, const u64 count, const u64 h,
+                                                                const u64 n, const u64 shard, const u32 gpus, u64* __restrict__ counts)
+{
+    __shared__ u32 c[CSA_MAX_GPUS];
+    if(threadIdx.x < CSA_MAX_GPUS) c[threadIdx.x] = 0;
+    __syncthreads();
+    u32 mine[CSA_MAX_GPUS];
+    #pragma unroll
+    for(int g = 0; g < CSA_MAX_GPUS; ++g) mine[g] = 0;
+    for(int i = 0; i < EX_ITEMS; ++i)
+    {
+        const u64 k = u64(blockIdx.x) * EX_TILE + u64(i) * EX_BLOCK + threadIdx.x;
+        if(k >= count) break;
+        const u64 x = PACKED ? (packed[k] & 0xFFFFFFFFull) : u64(pos[k]) + h;
+        if(x >= n) continue;
+        const u32 o = owner_of(x, shard);
+        #pragma unroll
+        for(int g = 0; g < CSA_MAX_GPUS; ++g) mine[g] += (o == u32(g));
+    }
+    #pragma unroll
+    for(int g = 0; g < CSA_MAX_GPUS; ++g)
+    {
+        u32 v = mine[g];
+        for(int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        if(lane_id() == 0 && v) atomicAdd(&c[g], v);
+    }
+    __syncthreads();
+    if(threadIdx.x < gpus && c[threadIdx.x]) atomicAdd(&counts[threadIdx.x], u64(c[threadIdx.x]));
+}
+
+// One block buckets EX_TILE records: counts per destination in shared memory, reserves one run per destination with one
+// atomic on the destination's cursor, then writes each record into its run.
+template <bool PACKED>
+__global__ void __launch_bounds__(EX_BLOCK) bucket_kernel(const u32* __restrict__ pos, const u64* __restrict__ packed, const u64 count, const u64 h,
+                                                          const u64 n, const u64 shard, const u32 gpus, u64* __restrict__ cursor,
+                                                          u32* __restrict__ req_out, u32* __restrict__ perm_out, u64* __restrict__ upd_out)
+{
+    __shared__ u32 c[CSA_MAX_GPUS];
+    __shared__ u64 base[CSA_MAX_GPUS];
+    if(threadIdx.x < CSA_MAX_GPUS) c[threadIdx.x] = 0;
+    __syncthreads();
+    u32 own[EX_ITEMS], r[EX_ITEMS];
+    u64 x[EX_ITEMS];
+    #pragma unroll
+    for(int i = 0; i < EX_ITEMS; ++i)
+    {
+        const u64 k = u64(blockIdx.x) * EX_TILE + u64(i) * EX_BLOCK + threadIdx.x;
+        own[i] = 0xFFFFFFFFu;
+        if(k < count)
+        {
+            x[i] = PACKED ? (packed[k] & 0xFFFFFFFFull) : u64(pos[k]) + h;
+            if(x[i] < n) own[i] = owner_of(x[i], shard);
+        }
+        // lanes with the same destination share one shared-memory atomic
+        const u32 o = own[i];
+        u32 peers = __match_any_sync(0xFFFFFFFFu, o);
+        u32 old = 0;
+        if(o != 0xFFFFFFFFu && (peers & lanemask_lt()) == 0) old = atomicAdd(&c[o], u32(__popc(peers)));
+        old = __shfl_sync(0xFFFFFFFFu, old, __ffs(peers) - 1);
+        r[i] = old + __popc(peers & lanemask_lt());
+    }
+    __syncthreads();
+    if(threadIdx.x < gpus && c[threadIdx.x]) base[threadIdx.x] = atomicAdd(&cursor[threadIdx.x], u64(c[threadIdx.x]));
+    __syncthreads();
+    #pragma unroll
+    for(int i = 0; i < EX_ITEMS; ++i)
+    {
+        if(own[i] == 0xFFFFFFFFu) continue;
+        const u64 k = u64(blockIdx.x) * EX_TILE + u64(i) * EX_BLOCK + threadIdx.x;
+        const u64 at = base[own[i]] + r[i];
+        const u32 local = u32(x[i] - u64(own[i]) * shard);
+        if(PACKED) upd_out[at] = (packed[k] & 0xFFFFFFFF00000000ull) | local;
+        else { req_out[at] = local; perm_out[at] = u32(k); }
+    }
+}
+
+__global__ void serve_requests_kernel(const u32* __restrict__ isa_local, const u32* __restrict__ req, const u64 count, u32* __restrict__ resp)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) resp[i] = isa_local[req[i]];
+}
+
+__global__ void apply_updates_kernel(u32* __restrict__ isa_local, const u64* __restrict__ upd, const u64 count)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) { const u64 u = upd[i]; isa_local[u32(u)] = u32(u >> 32); }
+}
+
+__global__ void keys_init_kernel(const u32* __restrict__ head, const u32* __restrict__ pos, const u64 count, const u64 n, const u64 h, const int sec_bits,
+                                 u64* __restrict__ keys)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= count) return;
+    const u64 x = u64(pos[i]) + h;
+    keys[i] = (u64(head[i]) << sec_bits) | (x >= n ? (n - 1 + h - x) : 0ull);
+}
+
+__global__ void keys_add_kernel(const u32* __restrict__ perm, const u32* __restrict__ resp, const u64 count, const u64 h, u64* __restrict__ keys)
+{
+    const u64 j = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(j < count) keys[perm[j]] += u64(resp[j]) + h;
+}
+
+}   // namespace
+
+int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* counts)
+{
+    if(count == 0) return CSA_OK;
+    if(packed) count_owners_kernel<true><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, packed, count, h, n, shard, gpus, counts);
+    else count_owners_kernel<false><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, packed, count, h, n, shard, gpus, counts);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+int launch_bucket_requests(csa_ctx* ctx, const u32* pos, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* cursor, u32* req_out, u32* perm_out)
+{
+    if(count == 0) return CSA_OK;
+    bucket_kernel<false><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, nullptr, count, h, n, shard, gpus, cursor, req_out, perm_out, nullptr);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard, u32 gpus, u64* cursor, u64* out)
+{
+    if(count == 0) return CSA_OK;
+    bucket_kernel<true><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(nullptr, updates, count, 0, ~0ull, shard, gpus, cursor, nullptr, nullptr, out);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+int launch_serve_requests(csa_ctx* ctx, const u32* isa_local, const u32* req, u64 count, u32* resp)
+{
+    if(count == 0) return CSA_OK;
+    serve_requests_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(isa_local, req, count, resp);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count)
+{
+    if(count == 0) return CSA_OK;
+    apply_updates_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(isa_local, upd, count);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+int launch_keys_init(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u64 n, u64 h, int sec_bits, u64* keys)
+{
+    if(count == 0) return CSA_OK;
+    keys_init_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(head, pos, count, n, h, sec_bits, keys);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+int launch_keys_add(csa_ctx* ctx, const u32* perm, const u32* resp, u64 count, u64 h, u64* keys)
+{
+    if(count == 0) return CSA_OK;
+    keys_add_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(perm, resp, count, h, keys);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}

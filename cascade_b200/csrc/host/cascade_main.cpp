@@ -1,0 +1,104 @@
+// `cascade <text-file> <suffix-array-file>`: the builder's command line, as the reference's (src/main.cu:12-46): reads a
+// text of little-endian u16 symbols, builds its suffix array on the GPU, writes 5-byte entries. An empty output path
+// builds without writing (include/GPU_SACA.hpp:301-304).
+//
+// Environment, names as in the reference where they apply:
+//   GPU_SACA_P_TARGET     partitions to form (default 64)
+//   GPU_SACA_SCRATCH      accepted for compatibility; the in-HBM build spills nothing
+//   CASCADE_DEVICE        CUDA device (default 0)
+//   CASCADE_INDEX_DIR     if set, an index.meta for `query` is written there (what `sa_convert --meta-only` does)
+//   CASCADE_VALIDATE      if set, spot-checks the order of 100000 random neighbours of the result on the host
+#include "../../../include/cascade_b200.h"
+#include "formats.hpp"
+
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdlib>
+#include <random>
+
+using namespace cascade_host;
+
+static int cmp_suffixes(const uint16_t* T, uint64_t n, uint64_t i, uint64_t j, uint64_t max_cmp)
+{
+    const uint64_t li = n - i, lj = n - j, len = li < lj ? li : lj, lim = len < max_cmp ? len : max_cmp;
+    for(uint64_t k = 0; k < lim; ++k) if(T[i + k] != T[j + k]) return T[i + k] < T[j + k] ? -1 : 1;
+    if(lim == max_cmp && len > max_cmp) return 0;
+    return li < lj ? -1 : 1;
+}
+
+int main(int argc, char** argv)
+{
+    if(argc != 3)
+    {
+        std::fprintf(stderr, "Usage: cascade <text-file> <suffix-array-file>\n");
+        return EXIT_FAILURE;
+    }
+    const std::string text_path = argv[1], sa_path = argv[2];
+    const auto env_u64 = [](const char* k, uint64_t d) { const char* v = std::getenv(k); return v && *v ? std::strtoull(v, nullptr, 10) : d; };
+    const int device = int(env_u64("CASCADE_DEVICE", 0));
+    const uint32_t p = uint32_t(env_u64("GPU_SACA_P_TARGET", 64));
+
+    uint64_t bytes = 0;
+    if(!file_size(text_path, bytes) || bytes == 0 || bytes % 2 != 0)
+    {
+        std::fprintf(stderr, "error: cannot use %s as a text of 2-byte symbols\n", text_path.c_str());
+        return EXIT_FAILURE;
+    }
+    const uint64_t n = bytes / 2;
+    const auto t0 = std::chrono::steady_clock::now();
+    const auto since = [&] { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); };
+
+    if(cudaSetDevice(device) != cudaSuccess) { std::fprintf(stderr, "error: no CUDA device %d\n", device); return EXIT_FAILURE; }
+    uint16_t* T = nullptr; uint8_t* SA = nullptr;
+    if(cudaMallocHost(&T, (n + CSA_TEXT_PAD) * 2) != cudaSuccess || cudaMallocHost(&SA, 5 * n + CSA_SA_PAD_BYTES) != cudaSuccess)
+    {
+        std::fprintf(stderr, "error: cannot pin %.1f GB of host memory\n", double(7 * n) / 1e9);
+        return EXIT_FAILURE;
+    }
+    std::string err;
+    if(!read_file(text_path, T, bytes, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return EXIT_FAILURE; }
+    std::memset(T + n, 0, CSA_TEXT_PAD * 2);
+    std::fprintf(stderr, "Loaded the text of %llu symbols. Time taken: %.3f s.\n", (unsigned long long)n, since());
+
+    csa_ctx* ctx = nullptr;
+    if(csa_ctx_create(device, &ctx) != CSA_OK) { std::fprintf(stderr, "error: cannot create a device context\n"); return EXIT_FAILURE; }
+    csa_build_stats st{};
+    const double b0 = since();
+    const int rc = csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
+    if(rc != CSA_OK) { std::fprintf(stderr, "error: build failed (%d): %s\n", rc, csa_last_error(ctx)); return EXIT_FAILURE; }
+    const double build_s = since() - b0;
+    std::fprintf(stderr, "Built the suffix array: %u partitions (largest %llu), %u doubling generations, %llu digit passes.\n", st.partitions,
+                 (unsigned long long)st.max_partition, st.generations, (unsigned long long)st.sort_passes);
+    std::fprintf(stderr, "Device time: partition %.1f ms, initial ranking %.1f ms, doubling %.1f ms, output %.1f ms; with copies %.3f s (%.1f M suffixes/s).\n",
+                 st.ms_partition, st.ms_gen0, st.ms_doubling, st.ms_output, build_s, double(n) / build_s / 1e6);
+
+    if(std::getenv("CASCADE_VALIDATE"))
+    {
+        std::mt19937_64 rng(1);
+        uint64_t bad = 0;
+        const auto at = [&](uint64_t r) { uint64_t v = 0; std::memcpy(&v, SA + 5 * r, 5); return v; };
+        for(uint64_t k = 0; k < 100000 && n > 1; ++k)
+        {
+            const uint64_t r = k == 0 ? 0 : (k == 1 ? n - 2 : rng() % (n - 1));
+            const uint64_t i = at(r), j = at(r + 1);
+            if(i >= n || j >= n || i == j || cmp_suffixes(T, n, i, j, 1000) > 0) ++bad;
+        }
+        std::fprintf(stderr, "Order spot-check of 100000 neighbours: %s.\n", bad ? "FAILS" : "passes");
+        if(bad) return EXIT_FAILURE;
+    }
+    if(!sa_path.empty())
+    {
+        if(!write_file(sa_path, SA, 5 * n, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return EXIT_FAILURE; }
+        std::fprintf(stderr, "Wrote %llu bytes to %s. Total time: %.3f s.\n", (unsigned long long)(5 * n), sa_path.c_str(), since());
+        if(const char* dir = std::getenv("CASCADE_INDEX_DIR"))
+        {
+            Index_Meta m;
+            m.n = n; m.text = text_path; m.sa_part = {sa_path}; m.sa_part_off = {0};
+            if(!write_index_meta(dir, m, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return EXIT_FAILURE; }
+        }
+    }
+    csa_ctx_destroy(ctx);
+    cudaFreeHost(T); cudaFreeHost(SA);
+    return EXIT_SUCCESS;
+}

@@ -25,8 +25,27 @@ int launch_keys_gen(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u6
 // slot_base is the global rank of local slot 0. *act_count (device) is the running length of the next list.
 // scratch holds 3 words per tile of RANK_TILE records.
 constexpr int RANK_BLOCK = 256, RANK_ITEMS = 8, RANK_TILE = RANK_BLOCK * RANK_ITEMS;
+// If `updates` is non-null the new ranks are not written into the inverse array but listed there, record i of the sorted
+// list as (rank << 32) | position, for a bulk exchange between GPUs.
 int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 count, int prim_shift, u32 fixed_head, Isa_View isa,
-                            u64 slot_base, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch);
+                            u64 slot_base, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates = nullptr);
+
+// ---- bulk exchange of ranks between GPUs (exchange.cu) ----------------------------------------------------------------
+// counts[g] += the records whose position (offset by h; positions at or past n are skipped) lies in shard g.
+int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* counts);
+// Requests: for record k with x = pos[k] + h < n, writes x's index inside its shard and k into the bucket of x's owner.
+// cursor[g] must hold the bucket starts; they are advanced.
+int launch_bucket_requests(csa_ctx* ctx, const u32* pos, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* cursor, u32* req_out, u32* perm_out);
+// Updates: (rank << 32 | position) records go to the bucket of the position's owner as (rank << 32 | index inside the shard).
+int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard, u32 gpus, u64* cursor, u64* out);
+// resp[i] = isa_local[req[i]]
+int launch_serve_requests(csa_ctx* ctx, const u32* isa_local, const u32* req, u64 count, u32* resp);
+// isa_local[low 32 bits] = high 32 bits
+int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count);
+// keys[k] = head[k] << sec_bits | (n - 1 + h - x if x = pos[k] + h >= n, else 0)
+int launch_keys_init(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u64 n, u64 h, int sec_bits, u64* keys);
+// keys[perm[j]] += resp[j] + h
+int launch_keys_add(csa_ctx* ctx, const u32* perm, const u32* resp, u64 count, u64 h, u64* keys);
 
 // sa40[5 r, 5 r + 5) = sa[r], little-endian, for r < count.
 int launch_pack_sa40(csa_ctx* ctx, const u32* sa, u64 count, u8* sa40);

@@ -1,0 +1,91 @@
+"""The command lines of the drop-in surface. CPU part: `query gen` / `query info` and the file formats; GPU part: `cascade`
+builds a file byte-equal to the oracle's array and `query find` reproduces the oracle's intervals and counts hash."""
+import os
+import struct
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+BIN = os.path.join(ROOT, "cascade_b200", "bin")
+
+
+def _write_index(tmp, T, sa40=None):
+    T.astype("<u2").tofile(os.path.join(tmp, "text.u16"))
+    if sa40 is not None:
+        sa40[:5 * len(T)].tofile(os.path.join(tmp, "text.sa40"))
+    with open(os.path.join(tmp, "index.meta"), "w") as f:
+        f.write(f"format=gpu_saca_query_index\nformat_version=1\nn={len(T)}\nsym_bytes=2\nsa_width=5\nsa_order=numeric_eot_smallest\n"
+                f"text=text.u16\nsa_part_c=1\nsa_part_0=text.sa40\nsa_part_off_0=0\nsep=65535\nsa_source=test\ncreated_utc=2026-01-01T00:00:00Z\n")
+
+
+def _read_qry(path):
+    b = open(path, "rb").read()
+    magic, version, sym_bytes, q_c, sym_c, mn, mx, seed, _ = struct.unpack("<8sIIQQQQQQ", b[:64])
+    assert magic == b"GSAQRY01" and version == 1 and sym_bytes == 2
+    off = np.frombuffer(b, dtype="<u8", count=q_c + 1, offset=64)
+    sym = np.frombuffer(b, dtype="<u2", count=sym_c, offset=64 + 8 * (q_c + 1))
+    return off, sym, (mn, mx, seed)
+
+
+def _kv(out):
+    return dict(line.split("=", 1) for line in out.strip().splitlines() if "=" in line)
+
+
+def test_query_gen_and_info_without_a_gpu(tmp_path):
+    from cascade_b200 import api
+    tmp = str(tmp_path)
+    T = api.gen_corpus_host(50000, 1, 128)[:50000]
+    _write_index(tmp, T)
+    for kind, seed in (("substring", 1), ("random", 2)):
+        out = os.path.join(tmp, kind + ".qry")
+        r = subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", out, "--kind", kind, "--q", "300", "--len",
+                            "1,2,3,4,5,6,7,8,9,10,11,12,13,14,15,16", "--seed", str(seed), "--vocab", "50257"], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        off, sym, (mn, mx, sd) = _read_qry(out)
+        woff, wsym = api.gen_queries(kind, T if kind == "substring" else None, 50000 if kind == "substring" else 0, 300, seed=seed)
+        assert np.array_equal(off, woff) and np.array_equal(sym, wsym) and sd == seed and 1 <= mn <= mx <= 16
+    r = subprocess.run([os.path.join(BIN, "query"), "info", "--index", tmp], capture_output=True, text=True)
+    assert r.returncode == 0 and _kv(r.stdout)["n"] == "50000"
+    r = subprocess.run([os.path.join(BIN, "query"), "bogus"], capture_output=True, text=True)
+    assert r.returncode != 0 and "Usage" in r.stderr
+    r = subprocess.run([os.path.join(BIN, "cascade")], capture_output=True, text=True)
+    assert r.returncode != 0 and "Usage: cascade <text-file> <suffix-array-file>" in r.stderr
+
+
+@pytest.mark.gpu
+def test_cascade_and_query_find_against_the_oracle(tmp_path, oracle):
+    from cascade_b200 import api
+    tmp = str(tmp_path)
+    n = 300000
+    T = api.gen_corpus_host(n, 2, 256)[:n]
+    _write_index(tmp, T)
+    env = dict(os.environ, GPU_SACA_P_TARGET="8", CASCADE_VALIDATE="1")
+    r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), os.path.join(tmp, "text.sa40")], capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stderr
+    got = np.fromfile(os.path.join(tmp, "text.sa40"), dtype=np.uint8)
+    want = oracle.build_sa40(T)
+    assert got.size == 5 * n and np.array_equal(got, want[:5 * n])
+
+    q = os.path.join(tmp, "a.qry")
+    assert subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", q, "--kind", "substring", "--q", "5000", "--len", "1,2,4,8,16",
+                           "--seed", "1"], capture_output=True).returncode == 0
+    r = subprocess.run([os.path.join(BIN, "query"), "find", "--index", tmp, "--queries", q, "--reps", "2", "--validate", "--locate", "100",
+                        "--itv-out", os.path.join(tmp, "a.itv"), "--cnt-dir", tmp, "--pos-out", os.path.join(tmp, "a.pos")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    kv = _kv(r.stdout)
+    off, sym, _ = _read_qry(q)
+    want_itv = oracle.find_batch(T, want, off, sym)
+    itv = np.fromfile(os.path.join(tmp, "a.itv"), dtype="<u8")
+    cnt = np.fromfile(os.path.join(tmp, "a.cnt"), dtype="<u8")
+    assert np.array_equal(itv, want_itv) and np.array_equal(cnt, want_itv[1::2] - want_itv[0::2])
+    assert kv["validate"] == "ok" and int(kv["counts_hash"], 16) == oracle.counts_hash(want_itv)
+    blob = np.fromfile(os.path.join(tmp, "a.pos"), dtype="<u8")
+    qn, total = int(blob[0]), int(blob[1])
+    poff, pos = blob[2:2 + qn + 1], blob[2 + qn + 1:]
+    wp, wc = oracle.locate_batch(want, want_itv, 100)
+    assert qn == 5000 and total == int(wc.sum()) == pos.size
+    for i in range(0, qn, 53):
+        assert np.array_equal(pos[int(poff[i]):int(poff[i + 1])], wp[i, :wc[i]])
