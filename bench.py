@@ -206,11 +206,12 @@ def run_ours(args):
         torch.cuda.synchronize()
         wall_ms = 1e3 * (time.perf_counter() - t0) / args.steps
     ms = sum(step_ms) / len(step_ms)
-    pm, pc, pr = ctypes.c_double(0), c_u64(0), c_u64(0)
-    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr))
+    pm, pc, pr, pb = ctypes.c_double(0), c_u64(0), c_u64(0), c_u64(0)
+    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr), ctypes.byref(pb))
     ctx.L.csa_set_pass_timing(ctx.h, 0)
-    rec_bytes = 2 * (8 + 4)          # one read and one write of a 64-bit key + 32-bit position
-    achieved = (pr.value * rec_bytes) / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
+    # algorithmic bytes: one read and one write of every record of every pass (12-byte key + position records; 8-byte
+    # records in the keys-only passes that order rank updates by address)
+    achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort)", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
                 "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value, "share_of_step": pm.value / (ms * args.steps)}
@@ -314,9 +315,9 @@ def run_micro_sort(args):
         ctx.check(ctx.L.csa_sort_pairs(ctx.h, keys.data_ptr(), ka.data_ptr(), vals.data_ptr(), va.data_ptr(), 4, n, 0, args.bits, ws.data_ptr(), wsb,
                                        ctypes.byref(in_alt)))
         ctx.sync()
-    pm, pc, pr = ctypes.c_double(0), c_u64(0), c_u64(0)
-    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr))
-    gbs = pr.value * 24 / (pm.value * 1e-3) / 1e9
+    pm, pc, pr, pb = ctypes.c_double(0), c_u64(0), c_u64(0), c_u64(0)
+    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr), ctypes.byref(pb))
+    gbs = pb.value / (pm.value * 1e-3) / 1e9
     print(json.dumps({"micro": "sort", "records": n, "bits": args.bits, "passes": pc.value, "ms_per_pass": pm.value / max(1, pc.value),
                       "achieved_gbs": gbs, "peak_gbs": peak, "frac": gbs / peak, "peak_kind": kind, "variant": args.variant}))
     ctx.close()

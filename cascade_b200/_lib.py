@@ -47,7 +47,7 @@ _SIGS = {
     "csa_sort_pairs_static": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_u64, c_int, c_int, ctypes.POINTER(c_int)]),
     "csa_debug_set": (c_int, [c_int, c_u64]),
     "csa_set_pass_timing": (c_int, [c_vp, c_int]),
-    "csa_get_pass_timing": (c_int, [c_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_u64), ctypes.POINTER(c_u64)]),
+    "csa_get_pass_timing": (c_int, [c_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_u64), ctypes.POINTER(c_u64), ctypes.POINTER(c_u64)]),
     "csa_sample_kgrams": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u64, c_vp]),
     "csa_select_pivots": (c_int, [c_vp, c_u64, c_u32, c_vp, ctypes.POINTER(c_u32)]),
     "csa_partition_ids": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u64, c_vp, c_u32, c_vp, c_vp]),

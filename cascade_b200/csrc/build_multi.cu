@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "part.cuh"
 
+#include <chrono>
 #include <cstdlib>
 #include <vector>
 
@@ -68,13 +69,13 @@ Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
     L.head = align_up256(cap * 4);
     L.isa = align_up256(shard * 4 + 64);
     L.sa = align_up256(cap * 4 + 64);
-    L.sort_ws = align_up256(csa_sort_workspace_bytes(cap));
+    L.sort_ws = align_up256(csa_sort_workspace_bytes(cap > shard ? cap : shard));
     L.scratch = align_up256(div_up(cap, RANK_TILE) * 3 * 4 + 256);
     L.pid = align_up256(shard * 2 + 64);
     L.small = align_up256(size_t(p) * 8) * 3 + align_up256(size_t(2) * p * 8) + 4096;
     L.xin = align_up256(shard * 8 + 64);        // inbox of the bulk exchange: updates (8 bytes) or requests + responses (4 + 4)
     L.resp = align_up256(cap * 4 + 64);         // responses to this GPU's requests
-    L.upd = align_up256(cap * 8 + 64);          // (rank, position) updates before they are bucketed
+    L.upd = align_up256((cap > shard ? cap : shard) * 8 + 64);   // (position, rank) updates before they are bucketed; pass buffer of the apply
     L.total = L.isa + L.sa + 2 * L.keys + 2 * L.pos + L.head + L.sort_ws + L.scratch + L.pid + L.small + L.xin + L.resp + L.upd + 4096;
     return L;
 }
@@ -117,6 +118,15 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     st.n = n;
     const u64 launches_before = ctx->counters[0], passes_before = ctx->counters[1], records_before = ctx->counters[2];
     const bool debug = std::getenv("CSA_DEBUG") != nullptr;
+    auto wall0 = std::chrono::steady_clock::now();
+    auto lap = [&](const char* what)       // debug only: wall time since the last lap, after draining the stream
+    {
+        if(!debug) return;
+        cudaStreamSynchronize(ctx->stream);
+        const auto now = std::chrono::steady_clock::now();
+        std::fprintf(stderr, "[csa %u/%u]   %-28s %8.2f ms\n", comm->rank, comm->world, what, std::chrono::duration<double, std::milli>(now - wall0).count());
+        wall0 = now;
+    };
 
     cudaEvent_t ev[5];
     for(auto& e : ev) CSA_CUDA(ctx, cudaEventCreate(&e));
@@ -162,6 +172,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
     st.partitions = p_eff;
+    lap("splitters + sizes");
 
     // ---- plan: the same on every rank ------------------------------------------------------------------------------
     std::vector<u64> hist_all(size_t(G) * p_eff), send_hist(my_hist.begin(), my_hist.begin() + p_eff);
@@ -243,6 +254,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         }
         peer_arena[g] = static_cast<u8*>(ctx->peer_base[g]);
     }
+    lap("plan + arena + peer maps");
     Isa_View iv;
     std::memset(&iv, 0, sizeof(iv));
     iv.gpus = G; iv.shard_size = shard;
@@ -269,8 +281,8 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     auto out_off = [&](u32 s, u32 d) { u64 o = 0; for(u32 x = 0; x < d; ++x) o += C[size_t(s) * G + x]; return o; };    // in s's bucketed buffer
     auto in_off = [&](u32 s, u32 d) { u64 o = 0; for(u32 x = 0; x < s; ++x) o += C[size_t(x) * G + d]; return o; };     // in d's inbox
     auto inbox_total = [&]() { u64 o = 0; for(u32 x = 0; x < G; ++x) o += C[size_t(x) * G + me]; return o; };
-    // Routes `count` (rank << 32 | position) updates from `list` to the positions' owners and applies what arrives here.
-    auto route_updates = [&](const u64* list, u64 count, u64* bucketed) -> int
+    // Routes `count` (position << 32 | rank) updates from `list` to the positions' owners and applies what arrives here.
+    auto route_updates = [&](u64* list, u64 count, u64* bucketed) -> int
     {
         CSA_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, G * 8, ctx->stream));
         CSA_TRY(launch_count_owners(ctx, nullptr, list, count, 0, ~0ull, shard, G, counts_dev));
@@ -286,7 +298,8 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
             if(d != me) route_bytes += c * 8;
         }
         CSA_TRY(barrier(ctx, comm));                                   // every inbox is complete
-        CSA_TRY(launch_apply_updates(ctx, isa, reinterpret_cast<const u64*>(xin), inbox_total()));
+        // `list` has been bucketed and sent, so its buffer serves the address-ordering pass of what arrived
+        CSA_TRY(apply_updates_in_address_order(ctx, isa, reinterpret_cast<u64*>(xin), const_cast<u64*>(list), inbox_total(), bits_for(shard - 1), sort_ws, L.sort_ws));
         return CSA_OK;
     };
     // Builds keys[k] = head[k] << sec_bits | secondary(pos[k] + h) for the active list, fetching the ranks from their owners.
@@ -343,7 +356,9 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
     CSA_CUDA(ctx, cudaEventRecord(ev[1], ctx->stream));
+    lap("ids + scatter");
     CSA_TRY(barrier(ctx, comm));        // every position has reached its owner
+    lap("barrier");
 
     // ---- generation 0 over this rank's partitions -------------------------------------------------------------------
     u64* act_count = ctx->d_scalars;
@@ -362,7 +377,9 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         const u32* ps = in_alt ? posB : sa + first;
         CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, base_slot, sa, head, posA, act_count, scratch, G > 1 ? upd + first : nullptr));
     }
+    lap("generation 0 sorts + ranks");
     if(G > 1) CSA_TRY(route_updates(upd, n_local, keysA));      // generation 0's ranks go to the owners of their positions
+    lap("generation 0 rank exchange");
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaEventRecord(ev[2], ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -387,6 +404,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         if(sec_bits + prim_bits > 64) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: rank pair does not fit a 64-bit key");
         if(G > 1) CSA_TRY(route_keys(head, pos_cur, active, h, sec_bits, keysA, reinterpret_cast<u32*>(keysB), reinterpret_cast<u32*>(keysB) + n_local_max));
         else CSA_TRY(launch_keys_gen(ctx, head, pos_cur, active, n, h, sec_bits, iv, keysA));
+        lap("keys (rank requests)");
         int in_alt = 0;
         if(active) CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), pos_cur, pos_other, 4, active, 0,
                                           sec_bits + prim_bits, sort_ws, L.sort_ws, &in_alt));
@@ -395,7 +413,9 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         u32* pn = in_alt ? pos_cur : pos_other;
         CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
         CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, base_slot, sa, head, pn, act_count, scratch, G > 1 ? upd : nullptr));
-        if(G > 1) CSA_TRY(route_updates(upd, active, const_cast<u64*>(ks)));     // the sorted keys are spent: their buffer holds the buckets
+        lap("sort + ranks");
+        if(G > 1) CSA_TRY(route_updates(upd, active, const_cast<u64*>(ks)));
+        lap("rank exchange");     // the sorted keys are spent: their buffer holds the buckets
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

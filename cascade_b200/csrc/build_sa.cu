@@ -24,7 +24,7 @@ size_t align256(size_t b) { return (b + 255) & ~size_t(255); }
 
 struct Build_Layout
 {
-    size_t keys, pos, head, isa, sa, sort_ws, scratch, small, total;
+    size_t keys, pos, head, isa, sa, sort_ws, scratch, small, upd, total;
 };
 
 Build_Layout layout_for(u64 n, u32 p)
@@ -39,7 +39,8 @@ Build_Layout layout_for(u64 n, u32 p)
     L.sort_ws = align256(csa_sort_workspace_bytes(n));
     L.scratch = align256(div_up(n, RANK_TILE) * 3 * 4 + 256);
     L.small = align256(size_t(p) * 8) * 3 + align256(size_t(2) * p * 8) + align256(size_t(1) << 24) + 4096;   // hist, cursors, bases, pivots, samples
-    L.total = 2 * L.keys + 2 * L.pos + L.head + L.isa + L.sa + L.sort_ws + L.scratch + L.small + 4096;
+    L.upd = align256(cap * 8);     // (position, rank) updates of one step, applied to `isa` in address order
+    L.total = 2 * L.keys + 2 * L.pos + L.head + L.isa + L.sa + L.sort_ws + L.scratch + L.small + L.upd + 4096;
     return L;
 }
 
@@ -73,6 +74,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     u32** part_base = cv.take<u32*>(p);
     u64* pivots_dev = cv.take<u64>(2 * u64(p));
     u64* samples_dev = cv.take<u64>(2 * MAX_SAMPLES);
+    u64* upd = cv.take<u64>(L.upd / 8);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "build: workspace too small");
     u16* pid = reinterpret_cast<u16*>(keysB);      // partition ids live only until the scatter; the keys come later
 
@@ -132,8 +134,11 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
                                L.sort_ws, &in_alt));
         const u64* ks = in_alt ? keysB : keysA;
         const u32* ps = in_alt ? posB : sa + first;
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, 0, sa, head, posA, act_count, scratch));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, 0, sa, head, posA, act_count, scratch, upd + first));
     }
+    // The ranks of generation 0 reach the inverse array in address order: one keys-only digit pass, then a streaming apply.
+    const int position_bits = bits_for(n - 1);
+    CSA_TRY(apply_updates_in_address_order(ctx, isa, upd, keysA, n, position_bits, sort_ws, L.sort_ws));
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaEventRecord(ev.e[2], ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -160,7 +165,8 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
         u32* ps = in_alt ? pos_other : pos_cur;
         u32* pn = in_alt ? pos_cur : pos_other;
         CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, 0, sa, head, pn, act_count, scratch));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, 0, sa, head, pn, act_count, scratch, upd));
+        CSA_TRY(apply_updates_in_address_order(ctx, isa, upd, const_cast<u64*>(ks), active, position_bits, sort_ws, L.sort_ws));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

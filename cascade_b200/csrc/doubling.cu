@@ -218,8 +218,8 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
         const u32 ps = pos[idx];
         if(sa + slot != pos + idx) sa[slot] = ps;
         // The new rank goes straight into the inverse array, or, when the array is spread over several GPUs, into a list
-        // of (rank, position) updates that is routed to the positions' owners in bulk.
-        if(updates) updates[idx] = (u64(u32(slot_base + new_head)) << 32) | ps;
+        // of (position, rank) updates that is applied in address order (and, over several GPUs, routed to the positions' owners).
+        if(updates) updates[idx] = (u64(ps) << 32) | u32(slot_base + new_head);
         else *isa_slot(isa, ps) = u32(slot_base + new_head);
         if(f.active & (1u << i))
         {

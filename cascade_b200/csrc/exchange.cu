@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(EX_BLOCK) count_owners_kernel(const u32* __res
     {
         const u64 k = u64(blockIdx.x) * EX_TILE + u64(i) * EX_BLOCK + threadIdx.x;
         if(k >= count) break;
-        const u64 x = PACKED ? (packed[k] & 0xFFFFFFFFull) : u64(pos[k]) + h;
+        const u64 x = PACKED ? (packed[k] >> 32) : u64(pos[k]) + h;
         if(x >= n) continue;
         const u32 o = owner_of(x, shard);
         #pragma unroll
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(EX_BLOCK) bucket_kernel(const u32* __restrict_
         own[i] = 0xFFFFFFFFu;
         if(k < count)
         {
-            x[i] = PACKED ? (packed[k] & 0xFFFFFFFFull) : u64(pos[k]) + h;
+            x[i] = PACKED ? (packed[k] >> 32) : u64(pos[k]) + h;
             if(x[i] < n) own[i] = owner_of(x[i], shard);
         }
         // lanes with the same destination share one shared-memory atomic
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(EX_BLOCK) bucket_kernel(const u32* __restrict_
         const u64 k = u64(blockIdx.x) * EX_TILE + u64(i) * EX_BLOCK + threadIdx.x;
         const u64 at = base[own[i]] + r[i];
         const u32 local = u32(x[i] - u64(own[i]) * shard);
-        if(PACKED) upd_out[at] = (packed[k] & 0xFFFFFFFF00000000ull) | local;
+        if(PACKED) upd_out[at] = (u64(local) << 32) | (packed[k] & 0xFFFFFFFFull);
         else { req_out[at] = local; perm_out[at] = u32(k); }
     }
 }
@@ -100,7 +100,7 @@ __global__ void serve_requests_kernel(const u32* __restrict__ isa_local, const u
 __global__ void apply_updates_kernel(u32* __restrict__ isa_local, const u64* __restrict__ upd, const u64 count)
 {
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    if(i < count) { const u64 u = upd[i]; isa_local[u32(u)] = u32(u >> 32); }
+    if(i < count) { const u64 u = upd[i]; isa_local[u32(u >> 32)] = u32(u); }
 }
 
 __global__ void keys_init_kernel(const u32* __restrict__ head, const u32* __restrict__ pos, const u64 count, const u64 n, const u64 h, const int sec_bits,
@@ -175,4 +175,19 @@ int launch_keys_add(csa_ctx* ctx, const u32* perm, const u32* resp, u64 count, u
     keys_add_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(perm, resp, count, h, keys);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
+}
+
+int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* alt, u64 count, int position_bits, void* sort_ws, size_t sort_ws_bytes)
+{
+    if(count == 0) return CSA_OK;
+    const u64* list = upd;
+    // Worth a pass only when the array is much larger than L2 and the list is long enough to pay for the pass.
+    if(position_bits > 24 && count >= (u64(1) << 20))
+    {
+        const int top = 32 + position_bits, begin = top - 8;
+        int in_alt = 0;
+        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(upd), reinterpret_cast<uint64_t*>(alt), nullptr, nullptr, 4, count, begin, top, sort_ws, sort_ws_bytes, &in_alt));
+        list = in_alt ? alt : upd;
+    }
+    return launch_apply_updates(ctx, isa_local, list, count);
 }

@@ -36,12 +36,16 @@ int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 cou
 // Requests: for record k with x = pos[k] + h < n, writes x's index inside its shard and k into the bucket of x's owner.
 // cursor[g] must hold the bucket starts; they are advanced.
 int launch_bucket_requests(csa_ctx* ctx, const u32* pos, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* cursor, u32* req_out, u32* perm_out);
-// Updates: (rank << 32 | position) records go to the bucket of the position's owner as (rank << 32 | index inside the shard).
+// Updates: (position << 32 | rank) records go to the bucket of the position's owner as (index inside the shard << 32 | rank).
 int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard, u32 gpus, u64* cursor, u64* out);
 // resp[i] = isa_local[req[i]]
 int launch_serve_requests(csa_ctx* ctx, const u32* isa_local, const u32* req, u64 count, u32* resp);
-// isa_local[low 32 bits] = high 32 bits
+// isa_local[high 32 bits] = low 32 bits
 int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count);
+// The same after one keys-only radix pass on the top bits of the index (positions_bits of them are in use), so that the
+// writes of one stretch of the list fall into one L2-sized stretch of the array. alt holds count records; sort_ws is a
+// sort workspace. Short lists are applied directly.
+int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* alt, u64 count, int position_bits, void* sort_ws, size_t sort_ws_bytes);
 // keys[k] = head[k] << sec_bits | (n - 1 + h - x if x = pos[k] + h >= n, else 0)
 int launch_keys_init(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u64 n, u64 h, int sec_bits, u64* keys);
 // keys[perm[j]] += resp[j] + h

@@ -164,7 +164,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
     for(int i = 0; i < ITEMS; ++i)
     {
         const u32 idx = warp_first + i * 32 + lane;
-        if(FULL || idx < valid) val[i] = vals_in[tile_base + idx];
+        if(vals_in != nullptr && (FULL || idx < valid)) val[i] = vals_in[tile_base + idx];
     }
 
     // Rank of every record among the records of its digit within the warp, and the warp's digit counts. The lanes that
@@ -300,7 +300,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
     for(int i = 0; i < ITEMS; ++i)
     {
         const u32 idx = warp_first + i * 32 + lane;
-        if(FULL || idx < valid) stage_vals[rank[i]] = val[i];
+        if(vals_in != nullptr && (FULL || idx < valid)) stage_vals[rank[i]] = val[i];
     }
     __syncthreads();
 
@@ -314,7 +314,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
             const u64 kk = stage_keys[p];
             const u64 dst = g_off[u32(kk >> shift) & dmask] + p;
             keys_out[dst] = kk;
-            vals_out[dst] = stage_vals[p];
+            if(vals_in != nullptr) vals_out[dst] = stage_vals[p];
         }
     }
 }
@@ -387,7 +387,7 @@ struct Pass_Timer
 {
     bool on = false;
     std::vector<cudaEvent_t> ev;    // pairs
-    u64 passes = 0, records = 0;
+    u64 passes = 0, records = 0, bytes = 0;
 };
 Pass_Timer g_timer[64];
 
@@ -418,7 +418,7 @@ int csa_set_pass_timing(csa_ctx* ctx, int on)
     return CSA_OK;
 }
 
-int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64_t* records)
+int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64_t* records, uint64_t* bytes)
 {
     if(!ctx) return CSA_E_INVALID;
     Pass_Timer& t = g_timer[ctx->device & 63];
@@ -433,6 +433,7 @@ int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64
     if(total_ms) *total_ms = ms;
     if(passes) *passes = t.passes;
     if(records) *records = t.records;
+    if(bytes) *bytes = t.bytes;
     return CSA_OK;
 }
 
@@ -441,7 +442,7 @@ void sort_reset_timing(csa_ctx* ctx)
     Pass_Timer& t = g_timer[ctx->device & 63];
     for(auto e : t.ev) cudaEventDestroy(e);
     t.ev.clear();
-    t.passes = t.records = 0;
+    t.passes = t.records = t.bytes = 0;
 }
 
 int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals, void* vals_alt, uint32_t val_bytes, uint64_t n,
@@ -451,7 +452,7 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     *in_alt = 0;
     if(begin_bit < 0 || end_bit > 64 || begin_bit > end_bit || (val_bytes != 4 && val_bytes != 8)) return csa_fail(ctx, CSA_E_INVALID, "csa_sort_pairs: bad bit range or value width");
     if(n <= 1 || begin_bit == end_bit) return CSA_OK;
-    if(!keys || !keys_alt || !vals || !vals_alt || !workspace) return csa_fail(ctx, CSA_E_INVALID, "csa_sort_pairs: null buffer");
+    if(!keys || !keys_alt || !workspace || ((vals == nullptr) != (vals_alt == nullptr))) return csa_fail(ctx, CSA_E_INVALID, "csa_sort_pairs: null buffer");
     if(workspace_bytes < csa_sort_workspace_bytes(n)) return csa_fail(ctx, CSA_E_NOMEM, "csa_sort_pairs: workspace too small");
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
 
@@ -508,8 +509,8 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
         {
             const u64 first = u64(P) * PORTION, cnt = (n - first < PORTION ? n - first : PORTION);
             u64* db = base + (u64(p) * (portions + 1) + P) * RADIX;
-            if(val_bytes == 4)
-                CSA_TRY(launch_pass_variant<u32>(ctx, kin + first, kout, static_cast<const u32*>(vin) + first, static_cast<u32*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
+            if(val_bytes == 4 || vin == nullptr)
+                CSA_TRY(launch_pass_variant<u32>(ctx, kin + first, kout, vin ? static_cast<const u32*>(vin) + first : nullptr, static_cast<u32*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
             else
                 CSA_TRY(launch_pass_variant<u64>(ctx, kin + first, kout, static_cast<const u64*>(vin) + first, static_cast<u64*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
         }
@@ -517,10 +518,11 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
         {
             CSA_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
             timer.ev.push_back(e0); timer.ev.push_back(e1);
-            timer.passes++; timer.records += n;
+            timer.passes++; timer.records += n; timer.bytes += 2 * n * (8 + (vin ? val_bytes : 0));
         }
         ctx->counters[1]++;          // digit passes
         ctx->counters[2] += n;       // records moved
+        if(vin == nullptr) ctx->counters[3] += n;     // of which without a value (16 instead of 24 bytes per record and pass)
         u64* tk = kin; kin = kout; kout = tk;
         void* tv = vin; vin = vout; vout = tv;
         ++flips;

@@ -113,10 +113,10 @@ def bench(args, rank, world, local):
         dist.barrier()
         torch.cuda.synchronize()
     ms = sum(step_ms) / len(step_ms)
-    pm, pc, pr = ctypes.c_double(0), c_u64(0), c_u64(0)
-    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr))
+    pm, pc, pr, pb = ctypes.c_double(0), c_u64(0), c_u64(0), c_u64(0)
+    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr), ctypes.byref(pb))
     ctx.L.csa_set_pass_timing(ctx.h, 0)
-    achieved = (pr.value * 24) / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
+    achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
 
     # cheap check of this rank's slice: sizes add up, and sampled neighbours are in order on their first 4 symbols
     total = _sum_over_ranks(count, dev)
@@ -166,6 +166,7 @@ def bench(args, rank, world, local):
                              "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value},
                 "nvlink": {"peer_bytes_per_step_all_ranks": peer_all / args.steps, "generations": st.generations,
                            "note": "positions to partition owners + ranks to and from position owners, 4 bytes each, (G-1)/G of them remote"},
+                "phases_ms_rank0": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
                 "verified": {"slices_add_up_to_n": total == n, "sampled_neighbours_in_order": ok_all}}
         print(json.dumps(line))
     dist.barrier()

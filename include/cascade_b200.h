@@ -70,7 +70,7 @@ size_t csa_sort_workspace_bytes(uint64_t n);
 /* Stable least-significant-digit radix sort of n (64-bit key, value) records on key bits [begin_bit, end_bit),
  * 8 bits per pass, each pass one sweep over the records. val_bytes is 4 or 8. The records ping-pong between
  * (keys, vals) and (keys_alt, vals_alt); *in_alt is set to 1 if the sorted records end in the alt buffers, else 0.
- * Passes whose digit is the same for every key are skipped. */
+ * Passes whose digit is the same for every key are skipped. With vals_dev and vals_alt_dev both null only keys are sorted. */
 int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, void* vals_dev, void* vals_alt_dev,
                    uint32_t val_bytes, uint64_t n, int begin_bit, int end_bit, void* workspace_dev, size_t workspace_bytes,
                    int* in_alt);
@@ -92,9 +92,9 @@ int csa_sort_pairs_static(void* stream, uint64_t* keys_dev, uint64_t* keys_alt_d
 int csa_debug_set(int key, uint64_t value);
 /* Average device time of the digit passes of the sorts run on ctx since the last csa_reset_counters, measured
  * with CUDA events on the context's stream when pass timing is on (csa_set_pass_timing): total milliseconds,
- * the passes timed and the records they moved. */
+ * the passes timed, the records they moved and the algorithmic bytes of that (one read and one write of every record). */
 int csa_set_pass_timing(csa_ctx* ctx, int on);
-int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64_t* records);
+int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64_t* records, uint64_t* bytes);
 
 /* ---- build: sampling and partitioning ---------------------------------------------------------------- */
 
