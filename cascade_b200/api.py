@@ -205,13 +205,17 @@ def build_sa_host(ctx, text_host, n, p=1, seed=0, out=None):
 class SuffixIndex:
     """Text, suffix array and sample table of one index on a device (the reference's Suffix_Index + Sample_Table)."""
 
-    def __init__(self, ctx, text_dev, sa40_dev, n, stride=32):
+    def __init__(self, ctx, text_dev, sa40_dev, n, stride=32, table=None):
+        """sa40_dev may also be a pinned host tensor: the device then reads the suffix array over PCIe."""
         self.ctx, self.text, self.sa40, self.n, self.stride = ctx, text_dev, sa40_dev, n, stride
         entries = (n + stride - 1) // stride
-        self.table = torch.zeros(2 * entries, dtype=torch.int64, device=text_dev.device)
-        torch.cuda.synchronize(text_dev.device)
-        ctx.check(ctx.L.csa_table_build(ctx.h, text_dev.data_ptr(), n, sa40_dev.data_ptr(), stride, self.table.data_ptr()))
-        ctx.sync()
+        if table is not None:
+            self.table = table
+        else:
+            self.table = torch.zeros(2 * entries, dtype=torch.int64, device=text_dev.device)
+            torch.cuda.synchronize(text_dev.device)
+            ctx.check(ctx.L.csa_table_build(ctx.h, text_dev.data_ptr(), n, sa40_dev.data_ptr(), stride, self.table.data_ptr()))
+            ctx.sync()
         self.c = Index(text_dev.data_ptr(), sa40_dev.data_ptr(), self.table.data_ptr(), n, stride)
 
     def find(self, off_dev, sym_dev, q):

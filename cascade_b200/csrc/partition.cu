@@ -189,6 +189,125 @@ __global__ void __launch_bounds__(BLOCK) scatter_by_pid_kernel(const u16* __rest
     }
 }
 
+
+// The same scatter for up to 256 partitions, built like a digit pass of the radix sort: the lanes of a warp that hold the
+// same partition id find one another with ballots, warps keep private counters, the block reserves one run per partition
+// with a single atomic on the partition's cursor, positions are staged in shared memory in partition order and written
+// out as coalesced runs. Within a block's run the positions stay in increasing order.
+template <int BLOCK, int ITEMS>
+__global__ void __launch_bounds__(BLOCK) scatter_by_pid_ranked_kernel(const u16* __restrict__ pid, const u64 first, const u64 count, const u32 p,
+                                                                     const int id_bits, u32* const* __restrict__ part_base, u64* __restrict__ cursor)
+{
+    constexpr int TILE = BLOCK * ITEMS;
+    constexpr int WARPS = BLOCK / 32;
+    constexpr int BINS = 256;
+    __shared__ u32 stage[TILE];
+    __shared__ u32 warp_cnt[WARPS * BINS];
+    __shared__ u32 bin_start[BINS];       // start of the partition's records inside the tile
+    __shared__ u64 bin_base[BINS];        // where the tile's run of the partition starts in the partition's array, minus bin_start
+    __shared__ u32 scan_tot[BINS / 32];
+    const u32 tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const u64 tile_first = u64(blockIdx.x) * TILE;
+    const u32 valid = (count - tile_first < u64(TILE)) ? u32(count - tile_first) : u32(TILE);
+    for(int i = tid; i < WARPS * BINS; i += BLOCK) warp_cnt[i] = 0;
+    __syncthreads();
+
+    u32 id[ITEMS], rank[ITEMS];
+    const u32 warp_first = warp * 32 * ITEMS;
+    #pragma unroll
+    for(int i = 0; i < ITEMS; ++i)
+    {
+        const u32 idx = warp_first + i * 32 + lane;
+        id[i] = (idx < valid) ? u32(pid[tile_first + idx]) : (BINS - 1);     // fillers rank last in the last bin
+    }
+    u32* const wc = warp_cnt + warp * BINS;
+    {
+        u32 peers[ITEMS], old[ITEMS];
+        #pragma unroll
+        for(int i = 0; i < ITEMS; ++i)
+        {
+            u32 m = 0xFFFFFFFFu;
+            for(int b = 0; b < id_bits; ++b)
+            {
+                const u32 sel = 0u - ((id[i] >> b) & 1u);
+                const u32 v = __ballot_sync(0xFFFFFFFFu, sel != 0);
+                m &= ~(v ^ sel);
+            }
+            const u32 idx = warp_first + i * 32 + lane;
+            // fillers must not meet real records of the last bin: split them off by their validity
+            const u32 live = __ballot_sync(0xFFFFFFFFu, idx < valid);
+            m &= (idx < valid) ? live : ~live;
+            peers[i] = m;
+        }
+        #pragma unroll
+        for(int i = 0; i < ITEMS; ++i)
+        {
+            const u32 idx = warp_first + i * 32 + lane;
+            old[i] = 0;
+            if(idx < valid && (peers[i] & lanemask_lt()) == 0) old[i] = atomicAdd(&wc[id[i]], u32(__popc(peers[i])));
+        }
+        #pragma unroll
+        for(int i = 0; i < ITEMS; ++i)
+            rank[i] = __shfl_sync(0xFFFFFFFFu, old[i], __ffs(peers[i]) - 1) + __popc(peers[i] & lanemask_lt());
+    }
+    __syncthreads();
+    // per partition: the warps' offsets, the tile's count, an exclusive scan over the partitions, and the run's place
+    u32 cnt = 0;
+    u32 wsum[WARPS];
+    if(tid < BINS)
+    {
+        #pragma unroll
+        for(int w = 0; w < WARPS; ++w) { wsum[w] = warp_cnt[w * BINS + tid]; cnt += wsum[w]; }
+    }
+    u32 inc = cnt;
+    if(tid < BINS)
+    {
+        #pragma unroll
+        for(int o = 1; o < 32; o <<= 1)
+        {
+            const u32 t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if(int(lane) >= o) inc += t;
+        }
+        if(lane == 31) scan_tot[warp] = inc;
+    }
+    __syncthreads();
+    if(tid < BINS)
+    {
+        u32 pre = 0;
+        for(u32 w = 0; w < warp; ++w) pre += scan_tot[w];
+        u32 run = pre + inc - cnt;
+        bin_start[tid] = run;
+        if(cnt && tid < p) bin_base[tid] = atomicAdd(&cursor[tid], u64(cnt)) - run;
+        #pragma unroll
+        for(int w = 0; w < WARPS; ++w) { warp_cnt[w * BINS + tid] = run; run += wsum[w]; }
+    }
+    __syncthreads();
+    // Positions are staged in partition order; at write-out a record's partition is found again from its place in the tile
+    // by a search over the partitions' starts (256 entries, 8 steps).
+    #pragma unroll
+    for(int i = 0; i < ITEMS; ++i)
+    {
+        const u32 idx = warp_first + i * 32 + lane;
+        if(idx < valid) stage[wc[id[i]] + rank[i]] = u32(first + tile_first + idx);
+    }
+    __syncthreads();
+    #pragma unroll
+    for(int k = 0; k < ITEMS; ++k)
+    {
+        const u32 j = tid + k * BLOCK;
+        if(j < valid)
+        {
+            u32 a = 0, b = BINS - 1;            // the last partition whose start is not after j
+            while(a < b)
+            {
+                const u32 mid = (a + b + 1) >> 1;
+                if(bin_start[mid] <= j) a = mid; else b = mid - 1;
+            }
+            part_base[a][bin_base[a] + j] = stage[j];
+        }
+    }
+}
+
 }   // namespace
 
 extern "C" int csa_sample_kgrams(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t n_samples, uint64_t seed, uint64_t* samples)
@@ -251,6 +370,14 @@ extern "C" int csa_scatter_by_pid(csa_ctx* ctx, const uint16_t* pid, uint64_t fi
     if(first + count > 0xFFFFFFFFull) return csa_fail(ctx, CSA_E_LIMIT, "csa_scatter_by_pid: positions must fit 32 bits");
     if(count == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    if(p <= 256)
+    {
+        constexpr int RB = 512, RI = 8;
+        scatter_by_pid_ranked_kernel<RB, RI><<<unsigned(div_up(count, RB * RI)), RB, 0, ctx->stream>>>(pid, first, count, p, bits_for(p - 1), part_base,
+                                                                                                     reinterpret_cast<u64*>(cursor));
+        CSA_LAUNCH_CHECK(ctx);
+        return CSA_OK;
+    }
     constexpr int TILE = PID_BLOCK * PID_ITEMS;
     const size_t smem = size_t(p) * 12;
     auto kern = scatter_by_pid_kernel<PID_BLOCK, PID_ITEMS>;

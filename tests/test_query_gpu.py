@@ -119,3 +119,27 @@ def test_zipf_index_batch_and_host_entry_point(ctx, oracle):
     assert np.array_equal(cnt_h, wc) and total == int(wc.sum()) and int(poff_h[-1]) == total
     for i in list(range(0, q, 997)) + [q - 1]:
         assert np.array_equal(pos_h[int(poff_h[i]):int(poff_h[i + 1])], wp[i, :wc[i]])
+
+
+def test_suffix_array_in_pinned_host_memory(ctx, oracle):
+    """The index with its suffix array in pinned host memory (read by the device over PCIe) gives the same intervals and positions."""
+    from cascade_b200 import api
+    rng = np.random.default_rng(4)
+    n = 200000
+    T = rng.integers(0, 50, n).astype(np.uint16)
+    sa = oracle.build_sa40(T)
+    Tp = np.concatenate([T, np.zeros(api.TEXT_PAD, np.uint16)])
+    td = torch.from_numpy(Tp.view(np.int16)).cuda().view(torch.uint16)
+    sa_pinned = torch.from_numpy(np.ascontiguousarray(sa)).pin_memory()
+    idx = api.SuffixIndex(ctx, td, sa_pinned, n, 32)
+    off, sym, _ = conftest.fixture_queries(T, rng, 500)
+    o, s_ = _dev(off, sym)
+    itv = idx.find(o, s_, 500)
+    want = oracle.find_batch(T, sa, off, sym)
+    assert np.array_equal(itv.cpu().numpy().view(np.uint64), want)
+    pos, cnt = idx.locate(itv, 500, 100)
+    wp, wc = oracle.locate_batch(sa, want, 100)
+    assert np.array_equal(cnt.cpu().numpy().view(np.uint32), wc)
+    pn = pos.cpu().numpy().view(np.uint64)
+    for i in range(0, 500, 7):
+        assert np.array_equal(pn[i, :wc[i]], wp[i, :wc[i]])
