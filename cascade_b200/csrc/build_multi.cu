@@ -72,7 +72,7 @@ Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
     L.sort_ws = align_up256(csa_sort_workspace_bytes(cap > shard ? cap : shard));
     L.scratch = align_up256(div_up(cap, RANK_TILE) * 3 * 4 + 256);
     L.pid = align_up256(shard * 2 + 64);
-    L.small = align_up256(size_t(p) * 8) * 3 + align_up256(size_t(2) * p * 8) + 4096;
+    L.small = align_up256(size_t(p) * 8) * 3 + align_up256(size_t(2) * p * 8) + align_up256(65536 * 4) + 4096;
     L.xin = align_up256(shard * 8 + 64);        // inbox of the bulk exchange: updates (8 bytes) or requests + responses (4 + 4)
     L.resp = align_up256(cap * 4 + 64);         // responses to this GPU's requests
     L.upd = align_up256((cap > shard ? cap : shard) * 8 + 64);   // (position, rank) updates before they are bucketed; pass buffer of the apply
@@ -214,6 +214,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     u8* xin = cv.take<u8>(L.xin);
     u32* resp_in = cv.take<u32>(L.resp / 4);
     u64* upd = cv.take<u64>(L.upd / 8);
+    u32* symbol_range = cv.take<u32>(65536);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: arena too small");
     if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
 
@@ -342,7 +343,10 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     u64 peer_bytes = 0;
     {
         CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
-        if(my_count) CSA_TRY(csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist)));
+        if(p_eff > 1) CSA_TRY(partition_install_symbol_ranges(ctx, pivots.data(), p_eff, symbol_range));
+        const int pid_rc = my_count ? csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist)) : CSA_OK;
+        partition_install_symbol_ranges(ctx, nullptr, 0, nullptr);
+        CSA_TRY(pid_rc);
         std::vector<u32*> bases(p_eff);
         for(u32 q = 0; q < p_eff; ++q)
         {

@@ -38,7 +38,7 @@ Build_Layout layout_for(u64 n, u32 p)
     L.sa = align256(n * 4 + 64);
     L.sort_ws = align256(csa_sort_workspace_bytes(n));
     L.scratch = align256(div_up(n, RANK_TILE) * 3 * 4 + 256);
-    L.small = align256(size_t(p) * 8) * 3 + align256(size_t(2) * p * 8) + align256(size_t(1) << 24) + 4096;   // hist, cursors, bases, pivots, samples
+    L.small = align256(size_t(p) * 8) * 3 + align256(size_t(2) * p * 8) + align256(size_t(1) << 24) + align256(65536 * 4) + 4096;   // hist, cursors, bases, pivots, samples, first-symbol table
     L.upd = align256(cap * 8);     // (position, rank) updates of one step, applied to `isa` in address order
     L.total = 2 * L.keys + 2 * L.pos + L.head + L.isa + L.sa + L.sort_ws + L.scratch + L.small + L.upd + 4096;
     return L;
@@ -75,6 +75,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     u64* pivots_dev = cv.take<u64>(2 * u64(p));
     u64* samples_dev = cv.take<u64>(2 * MAX_SAMPLES);
     u64* upd = cv.take<u64>(L.upd / 8);
+    u32* symbol_range = cv.take<u32>(65536);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "build: workspace too small");
     u16* pid = reinterpret_cast<u16*>(keysB);      // partition ids live only until the scatter; the keys come later
 
@@ -98,7 +99,10 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
 
     // ---- partition ids and sizes ---------------------------------------------------------------------------
     CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
-    CSA_TRY(csa_partition_ids(ctx, T, n, 0, n, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist)));
+    if(p_eff > 1) CSA_TRY(partition_install_symbol_ranges(ctx, pivots.data(), p_eff, symbol_range));
+    const int pid_rc = csa_partition_ids(ctx, T, n, 0, n, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist));
+    partition_install_symbol_ranges(ctx, nullptr, 0, nullptr);
+    CSA_TRY(pid_rc);
     std::vector<u64> part_size(p_eff), part_off(p_eff + 1, 0);
     CSA_CUDA(ctx, cudaMemcpyAsync(part_size.data(), hist, size_t(p_eff) * 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

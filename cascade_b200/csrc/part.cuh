@@ -11,6 +11,10 @@ struct Isa_View
     u32 gpus;
 };
 
+// Installs (table_dev = 65536 words) or removes (null) the first-symbol table that narrows csa_partition_ids' search on this
+// context's device. It must be removed before the table's memory is reused.
+int partition_install_symbol_ranges(csa_ctx* ctx, const u64* pivots_host, u32 p, u32* table_dev);
+
 // key[i] = the 4 symbols at position pos[i], packed most-significant first.
 int launch_keys_gen0(csa_ctx* ctx, const u16* T, const u32* pos, u64 count, u64* keys);
 

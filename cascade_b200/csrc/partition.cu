@@ -62,8 +62,8 @@ __device__ __forceinline__ bool bulk_wait(u64* bar, u32 parity)
 // K-gram over its ITEMS positions and searches the splitters, kept in shared memory too.
 template <int BLOCK, int ITEMS>
 __global__ void __launch_bounds__(BLOCK) partition_ids_kernel(const u16* __restrict__ T, const u64 n, const u64 first, const u64 count,
-                                                             const u64* __restrict__ pivots, const u32 p, u16* __restrict__ pid_out,
-                                                             u64* __restrict__ hist, u64* __restrict__ dev_status)
+                                                             const u64* __restrict__ pivots, const u32 p, const u32* __restrict__ first_symbol_range,
+                                                             u16* __restrict__ pid_out, u64* __restrict__ hist, u64* __restrict__ dev_status)
 {
     constexpr int TILE = BLOCK * ITEMS;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -108,8 +108,14 @@ __global__ void __launch_bounds__(BLOCK) partition_ids_kernel(const u16* __restr
         #pragma unroll
         for(int k = 0; k < ITEMS; ++k)
         {
-            // lower bound: the first splitter that is not smaller than the K-gram
+            // lower bound: the first splitter that is not smaller than the K-gram, searched inside the range of partitions
+            // that the K-gram's first symbol allows (a 65536-entry table; most symbols allow one partition only)
             u32 a = 0, b = p - 1;
+            if(first_symbol_range != nullptr)
+            {
+                const u32 r = __ldg(first_symbol_range + u32(hi >> 48));
+                a = r & 0xFFFFu; b = r >> 16;
+            }
             while(a < b)
             {
                 const u32 mid = (a + b) >> 1;
@@ -343,6 +349,29 @@ extern "C" int csa_select_pivots(const uint64_t* samples, uint64_t n_samples, ui
 
 constexpr int PID_BLOCK = 256, PID_ITEMS = 16;
 
+// Optional per-device table for csa_partition_ids: for every first symbol the lowest and the highest partition that a
+// K-gram starting with it can fall into (low and high 16 bits). Installed by partition_install_symbol_ranges.
+const u32* g_symbol_range[64] = {nullptr};
+
+int partition_install_symbol_ranges(csa_ctx* ctx, const u64* pivots_host, u32 p, u32* table_dev)
+{
+    if(table_dev == nullptr) { g_symbol_range[ctx->device & 63] = nullptr; return CSA_OK; }
+    std::vector<u32> t(65536);
+    // pid(k) = number of splitters smaller than k. For K-grams starting with s: from pid(s,0,...,0) to pid(s,FFFF,...,FFFF).
+    u32 a = 0, b = 0;
+    for(u32 s = 0; s < 65536; ++s)
+    {
+        const u64 lo_h = u64(s) << 48, hi_h = lo_h | 0x0000FFFFFFFFFFFFull;
+        while(a < p - 1 && (pivots_host[2 * a] < lo_h)) ++a;                                     // splitters < (lo_h, 0): hi word smaller
+        while(b < p - 1 && (pivots_host[2 * b] < hi_h || (pivots_host[2 * b] == hi_h && pivots_host[2 * b + 1] < ~0ull))) ++b;
+        t[s] = a | (b << 16);
+    }
+    CSA_CUDA(ctx, cudaMemcpyAsync(table_dev, t.data(), 65536 * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    g_symbol_range[ctx->device & 63] = table_dev;
+    return CSA_OK;
+}
+
 extern "C" int csa_partition_ids(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t first, uint64_t count, const uint64_t* pivots,
                                  uint32_t p, uint16_t* pid, uint64_t* hist)
 {
@@ -356,7 +385,7 @@ extern "C" int csa_partition_ids(csa_ctx* ctx, const uint16_t* text, uint64_t n,
     const size_t smem = (TILE + 8) * 2 + 16 + size_t(2) * (p > 1 ? p - 1 : 1) * 8 + size_t(p) * 4;
     auto kern = partition_ids_kernel<PID_BLOCK, PID_ITEMS>;
     CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(text, n, first, count, reinterpret_cast<const u64*>(pivots), p, pid,
+    kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(text, n, first, count, reinterpret_cast<const u64*>(pivots), p, g_symbol_range[ctx->device & 63], pid,
                                                                           reinterpret_cast<u64*>(hist), ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
