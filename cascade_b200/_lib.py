@@ -26,7 +26,7 @@ ALLGATHER_FN = ctypes.CFUNCTYPE(c_int, c_vp, c_vp, c_vp, c_u64)
 
 
 class Comm(ctypes.Structure):
-    _fields_ = [("rank", c_u32), ("world", c_u32), ("allgather", ALLGATHER_FN), ("user", c_vp)]
+    _fields_ = [("rank", c_u32), ("world", c_u32), ("policy", c_u32), ("allgather", ALLGATHER_FN), ("user", c_vp)]
 
 
 class Index(ctypes.Structure):
@@ -55,8 +55,8 @@ _SIGS = {
     "csa_build_device_bytes": (ctypes.c_size_t, [c_u64, c_u32]),
     "csa_build_sa": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_build_sa_host": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
-    "csa_plan_shards": (c_int, [c_vp, c_u32, c_u32, c_vp, c_vp, c_vp, c_vp]),
-    "csa_build_sa_multi": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, ctypes.POINTER(c_u64), ctypes.POINTER(c_u64), ctypes.POINTER(BuildStats)]),
+    "csa_plan_shards": (c_int, [c_vp, c_u32, c_u32, c_u32, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "csa_build_sa_multi": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, c_vp, c_vp, ctypes.POINTER(c_u32), ctypes.POINTER(BuildStats)]),
     "csa_table_build": (c_int, [c_vp, c_vp, c_u64, c_vp, c_u64, c_vp]),
     "csa_find": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp]),
     "csa_locate": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp, c_vp]),

@@ -18,10 +18,11 @@
 #include <cstdlib>
 #include <vector>
 
-extern "C" int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t world, uint64_t* part_off, uint32_t* owner, uint64_t* slot_base,
-                               uint64_t* cursor_all)
+extern "C" int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t world, uint32_t policy, uint64_t* part_off, uint32_t* owner,
+                               uint64_t* local_first, uint64_t* local_count, uint64_t* cursor_all)
 {
-    if(!hist_all || !part_off || !owner || !slot_base || !cursor_all || p == 0 || world == 0 || world > CSA_MAX_GPUS) return CSA_E_INVALID;
+    if(!hist_all || !part_off || !owner || !local_first || !local_count || !cursor_all || p == 0 || world == 0 || world > CSA_MAX_GPUS || policy > 1)
+        return CSA_E_INVALID;
     part_off[0] = 0;
     for(uint32_t q = 0; q < p; ++q)
     {
@@ -30,24 +31,32 @@ extern "C" int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t wo
         part_off[q + 1] = part_off[q] + size;
     }
     const uint64_t n = part_off[p];
-    // A partition goes to the GPU in whose equal share of the suffix array its middle falls: owners are non-decreasing.
-    uint32_t last = 0;
-    for(uint32_t q = 0; q < p; ++q)
+    if(policy == 1 && p >= world)
     {
-        const uint64_t mid = part_off[q] + (part_off[q + 1] - part_off[q]) / 2;
-        uint32_t g = n == 0 ? 0 : uint32_t((static_cast<unsigned __int128>(mid) * world) / n);
-        if(g >= world) g = world - 1;
-        if(g < last) g = last;
-        owner[q] = g;
-        last = g;
+        // Interleaved: neighbouring partitions go to different GPUs. Suffixes that start with frequent symbols stay tied
+        // for longer, and they are neighbours in the suffix array, so dealing partitions round spreads the later
+        // generations' work as well as the first one's.
+        for(uint32_t q = 0; q < p; ++q) owner[q] = q % world;
     }
-    // Owners are non-decreasing, so GPU g's slice starts at the first partition whose owner is g or later.
-    for(uint32_t g = 0; g <= world; ++g)
+    else
     {
-        uint64_t start = n;
+        // Contiguous: a partition goes to the GPU in whose equal share of the suffix array its middle falls.
+        uint32_t last = 0;
         for(uint32_t q = 0; q < p; ++q)
-            if(g < world && owner[q] >= g) { start = part_off[q]; break; }
-        slot_base[g] = start;
+        {
+            const uint64_t mid = part_off[q] + (part_off[q + 1] - part_off[q]) / 2;
+            uint32_t g = n == 0 ? 0 : uint32_t((static_cast<unsigned __int128>(mid) * world) / n);
+            if(g >= world) g = world - 1;
+            if(g < last) g = last;
+            owner[q] = g;
+            last = g;
+        }
+    }
+    for(uint32_t g = 0; g < world; ++g) local_count[g] = 0;
+    for(uint32_t q = 0; q < p; ++q)        // a GPU keeps its partitions one after another, in increasing order
+    {
+        local_first[q] = local_count[owner[q]];
+        local_count[owner[q]] += part_off[q + 1] - part_off[q];
     }
     return CSA_OK;
 }
@@ -71,8 +80,8 @@ Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
     L.sa = align_up256(cap * 4 + 64);
     L.sort_ws = align_up256(csa_sort_workspace_bytes(cap > shard ? cap : shard));
     L.scratch = align_up256(div_up(cap, RANK_TILE) * 3 * 4 + 256);
-    L.pid = align_up256(shard * 2 + 64);
-    L.small = align_up256(size_t(p) * 8) * 3 + align_up256(size_t(2) * p * 8) + align_up256(65536 * 4) + 4096;
+    L.pid = 0;
+    L.small = align_up256(size_t(p) * 8) * 5 + align_up256(size_t(2) * p * 8) + 4096;
     L.xin = align_up256(shard * 8 + 64);        // inbox of the bulk exchange: updates (8 bytes) or requests + responses (4 + 4)
     L.resp = align_up256(cap * 4 + 64);         // responses to this GPU's requests
     L.upd = align_up256((cap > shard ? cap : shard) * 8 + 64);   // (position, rank) updates before they are bucketed; pass buffer of the apply
@@ -102,9 +111,9 @@ int barrier(csa_ctx* ctx, const csa_comm* comm)
 }   // namespace
 
 extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint16_t* T, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40,
-                                  uint64_t capacity_entries, uint64_t* slot_first, uint64_t* slot_count, csa_build_stats* stats)
+                                  uint64_t capacity_entries, uint64_t* seg_first, uint64_t* seg_count, uint32_t* seg_c, csa_build_stats* stats)
 {
-    if(!ctx || !comm || !comm->allgather || !T || !sa40 || !slot_first || !slot_count) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: null argument");
+    if(!ctx || !comm || !comm->allgather || !T || !sa40 || !seg_first || !seg_count || !seg_c) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: null argument");
     const u32 G = comm->world, me = comm->rank;
     if(G == 0 || G > CSA_MAX_GPUS || me >= G) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: bad rank or world size");
     if(n == 0 || p == 0 || p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: n or partition count out of range");
@@ -143,6 +152,11 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     void* ws = nullptr;
     const size_t pre_bytes = align_up256(2 * MAX_SAMPLES * 8) + align_up256(size_t(2) * p * 8) + align_up256(size_t(p) * 8) + 4096;
     CSA_TRY(csa_arena(ctx, pre_bytes, &ws));
+    // The partition ids of this rank's positions are made once, before the arena gets its final size, so they live apart.
+    void* aux = nullptr;
+    CSA_TRY(csa_aux(ctx, align_up256(shard * 2 + 64) + align_up256(65536 * 4), &aux));
+    u16* const pid = static_cast<u16*>(aux);
+    u32* const symbol_range = reinterpret_cast<u32*>(static_cast<u8*>(aux) + align_up256(shard * 2 + 64));
     u32 p_eff = 1;
     std::vector<u64> pivots(2 * size_t(p));
     std::vector<u64> my_hist(p, 0);
@@ -165,9 +179,12 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
             if(r != CSA_OK) return csa_fail(ctx, r, "multi-GPU build: splitter selection failed");
             if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
         }
-        // sizes of the partitions over this rank's positions (ids are made again once the arena has its final size)
+        // ids and sizes of the partitions over this rank's positions
         CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
-        if(my_count) CSA_TRY(csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, nullptr, reinterpret_cast<uint64_t*>(hist)));
+        if(p_eff > 1) CSA_TRY(partition_install_symbol_ranges(ctx, pivots.data(), p_eff, symbol_range));
+        const int pid_rc = my_count ? csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist)) : CSA_OK;
+        partition_install_symbol_ranges(ctx, nullptr, 0, nullptr);
+        CSA_TRY(pid_rc);
         CSA_CUDA(ctx, cudaMemcpyAsync(my_hist.data(), hist, size_t(p_eff) * 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
@@ -177,19 +194,31 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     // ---- plan: the same on every rank ------------------------------------------------------------------------------
     std::vector<u64> hist_all(size_t(G) * p_eff), send_hist(my_hist.begin(), my_hist.begin() + p_eff);
     CSA_TRY(gather(ctx, comm, send_hist.data(), hist_all.data(), size_t(p_eff) * 8));
-    std::vector<u64> part_off(p_eff + 1), slot_base(G + 1), cursor_all(size_t(G) * p_eff);
+    std::vector<u64> part_off(p_eff + 1), local_first(p_eff), local_count(G), cursor_all(size_t(G) * p_eff);
     std::vector<u32> owner(p_eff);
-    if(csa_plan_shards(reinterpret_cast<const uint64_t*>(hist_all.data()), p_eff, G, reinterpret_cast<uint64_t*>(part_off.data()), owner.data(),
-                       reinterpret_cast<uint64_t*>(slot_base.data()), reinterpret_cast<uint64_t*>(cursor_all.data())) != CSA_OK)
+    if(csa_plan_shards(reinterpret_cast<const uint64_t*>(hist_all.data()), p_eff, G, comm->policy, reinterpret_cast<uint64_t*>(part_off.data()), owner.data(),
+                       reinterpret_cast<uint64_t*>(local_first.data()), reinterpret_cast<uint64_t*>(local_count.data()),
+                       reinterpret_cast<uint64_t*>(cursor_all.data())) != CSA_OK)
         return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: shard plan failed");
     if(part_off[p_eff] != n) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: partition sizes do not add up to n");
-    const u64 n_local = slot_base[me + 1] - slot_base[me];
+    const u64 n_local = local_count[me];
     u64 max_part = 0, n_local_max = 0;
     for(u32 q = 0; q < p_eff; ++q) if(part_off[q + 1] - part_off[q] > max_part) max_part = part_off[q + 1] - part_off[q];
-    for(u32 g = 0; g < G; ++g) if(slot_base[g + 1] - slot_base[g] > n_local_max) n_local_max = slot_base[g + 1] - slot_base[g];
+    for(u32 g = 0; g < G; ++g) if(local_count[g] > n_local_max) n_local_max = local_count[g];
     st.max_partition = max_part;
-    *slot_first = slot_base[me];
-    *slot_count = n_local;
+    // This rank's slice of the suffix array: its partitions' global ranges, in the order in which they lie in its output.
+    std::vector<u32> seg_first_local;
+    std::vector<u64> seg_delta;
+    *seg_c = 0;
+    for(u32 q = 0; q < p_eff; ++q)
+    {
+        if(owner[q] != me) continue;
+        seg_first[*seg_c] = part_off[q];
+        seg_count[*seg_c] = part_off[q + 1] - part_off[q];
+        ++*seg_c;
+        seg_first_local.push_back(u32(local_first[q]));
+        seg_delta.push_back(part_off[q] - local_first[q]);
+    }
     if(n_local > capacity_entries) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: the output buffer holds fewer entries than this rank's slice");
 
     // ---- arena of the final size; peers map one another's arenas ---------------------------------------------------
@@ -206,15 +235,15 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     u32* head = cv.take<u32>(L.head / 4);
     void* sort_ws = cv.take<u8>(L.sort_ws);
     u32* scratch = cv.take<u32>(L.scratch / 4);
-    u16* pid = cv.take<u16>(L.pid / 2);
     u64* hist = cv.take<u64>(p_eff);
     u64* cursor = cv.take<u64>(p_eff);
     u32** part_base = cv.take<u32*>(p_eff);
     u64* pivots_dev = cv.take<u64>(2 * u64(p_eff));
+    u32* seg_first_dev = cv.take<u32>(p_eff);
+    u64* seg_delta_dev = cv.take<u64>(p_eff);
     u8* xin = cv.take<u8>(L.xin);
     u32* resp_in = cv.take<u32>(L.resp / 4);
     u64* upd = cv.take<u64>(L.upd / 8);
-    u32* symbol_range = cv.take<u32>(65536);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: arena too small");
     if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
 
@@ -342,21 +371,24 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     // ---- partition ids of this rank's positions, then the scatter to the partitions' owners ------------------------
     u64 peer_bytes = 0;
     {
-        CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
-        if(p_eff > 1) CSA_TRY(partition_install_symbol_ranges(ctx, pivots.data(), p_eff, symbol_range));
-        const int pid_rc = my_count ? csa_partition_ids(ctx, T, n, my_first, my_count, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid, reinterpret_cast<uint64_t*>(hist)) : CSA_OK;
-        partition_install_symbol_ranges(ctx, nullptr, 0, nullptr);
-        CSA_TRY(pid_rc);
+        // Positions are first grouped by partition in a local buffer (one run per partition), then every run crosses to the
+        // partition's owner as one contiguous copy: long coalesced transfers instead of scattered peer stores.
+        u32* const local = reinterpret_cast<u32*>(upd);
         std::vector<u32*> bases(p_eff);
+        std::vector<u64> local_off(p_eff + 1, 0);
+        for(u32 q = 0; q < p_eff; ++q) { local_off[q + 1] = local_off[q] + hist_all[size_t(me) * p_eff + q]; bases[q] = local + local_off[q]; }
+        CSA_CUDA(ctx, cudaMemcpyAsync(part_base, bases.data(), size_t(p_eff) * sizeof(u32*), cudaMemcpyHostToDevice, ctx->stream));
+        CSA_CUDA(ctx, cudaMemsetAsync(cursor, 0, size_t(p_eff) * 8, ctx->stream));
+        if(my_count) CSA_TRY(csa_scatter_by_pid(ctx, pid, my_first, my_count, p_eff, part_base, reinterpret_cast<uint64_t*>(cursor)));
         for(u32 q = 0; q < p_eff; ++q)
         {
+            const u64 c = hist_all[size_t(me) * p_eff + q];
+            if(c == 0) continue;
             const u32 o = owner[q];
-            bases[q] = reinterpret_cast<u32*>(peer_arena[o] + peers[o].off_sa) + (part_off[q] - slot_base[o]);
-            if(o != me) peer_bytes += hist_all[size_t(me) * p_eff + q] * 4;
+            u32* dst = reinterpret_cast<u32*>(peer_arena[o] + peers[o].off_sa) + local_first[q] + cursor_all[size_t(me) * p_eff + q];
+            CSA_CUDA(ctx, cudaMemcpyAsync(dst, local + local_off[q], c * 4, cudaMemcpyDefault, ctx->stream));
+            if(o != me) peer_bytes += c * 4;
         }
-        CSA_CUDA(ctx, cudaMemcpyAsync(part_base, bases.data(), size_t(p_eff) * sizeof(u32*), cudaMemcpyHostToDevice, ctx->stream));
-        CSA_CUDA(ctx, cudaMemcpyAsync(cursor, cursor_all.data() + size_t(me) * p_eff, size_t(p_eff) * 8, cudaMemcpyHostToDevice, ctx->stream));
-        if(my_count) CSA_TRY(csa_scatter_by_pid(ctx, pid, my_first, my_count, p_eff, part_base, reinterpret_cast<uint64_t*>(cursor)));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
     CSA_CUDA(ctx, cudaEventRecord(ev[1], ctx->stream));
@@ -367,11 +399,16 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     // ---- generation 0 over this rank's partitions -------------------------------------------------------------------
     u64* act_count = ctx->d_scalars;
     CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
-    const u64 base_slot = slot_base[me];
+    if(!seg_delta.empty())
+    {
+        CSA_CUDA(ctx, cudaMemcpyAsync(seg_first_dev, seg_first_local.data(), seg_first_local.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        CSA_CUDA(ctx, cudaMemcpyAsync(seg_delta_dev, seg_delta.data(), seg_delta.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    const Slot_Map slot_map{seg_first_dev, seg_delta_dev, u32(seg_delta.size()), 0};
     for(u32 q = 0; q < p_eff; ++q)
     {
         if(owner[q] != me) continue;
-        const u64 S = part_off[q + 1] - part_off[q], first = part_off[q] - base_slot;
+        const u64 S = part_off[q + 1] - part_off[q], first = local_first[q];
         if(S == 0) continue;
         CSA_TRY(launch_keys_gen0(ctx, T, sa + first, S, keysA));
         int in_alt = 0;
@@ -379,7 +416,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
                                L.sort_ws, &in_alt));
         const u64* ks = in_alt ? keysB : keysA;
         const u32* ps = in_alt ? posB : sa + first;
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, base_slot, sa, head, posA, act_count, scratch, G > 1 ? upd + first : nullptr));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, Slot_Map{nullptr, nullptr, 0, part_off[q] - first}, sa, head, posA, act_count, scratch, G > 1 ? upd + first : nullptr));
     }
     lap("generation 0 sorts + ranks");
     if(G > 1) CSA_TRY(route_updates(upd, n_local, keysA));      // generation 0's ranks go to the owners of their positions
@@ -416,7 +453,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         u32* ps = in_alt ? pos_other : pos_cur;
         u32* pn = in_alt ? pos_cur : pos_other;
         CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, base_slot, sa, head, pn, act_count, scratch, G > 1 ? upd : nullptr));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, slot_map, sa, head, pn, act_count, scratch, G > 1 ? upd : nullptr));
         lap("sort + ranks");
         if(G > 1) CSA_TRY(route_updates(upd, active, const_cast<u64*>(ks)));
         lap("rank exchange");     // the sorted keys are spent: their buffer holds the buckets

@@ -126,6 +126,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     Isa_View iv;
     std::memset(&iv, 0, sizeof(iv));
     iv.shard[0] = isa; iv.shard_size = n; iv.gpus = 1;
+    const Slot_Map whole{nullptr, nullptr, 0, 0};      // one GPU: local slots are global ranks
     u64* act_count = ctx->d_scalars;       // running length of the next active list
     CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
     for(u32 q = 0; q < p_eff; ++q)
@@ -138,7 +139,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
                                L.sort_ws, &in_alt));
         const u64* ks = in_alt ? keysB : keysA;
         const u32* ps = in_alt ? posB : sa + first;
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, 0, sa, head, posA, act_count, scratch, upd + first));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, whole, sa, head, posA, act_count, scratch, upd + first));
     }
     // The ranks of generation 0 reach the inverse array in address order: one keys-only digit pass, then a streaming apply.
     const int position_bits = bits_for(n - 1);
@@ -169,7 +170,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
         u32* ps = in_alt ? pos_other : pos_cur;
         u32* pn = in_alt ? pos_cur : pos_other;
         CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
-        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, 0, sa, head, pn, act_count, scratch, upd));
+        CSA_TRY(launch_rank_and_compact(ctx, ks, ps, active, sec_bits, 0, iv, whole, sa, head, pn, act_count, scratch, upd));
         CSA_TRY(apply_updates_in_address_order(ctx, isa, upd, const_cast<u64*>(ks), active, position_bits, sort_ws, L.sort_ws));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));

@@ -36,6 +36,8 @@ struct csa_ctx
     u64* d_scalars = nullptr;      // device, 64 words
     void* arena = nullptr;         // grow-only scratch
     size_t arena_bytes = 0;
+    void* aux = nullptr;           // a second grow-only buffer, for data that must survive a regrowth of the arena
+    size_t aux_bytes = 0;
     std::string err;
     u64 counters[16] = {0};        // launch and byte counters for the benchmark
     // Mappings of other GPUs' arenas opened through CUDA IPC (multi-GPU builds), kept while the peers' handles stay the same.
@@ -80,6 +82,7 @@ static inline int csa_fail(csa_ctx* ctx, int code, const std::string& why)
 
 // Returns in *out a scratch pointer of at least `bytes` bytes from the context's grow-only arena.
 int csa_arena(csa_ctx* ctx, size_t bytes, void** out);
+int csa_aux(csa_ctx* ctx, size_t bytes, void** out);
 
 static inline size_t align_up256(size_t b) { return (b + 255) & ~size_t(255); }
 static inline u64 div_up(u64 a, u64 b) { return (a + b - 1) / b; }

@@ -35,6 +35,7 @@ extern "C" void csa_ctx_destroy(csa_ctx* ctx)
     sort_reset_timing(ctx);
     for(int g = 0; g < CSA_MAX_GPUS; ++g) if(ctx->peer_open[g]) cudaIpcCloseMemHandle(ctx->peer_base[g]);
     if(ctx->arena) cudaFree(ctx->arena);
+    if(ctx->aux) cudaFree(ctx->aux);
     if(ctx->d_status) cudaFree(ctx->d_status);
     if(ctx->d_scalars) cudaFree(ctx->d_scalars);
     if(ctx->h_scalars) cudaFreeHost(ctx->h_scalars);
@@ -87,5 +88,24 @@ int csa_arena(csa_ctx* ctx, size_t bytes, void** out)
         ctx->arena_bytes = bytes;
     }
     *out = ctx->arena;
+    return CSA_OK;
+}
+
+int csa_aux(csa_ctx* ctx, size_t bytes, void** out)
+{
+    if(bytes > ctx->aux_bytes)
+    {
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if(ctx->aux) { cudaFree(ctx->aux); ctx->aux = nullptr; ctx->aux_bytes = 0; }
+        const cudaError_t e = cudaMalloc(&ctx->aux, bytes);
+        if(e != cudaSuccess)
+        {
+            cudaGetLastError();
+            ctx->err = "device allocation of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e);
+            return CSA_E_NOMEM;
+        }
+        ctx->aux_bytes = bytes;
+    }
+    *out = ctx->aux;
     return CSA_OK;
 }

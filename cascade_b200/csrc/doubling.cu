@@ -24,6 +24,18 @@ __device__ __forceinline__ u32* isa_slot(const Isa_View& v, u64 x)
     return v.shard[g] + (x - g * v.shard_size);
 }
 
+__device__ __forceinline__ u64 global_of(const Slot_Map& m, u32 slot)
+{
+    if(m.segs == 0) return m.base + slot;
+    u32 a = 0, b = m.segs - 1;             // the last local partition that starts at or before the slot
+    while(a < b)
+    {
+        const u32 mid = (a + b + 1) >> 1;
+        if(__ldg(m.seg_first + mid) <= slot) a = mid; else b = mid - 1;
+    }
+    return __ldg(m.seg_delta + a) + slot;
+}
+
 __global__ void keys_gen0_kernel(const u16* __restrict__ T, const u32* __restrict__ pos, const u64 count, u64* __restrict__ keys)
 {
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -178,7 +190,7 @@ __global__ void __launch_bounds__(1024) rank_carry_kernel(u32* __restrict__ agg,
 // Phase 3: every record gets its slot and rank; tied records go to the next list.
 // `pos` may be the very slot range of `sa` that the records go to (generation 0 sorts in place): such a record is not rewritten.
 __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __restrict__ keys, const u32* pos, const u64 count,
-                                                               const int prim_shift, const u32 fixed_head, const Isa_View isa, const u64 slot_base,
+                                                               const int prim_shift, const u32 fixed_head, const Isa_View isa, const Slot_Map map,
                                                                u32* sa, u32* __restrict__ next_head, u32* __restrict__ next_pos,
                                                                const u32* __restrict__ agg, u64* __restrict__ updates)
 {
@@ -219,8 +231,9 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
         if(sa + slot != pos + idx) sa[slot] = ps;
         // The new rank goes straight into the inverse array, or, when the array is spread over several GPUs, into a list
         // of (position, rank) updates that is applied in address order (and, over several GPUs, routed to the positions' owners).
-        if(updates) updates[idx] = (u64(ps) << 32) | u32(slot_base + new_head);
-        else *isa_slot(isa, ps) = u32(slot_base + new_head);
+        const u32 global_rank = u32(global_of(map, head) + (new_head - head));      // a group lies inside one partition
+        if(updates) updates[idx] = (u64(ps) << 32) | global_rank;
+        else *isa_slot(isa, ps) = global_rank;
         if(f.active & (1u << i))
         {
             next_head[out] = new_head;
@@ -286,7 +299,7 @@ int launch_keys_gen(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u6
 }
 
 int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 count, int prim_shift, u32 fixed_head, Isa_View isa,
-                            u64 slot_base, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates)
+                            Slot_Map map, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates)
 {
     if(count == 0) return CSA_OK;
     const u64 tiles = div_up(count, RANK_TILE);
@@ -294,7 +307,7 @@ int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 c
     CSA_LAUNCH_CHECK(ctx);
     rank_carry_kernel<<<1, 1024, 0, ctx->stream>>>(scratch, tiles, act_count);
     CSA_LAUNCH_CHECK(ctx);
-    rank_apply_kernel<<<unsigned(tiles), RANK_BLOCK, 0, ctx->stream>>>(keys, pos, count, prim_shift, fixed_head, isa, slot_base, sa, next_head,
+    rank_apply_kernel<<<unsigned(tiles), RANK_BLOCK, 0, ctx->stream>>>(keys, pos, count, prim_shift, fixed_head, isa, map, sa, next_head,
                                                                        next_pos, scratch, updates);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;

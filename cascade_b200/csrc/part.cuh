@@ -15,6 +15,16 @@ struct Isa_View
 // context's device. It must be removed before the table's memory is reused.
 int partition_install_symbol_ranges(csa_ctx* ctx, const u64* pivots_host, u32 p, u32* table_dev);
 
+// Global rank of a local slot. A GPU's local slots hold its partitions one after another; a partition's global range starts
+// at its own offset, so global = local + a per-partition difference. With segs = 0 the difference is `base` for all slots.
+struct Slot_Map
+{
+    const u32* seg_first;   // local first slot of every local partition, ascending
+    const u64* seg_delta;   // global first slot minus local first slot
+    u32 segs;
+    u64 base;
+};
+
 // key[i] = the 4 symbols at position pos[i], packed most-significant first.
 int launch_keys_gen0(csa_ctx* ctx, const u16* T, const u32* pos, u64 count, u64* keys);
 
@@ -26,13 +36,13 @@ int launch_keys_gen(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u6
 // inverse suffix array, and appends the suffixes that are still tied to the next active list.
 //   prim_shift < 64: records are grouped by key >> prim_shift, which is the group's first local slot;
 //   prim_shift = 64: all records form one group whose first local slot is fixed_head.
-// slot_base is the global rank of local slot 0. *act_count (device) is the running length of the next list.
+// `map` turns local slots into global ranks. *act_count (device) is the running length of the next list.
 // scratch holds 3 words per tile of RANK_TILE records.
 constexpr int RANK_BLOCK = 256, RANK_ITEMS = 8, RANK_TILE = RANK_BLOCK * RANK_ITEMS;
 // If `updates` is non-null the new ranks are not written into the inverse array but listed there, record i of the sorted
 // list as (rank << 32) | position, for a bulk exchange between GPUs.
 int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 count, int prim_shift, u32 fixed_head, Isa_View isa,
-                            u64 slot_base, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates = nullptr);
+                            Slot_Map map, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates = nullptr);
 
 // ---- bulk exchange of ranks between GPUs (exchange.cu) ----------------------------------------------------------------
 // counts[g] += the records whose position (offset by h; positions at or past n are skipped) lies in shard g.

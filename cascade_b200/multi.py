@@ -18,8 +18,9 @@ from . import api
 from ._lib import ALLGATHER_FN, BuildStats, Comm, c_u64
 
 
-def make_comm(rank, world, device=None):
-    """Returns (Comm, keepalive). `device` is the torch device for NCCL groups, None for gloo."""
+def make_comm(rank, world, device=None, policy=1):
+    """Returns (Comm, keepalive). `device` is the torch device for NCCL groups, None for gloo. policy: 0 deals the partitions
+    to the GPUs in contiguous blocks, 1 (default) interleaves them."""
     def _allgather(user, send, recv, nbytes):
         try:
             n = int(nbytes)
@@ -41,37 +42,43 @@ def make_comm(rank, world, device=None):
             return 1
 
     fn = ALLGATHER_FN(_allgather)
-    return Comm(rank, world, fn, None), fn
+    return Comm(rank, world, policy, fn, None), fn
 
 
-def plan_shards(hist_all, world):
-    """Host-side shard plan (csa_plan_shards) from hist_all[world][p]. Returns (part_off, owner, slot_base, cursor_all)."""
+def plan_shards(hist_all, world, policy=1):
+    """Host-side shard plan (csa_plan_shards) from hist_all[world][p]. Returns (part_off, owner, local_first, local_count, cursor_all)."""
     from ._lib import lib
     hist_all = np.ascontiguousarray(hist_all, dtype=np.uint64)
     p = hist_all.shape[1]
     part_off = np.zeros(p + 1, np.uint64)
     owner = np.zeros(p, np.uint32)
-    slot_base = np.zeros(world + 1, np.uint64)
+    local_first = np.zeros(p, np.uint64)
+    local_count = np.zeros(world, np.uint64)
     cursor = np.zeros((world, p), np.uint64)
-    rc = lib().csa_plan_shards(hist_all.ctypes.data, p, world, part_off.ctypes.data, owner.ctypes.data, slot_base.ctypes.data, cursor.ctypes.data)
+    rc = lib().csa_plan_shards(hist_all.ctypes.data, p, world, policy, part_off.ctypes.data, owner.ctypes.data, local_first.ctypes.data,
+                               local_count.ctypes.data, cursor.ctypes.data)
     if rc != 0:
         raise api.CascadeError(rc, "csa_plan_shards")
-    return part_off, owner, slot_base, cursor
+    return part_off, owner, local_first, local_count, cursor
 
 
 def build_sa_multi(ctx, comm, text_dev, n, p, seed=0, out=None, capacity=None):
-    """This rank's slice of the suffix array of text_dev[0, n). Returns (sa40 slice tensor, first, count, stats)."""
+    """This rank's part of the suffix array of text_dev[0, n). Returns (sa40 tensor, segments, stats): the tensor holds the
+    rank's partitions one after another; segments = [(first global rank, count), ...] in that order."""
     world = comm.world
     if capacity is None:
         capacity = n if world == 1 else min(n, n // world + n // max(1, min(p, 8)) + 1024)
     if out is None:
         out = torch.zeros(5 * capacity + api.SA_PAD_BYTES, dtype=torch.uint8, device=text_dev.device)
     st = BuildStats()
-    first, count = c_u64(0), c_u64(0)
+    seg_first = np.zeros(max(1, p), np.uint64)
+    seg_count = np.zeros(max(1, p), np.uint64)
+    seg_c = ctypes.c_uint32(0)
     torch.cuda.synchronize(text_dev.device)
     ctx.check(ctx.L.csa_build_sa_multi(ctx.h, ctypes.byref(comm), text_dev.data_ptr(), n, p, seed, out.data_ptr(), capacity,
-                                       ctypes.byref(first), ctypes.byref(count), ctypes.byref(st)))
-    return out, int(first.value), int(count.value), st
+                                       seg_first.ctypes.data, seg_count.ctypes.data, ctypes.byref(seg_c), ctypes.byref(st)))
+    segs = [(int(seg_first[k]), int(seg_count[k])) for k in range(seg_c.value)]
+    return out, segs, st
 
 
 def _max_over_ranks(x, device):
@@ -106,7 +113,8 @@ def bench(args, rank, world, local):
     step_ms, launches, peer = [], 0, 0
     with B.ClockSampler(local) as clocks:
         for _ in range(args.steps):
-            _, first, count, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            _, segs, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            count = sum(c for _, c in segs)
             step_ms.append(_max_over_ranks(st.ms_total, dev))
             launches += st.kernel_launches
             peer += st.peer_bytes
@@ -146,7 +154,8 @@ def bench(args, rank, world, local):
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             T.copy_(th, non_blocking=True)
-            _, first, count, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            _, segs, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            count = sum(c for _, c in segs)
             oh[:5 * count].copy_(out[:5 * count], non_blocking=True)
             torch.cuda.synchronize()
             dt = _max_over_ranks(time.perf_counter() - t0, dev)

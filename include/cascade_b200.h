@@ -164,26 +164,31 @@ typedef int (*csa_allgather_fn)(void* user, const void* send, void* recv, uint64
 typedef struct csa_comm
 {
     uint32_t rank, world;       /* world <= CSA_MAX_GPUS */
+    uint32_t policy;            /* how partitions are dealt to GPUs: 0 = contiguous blocks, 1 = interleaved (q mod world) */
     csa_allgather_fn allgather;
     void* user;
 } csa_comm;
 
 /* Host-side plan of a sharded build, the same on every rank: from every rank's partition sizes over its share of the
- * positions (hist_all[world][p]) the partitions' global offsets part_off[p + 1], their owners owner[p] (contiguous blocks
- * of partitions balanced by size, so a GPU owns one contiguous slice of the suffix array), the slice starts
- * slot_base[world + 1], and for every (rank, partition) the offset inside the partition at which that rank's positions
- * go (cursor_all[world][p]). Stands where the reference keeps every partition on its one GPU (src/GPU_SACA.cu:982-985). */
-int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t world, uint64_t* part_off, uint32_t* owner,
-                    uint64_t* slot_base, uint64_t* cursor_all);
+ * positions (hist_all[world][p]) the partitions' global offsets part_off[p + 1], their owners owner[p] (policy 0: contiguous
+ * blocks of partitions balanced by size, so a GPU owns one contiguous slice of the suffix array; policy 1: partition q goes
+ * to GPU q mod world, which also spreads the partitions that stay tied for many generations), the slot inside its owner's
+ * local array at which each partition starts (local_first[p]; a GPU keeps its partitions one after another in increasing
+ * order), the GPUs' totals local_count[world], and for every (rank, partition) the offset inside the partition at which
+ * that rank's positions go (cursor_all[world][p]). Stands where the reference keeps every partition on its one GPU
+ * (src/GPU_SACA.cu:982-985). */
+int csa_plan_shards(const uint64_t* hist_all, uint32_t p, uint32_t world, uint32_t policy, uint64_t* part_off, uint32_t* owner,
+                    uint64_t* local_first, uint64_t* local_count, uint64_t* cursor_all);
 /* The build of csa_build_sa spread over comm->world GPUs. Every rank passes the whole text in its own device memory
  * (same n, p, seed everywhere). Whole partitions are owned by one GPU; positions travel to their partition's owner and
- * ranks to the owner of their text position as plain stores into peer memory (CUDA IPC mappings, NVLink), and are read
- * back by peer loads; the ranks meet at host barriers between the steps. Rank r receives its contiguous slice of the
- * suffix array: entries [*slot_first, *slot_first + *slot_count) as 5-byte entries at sa40_dev, which must hold
- * capacity_entries entries (n / world + the largest partition is always enough; CSA_E_NOMEM if too few).
+ * ranks to the owner of their text position in bulk copies between the GPUs' memories (CUDA IPC mappings, NVLink); the
+ * ranks meet at host barriers between the steps. A rank receives the suffix-array entries of its partitions, one
+ * partition after another, as 5-byte entries at sa40_dev, which must hold capacity_entries entries (CSA_E_NOMEM if too
+ * few): segment k of the output holds the global ranks [seg_first[k], seg_first[k] + seg_count[k]); *seg_c segments, at
+ * most p (the arrays must hold p words).
  * Replaces the host-mediated exchange of the reference (messages through RAM or files, src/Partition_Backend.cpp:516-553). */
 int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint16_t* text_dev, uint64_t n, uint32_t p, uint64_t seed,
-                       uint8_t* sa40_dev, uint64_t capacity_entries, uint64_t* slot_first, uint64_t* slot_count,
+                       uint8_t* sa40_dev, uint64_t capacity_entries, uint64_t* seg_first, uint64_t* seg_count, uint32_t* seg_c,
                        csa_build_stats* stats);
 
 /* ---- query engine ------------------------------------------------------------------------------------- */

@@ -10,39 +10,48 @@ import torch.multiprocessing as mp
 from conftest import ROOT
 
 
-def _check_plan(hist_all, world):
+def _check_plan(hist_all, world, policy):
     from cascade_b200 import multi
-    part_off, owner, slot_base, cursor = multi.plan_shards(hist_all, world)
+    part_off, owner, local_first, local_count, cursor = multi.plan_shards(hist_all, world, policy)
     p = hist_all.shape[1]
     sizes = hist_all.sum(axis=0)
     n = int(sizes.sum())
     assert part_off[0] == 0 and np.array_equal(np.diff(part_off.astype(np.int64)), sizes.astype(np.int64))
-    assert np.all(np.diff(owner.astype(np.int64)) >= 0) and owner.max() < world          # contiguous blocks of partitions
-    assert slot_base[0] == 0 and slot_base[world] == n and np.all(np.diff(slot_base.astype(np.int64)) >= 0)
-    for q in range(p):
-        g = int(owner[q])
-        assert slot_base[g] <= part_off[q] and part_off[q + 1] <= slot_base[g + 1]      # a partition lies inside its owner's slice
-        # the ranks' runs inside a partition tile it exactly
+    assert owner.max() < world and int(local_count.sum()) == n
+    if policy == 0:
+        assert np.all(np.diff(owner.astype(np.int64)) >= 0)          # contiguous blocks of partitions
+    elif p >= world:
+        assert np.array_equal(owner, np.arange(p) % world)           # dealt round
+    # every GPU keeps its partitions one after another, in increasing order, without gaps
+    for g in range(world):
+        at = 0
+        for q in range(p):
+            if owner[q] == g:
+                assert local_first[q] == at
+                at += int(sizes[q])
+        assert at == local_count[g]
+    for q in range(p):      # the ranks' runs inside a partition tile it exactly
         assert cursor[0, q] == 0
         for r in range(1, world):
             assert cursor[r, q] == cursor[r - 1, q] + hist_all[r - 1, q]
-    return part_off, owner, slot_base
+    return local_count
 
 
 def test_plan_is_balanced_and_consistent():
     rng = np.random.default_rng(0)
-    for world in (1, 2, 4, 8):
-        for p in (1, 3, 64, 500):
-            h = rng.integers(0, 1000, size=(world, p)).astype(np.uint64)
-            part_off, owner, slot_base = _check_plan(h, world)
-            if p >= 64:
-                n = int(h.sum())
-                share = np.diff(slot_base.astype(np.int64))
-                assert share.max() <= n / world + 2 * int(h.sum(axis=0).max())
-    # degenerate: everything in one partition, more GPUs than partitions
-    h = np.zeros((4, 2), np.uint64)
-    h[:, 1] = 10
-    _check_plan(h, 4)
+    for policy in (0, 1):
+        for world in (1, 2, 4, 8):
+            for p in (1, 3, 64, 500):
+                h = rng.integers(0, 1000, size=(world, p)).astype(np.uint64)
+                local_count = _check_plan(h, world, policy)
+                if p >= 64:
+                    n = int(h.sum())
+                    slack = 2 * int(h.sum(axis=0).max()) if policy == 0 else 0.15 * n / world      # dealing round balances on average only
+                    assert int(local_count.max()) <= n / world + slack
+        # degenerate: everything in one partition, more GPUs than partitions
+        h = np.zeros((4, 2), np.uint64)
+        h[:, 1] = 10
+        _check_plan(h, 4, policy)
 
 
 def _free_port():
@@ -66,8 +75,8 @@ def _gloo_worker(rank, world, port, q):
     allh = np.zeros(world * p, np.uint64)
     rc = comm.allgather(None, mine.ctypes.data, allh.ctypes.data, mine.nbytes)   # the call the library makes
     assert rc == 0
-    part_off, owner, slot_base, cursor = multi.plan_shards(allh.reshape(world, p), world)
-    q.put((rank, allh.tolist(), part_off.tolist(), owner.tolist(), slot_base.tolist()))
+    part_off, owner, local_first, local_count, cursor = multi.plan_shards(allh.reshape(world, p), world)
+    q.put((rank, allh.tolist(), part_off.tolist(), owner.tolist(), local_first.tolist(), local_count.tolist()))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -23,8 +23,8 @@ def test_world_of_one_equals_the_single_gpu_build():
         T = api.gen_corpus_device(ctx, n, 3, 512)
         ref, _ = api.build_sa(ctx, T, n, 16)
         comm, keep = multi.make_comm(0, 1, None)
-        out, first, count, st = multi.build_sa_multi(ctx, comm, T, n, 16)
-        assert (first, count) == (0, n)
+        out, segs, st = multi.build_sa_multi(ctx, comm, T, n, 16)
+        assert segs[0][0] == 0 and sum(c for _, c in segs) == n and all(segs[k][0] + segs[k][1] == segs[k + 1][0] for k in range(len(segs) - 1))
         assert torch.equal(out[:5 * n], ref[:5 * n])
     finally:
         ctx.close()
@@ -38,7 +38,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, n, p, kind, q):
+def _worker(rank, world, port, n, p, kind, policy, q):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     from cascade_b200 import api, multi
@@ -53,39 +53,45 @@ def _worker(rank, world, port, n, p, kind, q):
     else:
         Th = api.gen_repeat_corpus_host(n, seed=1, base_docs=8, mean_doc=1024, mutate=0.002)
         T = torch.from_numpy(Th.view(np.int16)).cuda().view(torch.uint16)
-    comm, keep = multi.make_comm(rank, world, None)
+    comm, keep = multi.make_comm(rank, world, None, policy)
     for _ in range(2):      # twice: the second build reuses the peers' mappings
-        out, first, count, st = multi.build_sa_multi(ctx, comm, T, n, p)
-    sl = out[:5 * count].cpu().numpy()
+        out, segs, st = multi.build_sa_multi(ctx, comm, T, n, p)
+    sl = out[:5 * sum(c for _, c in segs)].cpu().numpy()
     ref = None
     if rank == 0:
         r, _ = api.build_sa(ctx, T, n, p)
         ref = r[:5 * n].cpu().numpy()
-    q.put((rank, first, count, sl, ref, st.generations, st.peer_bytes))
+    q.put((rank, segs, sl, ref, st.generations, st.peer_bytes))
     dist.barrier()
     ctx.close()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,n,p,kind", [(2, 3_000_000, 16, "zipf"), (2, 400_000, 8, "repeat"), (3, 1_000_003, 5, "zipf")])
-def test_sharded_build_equals_the_single_gpu_build(world, n, p, kind):
+@pytest.mark.parametrize("world,n,p,kind,policy", [(2, 3_000_000, 16, "zipf", 1), (2, 400_000, 8, "repeat", 1), (3, 1_000_003, 5, "zipf", 1),
+                                                    (2, 1_500_000, 16, "zipf", 0)])
+def test_sharded_build_equals_the_single_gpu_build(world, n, p, kind, policy):
     port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n, p, kind, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, p, kind, policy, q)) for r in range(world)]
     for pr in procs:
         pr.start()
     res = sorted((q.get(timeout=600) for _ in range(world)), key=lambda x: x[0])
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
-    ref = res[0][4]
-    at = 0
-    for rank, first, count, sl, _, gens, peer in res:
-        assert first == at, "slices must be contiguous in rank order"
-        assert np.array_equal(sl, ref[5 * first:5 * (first + count)]), f"rank {rank}'s slice differs"
-        at += count
-    assert at == n
+    ref = res[0][3]
+    covered = np.zeros(n, np.uint8)
+    for rank, segs, sl, _, gens, peer in res:
+        at = 0
+        for first, count in segs:       # a rank's output holds its partitions one after another
+            assert np.array_equal(sl[5 * at:5 * (at + count)], ref[5 * first:5 * (first + count)]), f"rank {rank}'s segment at {first} differs"
+            covered[first:first + count] += 1
+            at += count
+        assert 5 * at == sl.size
+        if policy == 0 and segs:
+            assert all(segs[k][0] + segs[k][1] == segs[k + 1][0] for k in range(len(segs) - 1)), "contiguous blocks give one contiguous slice"
+    assert np.all(covered == 1), "the ranks' segments tile the suffix array exactly"
     if kind == "repeat":
-        assert res[0][5] >= 5
-    assert sum(r[6] for r in res) > 0      # ranks and positions did cross between the GPUs' memories
+        assert res[0][4] >= 5
+    assert sum(r[5] for r in res) > 0      # ranks and positions did cross between the GPUs' memories
