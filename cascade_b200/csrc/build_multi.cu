@@ -319,13 +319,17 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_TRY(exchange_counts());
         if(inbox_total() > shard) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: more rank updates than positions in a shard");
         CSA_TRY(launch_bucket_updates(ctx, list, count, shard, G, cursor_dev, bucketed));
-        for(u32 d = 0; d < G; ++d)
         {
-            const u64 c = C[size_t(me) * G + d];
-            if(c == 0) continue;
-            u64* dst = reinterpret_cast<u64*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
-            CSA_CUDA(ctx, cudaMemcpyAsync(dst, bucketed + out_off(me, d), c * 8, cudaMemcpyDefault, ctx->stream));
-            if(d != me) route_bytes += c * 8;
+            void* dsts[CSA_MAX_GPUS]; const void* srcs[CSA_MAX_GPUS]; u64 bytes[CSA_MAX_GPUS];
+            for(u32 d = 0; d < G; ++d)
+            {
+                const u64 c = C[size_t(me) * G + d];
+                dsts[d] = reinterpret_cast<u64*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
+                srcs[d] = bucketed + out_off(me, d);
+                bytes[d] = c * 8;
+                if(d != me) route_bytes += c * 8;
+            }
+            CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
         CSA_TRY(barrier(ctx, comm));                                   // every inbox is complete
         // `list` has been bucketed and sent, so its buffer serves the address-ordering pass of what arrived
@@ -342,23 +346,31 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_TRY(launch_bucket_requests(ctx, poss, count, h, n, shard, G, cursor_dev, req_out, perm));
         u32* const req_in = reinterpret_cast<u32*>(xin);
         u32* const resp_out = req_in + shard;
-        for(u32 d = 0; d < G; ++d)
         {
-            const u64 c = C[size_t(me) * G + d];
-            if(c == 0) continue;
-            u32* dst = reinterpret_cast<u32*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
-            CSA_CUDA(ctx, cudaMemcpyAsync(dst, req_out + out_off(me, d), c * 4, cudaMemcpyDefault, ctx->stream));
-            if(d != me) route_bytes += c * 4;
+            void* dsts[CSA_MAX_GPUS]; const void* srcs[CSA_MAX_GPUS]; u64 bytes[CSA_MAX_GPUS];
+            for(u32 d = 0; d < G; ++d)
+            {
+                const u64 c = C[size_t(me) * G + d];
+                dsts[d] = reinterpret_cast<u32*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
+                srcs[d] = req_out + out_off(me, d);
+                bytes[d] = c * 4;
+                if(d != me) route_bytes += c * 4;
+            }
+            CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
         CSA_TRY(barrier(ctx, comm));                                   // every request has arrived
         CSA_TRY(launch_serve_requests(ctx, isa, req_in, inbox_total(), resp_out));
-        for(u32 s2 = 0; s2 < G; ++s2)
         {
-            const u64 c = C[size_t(s2) * G + me];
-            if(c == 0) continue;
-            u32* dst = reinterpret_cast<u32*>(peer_arena[s2] + peers[s2].off_resp) + out_off(s2, me);
-            CSA_CUDA(ctx, cudaMemcpyAsync(dst, resp_out + in_off(s2, me), c * 4, cudaMemcpyDefault, ctx->stream));
-            if(s2 != me) route_bytes += c * 4;
+            void* dsts[CSA_MAX_GPUS]; const void* srcs[CSA_MAX_GPUS]; u64 bytes[CSA_MAX_GPUS];
+            for(u32 s2 = 0; s2 < G; ++s2)
+            {
+                const u64 c = C[size_t(s2) * G + me];
+                dsts[s2] = reinterpret_cast<u32*>(peer_arena[s2] + peers[s2].off_resp) + out_off(s2, me);
+                srcs[s2] = resp_out + in_off(s2, me);
+                bytes[s2] = c * 4;
+                if(s2 != me) route_bytes += c * 4;
+            }
+            CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
         CSA_TRY(launch_keys_init(ctx, heads, poss, count, n, h, sec_bits, keys));
         CSA_TRY(barrier(ctx, comm));                                   // every response has arrived

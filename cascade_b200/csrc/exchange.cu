@@ -118,7 +118,62 @@ __global__ void keys_add_kernel(const u32* __restrict__ perm, const u32* __restr
     if(j < count) keys[perm[j]] += u64(resp[j]) + h;
 }
 
+// Up to CSA_MAX_GPUS contiguous copies in one launch, each possibly into another GPU's memory: every SM streams a share of
+// every segment, so the copies to all peers run side by side over NVLink instead of one after another.
+struct Copy_Segments
+{
+    void* dst[CSA_MAX_GPUS];
+    const void* src[CSA_MAX_GPUS];
+    u64 words[CSA_MAX_GPUS];        // 4-byte words
+    u32 count;
+};
+
+__global__ void __launch_bounds__(256) copy_segments_kernel(const Copy_Segments segs)
+{
+    for(u32 k = 0; k < segs.count; ++k)
+    {
+        const u64 words = segs.words[k];
+        const bool wide = ((reinterpret_cast<uintptr_t>(segs.dst[k]) | reinterpret_cast<uintptr_t>(segs.src[k])) & 15) == 0;
+        if(wide)
+        {
+            const uint4* s4 = static_cast<const uint4*>(segs.src[k]);
+            uint4* d4 = static_cast<uint4*>(segs.dst[k]);
+            const u64 quads = words >> 2;
+            for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < quads; i += u64(gridDim.x) * blockDim.x) d4[i] = s4[i];
+            const u32* s1 = static_cast<const u32*>(segs.src[k]);
+            u32* d1 = static_cast<u32*>(segs.dst[k]);
+            for(u64 i = (quads << 2) + u64(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += u64(gridDim.x) * blockDim.x) d1[i] = s1[i];
+        }
+        else
+        {
+            const u32* s1 = static_cast<const u32*>(segs.src[k]);
+            u32* d1 = static_cast<u32*>(segs.dst[k]);
+            for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += u64(gridDim.x) * blockDim.x) d1[i] = s1[i];
+        }
+    }
+}
+
 }   // namespace
+
+int launch_copy_segments(csa_ctx* ctx, void* const* dst, const void* const* src, const u64* bytes, u32 count)
+{
+    Copy_Segments segs;
+    segs.count = 0;
+    u64 total = 0;
+    for(u32 k = 0; k < count && segs.count < CSA_MAX_GPUS; ++k)
+    {
+        if(bytes[k] == 0) continue;
+        segs.dst[segs.count] = dst[k]; segs.src[segs.count] = src[k]; segs.words[segs.count] = bytes[k] / 4;
+        total += bytes[k];
+        ++segs.count;
+    }
+    if(segs.count == 0) return CSA_OK;
+    const u64 want = div_up(total / 16 + 1, 256 * 4);
+    const unsigned blocks = unsigned(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
+    copy_segments_kernel<<<blocks, 256, 0, ctx->stream>>>(segs);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
 
 int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* counts)
 {

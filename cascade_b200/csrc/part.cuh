@@ -52,6 +52,8 @@ int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 cou
 int launch_bucket_requests(csa_ctx* ctx, const u32* pos, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* cursor, u32* req_out, u32* perm_out);
 // Updates: (position << 32 | rank) records go to the bucket of the position's owner as (index inside the shard << 32 | rank).
 int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard, u32 gpus, u64* cursor, u64* out);
+// count (<= CSA_MAX_GPUS) contiguous copies, of a multiple of 4 bytes each, in one launch; destinations may be peer memory.
+int launch_copy_segments(csa_ctx* ctx, void* const* dst, const void* const* src, const u64* bytes, u32 count);
 // resp[i] = isa_local[req[i]]
 int launch_serve_requests(csa_ctx* ctx, const u32* isa_local, const u32* req, u64 count, u32* resp);
 // isa_local[high 32 bits] = low 32 bits

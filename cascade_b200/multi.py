@@ -45,6 +45,20 @@ def make_comm(rank, world, device=None, policy=1):
     return Comm(rank, world, policy, fn, None), fn
 
 
+def make_shm_comm(rank, world, name, policy=1):
+    """A communicator whose all-gather runs in the library over POSIX shared memory (ranks of one box). `name` must be the
+    same on all ranks and unique to the job. Returns (Comm, close): call close() after the last build."""
+    from ._lib import lib
+    comm = Comm()
+    rc = lib().csa_comm_open_shm(name.encode(), rank, world, policy, ctypes.byref(comm))
+    if rc != 0:
+        raise api.CascadeError(rc, "csa_comm_open_shm")
+
+    def close():
+        lib().csa_comm_close_shm(ctypes.byref(comm), 1 if rank == 0 else 0)
+    return comm, close
+
+
 def plan_shards(hist_all, world, policy=1):
     """Host-side shard plan (csa_plan_shards) from hist_all[world][p]. Returns (part_off, owner, local_first, local_count, cursor_all)."""
     from ._lib import lib
@@ -98,7 +112,9 @@ def bench(args, rank, world, local):
     import bench as B
     dev = torch.device("cuda", local)
     ctx = api.Context(local)
-    comm, keep = make_comm(rank, world, dev)
+    name = [f"/cascade_b200_{os.getpid()}_{int(time.time())}"]
+    dist.broadcast_object_list(name, src=0)            # one name for the job's shared-memory object
+    comm, close_comm = make_shm_comm(rank, world, name[0])
     n, p = args.tokens, B.C2_PARTITIONS
     peak, peak_kind = B.measured_peak_gbs()
     T = api.gen_corpus_device(ctx, n, 0, B.C2_MEAN_DOC)          # every rank makes the same text in its own HBM
@@ -179,5 +195,6 @@ def bench(args, rank, world, local):
                 "verified": {"slices_add_up_to_n": total == n, "sampled_neighbours_in_order": ok_all}}
         print(json.dumps(line))
     dist.barrier()
+    close_comm()
     ctx.close()
     dist.destroy_process_group()

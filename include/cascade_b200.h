@@ -169,6 +169,13 @@ typedef struct csa_comm
     void* user;
 } csa_comm;
 
+/* A ready-made communicator for ranks that run on one box: the all-gather goes through a POSIX shared-memory object
+ * called `name` (the same string on every rank, unique to the job; at most 48 KB per rank and call). Every rank calls
+ * csa_comm_open_shm before the first build and csa_comm_close_shm after the last (one rank passes unlink_name = 1).
+ * Waits are bounded (two minutes): a missing rank makes the others fail with CSA_E_COMM. */
+int csa_comm_open_shm(const char* name, uint32_t rank, uint32_t world, uint32_t policy, csa_comm* out);
+void csa_comm_close_shm(csa_comm* comm, int unlink_name);
+
 /* Host-side plan of a sharded build, the same on every rank: from every rank's partition sizes over its share of the
  * positions (hist_all[world][p]) the partitions' global offsets part_off[p + 1], their owners owner[p] (policy 0: contiguous
  * blocks of partitions balanced by size, so a GPU owns one contiguous slice of the suffix array; policy 1: partition q goes

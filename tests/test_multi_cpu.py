@@ -95,3 +95,35 @@ def test_allgather_callback_between_two_gloo_ranks():
     assert res[0][1:] == res[1][1:], "the ranks must see the same sizes and make the same plan"
     want = [(i + 1) * (r + 1) for r in range(world) for i in range(16)]
     assert res[0][1] == want
+
+
+def _shm_worker(rank, world, name, q):
+    sys.path.insert(0, ROOT)
+    from cascade_b200 import multi
+    comm, close = multi.make_shm_comm(rank, world, name)
+    out = []
+    for rnd in range(200):                       # many rounds: the two payload buffers of a rank alternate
+        mine = np.full(5, rank * 1000 + rnd, np.uint64)
+        allv = np.zeros(5 * world, np.uint64)
+        assert comm.allgather(comm.user, mine.ctypes.data, allv.ctypes.data, mine.nbytes) == 0
+        out.append(allv.reshape(world, 5)[:, 0].tolist())
+    big = np.zeros(49 * 1024, np.uint8)          # beyond the per-rank payload limit: refused, not truncated
+    assert comm.allgather(comm.user, big.ctypes.data, big.ctypes.data, big.nbytes) != 0
+    q.put((rank, out))
+    close()
+
+
+def test_shared_memory_allgather_between_processes():
+    world, name = 3, f"/cascade_b200_test_{os.getpid()}"
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_shm_worker, args=(r, world, name, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    for rank, out in res:
+        for rnd, row in enumerate(out):
+            assert row == [r * 1000 + rnd for r in range(world)]

@@ -53,7 +53,10 @@ def _worker(rank, world, port, n, p, kind, policy, q):
     else:
         Th = api.gen_repeat_corpus_host(n, seed=1, base_docs=8, mean_doc=1024, mutate=0.002)
         T = torch.from_numpy(Th.view(np.int16)).cuda().view(torch.uint16)
-    comm, keep = multi.make_comm(rank, world, None, policy)
+    if kind == "zipf" and policy == 1:
+        comm, keep = multi.make_shm_comm(rank, world, f"/cascade_b200_t{port}", policy)      # the in-library shared-memory all-gather
+    else:
+        comm, keep = multi.make_comm(rank, world, None, policy)                              # the caller's torch.distributed all-gather
     for _ in range(2):      # twice: the second build reuses the peers' mappings
         out, segs, st = multi.build_sa_multi(ctx, comm, T, n, p)
     sl = out[:5 * sum(c for _, c in segs)].cpu().numpy()
@@ -63,6 +66,8 @@ def _worker(rank, world, port, n, p, kind, policy, q):
         ref = r[:5 * n].cpu().numpy()
     q.put((rank, segs, sl, ref, st.generations, st.peer_bytes))
     dist.barrier()
+    if callable(keep) and not hasattr(keep, "restype"):
+        keep()
     ctx.close()
     dist.destroy_process_group()
 
