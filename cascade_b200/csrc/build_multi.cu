@@ -150,7 +150,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     // ---- splitters: every rank samples the same positions of the same text, so all get the same splitters ----------
     constexpr u64 MAX_SAMPLES = 1u << 19;
     void* ws = nullptr;
-    const size_t pre_bytes = align_up256(2 * MAX_SAMPLES * 8) + align_up256(size_t(2) * p * 8) + align_up256(size_t(p) * 8) + 4096;
+    const size_t pre_bytes = align_up256(pick_splitters_scratch_bytes(MAX_SAMPLES)) + align_up256(size_t(2) * p * 8) + align_up256(size_t(p) * 8) + 4096;
     CSA_TRY(csa_arena(ctx, pre_bytes, &ws));
     // The partition ids of this rank's positions are made once, before the arena gets its final size, so they live apart.
     void* aux = nullptr;
@@ -162,7 +162,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     std::vector<u64> my_hist(p, 0);
     {
         Carver cv(ws, ctx->arena_bytes);
-        u64* samples_dev = cv.take<u64>(2 * MAX_SAMPLES);
+        u64* samples_dev = reinterpret_cast<u64*>(cv.take<u8>(align_up256(pick_splitters_scratch_bytes(MAX_SAMPLES))));
         u64* pivots_dev = cv.take<u64>(2 * u64(p));
         u64* hist = cv.take<u64>(p);
         if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "multi-GPU build: arena too small");
@@ -171,12 +171,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
             u64 n_samples = u64(32) * p * u64(bits_for(n));
             if(n_samples > MAX_SAMPLES) n_samples = MAX_SAMPLES;
             if(n_samples < 1024) n_samples = 1024;
-            CSA_TRY(csa_sample_kgrams(ctx, T, n, n_samples, seed, reinterpret_cast<uint64_t*>(samples_dev)));
-            std::vector<u64> samples(2 * n_samples);
-            CSA_CUDA(ctx, cudaMemcpyAsync(samples.data(), samples_dev, samples.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
-            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-            const int r = csa_select_pivots(reinterpret_cast<const uint64_t*>(samples.data()), n_samples, p, reinterpret_cast<uint64_t*>(pivots.data()), &p_eff);
-            if(r != CSA_OK) return csa_fail(ctx, r, "multi-GPU build: splitter selection failed");
+            CSA_TRY(pick_splitters(ctx, T, n, p, seed, n_samples, samples_dev, pick_splitters_scratch_bytes(MAX_SAMPLES), pivots.data(), &p_eff));
             if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
         }
         // ids and sizes of the partitions over this rank's positions
@@ -392,8 +387,9 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_CUDA(ctx, cudaMemcpyAsync(part_base, bases.data(), size_t(p_eff) * sizeof(u32*), cudaMemcpyHostToDevice, ctx->stream));
         CSA_CUDA(ctx, cudaMemsetAsync(cursor, 0, size_t(p_eff) * 8, ctx->stream));
         if(my_count) CSA_TRY(csa_scatter_by_pid(ctx, pid, my_first, my_count, p_eff, part_base, reinterpret_cast<uint64_t*>(cursor)));
-        for(u32 q = 0; q < p_eff; ++q)
+        for(u32 k = 0; k < p_eff; ++k)
         {
+            const u32 q = (k + me) % p_eff;     // every rank starts with another partition, so the copies of one moment go to different GPUs
             const u64 c = hist_all[size_t(me) * p_eff + q];
             if(c == 0) continue;
             const u32 o = owner[q];

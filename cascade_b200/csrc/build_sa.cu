@@ -38,7 +38,7 @@ Build_Layout layout_for(u64 n, u32 p)
     L.sa = align256(n * 4 + 64);
     L.sort_ws = align256(csa_sort_workspace_bytes(n));
     L.scratch = align256(div_up(n, RANK_TILE) * 3 * 4 + 256);
-    L.small = align256(size_t(p) * 8) * 3 + align256(size_t(2) * p * 8) + align256(size_t(1) << 24) + align256(65536 * 4) + 4096;   // hist, cursors, bases, pivots, samples, first-symbol table
+    L.small = align256(size_t(p) * 8) * 3 + align256(size_t(2) * p * 8) + align256(pick_splitters_scratch_bytes(size_t(1) << 19)) + align256(65536 * 4) + 4096;   // hist, cursors, bases, pivots, splitter scratch, first-symbol table
     L.upd = align256(cap * 8);     // (position, rank) updates of one step, applied to `isa` in address order
     L.total = 2 * L.keys + 2 * L.pos + L.head + L.isa + L.sa + L.sort_ws + L.scratch + L.small + L.upd + 4096;
     return L;
@@ -73,7 +73,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     u64* cursor = cv.take<u64>(p);
     u32** part_base = cv.take<u32*>(p);
     u64* pivots_dev = cv.take<u64>(2 * u64(p));
-    u64* samples_dev = cv.take<u64>(2 * MAX_SAMPLES);
+    void* samples_dev = cv.take<u8>(align256(pick_splitters_scratch_bytes(MAX_SAMPLES)));
     u64* upd = cv.take<u64>(L.upd / 8);
     u32* symbol_range = cv.take<u32>(65536);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "build: workspace too small");
@@ -87,12 +87,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
         u64 n_samples = u64(32) * p * u64(bits_for(n));
         if(n_samples > MAX_SAMPLES) n_samples = MAX_SAMPLES;
         if(n_samples < 1024) n_samples = 1024;
-        CSA_TRY(csa_sample_kgrams(ctx, T, n, n_samples, seed, reinterpret_cast<uint64_t*>(samples_dev)));
-        std::vector<u64> samples(2 * n_samples);
-        CSA_CUDA(ctx, cudaMemcpyAsync(samples.data(), samples_dev, samples.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
-        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        const int r = csa_select_pivots(reinterpret_cast<const uint64_t*>(samples.data()), n_samples, p, reinterpret_cast<uint64_t*>(pivots.data()), &p_eff);
-        if(r != CSA_OK) return csa_fail(ctx, r, "build: splitter selection failed");
+        CSA_TRY(pick_splitters(ctx, T, n, p, seed, n_samples, samples_dev, pick_splitters_scratch_bytes(MAX_SAMPLES), pivots.data(), &p_eff));
         if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
     }
     st.partitions = p_eff;

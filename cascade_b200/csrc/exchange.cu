@@ -130,27 +130,25 @@ struct Copy_Segments
 
 __global__ void __launch_bounds__(256) copy_segments_kernel(const Copy_Segments segs)
 {
-    for(u32 k = 0; k < segs.count; ++k)
+    // Blocks are dealt to the segments round robin, so that all destinations are written at the same time: if every GPU
+    // wrote to GPU 0 first, then to GPU 1, ... each destination's link would carry all traffic in turn while the others idle.
+    const u32 k = blockIdx.x % segs.count;
+    const u64 lane_block = blockIdx.x / segs.count, blocks = (gridDim.x - k + segs.count - 1) / segs.count;      // blocks that serve segment k
+    const u64 first = lane_block * blockDim.x + threadIdx.x, stride = blocks * blockDim.x;
+    const u64 words = segs.words[k];
+    const bool wide = ((reinterpret_cast<uintptr_t>(segs.dst[k]) | reinterpret_cast<uintptr_t>(segs.src[k])) & 15) == 0;
+    const u32* s1 = static_cast<const u32*>(segs.src[k]);
+    u32* d1 = static_cast<u32*>(segs.dst[k]);
+    if(wide)
     {
-        const u64 words = segs.words[k];
-        const bool wide = ((reinterpret_cast<uintptr_t>(segs.dst[k]) | reinterpret_cast<uintptr_t>(segs.src[k])) & 15) == 0;
-        if(wide)
-        {
-            const uint4* s4 = static_cast<const uint4*>(segs.src[k]);
-            uint4* d4 = static_cast<uint4*>(segs.dst[k]);
-            const u64 quads = words >> 2;
-            for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < quads; i += u64(gridDim.x) * blockDim.x) d4[i] = s4[i];
-            const u32* s1 = static_cast<const u32*>(segs.src[k]);
-            u32* d1 = static_cast<u32*>(segs.dst[k]);
-            for(u64 i = (quads << 2) + u64(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += u64(gridDim.x) * blockDim.x) d1[i] = s1[i];
-        }
-        else
-        {
-            const u32* s1 = static_cast<const u32*>(segs.src[k]);
-            u32* d1 = static_cast<u32*>(segs.dst[k]);
-            for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += u64(gridDim.x) * blockDim.x) d1[i] = s1[i];
-        }
+        const uint4* s4 = static_cast<const uint4*>(segs.src[k]);
+        uint4* d4 = static_cast<uint4*>(segs.dst[k]);
+        const u64 quads = words >> 2;
+        for(u64 i = first; i < quads; i += stride) d4[i] = s4[i];
+        for(u64 i = (quads << 2) + first; i < words; i += stride) d1[i] = s1[i];
     }
+    else
+        for(u64 i = first; i < words; i += stride) d1[i] = s1[i];
 }
 
 }   // namespace
@@ -169,7 +167,8 @@ int launch_copy_segments(csa_ctx* ctx, void* const* dst, const void* const* src,
     }
     if(segs.count == 0) return CSA_OK;
     const u64 want = div_up(total / 16 + 1, 256 * 4);
-    const unsigned blocks = unsigned(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
+    unsigned blocks = unsigned(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
+    if(blocks < segs.count) blocks = segs.count;        // every segment needs a block
     copy_segments_kernel<<<blocks, 256, 0, ctx->stream>>>(segs);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;

@@ -25,6 +25,11 @@ struct Slot_Map
     u64 base;
 };
 
+// Samples, orders and picks up to p-1 splitters on the device (ties finished on the host); the result equals
+// csa_sample_kgrams + csa_select_pivots. scratch holds pick_splitters_scratch_bytes(n_samples) bytes of device memory.
+size_t pick_splitters_scratch_bytes(u64 n_samples);
+int pick_splitters(csa_ctx* ctx, const u16* T, u64 n, u32 p, u64 seed, u64 n_samples, void* scratch, size_t scratch_bytes, u64* pivots_host, u32* p_out);
+
 // key[i] = the 4 symbols at position pos[i], packed most-significant first.
 int launch_keys_gen0(csa_ctx* ctx, const u16* T, const u32* pos, u64 count, u64* keys);
 

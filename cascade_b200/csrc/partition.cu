@@ -332,12 +332,32 @@ extern "C" int csa_select_pivots(const uint64_t* samples, uint64_t n_samples, ui
     if(p > CSA_MAX_PARTITIONS) return CSA_E_LIMIT;
     std::vector<std::pair<u64, u64>> s(n_samples);
     for(u64 i = 0; i < n_samples; ++i) s[i] = {samples[2 * i], samples[2 * i + 1]};
-    std::sort(s.begin(), s.end());
-    u32 made = 0;
+    // Only the p-1 order statistics at equal strides are needed: they are placed by nested selections (O(n log p))
+    // instead of a full sort.
+    std::vector<u64> want;
     for(u32 j = 1; j < p && n_samples > 0; ++j)
     {
         const u64 at = (u64(j) * n_samples) / p;
-        const auto& c = s[at == 0 ? 0 : at - 1];
+        want.push_back(at == 0 ? 0 : at - 1);
+    }
+    struct Job { u64 lo, hi; size_t a, b; };           // select want[a, b) inside s[lo, hi)
+    std::vector<Job> jobs;
+    if(!want.empty()) jobs.push_back({0, n_samples, 0, want.size()});
+    while(!jobs.empty())
+    {
+        const Job j = jobs.back();
+        jobs.pop_back();
+        if(j.a >= j.b || j.lo >= j.hi) continue;
+        const size_t m = (j.a + j.b) / 2;
+        const u64 r = want[m];
+        std::nth_element(s.begin() + j.lo, s.begin() + r, s.begin() + j.hi);
+        jobs.push_back({j.lo, r, j.a, m});
+        jobs.push_back({r + 1, j.hi, m + 1, j.b});
+    }
+    u32 made = 0;
+    for(size_t k = 0; k < want.size(); ++k)
+    {
+        const auto& c = s[want[k]];
         if(made > 0 && pivots[2 * (made - 1)] == c.first && pivots[2 * (made - 1) + 1] == c.second) continue;    // equal K-grams never split
         pivots[2 * made] = c.first;
         pivots[2 * made + 1] = c.second;
@@ -348,6 +368,12 @@ extern "C" int csa_select_pivots(const uint64_t* samples, uint64_t n_samples, ui
 }
 
 constexpr int PID_BLOCK = 256, PID_ITEMS = 16;
+
+__global__ void split_samples_kernel(const u64* __restrict__ samples, const u64 count, u64* __restrict__ hi, u32* __restrict__ idx)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) { hi[i] = samples[2 * i]; idx[i] = u32(i); }
+}
 
 // Optional per-device table for csa_partition_ids: for every first symbol the lowest and the highest partition that a
 // K-gram starting with it can fall into (low and high 16 bits). Installed by partition_install_symbol_ranges.
@@ -413,5 +439,56 @@ extern "C" int csa_scatter_by_pid(csa_ctx* ctx, const uint16_t* pid, uint64_t fi
     CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(pid, first, count, p, part_base, reinterpret_cast<u64*>(cursor));
     CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+// Samples K-grams, orders them (the first words by the device's radix sort, ties on the first word by their second words
+// on the host) and picks the splitters as csa_select_pivots does. scratch must hold pick_splitters_scratch_bytes(n_samples).
+size_t pick_splitters_scratch_bytes(u64 n_samples)
+{
+    return align_up256(n_samples * 16) + 2 * align_up256(n_samples * 8) + 2 * align_up256(n_samples * 4) + align_up256(csa_sort_workspace_bytes(n_samples)) + 1024;
+}
+
+int pick_splitters(csa_ctx* ctx, const u16* T, u64 n, u32 p, u64 seed, u64 n_samples, void* scratch, size_t scratch_bytes, u64* pivots_host, u32* p_out)
+{
+    Carver cv(scratch, scratch_bytes);
+    u64* samples = cv.take<u64>(2 * n_samples);
+    u64* hiA = cv.take<u64>(n_samples);
+    u64* hiB = cv.take<u64>(n_samples);
+    u32* ixA = cv.take<u32>(n_samples);
+    u32* ixB = cv.take<u32>(n_samples);
+    const size_t wsb = csa_sort_workspace_bytes(n_samples);
+    void* ws = cv.take<u8>(wsb);
+    if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "splitters: scratch too small");
+    CSA_TRY(csa_sample_kgrams(ctx, T, n, n_samples, seed, reinterpret_cast<uint64_t*>(samples)));
+    split_samples_kernel<<<unsigned(div_up(n_samples, 256)), 256, 0, ctx->stream>>>(samples, n_samples, hiA, ixA);
+    CSA_LAUNCH_CHECK(ctx);
+    int in_alt = 0;
+    CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(hiA), reinterpret_cast<uint64_t*>(hiB), ixA, ixB, 4, n_samples, 0, 64, ws, wsb, &in_alt));
+    std::vector<u64> all(2 * n_samples);
+    std::vector<u32> order(n_samples);
+    CSA_CUDA(ctx, cudaMemcpyAsync(all.data(), samples, all.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_CUDA(ctx, cudaMemcpyAsync(order.data(), in_alt ? ixB : ixA, order.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // runs of equal first words are put in order of their second words
+    for(u64 a = 0; a < n_samples; )
+    {
+        u64 b = a + 1;
+        while(b < n_samples && all[2 * u64(order[b])] == all[2 * u64(order[a])]) ++b;
+        if(b - a > 1) std::sort(order.begin() + a, order.begin() + b, [&](u32 x, u32 y) { return all[2 * u64(x) + 1] < all[2 * u64(y) + 1]; });
+        a = b;
+    }
+    u32 made = 0;
+    for(u32 j = 1; j < p && n_samples > 0; ++j)
+    {
+        const u64 at = (u64(j) * n_samples) / p;
+        const u64 k = order[at == 0 ? 0 : at - 1];
+        const u64 h = all[2 * k], l = all[2 * k + 1];
+        if(made > 0 && pivots_host[2 * (made - 1)] == h && pivots_host[2 * (made - 1) + 1] == l) continue;      // equal K-grams never split
+        pivots_host[2 * made] = h;
+        pivots_host[2 * made + 1] = l;
+        ++made;
+    }
+    *p_out = made + 1;
     return CSA_OK;
 }
