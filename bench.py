@@ -31,7 +31,7 @@ C2_MEAN_DOC = 1024
 C5_QUERIES = 4_000_000
 # DRAM read + write of one launch of the digit-pass kernel over 31.25 M records (the partition size of config 2), from the ncu
 # capture summarised in profiles/onesweep_pass_kernel__sort_31m_records.md; the algorithmic bytes of that launch are 750e6.
-ONESWEEP_TRAFFIC = {"bytes_per_launch": 728.4e6, "records_per_launch": 31_250_000, "algorithmic_bytes_per_launch": 750e6}
+ONESWEEP_TRAFFIC = 728.4e6
 
 
 def measured_peak_gbs():
@@ -217,7 +217,8 @@ def run_ours(args):
     achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort)", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                "traffic": ONESWEEP_TRAFFIC, "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value, "share_of_step": pm.value / (ms * args.steps)}
+                "traffic": ONESWEEP_TRAFFIC, "traffic_note": "bytes per launch over 31.25 M records (algorithmic: 750e6), ncu capture in profiles/",
+                "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value, "share_of_step": pm.value / (ms * args.steps)}
 
     # ---- end to end through the host-buffer entry point --------------------------------------------------------------
     e2e = None
