@@ -340,6 +340,51 @@ def run_micro_sort(args):
     ctx.close()
 
 
+def run_repeat(args):
+    """BASELINE config 3, the worst case for prefix doubling: 4096 base documents (geometric, mean 2048, Zipf tokens), then
+    copies of random base documents with 0.1 % of their tokens replaced, 1e9 tokens in all. Reports the build alone."""
+    import torch
+    from cascade_b200 import api
+    n = args.tokens if args.tokens != C2_TOKENS else 1_000_000_000
+    ctx = api.Context(0)
+    t0 = time.perf_counter()
+    Th = api.gen_repeat_corpus_host(n, seed=0, base_docs=4096, mean_doc=2048, mutate=0.001)
+    T = torch.from_numpy(Th.view(np.int16)).cuda().view(torch.uint16)
+    gen_s = time.perf_counter() - t0
+    out = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8, device="cuda")
+    for _ in range(max(1, args.warmup - 2)):
+        api.build_sa(ctx, T, n, C2_PARTITIONS, out=out)
+    ms, st = [], None
+    for _ in range(args.steps):
+        _, st = api.build_sa(ctx, T, n, C2_PARTITIONS, out=out)
+        ms.append(st.ms_total)
+    # sampled order check on the device: neighbours compared on their first 64 symbols (undecided pairs count as consistent)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    r = torch.randint(0, n - 1, (1 << 20,), device="cuda", generator=g)
+    b = out[:5 * n].view(n, 5)
+    def entry(idx):
+        e = b[idx].to(torch.int64)
+        return e[:, 0] | (e[:, 1] << 8) | (e[:, 2] << 16) | (e[:, 3] << 24) | (e[:, 4] << 32)
+    pa, pb = entry(r), entry(r + 1)
+    Tl = T.view(torch.int16)
+    undecided = torch.ones_like(pa, dtype=torch.bool)
+    bad = torch.zeros_like(undecided)
+    for k in range(64):
+        xa = torch.where(pa + k < n, Tl[torch.clamp(pa + k, max=n)].to(torch.int64) & 0xFFFF, torch.full_like(pa, -1))
+        xb = torch.where(pb + k < n, Tl[torch.clamp(pb + k, max=n)].to(torch.int64) & 0xFFFF, torch.full_like(pb, -1))
+        bad |= undecided & (xa > xb)
+        undecided &= (xa == xb) & (xa >= 0)
+    m = sum(ms) / len(ms)
+    print(json.dumps({"metric": METRIC, "value": n / (m * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "ms_per_step": m,
+                      "config": {"workload": "repetitive corpus, BASELINE config 3", "tokens": n, "base_docs": 4096, "mean_doc": 2048, "mutate": 0.001,
+                                 "partitions": C2_PARTITIONS}, "generations": st.generations,
+                      "active_per_generation": [int(x) for x in st.active_per_gen[:st.generations]],
+                      "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
+                      "sort_passes": st.sort_passes, "order_violations_in_1M_sampled_neighbours": int(bad.sum().item()),
+                      "host_generation_s": gen_s}))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -352,6 +397,8 @@ def main():
     ap.add_argument("--ref-sample", type=int, default=1 << 24)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--workload", default="zipf", choices=["zipf", "repeat"],
+                    help="zipf: BASELINE config 2; repeat: config 3 (1e9 tokens of near-duplicate documents, build only)")
     ap.add_argument("--micro", default=None, choices=["sort"], help="time one kernel family alone instead of the build")
     ap.add_argument("--records", type=int, default=31_250_000)
     ap.add_argument("--bits", type=int, default=64)
@@ -359,6 +406,8 @@ def main():
     args = ap.parse_args()
     if args.micro == "sort":
         return run_micro_sort(args)
+    if args.workload == "repeat":
+        return run_repeat(args)
     if args.impl == "reference":
         run_reference(args)
     else:

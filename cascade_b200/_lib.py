@@ -30,7 +30,7 @@ class Comm(ctypes.Structure):
 
 
 class Index(ctypes.Structure):
-    _fields_ = [("text", c_vp), ("sa40", c_vp), ("table", c_vp), ("n", c_u64), ("stride", c_u64)]
+    _fields_ = [("text", c_vp), ("sa40", c_vp), ("table", c_vp), ("n", c_u64), ("stride", c_u64), ("sa_entries", c_u64), ("sa_first", c_u64)]
 
 
 _SIGS = {
@@ -60,6 +60,8 @@ _SIGS = {
     "csa_plan_shards": (c_int, [c_vp, c_u32, c_u32, c_u32, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "csa_build_sa_multi": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, c_vp, c_vp, ctypes.POINTER(c_u32), ctypes.POINTER(BuildStats)]),
     "csa_table_build": (c_int, [c_vp, c_vp, c_u64, c_vp, c_u64, c_vp]),
+    "csa_table_build_slice": (c_int, [c_vp, c_vp, c_u64, c_vp, c_u64, c_u64, c_vp]),
+    "csa_locate_window": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp]),
     "csa_find": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp]),
     "csa_locate": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp, c_vp]),
     "csa_certify": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp, c_vp]),

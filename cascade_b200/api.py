@@ -205,18 +205,28 @@ def build_sa_host(ctx, text_host, n, p=1, seed=0, out=None):
 class SuffixIndex:
     """Text, suffix array and sample table of one index on a device (the reference's Suffix_Index + Sample_Table)."""
 
-    def __init__(self, ctx, text_dev, sa40_dev, n, stride=32, table=None):
-        """sa40_dev may also be a pinned host tensor: the device then reads the suffix array over PCIe."""
+    def __init__(self, ctx, text_dev, sa40_dev, n, stride=32, table=None, sa_first=0, sa_entries=None):
+        """sa40_dev may also be a pinned host tensor: the device then reads the suffix array over PCIe. With sa_entries
+        given, sa40_dev holds only the slice [sa_first, sa_first + sa_entries) of the suffix array (one shard of a sharded
+        index): find() then returns per-slice counts that add up over the shards, see ShardedIndex in multi.py."""
         self.ctx, self.text, self.sa40, self.n, self.stride = ctx, text_dev, sa40_dev, n, stride
-        entries = (n + stride - 1) // stride
+        self.sa_first, self.sa_entries = sa_first, (n if sa_entries is None else sa_entries)
+        entries = max(1, (self.sa_entries + stride - 1) // stride)
         if table is not None:
             self.table = table
         else:
             self.table = torch.zeros(2 * entries, dtype=torch.int64, device=text_dev.device)
             torch.cuda.synchronize(text_dev.device)
-            ctx.check(ctx.L.csa_table_build(ctx.h, text_dev.data_ptr(), n, sa40_dev.data_ptr(), stride, self.table.data_ptr()))
+            ctx.check(ctx.L.csa_table_build_slice(ctx.h, text_dev.data_ptr(), n, sa40_dev.data_ptr(), self.sa_entries, stride, self.table.data_ptr()))
             ctx.sync()
-        self.c = Index(text_dev.data_ptr(), sa40_dev.data_ptr(), self.table.data_ptr(), n, stride)
+        self.c = Index(text_dev.data_ptr(), sa40_dev.data_ptr(), self.table.data_ptr(), n, stride, self.sa_entries, sa_first)
+
+    def locate_window(self, itv_global_dev, q, max_pos, rows):
+        """Adds this slice's share of the positions of global intervals to rows (a zero-initialised q x max_pos int64 tensor)."""
+        torch.cuda.synchronize(self.text.device)
+        self.ctx.check(self.ctx.L.csa_locate_window(self.ctx.h, ctypes.byref(self.c), itv_global_dev.data_ptr(), q, max_pos, rows.data_ptr()))
+        self.ctx.sync()
+        return rows
 
     def find(self, off_dev, sym_dev, q):
         itv = torch.zeros(2 * q, dtype=torch.int64, device=self.text.device)

@@ -39,9 +39,10 @@ __global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, co
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
     if(i >= q) return;
     const u64 n = idx.n, stride = idx.stride;
+    const u64 ne = idx.sa_entries ? idx.sa_entries : idx.n;      // entries of the suffix array (a slice of it in a sharded index)
     const u64 m = off[i + 1] - off[i];
     const u16* const P = sym + (off[i] - off[0]);
-    if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = n; return; }
+    if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = ne; return; }
 
     // The pattern's first min(m, K) symbols, packed like a table key, and the mask of those symbols.
     const u32 mm = m < CSA_K ? u32(m) : u32(CSA_K);
@@ -54,7 +55,7 @@ __global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, co
     const u64 mask_h = mm >= 4 ? ~0ull : ~0ull << (64 - 16 * mm);
     const u64 mask_l = mm <= 4 ? 0ull : (mm == 8 ? ~0ull : ~0ull << (64 - 16 * (mm - 4)));
 
-    const u64 J = (n + stride - 1) / stride;
+    const u64 J = (ne + stride - 1) / stride;
     const ulonglong2* const tab = reinterpret_cast<const ulonglong2*>(idx.table);
     // a = table keys (masked) smaller than the pattern's; b = those not greater.
     u64 a, b;
@@ -82,7 +83,7 @@ __global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, co
     // Sampled rank j * stride carries table key j. Ranks up to (a-1) stride are smaller than the pattern; ranks from
     // b stride on are greater.
     const u64 L = (a == 0) ? 0 : (a - 1) * stride + 1;
-    const u64 R = (b >= J) ? n : b * stride;
+    const u64 R = (b >= J) ? ne : b * stride;
     u64 lo_last = R, hi_first = L;
     if(m <= CSA_K)
     {
@@ -137,6 +138,21 @@ __global__ void locate_packed_kernel(const u8* __restrict__ sa40, const u64* __r
     const u64 c = (hi - lo < max_pos) ? hi - lo : max_pos;
     const u64 o = pos_off[w];
     for(u64 k = lane_id(); k < c; k += 32) pos[o + k] = sa40_load(sa40, lo + k);
+}
+
+// Sharded locate: the columns of a global interval's row that fall into this slice of the suffix array.
+__global__ void locate_window_kernel(const u8* __restrict__ sa40, const u64 sa_first, const u64 sa_entries, const u64* __restrict__ itv, const u64 q,
+                                     const u32 max_pos, u64* __restrict__ pos)
+{
+    const u64 w = (u64(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if(w >= q) return;
+    const u64 lo = itv[2 * w], hi = itv[2 * w + 1];
+    const u64 c = (hi - lo < max_pos) ? hi - lo : max_pos;
+    for(u64 k = lane_id(); k < c; k += 32)
+    {
+        const u64 r = lo + k;
+        if(r >= sa_first && r < sa_first + sa_entries) pos[w * max_pos + k] = sa40_load(sa40, r - sa_first);
+    }
 }
 
 __global__ void counts_kernel(const u64* __restrict__ itv, const u64 q, const u32 max_pos, u32* __restrict__ cnt)
@@ -264,6 +280,32 @@ extern "C" int csa_table_build(csa_ctx* ctx, const uint16_t* text, uint64_t n, c
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
     const u64 entries = div_up(n, stride);
     table_build_kernel<<<unsigned(div_up(entries, 256)), 256, 0, ctx->stream>>>(text, sa40, n, stride, entries, reinterpret_cast<u64*>(table));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_table_build_slice(csa_ctx* ctx, const uint16_t* text, uint64_t n, const uint8_t* sa40_slice, uint64_t sa_entries, uint64_t stride,
+                                     uint64_t* table)
+{
+    if(!ctx || !text || !sa40_slice || !table || n == 0 || stride == 0 || sa_entries > n) return csa_fail(ctx, CSA_E_INVALID, "csa_table_build_slice: bad argument");
+    if(reinterpret_cast<uintptr_t>(sa40_slice) & 3) return csa_fail(ctx, CSA_E_INVALID, "csa_table_build_slice: the slice must start 4-byte aligned");
+    if(sa_entries == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const u64 entries = div_up(sa_entries, stride);
+    table_build_kernel<<<unsigned(div_up(entries, 256)), 256, 0, ctx->stream>>>(text, sa40_slice, n, stride, entries, reinterpret_cast<u64*>(table));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_locate_window(csa_ctx* ctx, const csa_index* index, const uint64_t* itv, uint64_t q, uint32_t max_pos, uint64_t* pos)
+{
+    CSA_TRY(check_index(ctx, index));
+    if(q == 0) return CSA_OK;
+    if(!itv || !pos || max_pos == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_locate_window: bad argument");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const u64 ne = index->sa_entries ? index->sa_entries : index->n;
+    locate_window_kernel<<<unsigned(div_up(q * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, index->sa_first, ne, reinterpret_cast<const u64*>(itv), q, max_pos,
+                                                                                 reinterpret_cast<u64*>(pos));
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }

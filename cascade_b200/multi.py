@@ -95,6 +95,31 @@ def build_sa_multi(ctx, comm, text_dev, n, p, seed=0, out=None, capacity=None):
     return out, segs, st
 
 
+class ShardedIndex:
+    """A query index sharded by suffix-array range over the ranks of a process group: every rank holds the whole text, the
+    slice [first, first + count) of the 5-byte suffix array and a sample table over its slice. A batch is searched by every
+    rank in its slice; the per-slice counts add up to the global interval (one all-reduce of 16 bytes per query), and every
+    rank contributes the positions whose ranks it holds (one all-reduce of the position rows)."""
+
+    def __init__(self, ctx, text_dev, sa40_slice_dev, n, first, count, stride=32):
+        self.local = api.SuffixIndex(ctx, text_dev, sa40_slice_dev, n, stride, sa_first=first, sa_entries=count)
+        self.n, self.first, self.count = n, first, count
+
+    def find(self, off_dev, sym_dev, q, reduce=True):
+        itv = self.local.find(off_dev, sym_dev, q)
+        if reduce and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(itv, op=dist.ReduceOp.SUM)
+        return itv
+
+    def locate(self, itv_global_dev, q, max_pos=100, reduce=True):
+        rows = torch.zeros(q * max_pos, dtype=torch.int64, device=itv_global_dev.device)
+        self.local.locate_window(itv_global_dev, q, max_pos, rows)
+        if reduce and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(rows, op=dist.ReduceOp.SUM)
+        cnt = torch.clamp(itv_global_dev[1::2] - itv_global_dev[0::2], max=max_pos).to(torch.int32)
+        return rows.view(q, max_pos), cnt
+
+
 def _max_over_ranks(x, device):
     t = torch.tensor([x], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)

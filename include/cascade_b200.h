@@ -205,8 +205,10 @@ typedef struct csa_index
     const uint16_t* text;   /* n symbols + CSA_TEXT_PAD zero symbols, device memory */
     const uint8_t* sa40;    /* 5 n bytes + CSA_SA_PAD_BYTES; device memory, or pinned host memory mapped for the device */
     const uint64_t* table;  /* sample table: 2 words per sampled suffix, ceil(n / stride) entries; device memory */
-    uint64_t n;
+    uint64_t n;             /* symbols of the text */
     uint64_t stride;
+    uint64_t sa_entries;    /* entries of sa40: 0 or n for the whole suffix array, fewer for a slice of it (a shard) */
+    uint64_t sa_first;      /* global rank of the slice's first entry */
 } csa_index;
 
 /* table_dev[j] = the K-gram of suffix SA[j * stride], zero-padded past the text's end, for j < ceil(n / stride).
@@ -223,6 +225,17 @@ int csa_find(csa_ctx* ctx, const csa_index* index, const uint64_t* off_dev, cons
  * (include/query-file.hpp:18-19); this is the definition its intervals imply. */
 int csa_locate(csa_ctx* ctx, const csa_index* index, const uint64_t* itv_dev, uint64_t q, uint32_t max_pos,
                uint64_t* pos_dev, uint32_t* cnt_dev);
+/* Sharded indexes: when sa40 holds the slice [sa_first, sa_first + sa_entries) of the suffix array (the table built over that
+ * slice with csa_table_build, passing the slice and its entry count as n_entries), csa_find returns for every query the
+ * number of the slice's suffixes that are smaller than the pattern (lo) and the number that are not greater (hi). Summed
+ * over the slices of all shards these are the global interval. csa_locate_window then writes, for a GLOBAL interval, the
+ * positions whose global ranks lie in this slice into their columns of the q x max_pos rows (column k holds rank lo + k) and
+ * leaves the other columns untouched; rows that all shards write into, starting from zeros, add up to the full rows.
+ * The reference has one index on one GPU; sharding by SA range is this engine's. */
+int csa_table_build_slice(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint8_t* sa40_slice_dev, uint64_t sa_entries,
+                          uint64_t stride, uint64_t* table_dev);
+int csa_locate_window(csa_ctx* ctx, const csa_index* index, const uint64_t* itv_global_dev, uint64_t q, uint32_t max_pos,
+                      uint64_t* pos_dev);
 /* Interval certificate of ref::certify (include/CPU_Reference.hpp:79-101) for every query: result_dev[0] = number
  * of failing queries, result_dev[1] = first failing query (or ~0). Replaces certify_kernel (src/Query_Engine.cu:665-686). */
 int csa_certify(csa_ctx* ctx, const csa_index* index, const uint64_t* off_dev, const uint16_t* sym_dev, uint64_t q,

@@ -143,3 +143,35 @@ def test_suffix_array_in_pinned_host_memory(ctx, oracle):
     pn = pos.cpu().numpy().view(np.uint64)
     for i in range(0, 500, 7):
         assert np.array_equal(pn[i, :wc[i]], wp[i, :wc[i]])
+
+
+def test_index_sharded_by_suffix_array_range(ctx, oracle):
+    """Three slices of one suffix array, each with its own sample table: the per-slice counts add up to the oracle's interval
+    and the slices' position windows add up to the oracle's positions."""
+    from cascade_b200 import api, multi
+    rng = np.random.default_rng(9)
+    n = 150000
+    T = rng.integers(0, 30, n).astype(np.uint16)
+    T[rng.integers(0, 100, n) == 0] = 0xFFFF
+    sa = oracle.build_sa40(T)
+    Tp = np.concatenate([T, np.zeros(api.TEXT_PAD, np.uint16)])
+    td = torch.from_numpy(Tp.view(np.int16)).cuda().view(torch.uint16)
+    cuts = [0, 40000, 40064, 100032, n]          # slice starts are multiples of 4 entries (4-byte aligned bytes); one tiny slice
+    off, sym, _ = conftest.fixture_queries(T, rng, 600)
+    o, s_ = _dev(off, sym)
+    want = oracle.find_batch(T, sa, off, sym)
+    total = torch.zeros(1200, dtype=torch.int64, device="cuda")
+    shards = []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        sl = np.concatenate([sa[5 * a:5 * b], np.zeros(128, np.uint8)])
+        sh = multi.ShardedIndex(ctx, td, torch.from_numpy(sl).cuda(), n, a, b - a, stride=32)
+        shards.append(sh)
+        total += sh.find(o, s_, 600, reduce=False)
+    assert np.array_equal(total.cpu().numpy().view(np.uint64), want)
+    rows = torch.zeros(600 * 100, dtype=torch.int64, device="cuda")
+    for sh in shards:
+        sh.local.locate_window(total, 600, 100, rows)
+    wp, wc = oracle.locate_batch(sa, want, 100)
+    rn = rows.view(600, 100).cpu().numpy().view(np.uint64)
+    for i in range(600):
+        assert np.array_equal(rn[i, :wc[i]], wp[i, :wc[i]]), i
