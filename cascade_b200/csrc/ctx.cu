@@ -78,7 +78,12 @@ int csa_arena(csa_ctx* ctx, size_t bytes, void** out)
     {
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         if(ctx->arena) { cudaFree(ctx->arena); ctx->arena = nullptr; ctx->arena_bytes = 0; }
-        const cudaError_t e = cudaMalloc(&ctx->arena, bytes);
+        // A little head-room, so that a slightly larger request later (another deal of the partitions, say) does not regrow the
+        // arena: other GPUs may still hold a mapping of it, and its memory is not given back before they let go.
+        const size_t want = bytes + bytes / 16;
+        cudaError_t e = cudaMalloc(&ctx->arena, want);
+        if(e == cudaSuccess) bytes = want;
+        else { cudaGetLastError(); e = cudaMalloc(&ctx->arena, bytes); }
         if(e != cudaSuccess)
         {
             cudaGetLastError();

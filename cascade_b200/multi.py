@@ -173,14 +173,17 @@ def bench(args, rank, world, local):
     if count > 1:
         g = torch.Generator(device=dev).manual_seed(rank)
         r = torch.randint(0, count - 1, (min(count - 1, 1 << 20),), device=dev, generator=g)
-        b = out[:5 * count].view(count, 5).to(torch.int64)
-        posn = b[:, 0] | (b[:, 1] << 8) | (b[:, 2] << 16) | (b[:, 3] << 24) | (b[:, 4] << 32)
-        Tl = T.view(torch.int16).to(torch.int64) & 0xFFFF
+        e = out[:5 * count].view(count, 5)
+        def entry(ix):
+            v = e[ix].to(torch.int64)
+            return v[:, 0] | (v[:, 1] << 8) | (v[:, 2] << 16) | (v[:, 3] << 24) | (v[:, 4] << 32)
+        Ts = T.view(torch.int16)
         def key4(ps):
-            return (Tl[ps] << 48) | (Tl[ps + 1] << 32) | (Tl[ps + 2] << 16) | Tl[ps + 3]
-        a, c = key4(posn[r]), key4(posn[r + 1])
+            return sum((Ts[ps + k].to(torch.int64) & 0xFFFF) << (48 - 16 * k) for k in range(4))
+        a, c = key4(entry(r)), key4(entry(r + 1))
         ok = float(bool(((a >> 1) <= (c >> 1)).all()))      # compare as unsigned through a 63-bit view
-        del b, posn, Tl
+        del a, c, e, Ts
+    torch.cuda.empty_cache()
     ok_all = _sum_over_ranks(ok, dev) == world and total == n
 
     # end to end: pinned host text in, this rank's slice of the 5-byte array out
@@ -205,6 +208,35 @@ def bench(args, rank, world, local):
         e_ms = 1e3 * sum(ts) / len(ts)
         e2e = {"value": n / (e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": 2 * n * world, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms,
                "api": "csa_build_sa_multi between a pinned host text copy in and a pinned copy of the rank's sa40 slice out"}
+    # ---- batched queries on the index sharded by suffix-array range (BASELINE config 5 over N GPUs) ---------------------
+    query = None
+    if args.queries > 0:
+        comm0, close0 = make_shm_comm(rank, world, name[0] + "_q", policy=0)     # contiguous blocks: one slice of the array per rank
+        sl, segs0, _ = build_sa_multi(ctx, comm0, T, n, p, out=out, capacity=cap)
+        close0()
+        first0, count0 = (segs0[0][0], sum(c for _, c in segs0)) if segs0 else (0, 0)
+        sh = ShardedIndex(ctx, T, sl, n, first0, count0, stride=32)
+        q = args.queries
+        qa = [None, None, None, None]
+        if rank == 0:
+            tn = T.cpu().view(torch.int16).numpy().view(np.uint16)
+            oa, sa_ = api.gen_queries("substring", tn, n, q // 2, seed=1)
+            ob, sb = api.gen_queries("random", None, 0, q - q // 2, seed=2)
+            qa = [np.concatenate([oa, ob[1:] + oa[-1]]), np.concatenate([sa_, sb, np.zeros(8, np.uint16)])]
+        objs = [qa[0], qa[1]]
+        dist.broadcast_object_list(objs, src=0)
+        od = torch.from_numpy(objs[0].view(np.int64)).to(dev)
+        sd = torch.from_numpy(objs[1].view(np.int16)).to(dev)
+        for _ in range(2):
+            itv = sh.find(od, sd, q)
+        dist.barrier(); torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        itv = sh.find(od, sd, q)
+        rows, cnt = sh.locate(itv, q, 100)
+        torch.cuda.synchronize()
+        dq = _max_over_ranks(time.perf_counter() - t0, dev)
+        query = {"value": q / dq, "unit": f"queries/s (count + locate <= 100, suffix array sharded by range over {world} GPUs, text replicated)",
+                 "queries": q, "counts_hash": f"{api.counts_hash(itv.cpu().numpy().view(np.uint64)):016x}", "positions": int(cnt.sum().item())}
     launches_all = _sum_over_ranks(launches, dev)
     peer_all = _sum_over_ranks(peer, dev)
     if rank == 0:
@@ -217,6 +249,7 @@ def bench(args, rank, world, local):
                 "nvlink": {"peer_bytes_per_step_all_ranks": peer_all / args.steps, "generations": st.generations,
                            "note": "positions to partition owners + ranks to and from position owners, 4 bytes each, (G-1)/G of them remote"},
                 "phases_ms_rank0": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
+                "query": query,
                 "verified": {"slices_add_up_to_n": total == n, "sampled_neighbours_in_order": ok_all}}
         print(json.dumps(line))
     dist.barrier()
