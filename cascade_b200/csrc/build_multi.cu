@@ -13,6 +13,7 @@
 // The ranks meet at host barriers (the caller's all-gather) between the steps. No device-side waits on peers.
 #include "common.cuh"
 #include "part.cuh"
+#include "sort.cuh"
 
 #include <chrono>
 #include <cstdlib>
@@ -143,7 +144,12 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     CSA_CUDA(ctx, cudaEventRecord(ev[0], ctx->stream));
 
     // Position shards: equal, a multiple of 8 positions so that text windows start 16-byte aligned.
-    const u64 shard = ((div_up(n, G) + 7) / 8) * 8;
+    // They are also whole address buckets (the top 8 bits of a position), so that a list of updates ordered by bucket is a
+    // sequence of per-owner runs.
+    const int position_bits = bits_for(n - 1);
+    const int bucket_shift = position_bits > 8 ? position_bits - 8 : 0;
+    const u64 shard_unit = (u64(1) << bucket_shift) > 8 ? (u64(1) << bucket_shift) : 8;
+    const u64 shard = div_up(div_up(n, G), shard_unit) * shard_unit;
     const u64 my_first = u64(me) * shard < n ? u64(me) * shard : n;
     const u64 my_count = (my_first + shard <= n) ? shard : n - my_first;
 
@@ -309,26 +315,56 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     // Routes `count` (position << 32 | rank) updates from `list` to the positions' owners and applies what arrives here.
     auto route_updates = [&](u64* list, u64 count, u64* bucketed) -> int
     {
-        CSA_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, G * 8, ctx->stream));
-        CSA_TRY(launch_count_owners(ctx, nullptr, list, count, 0, ~0ull, shard, G, counts_dev));
-        CSA_TRY(exchange_counts());
+        // One keys-only digit pass orders the updates by the top 8 bits of their position. Shards are whole buckets, so the
+        // ordered list is one run per destination GPU, and inside a run the positions sweep the destination's shard once:
+        // the destination applies each run as it arrived, with L2-sized locality and no pass of its own.
+        int in_alt = 0;
+        u64 hist_host[256];
+        std::memset(hist_host, 0, sizeof(hist_host));
+        if(count > 1)
+        {
+            CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(list), reinterpret_cast<uint64_t*>(bucketed), nullptr, nullptr, 4, count,
+                                   32 + bucket_shift, 32 + position_bits, sort_ws, L.sort_ws, &in_alt));
+            CSA_CUDA(ctx, cudaMemcpyAsync(hist_host, sort_workspace_histograms(sort_ws, L.sort_ws, count), sizeof(hist_host), cudaMemcpyDeviceToHost, ctx->stream));
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        }
+        const u64* ordered = in_alt ? bucketed : list;
+        u64 mine_c[CSA_MAX_GPUS];
+        for(u32 g = 0; g < G; ++g) mine_c[g] = 0;
+        if(count == 1)
+        {
+            u64 one = 0;
+            CSA_CUDA(ctx, cudaMemcpyAsync(&one, list, 8, cudaMemcpyDeviceToHost, ctx->stream));
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            mine_c[(one >> 32) / shard] = 1;
+        }
+        else
+        {
+            const u64 buckets_per_shard = shard >> bucket_shift;
+            for(u32 bkt = 0; bkt < 256; ++bkt)
+            {
+                if(hist_host[bkt] == 0) continue;
+                const u64 g = bucket_shift ? bkt / buckets_per_shard : (u64(bkt) / shard);
+                if(g >= G) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: an update's position lies outside the text");
+                mine_c[g] += hist_host[bkt];
+            }
+        }
+        CSA_TRY(gather(ctx, comm, mine_c, C.data(), G * 8));
         if(inbox_total() > shard) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: more rank updates than positions in a shard");
-        CSA_TRY(launch_bucket_updates(ctx, list, count, shard, G, cursor_dev, bucketed));
         {
             void* dsts[CSA_MAX_GPUS]; const void* srcs[CSA_MAX_GPUS]; u64 bytes[CSA_MAX_GPUS];
             for(u32 d = 0; d < G; ++d)
             {
                 const u64 c = C[size_t(me) * G + d];
                 dsts[d] = reinterpret_cast<u64*>(peer_arena[d] + peers[d].off_xin) + in_off(me, d);
-                srcs[d] = bucketed + out_off(me, d);
+                srcs[d] = ordered + out_off(me, d);
                 bytes[d] = c * 8;
                 if(d != me) route_bytes += c * 8;
             }
             CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
         CSA_TRY(barrier(ctx, comm));                                   // every inbox is complete
-        // `list` has been bucketed and sent, so its buffer serves the address-ordering pass of what arrived
-        CSA_TRY(apply_updates_in_address_order(ctx, isa, reinterpret_cast<u64*>(xin), const_cast<u64*>(list), inbox_total(), bits_for(shard - 1), sort_ws, L.sort_ws));
+        CSA_TRY(launch_apply_updates(ctx, isa, reinterpret_cast<const u64*>(xin), inbox_total(), u64(me) * shard));
         return CSA_OK;
     };
     // Builds keys[k] = head[k] << sec_bits | secondary(pos[k] + h) for the active list, fetching the ranks from their owners.

@@ -97,10 +97,10 @@ __global__ void serve_requests_kernel(const u32* __restrict__ isa_local, const u
     if(i < count) resp[i] = isa_local[req[i]];
 }
 
-__global__ void apply_updates_kernel(u32* __restrict__ isa_local, const u64* __restrict__ upd, const u64 count)
+__global__ void apply_updates_kernel(u32* __restrict__ isa_local, const u64* __restrict__ upd, const u64 count, const u64 first_position)
 {
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    if(i < count) { const u64 u = upd[i]; isa_local[u32(u >> 32)] = u32(u); }
+    if(i < count) { const u64 u = upd[i]; isa_local[(u >> 32) - first_position] = u32(u); }
 }
 
 __global__ void keys_init_kernel(const u32* __restrict__ head, const u32* __restrict__ pos, const u64 count, const u64 n, const u64 h, const int sec_bits,
@@ -207,10 +207,10 @@ int launch_serve_requests(csa_ctx* ctx, const u32* isa_local, const u32* req, u6
     return CSA_OK;
 }
 
-int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count)
+int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count, u64 first_position)
 {
     if(count == 0) return CSA_OK;
-    apply_updates_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(isa_local, upd, count);
+    apply_updates_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(isa_local, upd, count, first_position);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
@@ -244,5 +244,5 @@ int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* 
         CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(upd), reinterpret_cast<uint64_t*>(alt), nullptr, nullptr, 4, count, begin, top, sort_ws, sort_ws_bytes, &in_alt));
         list = in_alt ? alt : upd;
     }
-    return launch_apply_updates(ctx, isa_local, list, count);
+    return launch_apply_updates(ctx, isa_local, list, count, 0);
 }

@@ -61,8 +61,8 @@ int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard
 int launch_copy_segments(csa_ctx* ctx, void* const* dst, const void* const* src, const u64* bytes, u32 count);
 // resp[i] = isa_local[req[i]]
 int launch_serve_requests(csa_ctx* ctx, const u32* isa_local, const u32* req, u64 count, u32* resp);
-// isa_local[high 32 bits] = low 32 bits
-int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count);
+// isa_local[high 32 bits - first_position] = low 32 bits
+int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count, u64 first_position = 0);
 // The same after one keys-only radix pass on the top bits of the index (positions_bits of them are in use), so that the
 // writes of one stretch of the list fall into one L2-sized stretch of the array. alt holds count records; sort_ws is a
 // sort workspace. Short lists are applied directly.

@@ -400,6 +400,17 @@ extern "C" int csa_debug_set(int key, uint64_t value)
     return CSA_E_INVALID;
 }
 
+// Device address of the digit histograms ([pass][RADIX] 64-bit counts) that the last csa_sort_pairs of n records left in
+// its workspace (the same carving as in csa_sort_pairs).
+const u64* sort_workspace_histograms(void* workspace, size_t workspace_bytes, u64 n)
+{
+    Carver cv(workspace, workspace_bytes);
+    const u64 tiles_max = div_up(n < PORTION ? n : PORTION, PASS_TILE) + 1;
+    cv.take<u32>(tiles_max * RADIX);
+    cv.take<u32>(64);
+    return cv.take<u64>(u64(8) * RADIX);
+}
+
 size_t csa_sort_workspace_bytes(uint64_t n)
 {
     const u64 portions = n == 0 ? 1 : div_up(n, PORTION);
