@@ -474,7 +474,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     u64 total_active = 0;
     for(u32 g = 0; g < G; ++g) total_active += counts[g];
     st.active_after_gen0 = total_active;
-    if(debug) std::fprintf(stderr, "[csa %u/%u] n=%llu local=%llu partitions=%u active after generation 0: %llu (all ranks %llu)\n", me, G, n, n_local,
+    if(debug) std::fprintf(stderr, "[csa %u/%u] n=%llu local=%llu partitions=%u active after generation 0: %llu (all ranks %llu)\n", me, G, (unsigned long long)n, n_local,
                            p_eff, active, total_active);
 
     // ---- doubling generations: all ranks run the same number of them ------------------------------------------------

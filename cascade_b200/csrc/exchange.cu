@@ -177,8 +177,8 @@ int launch_copy_segments(csa_ctx* ctx, void* const* dst, const void* const* src,
 int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* counts)
 {
     if(count == 0) return CSA_OK;
-    if(packed) count_owners_kernel<true><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, packed, count, h, n, shard, gpus, counts);
-    else count_owners_kernel<false><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, packed, count, h, n, shard, gpus, counts);
+    (void)packed;
+    count_owners_kernel<false><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, packed, count, h, n, shard, gpus, counts);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
@@ -187,14 +187,6 @@ int launch_bucket_requests(csa_ctx* ctx, const u32* pos, u64 count, u64 h, u64 n
 {
     if(count == 0) return CSA_OK;
     bucket_kernel<false><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(pos, nullptr, count, h, n, shard, gpus, cursor, req_out, perm_out, nullptr);
-    CSA_LAUNCH_CHECK(ctx);
-    return CSA_OK;
-}
-
-int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard, u32 gpus, u64* cursor, u64* out)
-{
-    if(count == 0) return CSA_OK;
-    bucket_kernel<true><<<unsigned(div_up(count, EX_TILE)), EX_BLOCK, 0, ctx->stream>>>(nullptr, updates, count, 0, ~0ull, shard, gpus, cursor, nullptr, nullptr, out);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }

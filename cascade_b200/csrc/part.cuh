@@ -55,8 +55,6 @@ int launch_count_owners(csa_ctx* ctx, const u32* pos, const u64* packed, u64 cou
 // Requests: for record k with x = pos[k] + h < n, writes x's index inside its shard and k into the bucket of x's owner.
 // cursor[g] must hold the bucket starts; they are advanced.
 int launch_bucket_requests(csa_ctx* ctx, const u32* pos, u64 count, u64 h, u64 n, u64 shard, u32 gpus, u64* cursor, u32* req_out, u32* perm_out);
-// Updates: (position << 32 | rank) records go to the bucket of the position's owner as (index inside the shard << 32 | rank).
-int launch_bucket_updates(csa_ctx* ctx, const u64* updates, u64 count, u64 shard, u32 gpus, u64* cursor, u64* out);
 // count (<= CSA_MAX_GPUS) contiguous copies, of a multiple of 4 bytes each, in one launch; destinations may be peer memory.
 int launch_copy_segments(csa_ctx* ctx, void* const* dst, const void* const* src, const u64* bytes, u32 count);
 // resp[i] = isa_local[req[i]]

@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(BLOCK) scatter_by_pid_kernel(const u16* __rest
                                                               u32* const* __restrict__ part_base, u64* __restrict__ cursor)
 {
     constexpr int TILE = BLOCK * ITEMS;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     u64* const base = reinterpret_cast<u64*>(smem_raw);        // p
     u32* const cnt = reinterpret_cast<u32*>(base + p);          // p
     const u32 tid = threadIdx.x;
