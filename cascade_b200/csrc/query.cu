@@ -34,16 +34,13 @@ __device__ __forceinline__ int cmp_suffix_pattern(const u16* __restrict__ T, con
     return len < m ? -1 : 0;
 }
 
-__global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, const u16* __restrict__ sym, const u64 q, u64* __restrict__ itv)
-{
-    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    if(i >= q) return;
-    const u64 n = idx.n, stride = idx.stride;
-    const u64 ne = idx.sa_entries ? idx.sa_entries : idx.n;      // entries of the suffix array (a slice of it in a sharded index)
-    const u64 m = off[i + 1] - off[i];
-    const u16* const P = sym + (off[i] - off[0]);
-    if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = ne; return; }
+// The ranks that can hold the two boundaries of a query's interval, from the sample table alone.
+struct Brackets { u64 lo_first, lo_last, hi_first, hi_last; };
 
+__device__ __forceinline__ Brackets table_brackets(const csa_index& idx, const u16* __restrict__ P, const u64 m)
+{
+    const u64 stride = idx.stride;
+    const u64 ne = idx.sa_entries ? idx.sa_entries : idx.n;      // entries of the suffix array (a slice of it in a sharded index)
     // The pattern's first min(m, K) symbols, packed like a table key, and the mask of those symbols.
     const u32 mm = m < CSA_K ? u32(m) : u32(CSA_K);
     u64 qh = 0, ql = 0;
@@ -79,41 +76,119 @@ __global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, co
         }
         b = x;
     }
-
     // Sampled rank j * stride carries table key j. Ranks up to (a-1) stride are smaller than the pattern; ranks from
     // b stride on are greater.
-    const u64 L = (a == 0) ? 0 : (a - 1) * stride + 1;
-    const u64 R = (b >= J) ? ne : b * stride;
-    u64 lo_last = R, hi_first = L;
+    Brackets br;
+    br.lo_first = (a == 0) ? 0 : (a - 1) * stride + 1;
+    br.hi_last = (b >= J) ? ne : b * stride;
+    br.lo_last = br.hi_last;
+    br.hi_first = br.lo_first;
     if(m <= CSA_K)
     {
         // Every suffix whose masked key equals the pattern's matches it, except suffixes that end inside the pattern and
         // owe the equality to zero padding; there are fewer than m of them and they need the pattern to end in a zero.
         const u64 e = (P[m - 1] == 0) ? m - 1 : 0;
         const u64 cap = a * stride + e;
-        if(cap < lo_last) lo_last = cap;
-        if(b > 0 && (b - 1) * stride + 1 > hi_first) hi_first = (b - 1) * stride + 1;
+        if(cap < br.lo_last) br.lo_last = cap;
+        if(b > 0 && (b - 1) * stride + 1 > br.hi_first) br.hi_first = (b - 1) * stride + 1;
     }
+    return br;
+}
 
-    const u8* const SA = idx.sa40;
+// Both boundaries of the interval by binary search inside the brackets. `sa_lo` / `sa_hi` are what entry r of the suffix
+// array is read from in each search: the array itself, or a gathered window shifted so that the same r addresses it.
+__device__ __forceinline__ void search_brackets(const csa_index& idx, const Brackets& br, const u16* __restrict__ P, const u64 m, const u8* sa_lo,
+                                                const u8* sa_hi, u64& lo_out, u64& hi_out)
+{
+    const u64 n = idx.n;
     const u16* const T = idx.text;
-    u64 x = L, y = lo_last;
+    u64 x = br.lo_first, y = br.lo_last;
     while(x < y)
     {
         const u64 mid = x + ((y - x) >> 1);
-        if(cmp_suffix_pattern(T, n, sa40_load(SA, mid), P, m) < 0) x = mid + 1; else y = mid;
+        if(cmp_suffix_pattern(T, n, sa40_load(sa_lo, mid), P, m) < 0) x = mid + 1; else y = mid;
     }
-    const u64 lo = x;
-    x = (hi_first > lo) ? hi_first : lo;
-    y = R;
+    lo_out = x;
+    x = (br.hi_first > x) ? br.hi_first : x;
+    y = br.hi_last;
     if(x > y) x = y;
     while(x < y)
     {
         const u64 mid = x + ((y - x) >> 1);
-        if(cmp_suffix_pattern(T, n, sa40_load(SA, mid), P, m) <= 0) x = mid + 1; else y = mid;
+        if(cmp_suffix_pattern(T, n, sa40_load(sa_hi, mid), P, m) <= 0) x = mid + 1; else y = mid;
     }
+    hi_out = x;
+}
+
+__global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, const u16* __restrict__ sym, const u64 q, u64* __restrict__ itv)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= q) return;
+    const u64 m = off[i + 1] - off[i];
+    const u16* const P = sym + (off[i] - off[0]);
+    if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = idx.sa_entries ? idx.sa_entries : idx.n; return; }
+    const Brackets br = table_brackets(idx, P, m);
+    u64 lo, hi;
+    search_brackets(idx, br, P, m, idx.sa40, idx.sa40, lo, hi);
     itv[2 * i] = lo;
-    itv[2 * i + 1] = x;
+    itv[2 * i + 1] = hi;
+}
+
+// ---- the same search when the suffix array lies in pinned host memory -------------------------------------------------
+// Every probe of the array would be a PCIe round trip, so the entries of both brackets are first gathered into device
+// memory, one warp per query with 16-byte loads (the reference's gather_kernel, src/Query_Engine.cu:334-354, does the same
+// for its pinned plan), and the binary searches then run on the gathered windows. A bracket wider than WINDOW_ENTRIES
+// (a long pattern whose K-gram prefix is very frequent) is searched in place.
+constexpr u32 WINDOW_ENTRIES = 64;
+constexpr u32 WINDOW_BYTES = 352;       // 5 * (WINDOW_ENTRIES + 1) entries' bytes + alignment slack + the load overrun, in 16-byte pieces
+
+__global__ void brackets_kernel(const csa_index idx, const u64* __restrict__ off, const u16* __restrict__ sym, const u64 q, Brackets* __restrict__ out)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= q) return;
+    const u64 m = off[i + 1] - off[i];
+    Brackets br{0, 0, 0, 0};
+    if(m > 0) br = table_brackets(idx, sym + (off[i] - off[0]), m);
+    out[i] = br;
+}
+
+__device__ __forceinline__ bool window_fits(u64 first, u64 last) { return last - first <= WINDOW_ENTRIES; }
+
+__global__ void gather_windows_kernel(const u8* __restrict__ sa40, const Brackets* __restrict__ br, const u64 q, u8* __restrict__ win)
+{
+    const u64 w = (u64(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if(w >= q) return;
+    const Brackets b = br[w];
+    #pragma unroll
+    for(int side = 0; side < 2; ++side)
+    {
+        const u64 first = side ? b.hi_first : b.lo_first, last = side ? b.hi_last : b.lo_last;
+        if(last < first || !window_fits(first, last)) continue;
+        const u64 byte0 = (5 * first) & ~u64(15), byte1 = 5 * last + 5 + 4;       // entry `last` may be probed; a load reads 8 bytes
+        const u32 pieces = u32((byte1 - byte0 + 15) >> 4);
+        const uint4* src = reinterpret_cast<const uint4*>(sa40 + byte0);
+        uint4* dst = reinterpret_cast<uint4*>(win + (2 * w + side) * WINDOW_BYTES);
+        if(lane_id() < pieces && lane_id() < WINDOW_BYTES / 16) dst[lane_id()] = src[lane_id()];
+    }
+}
+
+__global__ void search_windows_kernel(const csa_index idx, const u64* __restrict__ off, const u16* __restrict__ sym, const u64 q,
+                                      const Brackets* __restrict__ brs, const u8* __restrict__ win, u64* __restrict__ itv)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= q) return;
+    const u64 m = off[i + 1] - off[i];
+    if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = idx.sa_entries ? idx.sa_entries : idx.n; return; }
+    const Brackets br = brs[i];
+    // A window holds the array's bytes from (5 first) & ~15 on; shifting its base back by that much lets rank r address it.
+    const u8* sa_lo = idx.sa40;
+    const u8* sa_hi = idx.sa40;
+    if(br.lo_last >= br.lo_first && window_fits(br.lo_first, br.lo_last)) sa_lo = win + (2 * i) * WINDOW_BYTES - ((5 * br.lo_first) & ~u64(15));
+    if(br.hi_last >= br.hi_first && window_fits(br.hi_first, br.hi_last)) sa_hi = win + (2 * i + 1) * WINDOW_BYTES - ((5 * br.hi_first) & ~u64(15));
+    u64 lo, hi;
+    search_brackets(idx, br, sym + (off[i] - off[0]), m, sa_lo, sa_hi, lo, hi);
+    itv[2 * i] = lo;
+    itv[2 * i + 1] = hi;
 }
 
 // One warp per query: row i of pos receives SA[lo + k], k < min(max_pos, hi - lo).
@@ -316,8 +391,45 @@ extern "C" int csa_find(csa_ctx* ctx, const csa_index* index, const uint64_t* of
     if(q == 0) return CSA_OK;
     if(!off || !itv) return csa_fail(ctx, CSA_E_INVALID, "csa_find: null buffer");
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    find_kernel<<<unsigned(div_up(q, 128)), 128, 0, ctx->stream>>>(*index, reinterpret_cast<const u64*>(off), sym, q, reinterpret_cast<u64*>(itv));
-    CSA_LAUNCH_CHECK(ctx);
+    cudaPointerAttributes attr;
+    const bool sa_on_host = cudaPointerGetAttributes(&attr, index->sa40) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    if(!sa_on_host)
+    {
+        find_kernel<<<unsigned(div_up(q, 128)), 128, 0, ctx->stream>>>(*index, reinterpret_cast<const u64*>(off), sym, q, reinterpret_cast<u64*>(itv));
+        CSA_LAUNCH_CHECK(ctx);
+        return CSA_OK;
+    }
+    // Suffix array in pinned host memory: brackets from the table, the brackets' entries gathered over PCIe, search on the
+    // device. Batches of 2^20 queries bound the window buffer (about 0.8 GB).
+    constexpr u64 BATCH = u64(1) << 20;
+    const u64 per = (q < BATCH ? q : BATCH);
+    void* aux = nullptr;
+    CSA_TRY(csa_aux(ctx, align_up256(per * sizeof(Brackets)) + align_up256(per * 2 * WINDOW_BYTES + 256), &aux));
+    Brackets* brs = static_cast<Brackets*>(aux);
+    u8* win = static_cast<u8*>(aux) + align_up256(per * sizeof(Brackets));
+    for(u64 first = 0; first < q; first += BATCH)
+    {
+        const u64 c = (q - first < BATCH ? q - first : BATCH);
+        const u64* o = reinterpret_cast<const u64*>(off) + first;
+        // The kernels address pattern i at sym + (off[i] - off[0]) of the offsets they are given, so a later batch gets the
+        // symbol pointer moved on by the symbols that precede it.
+        const u16* sy = sym;
+        if(first > 0)
+        {
+            u64 begin[2] = {0, 0};
+            CSA_CUDA(ctx, cudaMemcpyAsync(&begin[0], off, 8, cudaMemcpyDefault, ctx->stream));
+            CSA_CUDA(ctx, cudaMemcpyAsync(&begin[1], o, 8, cudaMemcpyDefault, ctx->stream));
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            sy = sym + (begin[1] - begin[0]);
+        }
+        brackets_kernel<<<unsigned(div_up(c, 128)), 128, 0, ctx->stream>>>(*index, o, sy, c, brs);
+        CSA_LAUNCH_CHECK(ctx);
+        gather_windows_kernel<<<unsigned(div_up(c * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, brs, c, win);
+        CSA_LAUNCH_CHECK(ctx);
+        search_windows_kernel<<<unsigned(div_up(c, 128)), 128, 0, ctx->stream>>>(*index, o, sy, c, brs, win, reinterpret_cast<u64*>(itv) + 2 * first);
+        CSA_LAUNCH_CHECK(ctx);
+    }
     return CSA_OK;
 }
 

@@ -137,6 +137,16 @@ def test_suffix_array_in_pinned_host_memory(ctx, oracle):
     itv = idx.find(o, s_, 500)
     want = oracle.find_batch(T, sa, off, sym)
     assert np.array_equal(itv.cpu().numpy().view(np.uint64), want)
+    # a text with long runs: patterns longer than the table's K symbols whose K-gram is frequent get brackets wider than a
+    # gathered window and are searched in place
+    T2 = np.zeros(30000, np.uint16)
+    T2[rng.integers(0, 30000, 300)] = 1
+    sa2 = oracle.build_sa40(T2)
+    td2 = torch.from_numpy(np.concatenate([T2, np.zeros(api.TEXT_PAD, np.uint16)]).view(np.int16)).cuda().view(torch.uint16)
+    idx2 = api.SuffixIndex(ctx, td2, torch.from_numpy(np.ascontiguousarray(sa2)).pin_memory(), 30000, 16)
+    off2, sym2, _ = conftest.fixture_queries(T2, rng, 300)
+    o2, s2 = _dev(off2, sym2)
+    assert np.array_equal(idx2.find(o2, s2, 300).cpu().numpy().view(np.uint64), oracle.find_batch(T2, sa2, off2, sym2))
     pos, cnt = idx.locate(itv, 500, 100)
     wp, wc = oracle.locate_batch(sa, want, 100)
     assert np.array_equal(cnt.cpu().numpy().view(np.uint32), wc)
