@@ -40,6 +40,8 @@ struct csa_ctx
     size_t aux_bytes = 0;
     std::string err;
     u64 counters[16] = {0};        // launch and byte counters for the benchmark
+    const u32* symbol_range = nullptr;     // optional first-symbol table of csa_partition_ids (see partition_install_symbol_ranges)
+    void* pass_timer = nullptr;            // digit-pass event timing of the sorts on this context (owned by radix_sort.cu)
     // Mappings of other GPUs' arenas opened through CUDA IPC (multi-GPU builds), kept while the peers' handles stay the same.
     void* peer_base[CSA_MAX_GPUS] = {nullptr};
     unsigned char peer_handle[CSA_MAX_GPUS][64] = {{0}};

@@ -32,7 +32,7 @@ extern "C" void csa_ctx_destroy(csa_ctx* ctx)
     if(!ctx) return;
     cudaSetDevice(ctx->device);
     if(ctx->stream) cudaStreamSynchronize(ctx->stream);
-    sort_reset_timing(ctx);
+    sort_free_timing(ctx);
     for(int g = 0; g < CSA_MAX_GPUS; ++g) if(ctx->peer_open[g]) cudaIpcCloseMemHandle(ctx->peer_base[g]);
     if(ctx->arena) cudaFree(ctx->arena);
     if(ctx->aux) cudaFree(ctx->aux);

@@ -375,13 +375,12 @@ __global__ void split_samples_kernel(const u64* __restrict__ samples, const u64 
     if(i < count) { hi[i] = samples[2 * i]; idx[i] = u32(i); }
 }
 
-// Optional per-device table for csa_partition_ids: for every first symbol the lowest and the highest partition that a
-// K-gram starting with it can fall into (low and high 16 bits). Installed by partition_install_symbol_ranges.
-const u32* g_symbol_range[64] = {nullptr};
+// Optional table for csa_partition_ids, kept in the context: for every first symbol the lowest and the highest partition
+// that a K-gram starting with it can fall into (low and high 16 bits). Installed by partition_install_symbol_ranges.
 
 int partition_install_symbol_ranges(csa_ctx* ctx, const u64* pivots_host, u32 p, u32* table_dev)
 {
-    if(table_dev == nullptr) { g_symbol_range[ctx->device & 63] = nullptr; return CSA_OK; }
+    if(table_dev == nullptr) { ctx->symbol_range = nullptr; return CSA_OK; }
     std::vector<u32> t(65536);
     // pid(k) = number of splitters smaller than k. For K-grams starting with s: from pid(s,0,...,0) to pid(s,FFFF,...,FFFF).
     u32 a = 0, b = 0;
@@ -394,7 +393,7 @@ int partition_install_symbol_ranges(csa_ctx* ctx, const u64* pivots_host, u32 p,
     }
     CSA_CUDA(ctx, cudaMemcpyAsync(table_dev, t.data(), 65536 * 4, cudaMemcpyHostToDevice, ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    g_symbol_range[ctx->device & 63] = table_dev;
+    ctx->symbol_range = table_dev;
     return CSA_OK;
 }
 
@@ -411,7 +410,7 @@ extern "C" int csa_partition_ids(csa_ctx* ctx, const uint16_t* text, uint64_t n,
     const size_t smem = (TILE + 8) * 2 + 16 + size_t(2) * (p > 1 ? p - 1 : 1) * 8 + size_t(p) * 4;
     auto kern = partition_ids_kernel<PID_BLOCK, PID_ITEMS>;
     CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(text, n, first, count, reinterpret_cast<const u64*>(pivots), p, g_symbol_range[ctx->device & 63], pid,
+    kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(text, n, first, count, reinterpret_cast<const u64*>(pivots), p, ctx->symbol_range, pid,
                                                                           reinterpret_cast<u64*>(hist), ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;

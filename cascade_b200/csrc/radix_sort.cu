@@ -389,7 +389,12 @@ struct Pass_Timer
     std::vector<cudaEvent_t> ev;    // pairs
     u64 passes = 0, records = 0, bytes = 0;
 };
-Pass_Timer g_timer[64];
+
+Pass_Timer& timer_of(csa_ctx* ctx)
+{
+    if(!ctx->pass_timer) ctx->pass_timer = new Pass_Timer();
+    return *static_cast<Pass_Timer*>(ctx->pass_timer);
+}
 
 }   // namespace
 
@@ -425,14 +430,14 @@ size_t csa_sort_workspace_bytes(uint64_t n)
 int csa_set_pass_timing(csa_ctx* ctx, int on)
 {
     if(!ctx) return CSA_E_INVALID;
-    g_timer[ctx->device & 63].on = on != 0;
+    timer_of(ctx).on = on != 0;
     return CSA_OK;
 }
 
 int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64_t* records, uint64_t* bytes)
 {
     if(!ctx) return CSA_E_INVALID;
-    Pass_Timer& t = g_timer[ctx->device & 63];
+    Pass_Timer& t = timer_of(ctx);
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     double ms = 0;
     for(size_t i = 0; i + 1 < t.ev.size(); i += 2)
@@ -448,9 +453,18 @@ int csa_get_pass_timing(csa_ctx* ctx, double* total_ms, uint64_t* passes, uint64
     return CSA_OK;
 }
 
+void sort_free_timing(csa_ctx* ctx)
+{
+    if(!ctx->pass_timer) return;
+    Pass_Timer* t = static_cast<Pass_Timer*>(ctx->pass_timer);
+    for(auto e : t->ev) cudaEventDestroy(e);
+    delete t;
+    ctx->pass_timer = nullptr;
+}
+
 void sort_reset_timing(csa_ctx* ctx)
 {
-    Pass_Timer& t = g_timer[ctx->device & 63];
+    Pass_Timer& t = timer_of(ctx);
     for(auto e : t.ev) cudaEventDestroy(e);
     t.ev.clear();
     t.passes = t.records = t.bytes = 0;
@@ -501,7 +515,7 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     u64 skip[8];
     for(int p = 0; p < passes; ++p) skip[p] = ctx->h_scalars[32 + p];
 
-    Pass_Timer& timer = g_timer[ctx->device & 63];
+    Pass_Timer& timer = timer_of(ctx);
     u64* kin = reinterpret_cast<u64*>(keys); u64* kout = reinterpret_cast<u64*>(keys_alt);
     void* vin = vals; void* vout = vals_alt;
     int flips = 0;
