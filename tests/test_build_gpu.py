@@ -103,7 +103,7 @@ def test_partition_count_does_not_change_the_result(ctx):
     n = 3_000_000
     Td = api.gen_corpus_device(ctx, n, 5, 1024)
     ref, _ = api.build_sa(ctx, Td, n, 1)
-    for p in (2, 7, 64, 300):
+    for p in (2, 7, 64, 300, 4096):
         sa, st = api.build_sa(ctx, Td, n, p, seed=p)
         assert torch.equal(sa, ref), p
 
