@@ -16,6 +16,7 @@
 #include "sort.cuh"
 
 #include <chrono>
+#include <unistd.h>
 #include <cstdlib>
 #include <vector>
 
@@ -94,6 +95,8 @@ struct Peer_Info
 {
     unsigned char handle[64];
     u64 off_isa, off_sa, off_xin, off_resp, arena_bytes;
+    u64 process, arena_address;     // ranks that are threads of one process reach one another's arenas directly
+    int device;
 };
 
 int gather(csa_ctx* ctx, const csa_comm* comm, const void* send, void* recv, u64 bytes)
@@ -253,7 +256,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     if(G > 1)
     {
         cudaIpcMemHandle_t h;
-        CSA_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->arena));
+        CSA_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->arena));      // used by the ranks of other processes only
         static_assert(sizeof(h) == 64, "IPC handle size");
         std::memcpy(mine.handle, &h, 64);
     }
@@ -262,12 +265,27 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     mine.off_xin = xin - static_cast<u8*>(ctx->arena);
     mine.off_resp = reinterpret_cast<u8*>(resp_in) - static_cast<u8*>(ctx->arena);
     mine.arena_bytes = ctx->arena_bytes;
+    mine.process = u64(getpid());
+    mine.arena_address = reinterpret_cast<u64>(ctx->arena);
+    mine.device = ctx->device;
     std::vector<Peer_Info> peers(G);
     CSA_TRY(gather(ctx, comm, &mine, peers.data(), sizeof(Peer_Info)));
     u8* peer_arena[CSA_MAX_GPUS];
     for(u32 g = 0; g < G; ++g)
     {
         if(g == me) { peer_arena[g] = static_cast<u8*>(ctx->arena); continue; }
+        if(peers[g].process == mine.process)
+        {
+            // a rank that is a thread of this process: its arena is addressed as it is, once peer access is on
+            if(peers[g].device != ctx->device)
+            {
+                const cudaError_t e = cudaDeviceEnablePeerAccess(peers[g].device, 0);
+                if(e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) { ctx->err = std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(e); return CSA_E_CUDA; }
+                cudaGetLastError();
+            }
+            peer_arena[g] = reinterpret_cast<u8*>(peers[g].arena_address);
+            continue;
+        }
         if(ctx->peer_open[g] && std::memcmp(ctx->peer_handle[g], peers[g].handle, 64) != 0)
         {
             cudaIpcCloseMemHandle(ctx->peer_base[g]);

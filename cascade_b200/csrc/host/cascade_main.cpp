@@ -6,6 +6,8 @@
 //   GPU_SACA_P_TARGET     partitions to form (default 64)
 //   GPU_SACA_SCRATCH      accepted for compatibility; the in-HBM build spills nothing
 //   CASCADE_DEVICE        CUDA device (default 0)
+//   CASCADE_GPUS          GPUs to shard the build over (default 1): one host thread per GPU, devices CASCADE_DEVICE + i modulo
+//                         the number of devices present
 //   CASCADE_INDEX_DIR     if set, an index.meta for `query` is written there (what `sa_convert --meta-only` does)
 //   CASCADE_VALIDATE      if set, spot-checks the order of 100000 random neighbours of the result on the host
 #include "../../../include/cascade_b200.h"
@@ -16,6 +18,9 @@
 #include <chrono>
 #include <cstdlib>
 #include <random>
+#include <thread>
+#include <unistd.h>
+#include <vector>
 
 using namespace cascade_host;
 
@@ -61,17 +66,72 @@ int main(int argc, char** argv)
     std::memset(T + n, 0, CSA_TEXT_PAD * 2);
     std::fprintf(stderr, "Loaded the text of %llu symbols. Time taken: %.3f s.\n", (unsigned long long)n, since());
 
+    const uint32_t gpus = uint32_t(env_u64("CASCADE_GPUS", 1));
     csa_ctx* ctx = nullptr;
-    if(csa_ctx_create(device, &ctx) != CSA_OK) { std::fprintf(stderr, "error: cannot create a device context\n"); return EXIT_FAILURE; }
-    csa_build_stats st{};
     const double b0 = since();
-    const int rc = csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
-    if(rc != CSA_OK) { std::fprintf(stderr, "error: build failed (%d): %s\n", rc, csa_last_error(ctx)); return EXIT_FAILURE; }
+    if(gpus <= 1)
+    {
+        if(csa_ctx_create(device, &ctx) != CSA_OK) { std::fprintf(stderr, "error: cannot create a device context\n"); return EXIT_FAILURE; }
+        csa_build_stats st{};
+        const int rc = csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
+        if(rc != CSA_OK) { std::fprintf(stderr, "error: build failed (%d): %s\n", rc, csa_last_error(ctx)); return EXIT_FAILURE; }
+        std::fprintf(stderr, "Built the suffix array: %u partitions (largest %llu), %u doubling generations, %llu digit passes.\n", st.partitions,
+                     (unsigned long long)st.max_partition, st.generations, (unsigned long long)st.sort_passes);
+        std::fprintf(stderr, "Device time: partition %.1f ms, initial ranking %.1f ms, doubling %.1f ms, output %.1f ms.\n", st.ms_partition, st.ms_gen0,
+                     st.ms_doubling, st.ms_output);
+    }
+    else
+    {
+        // One host thread per GPU; the threads meet in the library's shared-memory all-gather; every GPU gets the whole text,
+        // builds its partitions' ranges and copies them to their places in the host array.
+        if(gpus > CSA_MAX_GPUS) { std::fprintf(stderr, "error: CASCADE_GPUS is at most %d\n", CSA_MAX_GPUS); return EXIT_FAILURE; }
+        int present = 0;
+        if(cudaGetDeviceCount(&present) != cudaSuccess || present < 1) { std::fprintf(stderr, "error: no CUDA device\n"); return EXIT_FAILURE; }
+        const std::string shm = "/cascade_b200_cli_" + std::to_string(getpid());
+        std::vector<int> rcs(gpus, CSA_OK);
+        std::vector<std::string> errs(gpus);
+        std::vector<csa_build_stats> sts(gpus);
+        std::vector<std::thread> pool;
+        for(uint32_t r = 0; r < gpus; ++r)
+            pool.emplace_back([&, r]
+            {
+                const int dev = (device + int(r)) % present;
+                auto fail = [&](int rc, const std::string& why) { rcs[r] = rc; errs[r] = why; };
+                if(cudaSetDevice(dev) != cudaSuccess) return fail(CSA_E_CUDA, "cudaSetDevice");
+                csa_comm comm{};
+                if(csa_comm_open_shm(shm.c_str(), r, gpus, 1, &comm) != CSA_OK) return fail(CSA_E_COMM, "csa_comm_open_shm");
+                csa_ctx* c = nullptr;
+                if(csa_ctx_create(dev, &c) != CSA_OK) return fail(CSA_E_CUDA, "csa_ctx_create");
+                uint16_t* T_d = nullptr; uint8_t* out_d = nullptr;
+                const uint64_t cap = n;     // room for any deal of the partitions
+                if(cudaMalloc(&T_d, (n + CSA_TEXT_PAD) * 2) != cudaSuccess || cudaMalloc(&out_d, 5 * cap + CSA_SA_PAD_BYTES) != cudaSuccess)
+                    return fail(CSA_E_NOMEM, "device memory for the text and the output");
+                cudaMemcpy(T_d, T, (n + CSA_TEXT_PAD) * 2, cudaMemcpyHostToDevice);
+                std::vector<uint64_t> seg_first(p), seg_count(p);
+                uint32_t seg_c = 0;
+                const int rc = csa_build_sa_multi(c, &comm, T_d, n, p, 0, out_d, cap, seg_first.data(), seg_count.data(), &seg_c, &sts[r]);
+                if(rc != CSA_OK) fail(rc, csa_last_error(c));
+                else
+                {
+                    uint64_t at = 0;
+                    for(uint32_t k = 0; k < seg_c; ++k)
+                    {
+                        cudaMemcpy(SA + 5 * seg_first[k], out_d + 5 * at, 5 * seg_count[k], cudaMemcpyDeviceToHost);
+                        at += seg_count[k];
+                    }
+                }
+                cudaFree(T_d); cudaFree(out_d);
+                csa_ctx_destroy(c);
+                csa_comm_close_shm(&comm, r == 0);
+            });
+        for(auto& t : pool) t.join();
+        for(uint32_t r = 0; r < gpus; ++r)
+            if(rcs[r] != CSA_OK) { std::fprintf(stderr, "error: build failed on GPU rank %u (%d): %s\n", r, rcs[r], errs[r].c_str()); return EXIT_FAILURE; }
+        std::fprintf(stderr, "Built the suffix array on %u GPUs: %u partitions, %u doubling generations; rank 0 device time %.1f ms.\n", gpus, sts[0].partitions,
+                     sts[0].generations, sts[0].ms_total);
+    }
     const double build_s = since() - b0;
-    std::fprintf(stderr, "Built the suffix array: %u partitions (largest %llu), %u doubling generations, %llu digit passes.\n", st.partitions,
-                 (unsigned long long)st.max_partition, st.generations, (unsigned long long)st.sort_passes);
-    std::fprintf(stderr, "Device time: partition %.1f ms, initial ranking %.1f ms, doubling %.1f ms, output %.1f ms; with copies %.3f s (%.1f M suffixes/s).\n",
-                 st.ms_partition, st.ms_gen0, st.ms_doubling, st.ms_output, build_s, double(n) / build_s / 1e6);
+    std::fprintf(stderr, "Build with copies: %.3f s (%.1f M suffixes/s).\n", build_s, double(n) / build_s / 1e6);
 
     if(std::getenv("CASCADE_VALIDATE"))
     {
@@ -98,7 +158,7 @@ int main(int argc, char** argv)
             if(!write_index_meta(dir, m, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return EXIT_FAILURE; }
         }
     }
-    csa_ctx_destroy(ctx);
+    if(ctx) csa_ctx_destroy(ctx);
     cudaFreeHost(T); cudaFreeHost(SA);
     return EXIT_SUCCESS;
 }

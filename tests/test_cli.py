@@ -69,6 +69,14 @@ def test_cascade_and_query_find_against_the_oracle(tmp_path, oracle):
     want = oracle.build_sa40(T)
     assert got.size == 5 * n and np.array_equal(got, want[:5 * n])
 
+    # the same file from a build sharded over in-process ranks (threads share the GPU when the box has only one)
+    for gpus in ("2", "3"):
+        out2 = os.path.join(tmp, f"text.g{gpus}.sa40")
+        r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), out2], capture_output=True, text=True,
+                           env=dict(env, CASCADE_GPUS=gpus))
+        assert r.returncode == 0, r.stderr
+        assert np.array_equal(np.fromfile(out2, dtype=np.uint8), want[:5 * n]), gpus
+
     q = os.path.join(tmp, "a.qry")
     assert subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", q, "--kind", "substring", "--q", "5000", "--len", "1,2,4,8,16",
                            "--seed", "1"], capture_output=True).returncode == 0
