@@ -173,33 +173,45 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
     // size to the warp's counter of the digit and hands the old value round. The steps run as separate sweeps over the
     // items so that their latencies overlap; shared-memory atomics of one warp take effect in program order, which keeps
     // the ranks stable.
-    u32 dig[ITEMS], rank[ITEMS];
+    // Ranks are below the tile size (at most 8192), so two share a register; digits are taken from the keys again where
+    // needed; the sweeps run over chunks of 8 items so that their temporaries stay few: this leaves registers for more
+    // items per thread, i.e. larger tiles with longer runs per digit and fewer look-backs per record.
+    u32 rank2[(ITEMS + 1) / 2];
     u32* const wh = warp_hist + warp * RADIX;
+    constexpr int CHUNK = 8;
+    #pragma unroll
+    for(int c = 0; c < ITEMS; c += CHUNK)
     {
-        u32 peers[ITEMS], old[ITEMS];
+        u32 peers[CHUNK], old[CHUNK];
         #pragma unroll
-        for(int i = 0; i < ITEMS; ++i)
+        for(int j = 0; j < CHUNK; ++j)
         {
-            dig[i] = u32(key[i] >> shift) & dmask;
-            u32 m = (MATCH_BITS > 0) ? __match_any_sync(0xFFFFFFFFu, dig[i] >> (RADIX_BITS - MATCH_BITS)) : 0xFFFFFFFFu;
+            if(c + j >= ITEMS) break;
+            const u32 d = u32(key[c + j] >> shift) & dmask;
+            u32 m = (MATCH_BITS > 0) ? __match_any_sync(0xFFFFFFFFu, d >> (RADIX_BITS - MATCH_BITS)) : 0xFFFFFFFFu;
             #pragma unroll
             for(int b = 0; b < RADIX_BITS - MATCH_BITS; ++b)
             {
-                const u32 sel = 0u - ((dig[i] >> b) & 1u);                  // all ones if the bit is set
+                const u32 sel = 0u - ((d >> b) & 1u);                       // all ones if the bit is set
                 const u32 v = __ballot_sync(0xFFFFFFFFu, sel != 0);
                 m &= ~(v ^ sel);                                            // lanes whose bit equals this lane's
             }
-            peers[i] = m;
+            peers[j] = m;
         }
         #pragma unroll
-        for(int i = 0; i < ITEMS; ++i)
+        for(int j = 0; j < CHUNK; ++j)
         {
-            old[i] = 0;
-            if((peers[i] & lanemask_lt()) == 0) old[i] = atomicAdd(&wh[dig[i]], u32(__popc(peers[i])));    // lowest lane of the group
+            if(c + j >= ITEMS) break;
+            old[j] = 0;
+            if((peers[j] & lanemask_lt()) == 0) old[j] = atomicAdd(&wh[u32(key[c + j] >> shift) & dmask], u32(__popc(peers[j])));    // lowest lane of the group
         }
         #pragma unroll
-        for(int i = 0; i < ITEMS; ++i)
-            rank[i] = __shfl_sync(0xFFFFFFFFu, old[i], __ffs(peers[i]) - 1) + __popc(peers[i] & lanemask_lt());
+        for(int j = 0; j < CHUNK; ++j)
+        {
+            if(c + j >= ITEMS) break;
+            const u32 r = __shfl_sync(0xFFFFFFFFu, old[j], __ffs(peers[j]) - 1) + __popc(peers[j] & lanemask_lt());
+            if(((c + j) & 1) == 0) rank2[(c + j) >> 1] = r; else rank2[(c + j) >> 1] |= r << 16;
+        }
     }
     __syncthreads();
 
@@ -293,14 +305,12 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
     for(int i = 0; i < ITEMS; ++i)
     {
         const u32 idx = warp_first + i * 32 + lane;
-        rank[i] += wh[dig[i]];
-        if(FULL || idx < valid) stage_keys[rank[i]] = key[i];
-    }
-    #pragma unroll
-    for(int i = 0; i < ITEMS; ++i)
-    {
-        const u32 idx = warp_first + i * 32 + lane;
-        if(vals_in != nullptr && (FULL || idx < valid)) stage_vals[rank[i]] = val[i];
+        const u32 pos = ((rank2[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu) + wh[u32(key[i] >> shift) & dmask];
+        if(FULL || idx < valid)
+        {
+            stage_keys[pos] = key[i];
+            if(vals_in != nullptr) stage_vals[pos] = val[i];
+        }
     }
     __syncthreads();
 
@@ -366,7 +376,7 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
 
 // Shapes of the pass kernel to choose from (block size x items per thread); the smallest tile sizes the workspace.
 int g_variant = 0;
-constexpr int PASS_TILE = 2048;     // smallest tile among the variants
+constexpr int PASS_TILE = 4096;     // smallest tile among the variants
 
 template <typename V>
 int launch_pass_variant(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, u64 n, int shift, u32 dmask, const u64* db, u64* nb, u32* status,
@@ -374,12 +384,16 @@ int launch_pass_variant(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V
 {
     switch(g_variant)
     {
-    case 1: return launch_pass<256, 8, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
-    case 2: return launch_pass<512, 4, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
-    case 3: return launch_pass<256, 12, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
-    case 4: return launch_pass<1024, 4, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
-    case 5: return launch_pass<512, 8, V, 4>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
-    default: return launch_pass<512, 8, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 1: return launch_pass<256, 16, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 2: return launch_pass<256, 20, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 3: return launch_pass<256, 24, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 4: return launch_pass<256, 28, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 5: return launch_pass<384, 16, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    case 6: return launch_pass<512, 8, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+    default:
+        // 24 records per thread hold in 128 registers with 4-byte values; 8-byte values spill beyond 16.
+        if constexpr(sizeof(V) == 4) return launch_pass<256, 24, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
+        else return launch_pass<256, 16, V, 3>(ctx, kin, kout, vin, vout, n, shift, dmask, db, nb, status, counter);
     }
 }
 
