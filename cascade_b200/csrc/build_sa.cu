@@ -107,6 +107,15 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     st.max_partition = max_part;
 
     // ---- scatter positions into the partitions' slot ranges ------------------------------------------------
+    // With up to 256 partitions the scatter also leaves every suffix's generation-0 key in the same slot of keysA.
+    const bool keys_from_scatter = p_eff <= 256;
+    if(keys_from_scatter)
+    {
+        CSA_CUDA(ctx, cudaMemcpyAsync(hist, part_off.data(), size_t(p_eff) * 8, cudaMemcpyHostToDevice, ctx->stream));
+        CSA_CUDA(ctx, cudaMemsetAsync(cursor, 0, size_t(p_eff) * 8, ctx->stream));
+        CSA_TRY(launch_scatter_with_keys(ctx, T, n + CSA_TEXT_PAD, pid, 0, n, p_eff, hist, cursor, sa, keysA));
+    }
+    else
     {
         std::vector<u32*> bases(p_eff);
         for(u32 q = 0; q < p_eff; ++q) bases[q] = sa + part_off[q];
@@ -128,11 +137,13 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     {
         const u64 S = part_size[q], first = part_off[q];
         if(S == 0) continue;
-        CSA_TRY(launch_keys_gen0(ctx, T, sa + first, S, keysA));
+        // The partition's keys: already in its slots of keysA, or made now from its positions.
+        u64* const kq = keys_from_scatter ? keysA + first : keysA;
+        if(!keys_from_scatter) CSA_TRY(launch_keys_gen0(ctx, T, sa + first, S, kq));
         int in_alt = 0;
-        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), sa + first, posB, 4, S, 0, 64, sort_ws,
+        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(kq), reinterpret_cast<uint64_t*>(keysB), sa + first, posB, 4, S, 0, 64, sort_ws,
                                L.sort_ws, &in_alt));
-        const u64* ks = in_alt ? keysB : keysA;
+        const u64* ks = in_alt ? keysB : kq;
         const u32* ps = in_alt ? posB : sa + first;
         CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, whole, sa, head, posA, act_count, scratch, upd + first));
     }

@@ -216,6 +216,24 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
     }
     if(first >= count) return;
 
+    // A thread's records are consecutive: positions come in and updates go out as 16-byte vectors where the thread's
+    // stretch is whole and aligned (every tile but the last is, as the lists start on 16-byte boundaries).
+    const bool whole = first + RANK_ITEMS <= count;
+    u32 ps[RANK_ITEMS];
+    if(whole && ((reinterpret_cast<uintptr_t>(pos + first) & 15) == 0))
+    {
+        const uint4* v = reinterpret_cast<const uint4*>(pos + first);
+        #pragma unroll
+        for(int i = 0; i < RANK_ITEMS; i += 4) { const uint4 t = v[i / 4]; ps[i] = t.x; ps[i + 1] = t.y; ps[i + 2] = t.z; ps[i + 3] = t.w; }
+    }
+    else
+    {
+        #pragma unroll
+        for(int i = 0; i < RANK_ITEMS; ++i) ps[i] = (first + i < count) ? pos[first + i] : 0;
+    }
+    const bool vector_updates = updates && whole && ((reinterpret_cast<uintptr_t>(updates + first) & 15) == 0);
+    u64 up[RANK_ITEMS];
+
     #pragma unroll
     for(int i = 0; i < RANK_ITEMS; ++i)
     {
@@ -227,19 +245,25 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
         const u32 head = (prim_shift < 64) ? u32(k[i] >> prim_shift) : fixed_head;
         const u32 slot = head + (u32(idx) - group_start);
         const u32 new_head = head + (sub_start - group_start);
-        const u32 ps = pos[idx];
-        if(sa + slot != pos + idx) sa[slot] = ps;
+        if(sa + slot != pos + idx) sa[slot] = ps[i];
         // The new rank goes straight into the inverse array, or, when the array is spread over several GPUs, into a list
         // of (position, rank) updates that is applied in address order (and, over several GPUs, routed to the positions' owners).
         const u32 global_rank = u32(global_of(map, head) + (new_head - head));      // a group lies inside one partition
-        if(updates) updates[idx] = (u64(ps) << 32) | global_rank;
-        else *isa_slot(isa, ps) = global_rank;
+        up[i] = (u64(ps[i]) << 32) | global_rank;
+        if(updates) { if(!vector_updates) updates[idx] = up[i]; }
+        else *isa_slot(isa, ps[i]) = global_rank;
         if(f.active & (1u << i))
         {
             next_head[out] = new_head;
-            next_pos[out] = ps;
+            next_pos[out] = ps[i];
             ++out;
         }
+    }
+    if(vector_updates)
+    {
+        ulonglong2* dst = reinterpret_cast<ulonglong2*>(updates + first);
+        #pragma unroll
+        for(int i = 0; i < RANK_ITEMS; i += 2) dst[i / 2] = make_ulonglong2(up[i], up[i + 1]);
     }
 }
 

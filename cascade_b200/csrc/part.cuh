@@ -30,6 +30,10 @@ struct Slot_Map
 size_t pick_splitters_scratch_bytes(u64 n_samples);
 int pick_splitters(csa_ctx* ctx, const u16* T, u64 n, u32 p, u64 seed, u64 n_samples, void* scratch, size_t scratch_bytes, u64* pivots_host, u32* p_out);
 
+// Scatter of positions by partition id that also writes each suffix's generation-0 key (its first 4 symbols) into the same
+// slot of `keys` as its position takes in `sa`; part_off (device) holds every partition's first slot. p <= 256.
+int launch_scatter_with_keys(csa_ctx* ctx, const u16* T, u64 text_limit, const u16* pid, u64 first, u64 count, u32 p, const u64* part_off, u64* cursor,
+                             u32* sa, u64* keys);
 // key[i] = the 4 symbols at position pos[i], packed most-significant first.
 int launch_keys_gen0(csa_ctx* ctx, const u16* T, const u32* pos, u64 count, u64* keys);
 

@@ -314,6 +314,164 @@ __global__ void __launch_bounds__(BLOCK) scatter_by_pid_ranked_kernel(const u16*
     }
 }
 
+
+// The ranked scatter with the generation-0 keys made on the way: a tile covers consecutive text positions, so the four
+// symbols a key packs come from one contiguous window of the text (read once, coalesced, into shared memory) instead of
+// one 32-byte sector per suffix later, when the positions of a partition lie scattered over the text. The key goes to the
+// same slot of `keys` as the position goes to in `sa`. text_limit = number of readable symbols (text and padding).
+template <int BLOCK, int ITEMS>
+__global__ void __launch_bounds__(BLOCK) scatter_keys_ranked_kernel(const u16* __restrict__ T, const u64 text_limit, const u16* __restrict__ pid,
+                                                                   const u64 first, const u64 count, const u32 p, const int id_bits,
+                                                                   const u64* __restrict__ part_off, u64* __restrict__ cursor,
+                                                                   u32* __restrict__ sa, u64* __restrict__ keys)
+{
+    constexpr int TILE = BLOCK * ITEMS;
+    constexpr int WARPS = BLOCK / 32;
+    constexpr int BINS = 256;
+    constexpr int WINDOW = TILE + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    u64* const stage_key = reinterpret_cast<u64*>(smem_raw);                          // TILE
+    u64* const bin_base = stage_key + TILE;                                           // BINS: slot in `sa` of the tile's run, minus bin_start
+    u32* const stage_pos = reinterpret_cast<u32*>(bin_base + BINS);                   // TILE
+    u32* const warp_cnt = stage_pos + TILE;                                           // WARPS * BINS
+    u32* const scan_tot = warp_cnt + WARPS * BINS;                                    // 8
+    u16* const window = reinterpret_cast<u16*>(scan_tot + 8);                         // WINDOW symbols
+    u8* const stage_id = reinterpret_cast<u8*>(window + WINDOW);                      // TILE
+    const u32 tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const u64 tile_first = u64(blockIdx.x) * TILE;
+    const u32 valid = (count - tile_first < u64(TILE)) ? u32(count - tile_first) : u32(TILE);
+    for(int i = tid; i < WARPS * BINS; i += BLOCK) warp_cnt[i] = 0;
+
+    // the text window of the tile: symbols [first + tile_first, + TILE + 8)
+    {
+        const u64 w0 = first + tile_first;
+        if((reinterpret_cast<uintptr_t>(T + w0) & 15) == 0)
+        {
+            for(u32 v = tid; v < WINDOW / 8; v += BLOCK)
+            {
+                const u64 a = w0 + u64(v) * 8;
+                uint4 t = make_uint4(0, 0, 0, 0);
+                if(a + 8 <= text_limit) t = *reinterpret_cast<const uint4*>(T + a);
+                else
+                {
+                    u16 e[8];
+                    #pragma unroll
+                    for(int j = 0; j < 8; ++j) e[j] = (a + j < text_limit) ? T[a + j] : u16(0);
+                    t = make_uint4(u32(e[0]) | (u32(e[1]) << 16), u32(e[2]) | (u32(e[3]) << 16), u32(e[4]) | (u32(e[5]) << 16), u32(e[6]) | (u32(e[7]) << 16));
+                }
+                reinterpret_cast<uint4*>(window)[v] = t;
+            }
+        }
+        else
+        {
+            for(u32 v = tid; v < WINDOW; v += BLOCK) window[v] = (w0 + v < text_limit) ? T[w0 + v] : u16(0);
+        }
+    }
+    __syncthreads();
+
+    u32 id[ITEMS];
+    u32 rank2[(ITEMS + 1) / 2];
+    const u32 warp_first = warp * 32 * ITEMS;
+    #pragma unroll
+    for(int i = 0; i < ITEMS; ++i)
+    {
+        const u32 idx = warp_first + i * 32 + lane;
+        id[i] = (idx < valid) ? u32(pid[tile_first + idx]) : (BINS - 1);     // fillers rank last in the last bin
+    }
+    u32* const wc = warp_cnt + warp * BINS;
+    constexpr int CHUNK = 8;
+    #pragma unroll
+    for(int c = 0; c < ITEMS; c += CHUNK)
+    {
+        u32 peers[CHUNK], old[CHUNK];
+        #pragma unroll
+        for(int j = 0; j < CHUNK; ++j)
+        {
+            u32 m = 0xFFFFFFFFu;
+            for(int b = 0; b < id_bits; ++b)
+            {
+                const u32 sel = 0u - ((id[c + j] >> b) & 1u);
+                const u32 v = __ballot_sync(0xFFFFFFFFu, sel != 0);
+                m &= ~(v ^ sel);
+            }
+            const u32 idx = warp_first + (c + j) * 32 + lane;
+            // fillers must not meet real records of the last bin: split them off by their validity
+            const u32 live = __ballot_sync(0xFFFFFFFFu, idx < valid);
+            m &= (idx < valid) ? live : ~live;
+            peers[j] = m;
+        }
+        #pragma unroll
+        for(int j = 0; j < CHUNK; ++j)
+        {
+            const u32 idx = warp_first + (c + j) * 32 + lane;
+            old[j] = 0;
+            if(idx < valid && (peers[j] & lanemask_lt()) == 0) old[j] = atomicAdd(&wc[id[c + j]], u32(__popc(peers[j])));
+        }
+        #pragma unroll
+        for(int j = 0; j < CHUNK; ++j)
+        {
+            const u32 r = __shfl_sync(0xFFFFFFFFu, old[j], __ffs(peers[j]) - 1) + __popc(peers[j] & lanemask_lt());
+            if(((c + j) & 1) == 0) rank2[(c + j) >> 1] = r; else rank2[(c + j) >> 1] |= r << 16;
+        }
+    }
+    __syncthreads();
+    // per partition: the warps' offsets, the tile's count, an exclusive scan over the partitions, and the run's place
+    static_assert(BLOCK >= BINS, "one thread per partition");
+    u32 cnt = 0;
+    u32 wsum[WARPS];
+    if(tid < BINS)
+    {
+        #pragma unroll
+        for(int w = 0; w < WARPS; ++w) { wsum[w] = warp_cnt[w * BINS + tid]; cnt += wsum[w]; }
+    }
+    u32 inc = cnt;
+    if(tid < BINS)
+    {
+        #pragma unroll
+        for(int o = 1; o < 32; o <<= 1)
+        {
+            const u32 t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if(int(lane) >= o) inc += t;
+        }
+        if(lane == 31) scan_tot[warp] = inc;
+    }
+    __syncthreads();
+    if(tid < BINS)
+    {
+        u32 pre = 0;
+        for(u32 w = 0; w < warp; ++w) pre += scan_tot[w];
+        u32 run = pre + inc - cnt;
+        if(cnt && tid < p) bin_base[tid] = part_off[tid] + atomicAdd(&cursor[tid], u64(cnt)) - run;
+        #pragma unroll
+        for(int w = 0; w < WARPS; ++w) { warp_cnt[w * BINS + tid] = run; run += wsum[w]; }
+    }
+    __syncthreads();
+    #pragma unroll
+    for(int i = 0; i < ITEMS; ++i)
+    {
+        const u32 idx = warp_first + i * 32 + lane;
+        if(idx < valid)
+        {
+            const u32 at = wc[id[i]] + ((rank2[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
+            stage_pos[at] = u32(first + tile_first + idx);
+            stage_key[at] = (u64(window[idx]) << 48) | (u64(window[idx + 1]) << 32) | (u64(window[idx + 2]) << 16) | u64(window[idx + 3]);
+            stage_id[at] = u8(id[i]);
+        }
+    }
+    __syncthreads();
+    #pragma unroll
+    for(int k = 0; k < ITEMS; ++k)
+    {
+        const u32 j = tid + k * BLOCK;
+        if(j < valid)
+        {
+            const u64 dst = bin_base[stage_id[j]] + j;
+            sa[dst] = stage_pos[j];
+            keys[dst] = stage_key[j];
+        }
+    }
+}
+
 }   // namespace
 
 extern "C" int csa_sample_kgrams(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t n_samples, uint64_t seed, uint64_t* samples)
@@ -437,6 +595,29 @@ extern "C" int csa_scatter_by_pid(csa_ctx* ctx, const uint16_t* pid, uint64_t fi
     auto kern = scatter_by_pid_kernel<PID_BLOCK, PID_ITEMS>;
     CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     kern<<<unsigned(div_up(count, TILE)), PID_BLOCK, smem, ctx->stream>>>(pid, first, count, p, part_base, reinterpret_cast<u64*>(cursor));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+
+// Scatter of the positions [first, first + count) into `sa` by partition id together with their generation-0 keys into
+// the same slots of `keys`; partition q owns the slots from part_off[q] on (device array). Up to 256 partitions.
+int launch_scatter_with_keys(csa_ctx* ctx, const u16* T, u64 text_limit, const u16* pid, u64 first, u64 count, u32 p, const u64* part_off, u64* cursor,
+                             u32* sa, u64* keys)
+{
+    if(p == 0 || p > 256) return csa_fail(ctx, CSA_E_LIMIT, "scatter with keys: 1 to 256 partitions");
+    if(first + count > 0xFFFFFFFFull) return csa_fail(ctx, CSA_E_LIMIT, "scatter with keys: positions must fit 32 bits");
+    if(count == 0) return CSA_OK;
+    constexpr int SB = 256, SI = 16, TILE = SB * SI;
+    constexpr size_t smem = size_t(TILE) * 8 + 256 * 8 + size_t(TILE) * 4 + size_t(SB / 32) * 256 * 4 + 8 * 4 + size_t(TILE + 8) * 2 + TILE;
+    auto kern = scatter_keys_ranked_kernel<SB, SI>;
+    static bool configured[64] = {false};
+    if(!configured[ctx->device & 63])
+    {
+        CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        configured[ctx->device & 63] = true;
+    }
+    kern<<<unsigned(div_up(count, TILE)), SB, smem, ctx->stream>>>(T, text_limit, pid, first, count, p, bits_for(p - 1), part_off, cursor, sa, keys);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }

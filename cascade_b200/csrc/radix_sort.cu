@@ -22,6 +22,7 @@ constexpr u32 FLAG_PREFIX = 2u << FLAG_SHIFT;
 u64 PORTION = 1ull << 29;                   // records per launch of a pass: tile counts stay below 2^30 (tests may lower it)
 constexpr u32 LOOKBACK_SPIN_LIMIT = 1u << 22;
 constexpr int LOOKBACK_BATCH = 8;
+constexpr int HIST_UNROLL = 4;             // 16-byte loads in flight per thread of the histogram kernel
 
 // The digit of a pass that starts at bit `shift` holds min(8, end_bit - shift) bits.
 __host__ __device__ __forceinline__ u32 digit_mask(int shift, int end_bit)
@@ -45,40 +46,68 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
     __syncthreads();
     u32* const mine = h + (threadIdx.x >> 5) * per_warp;
 
-    const u64 pairs = n >> 1;   // 128-bit loads of two keys
-    const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(keys);
-    const u64 stride = u64(gridDim.x) * BLOCK;
+    // 128-bit loads of two keys, HIST_UNROLL of them in flight per thread: the kernel is a single read of the keys and
+    // needs tens of KB outstanding per SM to keep the memory busy.
+    // A list that starts on an odd 8-byte boundary leaves its first key to the scalar tail below.
+    const u64 odd_lead = (n > 0 && (reinterpret_cast<uintptr_t>(keys) & 8)) ? 1 : 0;
+    const u64 pairs = (n - odd_lead) >> 1;
+    const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(keys + odd_lead);
+    const u64 chunk = u64(BLOCK) * HIST_UNROLL;
+    const u64 stride = u64(gridDim.x) * chunk;
     const u64 rounds = (pairs + stride - 1) / stride;       // whole warps take part in every round: the votes see a full mask
-    u64 i = u64(blockIdx.x) * BLOCK + threadIdx.x;
+    u64 i = u64(blockIdx.x) * chunk + threadIdx.x;
     for(u64 r = 0; r < rounds; ++r, i += stride)
     {
-        const bool live = i < pairs;
-        ulonglong2 v = make_ulonglong2(0, 0);
-        if(live) v = k2[i];
-        const bool all_live = __all_sync(0xFFFFFFFFu, live);
+        ulonglong2 v[HIST_UNROLL];
+        bool live[HIST_UNROLL];
+        bool mine_live = true;
+        #pragma unroll
+        for(int j = 0; j < HIST_UNROLL; ++j)
+        {
+            live[j] = i + u64(j) * BLOCK < pairs;
+            mine_live = mine_live && live[j];
+            v[j] = make_ulonglong2(0, 0);
+            if(live[j]) v[j] = k2[i + u64(j) * BLOCK];
+        }
+        const bool all_live = __all_sync(0xFFFFFFFFu, mine_live);
         #pragma unroll 1
         for(int p = 0; p < passes; ++p)
         {
             const int sh = begin_bit + p * RADIX_BITS;
             const u32 dm = digit_mask(sh, end_bit);
-            const u32 d0 = u32(v.x >> sh) & dm, d1 = u32(v.y >> sh) & dm;
-            const u32 lead = __shfl_sync(0xFFFFFFFFu, d0, 0);
-            if(all_live && __all_sync(0xFFFFFFFFu, d0 == lead && d1 == lead))
+            u32 d[2 * HIST_UNROLL];
+            #pragma unroll
+            for(int j = 0; j < HIST_UNROLL; ++j) { d[2 * j] = u32(v[j].x >> sh) & dm; d[2 * j + 1] = u32(v[j].y >> sh) & dm; }
+            const u32 lead = __shfl_sync(0xFFFFFFFFu, d[0], 0);
+            bool same = true;
+            #pragma unroll
+            for(int j = 0; j < 2 * HIST_UNROLL; ++j) same = same && d[j] == lead;
+            if(all_live && __all_sync(0xFFFFFFFFu, same))
             {
-                if(lane_id() == 0) atomicAdd(&mine[p * RADIX + lead], 64u);
+                if(lane_id() == 0) atomicAdd(&mine[p * RADIX + lead], u32(64 * HIST_UNROLL));
             }
-            else if(live)
+            else
             {
-                atomicAdd(&mine[p * RADIX + d0], 1u);
-                atomicAdd(&mine[p * RADIX + d1], 1u);
+                #pragma unroll
+                for(int j = 0; j < HIST_UNROLL; ++j)
+                    if(live[j])
+                    {
+                        atomicAdd(&mine[p * RADIX + d[2 * j]], 1u);
+                        atomicAdd(&mine[p * RADIX + d[2 * j + 1]], 1u);
+                    }
             }
         }
     }
-    if((n & 1) && blockIdx.x == 0 && threadIdx.x == 0)
+    if(blockIdx.x == 0 && threadIdx.x == 0)
     {
-        const u64 k = keys[n - 1];
-        for(int p = 0; p < passes; ++p)
-            atomicAdd(&mine[p * RADIX + (u32(k >> (begin_bit + p * RADIX_BITS)) & digit_mask(begin_bit + p * RADIX_BITS, end_bit))], 1u);
+        // the keys outside the 16-byte pairs: the first of an odd start, the last of an odd remainder
+        u64 rest[2];
+        int rests = 0;
+        if(odd_lead) rest[rests++] = keys[0];
+        if((n - odd_lead) & 1) rest[rests++] = keys[n - 1];
+        for(int e = 0; e < rests; ++e)
+            for(int p = 0; p < passes; ++p)
+                atomicAdd(&mine[p * RADIX + (u32(rest[e] >> (begin_bit + p * RADIX_BITS)) & digit_mask(begin_bit + p * RADIX_BITS, end_bit))], 1u);
     }
     __syncthreads();
     for(int i2 = threadIdx.x; i2 < per_warp; i2 += BLOCK)
@@ -517,7 +546,7 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     for(int P = 0; P < portions; ++P)
     {
         const u64 first = u64(P) * PORTION, cnt = (n - first < PORTION ? n - first : PORTION);
-        const unsigned blocks = unsigned(cnt / (2 * 256 * 8) < 1 ? 1 : (cnt / (2 * 256 * 8) > 148 * 8 ? 148 * 8 : cnt / (2 * 256 * 8)));
+        const unsigned blocks = unsigned(cnt / (2 * 256 * HIST_UNROLL) < 1 ? 1 : (cnt / (2 * 256 * HIST_UNROLL) > 148 * 3 ? 148 * 3 : cnt / (2 * 256 * HIST_UNROLL)));
         histogram_kernel<256><<<blocks, 256, size_t(8) * passes * RADIX * 4, ctx->stream>>>(reinterpret_cast<const u64*>(keys) + first, cnt, begin_bit, end_bit, passes, hist);
         CSA_LAUNCH_CHECK(ctx);
     }
@@ -640,7 +669,7 @@ extern "C" int csa_sort_pairs_static(void* stream_, uint64_t* keys, uint64_t* ke
     const u64 tiles = div_up(n, ST_TILE);
     // The array keeps the last call's contents: everything that must start at zero is cleared here.
     if(cudaMemsetAsync(base_addr + ST_OFF_COUNTER, 0, ST_BYTES - ST_OFF_COUNTER, stream) != cudaSuccess) return CSA_E_CUDA;
-    const unsigned hblocks = unsigned(n / (2 * 256 * 8) < 1 ? 1 : (n / (2 * 256 * 8) > 148 * 8 ? 148 * 8 : n / (2 * 256 * 8)));
+    const unsigned hblocks = unsigned(n / (2 * 256 * HIST_UNROLL) < 1 ? 1 : (n / (2 * 256 * HIST_UNROLL) > 148 * 3 ? 148 * 3 : n / (2 * 256 * HIST_UNROLL)));
     histogram_kernel<256><<<hblocks, 256, size_t(8) * passes * RADIX * 4, stream>>>(reinterpret_cast<const u64*>(keys), n, begin_bit, end_bit, passes, hist);
     digit_base_kernel<<<passes, RADIX, 0, stream>>>(hist, 1, n, base, skip);
     u64* kin = reinterpret_cast<u64*>(keys); u64* kout = reinterpret_cast<u64*>(keys_alt);

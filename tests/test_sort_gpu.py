@@ -59,6 +59,16 @@ def test_sort_64_bit_values(ctx):
     _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int64) * 3, 0, 40)
 
 
+@pytest.mark.parametrize("n", [1, 2, 5, 4097, 300008])
+def test_sort_of_a_list_on_an_odd_8_byte_boundary(ctx, n):
+    """A partition's records start wherever the partition starts: keys 8-byte aligned only, values 4-byte aligned only."""
+    g = torch.Generator(device="cuda").manual_seed(n)
+    keys = torch.randint(-(1 << 62), 1 << 62, (n + 1,), device="cuda", dtype=torch.int64, generator=g)[1:]
+    vals = torch.arange(n + 1, device="cuda", dtype=torch.int32)[1:]
+    assert keys.data_ptr() % 16 == 8
+    _check(ctx, keys, vals, 0, 64)
+
+
 def test_sort_many_tiles(ctx):
     n = 20_000_003
     g = torch.Generator(device="cuda").manual_seed(3)
