@@ -31,7 +31,7 @@ C2_MEAN_DOC = 1024
 C5_QUERIES = 4_000_000
 # DRAM read + write of one launch of the digit-pass kernel over 31.25 M records (the partition size of config 2), from the ncu
 # capture summarised in profiles/onesweep_pass_kernel__sort_31m_records.md; the algorithmic bytes of that launch are 750e6.
-ONESWEEP_TRAFFIC = 728.4e6
+ONESWEEP_TRAFFIC = 707.9e6
 
 
 def measured_peak_gbs():
