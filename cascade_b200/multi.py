@@ -120,6 +120,25 @@ class ShardedIndex:
         return rows.view(q, max_pos), cnt
 
 
+def upload_text_sharded(text_host, text_dev, scratch=None):
+    """Fills this rank's device copy of the text from host memory with every rank copying only its own 1/world share over
+    PCIe; the shares then meet by one all-gather over NVLink (NCCL). text_host: pinned uint16 tensor, text_dev: device uint16
+    tensor of the same length, the same on every rank. Returns the scratch tensor for reuse."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    host_bytes, dev_bytes = text_host.view(torch.uint8), text_dev.view(torch.uint8)
+    total = dev_bytes.numel()
+    share = (-(-total // world) + 15) // 16 * 16                  # equal shares, whole 16-byte pieces
+    if scratch is None or scratch.numel() != share * world:
+        scratch = torch.empty(share * world, dtype=torch.uint8, device=text_dev.device)
+    lo, hi = min(total, rank * share), min(total, (rank + 1) * share)
+    mine = scratch[rank * share:(rank + 1) * share]
+    if hi > lo:
+        mine[:hi - lo].copy_(host_bytes[lo:hi], non_blocking=True)
+    dist.all_gather_into_tensor(scratch, mine)
+    dev_bytes.copy_(scratch[:total])
+    return scratch
+
+
 def _max_over_ranks(x, device):
     t = torch.tensor([x], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -193,11 +212,12 @@ def bench(args, rank, world, local):
         th.copy_(T.cpu())
         oh = torch.empty(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
         ts = []
+        scratch = None
         for it in range(1 + max(1, min(args.steps, 2))):
             dist.barrier()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            T.copy_(th, non_blocking=True)
+            scratch = upload_text_sharded(th, T, scratch)         # 1/world of the text per rank over PCIe, the rest over NVLink
             _, segs, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
             count = sum(c for _, c in segs)
             oh[:5 * count].copy_(out[:5 * count], non_blocking=True)
@@ -206,8 +226,11 @@ def bench(args, rank, world, local):
             if it > 0:
                 ts.append(dt)
         e_ms = 1e3 * sum(ts) / len(ts)
-        e2e = {"value": n / (e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": 2 * n * world, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms,
-               "api": "csa_build_sa_multi between a pinned host text copy in and a pinned copy of the rank's sa40 slice out"}
+        e2e = {"value": n / (e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": 2 * n, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms,
+               "api": "upload_text_sharded (1/N of the pinned host text per rank, all-gather over NVLink) + csa_build_sa_multi + a pinned copy "
+                      "of the rank's sa40 slice out"}
+        del scratch
+        torch.cuda.empty_cache()
     # ---- batched queries on the index sharded by suffix-array range (BASELINE config 5 over N GPUs) ---------------------
     query = None
     if args.queries > 0:

@@ -97,6 +97,40 @@ def test_allgather_callback_between_two_gloo_ranks():
     assert res[0][1] == want
 
 
+def _upload_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from cascade_b200 import multi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok = True
+    scratch = None
+    for n in (1, 17, 100003):                       # shares are whole 16-byte pieces; the last rank's may be short or empty
+        host = ((torch.arange(n, dtype=torch.int64) * 2654435761) % 65521).to(torch.int32).to(torch.uint16)
+        dev = torch.zeros(n, dtype=torch.uint16)
+        scratch = multi.upload_text_sharded(host, dev, scratch)
+        ok = ok and torch.equal(dev.view(torch.int16), host.view(torch.int16))
+    q.put((rank, ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_text_upload_in_shares_with_all_gather_between_three_gloo_ranks():
+    world, port = 3, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_upload_worker, args=(r, world, port, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    assert res == [(r, True) for r in range(world)]
+
+
 def _shm_worker(rank, world, name, q):
     sys.path.insert(0, ROOT)
     from cascade_b200 import multi
