@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
                                                                const u32* __restrict__ agg, u64* __restrict__ updates)
 {
     __shared__ u32 s_prim[RANK_BLOCK / 32], s_full[RANK_BLOCK / 32], s_act[RANK_BLOCK / 32];
+    __shared__ u32 s_next_head[RANK_TILE], s_next_pos[RANK_TILE];     // the tile's tied records, gathered for a coalesced write
     const u64 first = u64(blockIdx.x) * RANK_TILE + u64(threadIdx.x) * RANK_ITEMS;
     u64 k[RANK_ITEMS];
     const Tile_Flags f = load_flags(keys, count, first, prim_shift, k);
@@ -207,63 +208,75 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
     if(lane_id() == 31) { s_prim[threadIdx.x >> 5] = ip; s_full[threadIdx.x >> 5] = ifl; s_act[threadIdx.x >> 5] = ia; }
     __syncthreads();
     u32 run_p = agg[3 * u64(blockIdx.x)], run_f = agg[3 * u64(blockIdx.x) + 1];
-    u32 out = agg[3 * u64(blockIdx.x) + 2];
-    for(u32 w = 0; w < (threadIdx.x >> 5); ++w) { run_p = max(run_p, s_prim[w]); run_f = max(run_f, s_full[w]); out += s_act[w]; }
+    const u32 out_base = agg[3 * u64(blockIdx.x) + 2];      // where the tile's tied records start in the next list
+    u32 out = 0, tile_active = 0;
+    for(u32 w = 0; w < RANK_BLOCK / 32; ++w)
+    {
+        if(w < (threadIdx.x >> 5)) { run_p = max(run_p, s_prim[w]); run_f = max(run_f, s_full[w]); out += s_act[w]; }
+        tile_active += s_act[w];
+    }
     {
         const u32 up = __shfl_up_sync(0xFFFFFFFFu, ip, 1), uf = __shfl_up_sync(0xFFFFFFFFu, ifl, 1);
         if(lane_id() > 0) { run_p = max(run_p, up); run_f = max(run_f, uf); }
         out += ia - ac;
     }
-    if(first >= count) return;
-
-    // A thread's records are consecutive: positions come in and updates go out as 16-byte vectors where the thread's
-    // stretch is whole and aligned (every tile but the last is, as the lists start on 16-byte boundaries).
-    const bool whole = first + RANK_ITEMS <= count;
-    u32 ps[RANK_ITEMS];
-    if(whole && ((reinterpret_cast<uintptr_t>(pos + first) & 15) == 0))
+    if(first < count)
     {
-        const uint4* v = reinterpret_cast<const uint4*>(pos + first);
-        #pragma unroll
-        for(int i = 0; i < RANK_ITEMS; i += 4) { const uint4 t = v[i / 4]; ps[i] = t.x; ps[i + 1] = t.y; ps[i + 2] = t.z; ps[i + 3] = t.w; }
-    }
-    else
-    {
-        #pragma unroll
-        for(int i = 0; i < RANK_ITEMS; ++i) ps[i] = (first + i < count) ? pos[first + i] : 0;
-    }
-    const bool vector_updates = updates && whole && ((reinterpret_cast<uintptr_t>(updates + first) & 15) == 0);
-    u64 up[RANK_ITEMS];
-
-    #pragma unroll
-    for(int i = 0; i < RANK_ITEMS; ++i)
-    {
-        const u64 idx = first + i;
-        if(idx >= count) break;
-        if(f.prim_head & (1u << i)) run_p = u32(idx) + 1;
-        if(f.full_head & (1u << i)) run_f = u32(idx) + 1;
-        const u32 group_start = run_p - 1, sub_start = run_f - 1;      // indices into the sorted list
-        const u32 head = (prim_shift < 64) ? u32(k[i] >> prim_shift) : fixed_head;
-        const u32 slot = head + (u32(idx) - group_start);
-        const u32 new_head = head + (sub_start - group_start);
-        if(sa + slot != pos + idx) sa[slot] = ps[i];
-        // The new rank goes straight into the inverse array, or, when the array is spread over several GPUs, into a list
-        // of (position, rank) updates that is applied in address order (and, over several GPUs, routed to the positions' owners).
-        const u32 global_rank = u32(global_of(map, head) + (new_head - head));      // a group lies inside one partition
-        up[i] = (u64(ps[i]) << 32) | global_rank;
-        if(updates) { if(!vector_updates) updates[idx] = up[i]; }
-        else *isa_slot(isa, ps[i]) = global_rank;
-        if(f.active & (1u << i))
+        // A thread's records are consecutive: positions come in and updates go out as 16-byte vectors where the thread's
+        // stretch is whole and aligned (every tile but the last is, as the lists start on 16-byte boundaries).
+        const bool whole = first + RANK_ITEMS <= count;
+        u32 ps[RANK_ITEMS];
+        if(whole && ((reinterpret_cast<uintptr_t>(pos + first) & 15) == 0))
         {
-            next_head[out] = new_head;
-            next_pos[out] = ps[i];
-            ++out;
+            const uint4* v = reinterpret_cast<const uint4*>(pos + first);
+            #pragma unroll
+            for(int i = 0; i < RANK_ITEMS; i += 4) { const uint4 t = v[i / 4]; ps[i] = t.x; ps[i + 1] = t.y; ps[i + 2] = t.z; ps[i + 3] = t.w; }
+        }
+        else
+        {
+            #pragma unroll
+            for(int i = 0; i < RANK_ITEMS; ++i) ps[i] = (first + i < count) ? pos[first + i] : 0;
+        }
+        const bool vector_updates = updates && whole && ((reinterpret_cast<uintptr_t>(updates + first) & 15) == 0);
+        u64 up[RANK_ITEMS];
+
+        #pragma unroll
+        for(int i = 0; i < RANK_ITEMS; ++i)
+        {
+            const u64 idx = first + i;
+            if(idx >= count) break;
+            if(f.prim_head & (1u << i)) run_p = u32(idx) + 1;
+            if(f.full_head & (1u << i)) run_f = u32(idx) + 1;
+            const u32 group_start = run_p - 1, sub_start = run_f - 1;      // indices into the sorted list
+            const u32 head = (prim_shift < 64) ? u32(k[i] >> prim_shift) : fixed_head;
+            const u32 slot = head + (u32(idx) - group_start);
+            const u32 new_head = head + (sub_start - group_start);
+            if(sa + slot != pos + idx) sa[slot] = ps[i];
+            // The new rank goes straight into the inverse array, or, when the array is spread over several GPUs, into a list
+            // of (position, rank) updates that is applied in address order (and, over several GPUs, routed to the positions' owners).
+            const u32 global_rank = u32(global_of(map, head) + (new_head - head));      // a group lies inside one partition
+            up[i] = (u64(ps[i]) << 32) | global_rank;
+            if(updates) { if(!vector_updates) updates[idx] = up[i]; }
+            else *isa_slot(isa, ps[i]) = global_rank;
+            if(f.active & (1u << i))
+            {
+                s_next_head[out] = new_head;
+                s_next_pos[out] = ps[i];
+                ++out;
+            }
+        }
+        if(vector_updates)
+        {
+            ulonglong2* dst = reinterpret_cast<ulonglong2*>(updates + first);
+            #pragma unroll
+            for(int i = 0; i < RANK_ITEMS; i += 2) dst[i / 2] = make_ulonglong2(up[i], up[i + 1]);
         }
     }
-    if(vector_updates)
+    __syncthreads();
+    for(u32 j = threadIdx.x; j < tile_active; j += RANK_BLOCK)
     {
-        ulonglong2* dst = reinterpret_cast<ulonglong2*>(updates + first);
-        #pragma unroll
-        for(int i = 0; i < RANK_ITEMS; i += 2) dst[i / 2] = make_ulonglong2(up[i], up[i + 1]);
+        next_head[out_base + j] = s_next_head[j];
+        next_pos[out_base + j] = s_next_pos[j];
     }
 }
 

@@ -47,18 +47,21 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
     u32* const mine = h + (threadIdx.x >> 5) * per_warp;
 
     // 128-bit loads of two keys, HIST_UNROLL of them in flight per thread: the kernel is a single read of the keys and
-    // needs tens of KB outstanding per SM to keep the memory busy.
+    // needs tens of KB outstanding per SM to keep the memory busy. A key is shifted and masked to its sorted bits once,
+    // after which the digit of pass p is byte p of it.
     // A list that starts on an odd 8-byte boundary leaves its first key to the scalar tail below.
     const u64 odd_lead = (n > 0 && (reinterpret_cast<uintptr_t>(keys) & 8)) ? 1 : 0;
     const u64 pairs = (n - odd_lead) >> 1;
     const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(keys + odd_lead);
+    const int width = end_bit - begin_bit;
+    const u64 width_mask = width >= 64 ? ~0ull : ((1ull << width) - 1);
     const u64 chunk = u64(BLOCK) * HIST_UNROLL;
     const u64 stride = u64(gridDim.x) * chunk;
     const u64 rounds = (pairs + stride - 1) / stride;       // whole warps take part in every round: the votes see a full mask
     u64 i = u64(blockIdx.x) * chunk + threadIdx.x;
     for(u64 r = 0; r < rounds; ++r, i += stride)
     {
-        ulonglong2 v[HIST_UNROLL];
+        u64 k[2 * HIST_UNROLL];
         bool live[HIST_UNROLL];
         bool mine_live = true;
         #pragma unroll
@@ -66,25 +69,27 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
         {
             live[j] = i + u64(j) * BLOCK < pairs;
             mine_live = mine_live && live[j];
-            v[j] = make_ulonglong2(0, 0);
-            if(live[j]) v[j] = k2[i + u64(j) * BLOCK];
+            ulonglong2 v = make_ulonglong2(0, 0);
+            if(live[j]) v = k2[i + u64(j) * BLOCK];
+            k[2 * j] = (v.x >> begin_bit) & width_mask;
+            k[2 * j + 1] = (v.y >> begin_bit) & width_mask;
         }
+        // Bits in which any key of the warp differs from the first key of lane 0: a pass whose byte of them is zero has one
+        // digit in the whole warp (the high bytes of token ids over long stretches), and one lane counts for all.
+        const u64 k0 = __shfl_sync(0xFFFFFFFFu, k[0], 0);
+        u64 diff = 0;
+        #pragma unroll
+        for(int j = 0; j < 2 * HIST_UNROLL; ++j) diff |= k[j] ^ k0;
+        const u32 diff_lo = __reduce_or_sync(0xFFFFFFFFu, u32(diff)), diff_hi = __reduce_or_sync(0xFFFFFFFFu, u32(diff >> 32));
         const bool all_live = __all_sync(0xFFFFFFFFu, mine_live);
-        #pragma unroll 1
-        for(int p = 0; p < passes; ++p)
+        #pragma unroll
+        for(int p = 0; p < 8; ++p)
         {
-            const int sh = begin_bit + p * RADIX_BITS;
-            const u32 dm = digit_mask(sh, end_bit);
-            u32 d[2 * HIST_UNROLL];
-            #pragma unroll
-            for(int j = 0; j < HIST_UNROLL; ++j) { d[2 * j] = u32(v[j].x >> sh) & dm; d[2 * j + 1] = u32(v[j].y >> sh) & dm; }
-            const u32 lead = __shfl_sync(0xFFFFFFFFu, d[0], 0);
-            bool same = true;
-            #pragma unroll
-            for(int j = 0; j < 2 * HIST_UNROLL; ++j) same = same && d[j] == lead;
-            if(all_live && __all_sync(0xFFFFFFFFu, same))
+            if(p >= passes) break;
+            const u32 dbyte = ((p < 4 ? diff_lo : diff_hi) >> (8 * (p & 3))) & 0xFFu;
+            if(all_live && dbyte == 0)
             {
-                if(lane_id() == 0) atomicAdd(&mine[p * RADIX + lead], u32(64 * HIST_UNROLL));
+                if(lane_id() == 0) atomicAdd(&mine[p * RADIX + (u32(k0 >> (8 * p)) & 0xFFu)], u32(64 * HIST_UNROLL));
             }
             else
             {
@@ -92,8 +97,8 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
                 for(int j = 0; j < HIST_UNROLL; ++j)
                     if(live[j])
                     {
-                        atomicAdd(&mine[p * RADIX + d[2 * j]], 1u);
-                        atomicAdd(&mine[p * RADIX + d[2 * j + 1]], 1u);
+                        atomicAdd(&mine[p * RADIX + (u32(k[2 * j] >> (8 * p)) & 0xFFu)], 1u);
+                        atomicAdd(&mine[p * RADIX + (u32(k[2 * j + 1] >> (8 * p)) & 0xFFu)], 1u);
                     }
             }
         }
