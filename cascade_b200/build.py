@@ -60,13 +60,15 @@ def build(force=False, verbose=False):
 
 
 def build_tools():
-    """The command lines of the drop-in surface: bin/cascade and bin/query, linked against the library."""
+    """The command lines of the drop-in surface: bin/cascade and bin/query, linked against the library, and bin/sa_convert
+    (host code only)."""
     bindir = os.path.join(HERE, "bin")
     os.makedirs(bindir, exist_ok=True)
     for name, src in (("cascade", "cascade_main.cpp"), ("query", "query_main.cpp")):
         cmd = [_nvcc(), "-O2", "-std=c++17", os.path.join(CSRC, "host", src), "-o", os.path.join(bindir, name), "-L" + HERE, "-lcascade_b200",
                "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/..", "-lcudart"]
         subprocess.check_call(cmd)
+    subprocess.check_call(["g++", "-O2", "-std=c++17", os.path.join(CSRC, "host", "sa_convert_main.cpp"), "-o", os.path.join(bindir, "sa_convert")])
 
 
 if __name__ == "__main__":

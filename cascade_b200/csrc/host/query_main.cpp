@@ -134,15 +134,20 @@ int run_find(const Args& a)
     std::vector<uint16_t> T(n + CSA_TEXT_PAD, 0);
     std::vector<uint8_t> SA(5 * n + CSA_SA_PAD_BYTES, 0);
     if(!read_file(m.text, T.data(), 2 * n, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
+    // Part i holds the bytes [sa_part_off[i], sa_part_off[i + 1]) of the array's byte stream, from the start of its file.
     uint64_t at = 0;
     for(size_t i = 0; i < m.sa_part.size(); ++i)
     {
+        const uint64_t begin = m.sa_part_off[i], end = (i + 1 < m.sa_part.size() ? m.sa_part_off[i + 1] : 5 * n);
         uint64_t b = 0;
         if(!file_size(m.sa_part[i], b)) { std::fprintf(stderr, "error: cannot open %s\n", m.sa_part[i].c_str()); return 1; }
-        b -= std::min(b, m.sa_part_off[i]);
-        b = std::min(b, 5 * n - at);
+        if(begin != at || end < begin || end > 5 * n || b != end - begin)
+        {
+            std::fprintf(stderr, "error: suffix-array part %s has %" PRIu64 " bytes; expected %" PRIu64 "\n", m.sa_part[i].c_str(), b, end - begin);
+            return 1;
+        }
         FILE* f = std::fopen(m.sa_part[i].c_str(), "rb");
-        if(!f || std::fseek(f, long(m.sa_part_off[i]), SEEK_SET) != 0 || std::fread(SA.data() + at, 1, b, f) != b) { std::fprintf(stderr, "error: cannot read %s\n", m.sa_part[i].c_str()); return 1; }
+        if(!f || std::fread(SA.data() + at, 1, b, f) != b) { std::fprintf(stderr, "error: cannot read %s\n", m.sa_part[i].c_str()); return 1; }
         std::fclose(f);
         at += b;
     }

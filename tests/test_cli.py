@@ -55,6 +55,70 @@ def test_query_gen_and_info_without_a_gpu(tmp_path):
     assert r.returncode != 0 and "Usage: cascade <text-file> <suffix-array-file>" in r.stderr
 
 
+def test_sa_convert_modes_without_a_gpu(tmp_path, oracle):
+    """`sa_convert` (host code): 64-bit entries into 5-byte parts with range, permutation and order checks; metadata for a
+    finished 5-byte array; widening back. A damaged array is refused."""
+    from cascade_b200 import api
+    from conftest import sa40_to_u64
+    tmp = str(tmp_path)
+    n = 20011
+    T = api.gen_corpus_host(n, 3, 64)[:n]
+    T.astype("<u2").tofile(os.path.join(tmp, "text.u16"))
+    sa40 = oracle.build_sa40(T)[:5 * n]
+    sa64 = sa40_to_u64(sa40, n).astype("<u8")
+    sa64.tofile(os.path.join(tmp, "sa.u64"))
+    tool = os.path.join(BIN, "sa_convert")
+    common = ["--text", os.path.join(tmp, "text.u16"), "--sym-bytes", "2"]
+
+    # conversion into one part, every adjacent pair checked
+    idx = os.path.join(tmp, "idx")
+    r = subprocess.run([tool, "--in", os.path.join(tmp, "sa.u64"), "--index-dir", idx, "--spot", str(n), "--sep", "65535"] + common, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert np.array_equal(np.fromfile(os.path.join(idx, "sa.u40"), dtype=np.uint8), sa40)
+    r = subprocess.run([os.path.join(BIN, "query"), "info", "--index", idx], capture_output=True, text=True)
+    kv = _kv(r.stdout)
+    assert r.returncode == 0 and kv["n"] == str(n) and kv["sa_part_c"] == "1" and kv["sep"] == "65535"
+
+    # conversion into three parts cut at 4096-byte pages
+    dirs = [os.path.join(tmp, f"d{i}") for i in range(3)]
+    idx3 = os.path.join(tmp, "idx3")
+    r = subprocess.run([tool, "--in", os.path.join(tmp, "sa.u64"), "--index-dir", idx3, "--parts", "3", "--part-dirs", ":".join(dirs)] + common,
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    parts = [np.fromfile(os.path.join(d, f"sa.u40.part{i}"), dtype=np.uint8) for i, d in enumerate(dirs)]
+    assert np.array_equal(np.concatenate(parts), sa40)
+    meta = _kv(open(os.path.join(idx3, "index.meta")).read())
+    offs = [int(meta[f"sa_part_off_{i}"]) for i in range(3)]
+    assert offs[0] == 0 and all(o % 4096 == 0 for o in offs) and offs == [0, parts[0].size, parts[0].size + parts[1].size]
+
+    # metadata only, for the array a build left behind
+    sa40.tofile(os.path.join(tmp, "native.sa40"))
+    idxm = os.path.join(tmp, "idxm")
+    r = subprocess.run([tool, "--meta-only", "--sa", os.path.join(tmp, "native.sa40"), "--index-dir", idxm] + common, capture_output=True, text=True)
+    assert r.returncode == 0 and "order spot-check passed" in r.stderr
+    assert _kv(open(os.path.join(idxm, "index.meta")).read())["sa_part_0"] == os.path.join(tmp, "native.sa40")
+
+    # widening returns the 64-bit entries
+    r = subprocess.run([tool, "--widen", "--in", os.path.join(tmp, "native.sa40"), "--out", os.path.join(tmp, "back.u64")], capture_output=True, text=True)
+    assert r.returncode == 0 and np.array_equal(np.fromfile(os.path.join(tmp, "back.u64"), dtype="<u8"), sa64)
+
+    # refusals: a duplicate entry, an entry out of range, two entries out of order, a bad command line
+    bad = sa64.copy(); bad[7] = bad[8]
+    bad.tofile(os.path.join(tmp, "dup.u64"))
+    r = subprocess.run([tool, "--in", os.path.join(tmp, "dup.u64"), "--index-dir", os.path.join(tmp, "x1")] + common, capture_output=True, text=True)
+    assert r.returncode == 1 and "not a permutation" in r.stderr
+    bad = sa64.copy(); bad[5] = n
+    bad.tofile(os.path.join(tmp, "range.u64"))
+    r = subprocess.run([tool, "--in", os.path.join(tmp, "range.u64"), "--index-dir", os.path.join(tmp, "x2"), "--check", "range"] + common, capture_output=True, text=True)
+    assert r.returncode == 1 and "out of range" in r.stderr
+    bad = sa64.copy(); bad[[100, 101]] = bad[[101, 100]]
+    bad.tofile(os.path.join(tmp, "swap.u64"))
+    r = subprocess.run([tool, "--in", os.path.join(tmp, "swap.u64"), "--index-dir", os.path.join(tmp, "x3"), "--spot", str(n)] + common, capture_output=True, text=True)
+    assert r.returncode == 1 and "order violated" in r.stderr and not os.path.exists(os.path.join(tmp, "x3", "index.meta"))
+    r = subprocess.run([tool, "--meta-only", "--text", os.path.join(tmp, "text.u16"), "--sym-bytes", "2", "--index-dir", tmp], capture_output=True, text=True)
+    assert r.returncode == 2 and "--meta-only requires --sa" in r.stderr
+
+
 @pytest.mark.gpu
 def test_cascade_and_query_find_against_the_oracle(tmp_path, oracle):
     from cascade_b200 import api
@@ -90,6 +154,16 @@ def test_cascade_and_query_find_against_the_oracle(tmp_path, oracle):
     cnt = np.fromfile(os.path.join(tmp, "a.cnt"), dtype="<u8")
     assert np.array_equal(itv, want_itv) and np.array_equal(cnt, want_itv[1::2] - want_itv[0::2])
     assert kv["validate"] == "ok" and int(kv["counts_hash"], 16) == oracle.counts_hash(want_itv)
+    # the same array split into two parts by sa_convert answers the same
+    tool = os.path.join(BIN, "sa_convert")
+    assert subprocess.run([tool, "--widen", "--in", os.path.join(tmp, "text.sa40"), "--out", os.path.join(tmp, "text.u64")], capture_output=True).returncode == 0
+    idx2 = os.path.join(tmp, "idx2")
+    r2 = subprocess.run([tool, "--in", os.path.join(tmp, "text.u64"), "--text", os.path.join(tmp, "text.u16"), "--sym-bytes", "2", "--index-dir", idx2, "--parts", "2",
+                         "--part-dirs", os.path.join(tmp, "p0") + ":" + os.path.join(tmp, "p1"), "--sep", "65535"], capture_output=True, text=True)
+    assert r2.returncode == 0, r2.stderr
+    r2 = subprocess.run([os.path.join(BIN, "query"), "find", "--index", idx2, "--queries", q, "--reps", "1"], capture_output=True, text=True)
+    assert r2.returncode == 0, r2.stderr
+    assert _kv(r2.stdout)["counts_hash"] == kv["counts_hash"]
     blob = np.fromfile(os.path.join(tmp, "a.pos"), dtype="<u8")
     qn, total = int(blob[0]), int(blob[1])
     poff, pos = blob[2:2 + qn + 1], blob[2 + qn + 1:]
