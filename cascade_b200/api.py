@@ -229,15 +229,17 @@ class SuffixIndex:
         return rows
 
     def find(self, off_dev, sym_dev, q):
-        itv = torch.zeros(2 * q, dtype=torch.int64, device=self.text.device)
+        itv = torch.empty(2 * q, dtype=torch.int64, device=self.text.device)     # every interval is written
         torch.cuda.synchronize(self.text.device)
         self.ctx.check(self.ctx.L.csa_find(self.ctx.h, ctypes.byref(self.c), off_dev.data_ptr(), sym_dev.data_ptr(), q, itv.data_ptr()))
         self.ctx.sync()
         return itv
 
     def locate(self, itv_dev, q, max_pos=100):
-        pos = torch.zeros(q * max_pos, dtype=torch.int64, device=self.text.device)
-        cnt = torch.zeros(q, dtype=torch.int32, device=self.text.device)
+        """Rows of up to max_pos positions per query, in rank order, and how many each row holds; a row's entries beyond its
+        count are unspecified (the buffer is not cleared: clearing 800 B per query would cost as much as the lookup)."""
+        pos = torch.empty(q * max_pos, dtype=torch.int64, device=self.text.device)
+        cnt = torch.empty(q, dtype=torch.int32, device=self.text.device)
         torch.cuda.synchronize(self.text.device)
         self.ctx.check(self.ctx.L.csa_locate(self.ctx.h, ctypes.byref(self.c), itv_dev.data_ptr(), q, max_pos, pos.data_ptr(), cnt.data_ptr()))
         self.ctx.sync()
