@@ -149,7 +149,7 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     }
     // The ranks of generation 0 reach the inverse array in address order: one keys-only digit pass, then a streaming apply.
     const int position_bits = bits_for(n - 1);
-    CSA_TRY(apply_updates_in_address_order(ctx, isa, upd, keysA, n, position_bits, sort_ws, L.sort_ws));
+    CSA_TRY(apply_updates_in_address_order(ctx, isa, upd, keysA, n, position_bits, sort_ws, L.sort_ws, true));     // every position was ranked once
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaEventRecord(ev.e[2], ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

@@ -118,6 +118,77 @@ __global__ void keys_add_kernel(const u32* __restrict__ perm, const u32* __restr
     if(j < count) keys[perm[j]] += u64(resp[j]) + h;
 }
 
+// Updates into 256 buckets by the top 8 bits of their position, for a list that holds every position of [0, n) exactly once:
+// bucket b then holds exactly the positions [b << low_bits, (b + 1) << low_bits) and starts at entry b << low_bits, so nothing
+// has to be counted first; and as the order inside a bucket does not matter, a record's place in its tile's run is simply what
+// a shared-memory atomic hands out (no stable ranking, no look-back): a block counts, reserves one run per bucket with an
+// atomic on the bucket's cursor, stages its records by bucket and writes coalesced runs. cursor: 256 words, zeroed.
+constexpr int BU_BLOCK = 256, BU_ITEMS = 16, BU_TILE = BU_BLOCK * BU_ITEMS;
+__global__ void __launch_bounds__(BU_BLOCK) bucket_updates_kernel(const u64* __restrict__ in, const u64 count, const int low_bits, u64* __restrict__ out,
+                                                                  u64* __restrict__ cursor, u64* __restrict__ dev_status)
+{
+    __shared__ u64 stage[BU_TILE];
+    __shared__ u64 base[256];         // entry of `out` where the tile's run of the bucket starts, minus the run's start in the tile
+    __shared__ u32 cnt[256];
+    __shared__ u32 warp_tot[8];
+    const u32 tid = threadIdx.x;
+    const u64 tile_first = u64(blockIdx.x) * BU_TILE;
+    const u32 valid = (count - tile_first < u64(BU_TILE)) ? u32(count - tile_first) : u32(BU_TILE);
+    cnt[tid] = 0;
+    __syncthreads();
+    u64 u[BU_ITEMS];
+    u32 r[BU_ITEMS];
+    #pragma unroll
+    for(int k = 0; k < BU_ITEMS; ++k)
+    {
+        const u32 j = tid + k * BU_BLOCK;
+        if(j < valid) u[k] = __ldcs(in + tile_first + j);
+    }
+    #pragma unroll
+    for(int k = 0; k < BU_ITEMS; ++k)
+    {
+        const u32 j = tid + k * BU_BLOCK;
+        if(j < valid) r[k] = atomicAdd(&cnt[u32(u[k] >> (32 + low_bits)) & 255u], 1u);
+    }
+    __syncthreads();
+    // exclusive scan of the 256 counts (one per thread), then the runs' places
+    const u32 c = cnt[tid];
+    u32 inc = c;
+    #pragma unroll
+    for(int o = 1; o < 32; o <<= 1)
+    {
+        const u32 t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if(int(tid & 31) >= o) inc += t;
+    }
+    if((tid & 31) == 31) warp_tot[tid >> 5] = inc;
+    __syncthreads();
+    u32 pre = 0;
+    for(u32 w = 0; w < (tid >> 5); ++w) pre += warp_tot[w];
+    const u32 start = pre + inc - c;
+    if(c) base[tid] = (u64(tid) << low_bits) + atomicAdd(reinterpret_cast<unsigned long long*>(cursor + tid), (unsigned long long)c) - start;
+    cnt[tid] = start;
+    __syncthreads();
+    #pragma unroll
+    for(int k = 0; k < BU_ITEMS; ++k)
+    {
+        const u32 j = tid + k * BU_BLOCK;
+        if(j < valid) stage[cnt[u32(u[k] >> (32 + low_bits)) & 255u] + r[k]] = u[k];
+    }
+    __syncthreads();
+    #pragma unroll
+    for(int k = 0; k < BU_ITEMS; ++k)
+    {
+        const u32 j = tid + k * BU_BLOCK;
+        if(j < valid)
+        {
+            const u64 v = stage[j];
+            const u64 at = base[u32(v >> (32 + low_bits)) & 255u] + j;
+            if(at < count) out[at] = v;
+            else atomicOr(reinterpret_cast<unsigned long long*>(dev_status), (unsigned long long)CSA_ST_RANGE);    // the list did not cover every position once
+        }
+    }
+}
+
 // Up to CSA_MAX_GPUS contiguous copies in one launch, each possibly into another GPU's memory: every SM streams a share of
 // every segment, so the copies to all peers run side by side over NVLink instead of one after another.
 struct Copy_Segments
@@ -223,7 +294,8 @@ int launch_keys_add(csa_ctx* ctx, const u32* perm, const u32* resp, u64 count, u
     return CSA_OK;
 }
 
-int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* alt, u64 count, int position_bits, void* sort_ws, size_t sort_ws_bytes)
+int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* alt, u64 count, int position_bits, void* sort_ws, size_t sort_ws_bytes,
+                                   bool every_position_once)
 {
     if(count == 0) return CSA_OK;
     const u64* list = upd;
@@ -231,10 +303,21 @@ int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* 
     if(position_bits > 24 && count >= (u64(1) << 20))
     {
         // 8 bits measured best at 2e9 positions: a stretch of the array per bucket (31 MB) stays in L2; 6 bits do not, 10-12 cost a second pass
-        const int top = 32 + position_bits, begin = top - 8;
-        int in_alt = 0;
-        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(upd), reinterpret_cast<uint64_t*>(alt), nullptr, nullptr, 4, count, begin, top, sort_ws, sort_ws_bytes, &in_alt));
-        list = in_alt ? alt : upd;
+        if(every_position_once && sort_ws_bytes >= 256 * sizeof(u64))
+        {
+            u64* cursor = static_cast<u64*>(sort_ws);
+            CSA_CUDA(ctx, cudaMemsetAsync(cursor, 0, 256 * sizeof(u64), ctx->stream));
+            bucket_updates_kernel<<<unsigned(div_up(count, BU_TILE)), BU_BLOCK, 0, ctx->stream>>>(upd, count, position_bits - 8, alt, cursor, ctx->d_status);
+            CSA_LAUNCH_CHECK(ctx);
+            list = alt;
+        }
+        else
+        {
+            const int top = 32 + position_bits, begin = top - 8;
+            int in_alt = 0;
+            CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(upd), reinterpret_cast<uint64_t*>(alt), nullptr, nullptr, 4, count, begin, top, sort_ws, sort_ws_bytes, &in_alt));
+            list = in_alt ? alt : upd;
+        }
     }
     return launch_apply_updates(ctx, isa_local, list, count, 0);
 }

@@ -68,7 +68,8 @@ int launch_apply_updates(csa_ctx* ctx, u32* isa_local, const u64* upd, u64 count
 // The same after one keys-only radix pass on the top bits of the index (positions_bits of them are in use), so that the
 // writes of one stretch of the list fall into one L2-sized stretch of the array. alt holds count records; sort_ws is a
 // sort workspace. Short lists are applied directly.
-int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* alt, u64 count, int position_bits, void* sort_ws, size_t sort_ws_bytes);
+int apply_updates_in_address_order(csa_ctx* ctx, u32* isa_local, u64* upd, u64* alt, u64 count, int position_bits, void* sort_ws, size_t sort_ws_bytes,
+                                   bool every_position_once = false);
 // keys[k] = head[k] << sec_bits | (n - 1 + h - x if x = pos[k] + h >= n, else 0)
 int launch_keys_init(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u64 n, u64 h, int sec_bits, u64* keys);
 // keys[perm[j]] += resp[j] + h

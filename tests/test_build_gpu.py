@@ -98,6 +98,19 @@ def test_config1_16m_tokens_single_partition(ctx, oracle):
     assert np.array_equal(sa_h[:5 * n], want[:5 * n])
 
 
+def test_just_above_16m_tokens_ranks_reach_the_inverse_array_through_buckets(ctx, oracle):
+    """Above 2^24 positions the rank updates are bucketed by the top 8 position bits before they are applied (generation 0 by
+    the counting-free bucket kernel, later generations by a digit pass); the last bucket is ragged here."""
+    from cascade_b200 import api
+    n = (1 << 24) + (1 << 20) + 13
+    Td = api.gen_corpus_device(ctx, n, 7, 256)
+    sa, st = api.build_sa(ctx, Td, n, 16)
+    assert st.generations >= 1
+    Th = Td.cpu().view(torch.int16).numpy().view(np.uint16)
+    want = oracle.build_sa40(Th[:n])
+    assert np.array_equal(sa.cpu().numpy()[:5 * n], want[:5 * n])
+
+
 def test_partition_count_does_not_change_the_result(ctx):
     from cascade_b200 import api
     n = 3_000_000
