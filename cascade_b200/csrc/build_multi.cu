@@ -194,6 +194,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     }
     st.partitions = p_eff;
     lap("splitters + sizes");
+    const Ties_In_Any_Order free_ties(ctx);     // from here on the sorts order suffixes whose ties the next generation resolves
 
     // ---- plan: the same on every rank ------------------------------------------------------------------------------
     std::vector<u64> hist_all(size_t(G) * p_eff), send_hist(my_hist.begin(), my_hist.begin() + p_eff);

@@ -92,6 +92,8 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     }
     st.partitions = p_eff;
 
+    const Ties_In_Any_Order free_ties(ctx);     // from here on the sorts order suffixes whose ties the next generation resolves
+
     // ---- partition ids and sizes ---------------------------------------------------------------------------
     CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, size_t(p_eff) * 8, ctx->stream));
     if(p_eff > 1) CSA_TRY(partition_install_symbol_ranges(ctx, pivots.data(), p_eff, symbol_range));

@@ -41,11 +41,23 @@ struct csa_ctx
     std::string err;
     u64 counters[16] = {0};        // launch and byte counters for the benchmark
     const u32* symbol_range = nullptr;     // optional first-symbol table of csa_partition_ids (see partition_install_symbol_ranges)
+    bool ties_in_any_order = false;        // set by callers whose sorts may leave records of equal keys in any order (see radix_sort.cu)
     void* pass_timer = nullptr;            // digit-pass event timing of the sorts on this context (owned by radix_sort.cu)
     // Mappings of other GPUs' arenas opened through CUDA IPC (multi-GPU builds), kept while the peers' handles stay the same.
     void* peer_base[CSA_MAX_GPUS] = {nullptr};
     unsigned char peer_handle[CSA_MAX_GPUS][64] = {{0}};
     bool peer_open[CSA_MAX_GPUS] = {false};
+};
+
+// While one of these lives, the context's sorts may leave records of equal keys in any order (their first pass is then
+// the cheap unordered one). The builds use it: tied suffixes are re-sorted by the next generation anyway.
+struct Ties_In_Any_Order
+{
+    csa_ctx* ctx;
+    explicit Ties_In_Any_Order(csa_ctx* c) : ctx(c) { ctx->ties_in_any_order = true; }
+    ~Ties_In_Any_Order() { ctx->ties_in_any_order = false; }
+    Ties_In_Any_Order(const Ties_In_Any_Order&) = delete;
+    Ties_In_Any_Order& operator=(const Ties_In_Any_Order&) = delete;
 };
 
 #define CSA_CUDA(ctx, call)                                                                             \

@@ -408,6 +408,106 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
     return CSA_OK;
 }
 
+// ---- the first pass of a sort whose caller accepts records of equal keys in any order --------------------------------
+// The least significant digit's pass has no earlier order to keep, so it need not be stable: a record's place among its
+// tile's records of the same digit is whatever a shared-memory atomic hands out, and a tile's run of a digit goes where
+// an atomic on the digit's global cursor puts it. No warp-level matching, no look-back, a third of the instructions: the
+// pass runs near copy speed. The later passes are stable as before, so the result is a correct sort whose ties come in
+// no particular order (the doubling steps re-sort ties anyway). cursor: the pass's digit offsets; they are advanced.
+constexpr int FP_BLOCK = 256, FP_ITEMS = 16, FP_TILE = FP_BLOCK * FP_ITEMS;
+constexpr size_t FP_SMEM = size_t(FP_TILE) * 12 + RADIX * 8 + RADIX * 4 + 64;
+__global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const u32* __restrict__ vals_in,
+                                                             u32* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
+                                                             u64* __restrict__ cursor)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    u64* const stage_keys = reinterpret_cast<u64*>(smem_raw);
+    u64* const base = stage_keys + FP_TILE;                         // output entry of the tile's run of a digit, minus the run's start in the tile
+    u32* const stage_vals = reinterpret_cast<u32*>(base + RADIX);
+    u32* const cnt = stage_vals + FP_TILE;
+    u32* const warp_tot = cnt + RADIX;
+    static_assert(FP_BLOCK == RADIX, "one thread per digit");
+    const u32 tid = threadIdx.x;
+    const u64 tile_first = u64(blockIdx.x) * FP_TILE;
+    const u32 valid = (n - tile_first < u64(FP_TILE)) ? u32(n - tile_first) : u32(FP_TILE);
+    cnt[tid] = 0;
+    __syncthreads();
+    u64 k[FP_ITEMS];
+    u32 v[FP_ITEMS], r[FP_ITEMS];
+    #pragma unroll
+    for(int i = 0; i < FP_ITEMS; ++i)
+    {
+        const u32 j = tid + i * FP_BLOCK;
+        if(j < valid) k[i] = keys_in[tile_first + j];
+    }
+    #pragma unroll
+    for(int i = 0; i < FP_ITEMS; ++i)
+    {
+        const u32 j = tid + i * FP_BLOCK;
+        if(vals_in != nullptr && j < valid) v[i] = vals_in[tile_first + j];
+    }
+    #pragma unroll
+    for(int i = 0; i < FP_ITEMS; ++i)
+    {
+        const u32 j = tid + i * FP_BLOCK;
+        if(j < valid) r[i] = atomicAdd(&cnt[u32(k[i] >> shift) & dmask], 1u);
+    }
+    __syncthreads();
+    const u32 c = cnt[tid];
+    u32 inc = c;
+    #pragma unroll
+    for(int o = 1; o < 32; o <<= 1)
+    {
+        const u32 t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if(int(tid & 31) >= o) inc += t;
+    }
+    if((tid & 31) == 31) warp_tot[tid >> 5] = inc;
+    __syncthreads();
+    u32 pre = 0;
+    for(u32 w = 0; w < (tid >> 5); ++w) pre += warp_tot[w];
+    const u32 start = pre + inc - c;
+    if(c) base[tid] = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + tid), (unsigned long long)c) - start;
+    cnt[tid] = start;
+    __syncthreads();
+    #pragma unroll
+    for(int i = 0; i < FP_ITEMS; ++i)
+    {
+        const u32 j = tid + i * FP_BLOCK;
+        if(j < valid)
+        {
+            const u32 at = cnt[u32(k[i] >> shift) & dmask] + r[i];
+            stage_keys[at] = k[i];
+            if(vals_in != nullptr) stage_vals[at] = v[i];
+        }
+    }
+    __syncthreads();
+    #pragma unroll
+    for(int i = 0; i < FP_ITEMS; ++i)
+    {
+        const u32 j = tid + i * FP_BLOCK;
+        if(j < valid)
+        {
+            const u64 kk = stage_keys[j];
+            const u64 dst = base[u32(kk >> shift) & dmask] + j;
+            keys_out[dst] = kk;
+            if(vals_in != nullptr) vals_out[dst] = stage_vals[j];
+        }
+    }
+}
+
+int launch_first_pass(csa_ctx* ctx, const u64* kin, u64* kout, const u32* vin, u32* vout, u64 n, int shift, u32 dmask, u64* cursor)
+{
+    static bool configured[64] = {false};
+    if(!configured[ctx->device & 63])
+    {
+        CSA_CUDA(ctx, cudaFuncSetAttribute(first_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(FP_SMEM)));
+        configured[ctx->device & 63] = true;
+    }
+    first_pass_kernel<<<unsigned(div_up(n, FP_TILE)), FP_BLOCK, FP_SMEM, ctx->stream>>>(kin, kout, vin, vout, n, shift, dmask, cursor);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
 // Shapes of the pass kernel to choose from (block size x items per thread); the smallest tile sizes the workspace.
 int g_variant = 0;
 constexpr int PASS_TILE = 4096;     // smallest tile among the variants
@@ -567,12 +667,16 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     u64* kin = reinterpret_cast<u64*>(keys); u64* kout = reinterpret_cast<u64*>(keys_alt);
     void* vin = vals; void* vout = vals_alt;
     int flips = 0;
+    // The first pass that moves anything may leave ties in any order where the caller said so (4-byte values or none).
+    bool first_pass_free = ctx->ties_in_any_order && (val_bytes == 4 || vals == nullptr);
     for(int p = 0; p < passes; ++p)
     {
         if(skip[p]) continue;
         const int shift = begin_bit + p * RADIX_BITS;
+        const bool unordered = first_pass_free;
+        first_pass_free = false;
         cudaEvent_t e0 = nullptr, e1 = nullptr;
-        if(timer.on)
+        if(timer.on && !unordered)          // the timer is the digit-pass kernel's: the unordered pass is another kernel
         {
             CSA_CUDA(ctx, cudaEventCreate(&e0));
             CSA_CUDA(ctx, cudaEventCreate(&e1));
@@ -582,12 +686,15 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
         {
             const u64 first = u64(P) * PORTION, cnt = (n - first < PORTION ? n - first : PORTION);
             u64* db = base + (u64(p) * (portions + 1) + P) * RADIX;
-            if(val_bytes == 4 || vin == nullptr)
+            if(unordered)       // one set of cursors serves all launches of the pass
+                CSA_TRY(launch_first_pass(ctx, kin + first, kout, vin ? static_cast<const u32*>(vin) + first : nullptr, static_cast<u32*>(vout), cnt, shift,
+                                          digit_mask(shift, end_bit), base + u64(p) * (portions + 1) * RADIX));
+            else if(val_bytes == 4 || vin == nullptr)
                 CSA_TRY(launch_pass_variant<u32>(ctx, kin + first, kout, vin ? static_cast<const u32*>(vin) + first : nullptr, static_cast<u32*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
             else
                 CSA_TRY(launch_pass_variant<u64>(ctx, kin + first, kout, static_cast<const u64*>(vin) + first, static_cast<u64*>(vout), cnt, shift, digit_mask(shift, end_bit), db, db + RADIX, status, counter));
         }
-        if(timer.on)
+        if(timer.on && !unordered)
         {
             CSA_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
             timer.ev.push_back(e0); timer.ev.push_back(e1);
