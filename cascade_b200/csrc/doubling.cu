@@ -152,46 +152,39 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_tile_kernel(const u64* __rest
 
 // Phase 2: one block turns the tile aggregates into carries: exclusive running maxima of the heads and the exclusive
 // running sum of the active counts, which starts at the current length of the next list; the length is then advanced.
-// A thread owns a contiguous stretch of tiles: it folds the stretch, the block scans the 1024 folds once, and the thread
-// walks its stretch again to leave the exclusive values: two barriers in all, however many tiles there are.
 __global__ void __launch_bounds__(1024) rank_carry_kernel(u32* __restrict__ agg, const u64 tiles, u64* __restrict__ act_count)
 {
     __shared__ u32 s_a[32], s_b[32];
     __shared__ u64 s_c[32];
-    const u64 per = (tiles + 1023) / 1024;
-    const u64 t0 = u64(threadIdx.x) * per, t1 = (t0 + per < tiles) ? t0 + per : tiles;
-    u32 a = 0, b = 0;
-    u64 c = 0;
-    for(u64 t = t0; t < t1; ++t) { a = max(a, agg[3 * t]); b = max(b, agg[3 * t + 1]); c += agg[3 * t + 2]; }
-    // inclusive scans over the threads: warp, then the 32 warp totals
-    u32 ia = warp_inclusive_max(a), ib = warp_inclusive_max(b);
-    u64 ic = c;
-    #pragma unroll
-    for(int o = 1; o < 32; o <<= 1)
-    {
-        const u64 v = __shfl_up_sync(0xFFFFFFFFu, ic, o);
-        if(int(lane_id()) >= o) ic += v;
-    }
-    if(lane_id() == 31) { s_a[threadIdx.x >> 5] = ia; s_b[threadIdx.x >> 5] = ib; s_c[threadIdx.x >> 5] = ic; }
+    __shared__ u32 carry_a, carry_b;
+    __shared__ u64 carry_c;
+    if(threadIdx.x == 0) { carry_a = 0; carry_b = 0; carry_c = *act_count; }
     __syncthreads();
-    u32 pa = 0, pb = 0;
-    u64 pc = *act_count;
-    for(u32 w = 0; w < (threadIdx.x >> 5); ++w) { pa = max(pa, s_a[w]); pb = max(pb, s_b[w]); pc += s_c[w]; }
+    for(u64 base = 0; base < tiles; base += 1024)
     {
-        const u32 ua = __shfl_up_sync(0xFFFFFFFFu, ia, 1), ub = __shfl_up_sync(0xFFFFFFFFu, ib, 1);
-        if(lane_id() > 0) { pa = max(pa, ua); pb = max(pb, ub); }
-        pc += ic - c;
+        const u64 t = base + threadIdx.x;
+        u32 a = 0, b = 0; u32 c = 0;
+        if(t < tiles) { a = agg[3 * t]; b = agg[3 * t + 1]; c = agg[3 * t + 2]; }
+        const u32 ia = warp_inclusive_max(a), ib = warp_inclusive_max(b), ic = warp_inclusive_sum(c);
+        if(lane_id() == 31) { s_a[threadIdx.x >> 5] = ia; s_b[threadIdx.x >> 5] = ib; s_c[threadIdx.x >> 5] = ic; }
+        __syncthreads();
+        u32 pa = carry_a, pb = carry_b; u64 pc = carry_c;
+        for(u32 w = 0; w < (threadIdx.x >> 5); ++w) { pa = max(pa, s_a[w]); pb = max(pb, s_b[w]); pc += s_c[w]; }
+        // exclusive values for this tile
+        const u32 ea = max(pa, __shfl_up_sync(0xFFFFFFFFu, ia, 1) * (lane_id() > 0));
+        const u32 eb = max(pb, __shfl_up_sync(0xFFFFFFFFu, ib, 1) * (lane_id() > 0));
+        const u64 ec = pc + (ic - c);
+        __syncthreads();
+        if(threadIdx.x == 1023) { carry_a = max(pa, ia); carry_b = max(pb, ib); carry_c = pc + ic; }
+        if(t < tiles)
+        {
+            agg[3 * t] = ea; agg[3 * t + 1] = eb;
+            // the running sum may pass 2^32 only if the list does, which the build's size limit excludes
+            agg[3 * t + 2] = u32(ec);
+        }
+        __syncthreads();
     }
-    __syncthreads();        // every thread has read the list's old length
-    if(threadIdx.x == 1023) *act_count = pc + c;
-    for(u64 t = t0; t < t1; ++t)
-    {
-        const u32 ta = agg[3 * t], tb = agg[3 * t + 1], tc = agg[3 * t + 2];
-        agg[3 * t] = pa; agg[3 * t + 1] = pb;
-        // the running sum may pass 2^32 only if the list does, which the build's size limit excludes
-        agg[3 * t + 2] = u32(pc);
-        pa = max(pa, ta); pb = max(pb, tb); pc += tc;
-    }
+    if(threadIdx.x == 0) *act_count = carry_c;
 }
 
 // Phase 3: every record gets its slot and rank; tied records go to the next list.
