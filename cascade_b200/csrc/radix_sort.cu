@@ -415,7 +415,8 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
 // pass runs near copy speed. The later passes are stable as before, so the result is a correct sort whose ties come in
 // no particular order (the doubling steps re-sort ties anyway). cursor: the pass's digit offsets; they are advanced.
 constexpr int FP_BLOCK = 256, FP_ITEMS = 16, FP_TILE = FP_BLOCK * FP_ITEMS;
-constexpr size_t FP_SMEM = size_t(FP_TILE) * 12 + RADIX * 8 + RADIX * 4 + 64;
+constexpr int FP_COPIES = 4;     // counters per digit, taken by lane: a digit that many records share (the low byte of a frequent token id) then serialises a quarter as many lanes of an atomic instruction
+constexpr size_t FP_SMEM = size_t(FP_TILE) * 12 + RADIX * 8 + RADIX * FP_COPIES * 4 + 64;
 __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const u32* __restrict__ vals_in,
                                                              u32* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
                                                              u64* __restrict__ cursor)
@@ -424,13 +425,14 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
     u64* const stage_keys = reinterpret_cast<u64*>(smem_raw);
     u64* const base = stage_keys + FP_TILE;                         // output entry of the tile's run of a digit, minus the run's start in the tile
     u32* const stage_vals = reinterpret_cast<u32*>(base + RADIX);
-    u32* const cnt = stage_vals + FP_TILE;
-    u32* const warp_tot = cnt + RADIX;
+    u32* const cnt = stage_vals + FP_TILE;                          // [digit][copy]
+    u32* const warp_tot = cnt + RADIX * FP_COPIES;
     static_assert(FP_BLOCK == RADIX, "one thread per digit");
-    const u32 tid = threadIdx.x;
+    const u32 tid = threadIdx.x, copy = tid & (FP_COPIES - 1);
     const u64 tile_first = u64(blockIdx.x) * FP_TILE;
     const u32 valid = (n - tile_first < u64(FP_TILE)) ? u32(n - tile_first) : u32(FP_TILE);
-    cnt[tid] = 0;
+    #pragma unroll
+    for(int j = 0; j < FP_COPIES; ++j) cnt[tid * FP_COPIES + j] = 0;
     __syncthreads();
     u64 k[FP_ITEMS];
     u32 v[FP_ITEMS], r[FP_ITEMS];
@@ -450,10 +452,14 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
     for(int i = 0; i < FP_ITEMS; ++i)
     {
         const u32 j = tid + i * FP_BLOCK;
-        if(j < valid) r[i] = atomicAdd(&cnt[u32(k[i] >> shift) & dmask], 1u);
+        if(j < valid) r[i] = atomicAdd(&cnt[(u32(k[i] >> shift) & dmask) * FP_COPIES + copy], 1u);
     }
     __syncthreads();
-    const u32 c = cnt[tid];
+    // thread d: the digit's count over its copies, an exclusive scan over the digits, and the copies' starts inside the run
+    u32 cc[FP_COPIES];
+    u32 c = 0;
+    #pragma unroll
+    for(int j = 0; j < FP_COPIES; ++j) { cc[j] = cnt[tid * FP_COPIES + j]; c += cc[j]; }
     u32 inc = c;
     #pragma unroll
     for(int o = 1; o < 32; o <<= 1)
@@ -467,7 +473,11 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
     for(u32 w = 0; w < (tid >> 5); ++w) pre += warp_tot[w];
     const u32 start = pre + inc - c;
     if(c) base[tid] = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + tid), (unsigned long long)c) - start;
-    cnt[tid] = start;
+    {
+        u32 run = start;
+        #pragma unroll
+        for(int j = 0; j < FP_COPIES; ++j) { cnt[tid * FP_COPIES + j] = run; run += cc[j]; }
+    }
     __syncthreads();
     #pragma unroll
     for(int i = 0; i < FP_ITEMS; ++i)
@@ -475,7 +485,7 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
         const u32 j = tid + i * FP_BLOCK;
         if(j < valid)
         {
-            const u32 at = cnt[u32(k[i] >> shift) & dmask] + r[i];
+            const u32 at = cnt[(u32(k[i] >> shift) & dmask) * FP_COPIES + copy] + r[i];
             stage_keys[at] = k[i];
             if(vals_in != nullptr) stage_vals[at] = v[i];
         }
