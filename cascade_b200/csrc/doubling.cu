@@ -197,6 +197,24 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
     __shared__ u32 s_prim[RANK_BLOCK / 32], s_full[RANK_BLOCK / 32], s_act[RANK_BLOCK / 32];
     __shared__ u32 s_next_head[RANK_TILE], s_next_pos[RANK_TILE];     // the tile's tied records, gathered for a coalesced write
     const u64 first = u64(blockIdx.x) * RANK_TILE + u64(threadIdx.x) * RANK_ITEMS;
+    // Everything the block reads is asked for at once: the tile's carries, the thread's positions, then its keys.
+    const u32 carry_p = agg[3 * u64(blockIdx.x)], carry_f = agg[3 * u64(blockIdx.x) + 1];
+    const u32 out_base = agg[3 * u64(blockIdx.x) + 2];      // where the tile's tied records start in the next list
+    // A thread's records are consecutive: positions come in and updates go out as 16-byte vectors where the thread's
+    // stretch is whole and aligned (every tile but the last is, as the lists start on 16-byte boundaries).
+    const bool whole = first + RANK_ITEMS <= count;
+    u32 ps[RANK_ITEMS];
+    if(whole && ((reinterpret_cast<uintptr_t>(pos + first) & 15) == 0))
+    {
+        const uint4* v = reinterpret_cast<const uint4*>(pos + first);
+        #pragma unroll
+        for(int i = 0; i < RANK_ITEMS; i += 4) { const uint4 t = v[i / 4]; ps[i] = t.x; ps[i + 1] = t.y; ps[i + 2] = t.z; ps[i + 3] = t.w; }
+    }
+    else
+    {
+        #pragma unroll
+        for(int i = 0; i < RANK_ITEMS; ++i) ps[i] = (first + i < count) ? pos[first + i] : 0;
+    }
     u64 k[RANK_ITEMS];
     const Tile_Flags f = load_flags(keys, count, first, prim_shift, k);
 
@@ -207,8 +225,7 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
     const u32 ip = warp_inclusive_max(lp), ifl = warp_inclusive_max(lf), ia = warp_inclusive_sum(ac);
     if(lane_id() == 31) { s_prim[threadIdx.x >> 5] = ip; s_full[threadIdx.x >> 5] = ifl; s_act[threadIdx.x >> 5] = ia; }
     __syncthreads();
-    u32 run_p = agg[3 * u64(blockIdx.x)], run_f = agg[3 * u64(blockIdx.x) + 1];
-    const u32 out_base = agg[3 * u64(blockIdx.x) + 2];      // where the tile's tied records start in the next list
+    u32 run_p = carry_p, run_f = carry_f;
     u32 out = 0, tile_active = 0;
     for(u32 w = 0; w < RANK_BLOCK / 32; ++w)
     {
@@ -222,21 +239,6 @@ __global__ void __launch_bounds__(RANK_BLOCK) rank_apply_kernel(const u64* __res
     }
     if(first < count)
     {
-        // A thread's records are consecutive: positions come in and updates go out as 16-byte vectors where the thread's
-        // stretch is whole and aligned (every tile but the last is, as the lists start on 16-byte boundaries).
-        const bool whole = first + RANK_ITEMS <= count;
-        u32 ps[RANK_ITEMS];
-        if(whole && ((reinterpret_cast<uintptr_t>(pos + first) & 15) == 0))
-        {
-            const uint4* v = reinterpret_cast<const uint4*>(pos + first);
-            #pragma unroll
-            for(int i = 0; i < RANK_ITEMS; i += 4) { const uint4 t = v[i / 4]; ps[i] = t.x; ps[i + 1] = t.y; ps[i + 2] = t.z; ps[i + 3] = t.w; }
-        }
-        else
-        {
-            #pragma unroll
-            for(int i = 0; i < RANK_ITEMS; ++i) ps[i] = (first + i < count) ? pos[first + i] : 0;
-        }
         const bool vector_updates = updates && whole && ((reinterpret_cast<uintptr_t>(updates + first) & 15) == 0);
         u64 up[RANK_ITEMS];
 
