@@ -180,6 +180,7 @@ __global__ void gather_windows_kernel(const u8* __restrict__ sa40, const Bracket
     {
         const u64 first = side ? b.hi_first : b.lo_first, last = side ? b.hi_last : b.lo_last;
         if(last < first || !window_fits(first, last)) continue;
+        if(side == 1 && b.hi_first == b.lo_first && b.hi_last == b.lo_last) continue;     // one window serves both searches (patterns longer than K)
         const u64 byte0 = (5 * first) & ~u64(15), byte1 = 5 * last + 5 + 4;       // entry `last` may be probed; a load reads 8 bytes
         const u32 pieces = u32((byte1 - byte0 + 15) >> 4);
         const uint4* src = reinterpret_cast<const uint4*>(sa40 + byte0);
@@ -200,7 +201,11 @@ __global__ void search_windows_kernel(const csa_index idx, const u64* __restrict
     const u8* sa_lo = idx.sa40;
     const u8* sa_hi = idx.sa40;
     if(br.lo_last >= br.lo_first && window_fits(br.lo_first, br.lo_last)) sa_lo = win + (2 * i) * WINDOW_BYTES - ((5 * br.lo_first) & ~u64(15));
-    if(br.hi_last >= br.hi_first && window_fits(br.hi_first, br.hi_last)) sa_hi = win + (2 * i + 1) * WINDOW_BYTES - ((5 * br.hi_first) & ~u64(15));
+    if(br.hi_last >= br.hi_first && window_fits(br.hi_first, br.hi_last))
+    {
+        const bool shared = br.hi_first == br.lo_first && br.hi_last == br.lo_last;
+        sa_hi = win + (2 * i + (shared ? 0 : 1)) * WINDOW_BYTES - ((5 * br.hi_first) & ~u64(15));
+    }
     u64 lo, hi;
     search_brackets(idx, br, sym + (off[i] - off[0]), m, sa_lo, sa_hi, lo, hi);
     itv[2 * i] = lo;
