@@ -2,6 +2,8 @@
 // ONE sweep over the records: a tile ranks its records by digit with warp-level multisplit (match.any), publishes
 // its per-digit counts, finds its global offsets by looking back over the tiles before it (decoupled look-back),
 // stages the records in shared memory in digit order and writes them out in coalesced runs.
+// Every pass is stable. Where the caller accepts records of equal keys in any order (the suffix-array builds do), the
+// first pass is replaced by a cheaper unordered one (first_pass_kernel below): it has no earlier order to keep.
 //
 // It stands where the reference calls cub::DeviceRadixSort::SortPairs (src/GPU_SACA.cu:1175, 1203, 1783, 1849);
 // no library sort is used.
