@@ -403,8 +403,14 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
         configured[ctx->device & 63] = true;
     }
     const u64 tiles = div_up(n, S::TILE);
-    CSA_CUDA(ctx, cudaMemsetAsync(status, 0, tiles * RADIX * sizeof(u32), ctx->stream));
-    CSA_CUDA(ctx, cudaMemsetAsync(counter, 0, sizeof(u32), ctx->stream));
+    // The tile counter lies right before the status words (csa_sort_pairs carves them so): one clear covers both.
+    if(reinterpret_cast<unsigned char*>(counter) + 256 == reinterpret_cast<unsigned char*>(status))
+        CSA_CUDA(ctx, cudaMemsetAsync(counter, 0, 256 + tiles * RADIX * sizeof(u32), ctx->stream));
+    else
+    {
+        CSA_CUDA(ctx, cudaMemsetAsync(status, 0, tiles * RADIX * sizeof(u32), ctx->stream));
+        CSA_CUDA(ctx, cudaMemsetAsync(counter, 0, sizeof(u32), ctx->stream));
+    }
     kern<<<unsigned(tiles), BLOCK, S::bytes, ctx->stream>>>(kin, kout, vin, vout, n, shift, dmask, digit_base, next_base, status, counter, ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
@@ -571,8 +577,8 @@ const u64* sort_workspace_histograms(void* workspace, size_t workspace_bytes, u6
 {
     Carver cv(workspace, workspace_bytes);
     const u64 tiles_max = div_up(n < PORTION ? n : PORTION, PASS_TILE) + 1;
-    cv.take<u32>(tiles_max * RADIX);
     cv.take<u32>(64);
+    cv.take<u32>(tiles_max * RADIX);
     return cv.take<u64>(u64(8) * RADIX);
 }
 
@@ -645,8 +651,8 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     const int portions = int(div_up(n, PORTION));
     Carver cv(workspace, workspace_bytes);
     const u64 tiles_max = div_up(n < PORTION ? n : PORTION, PASS_TILE) + 1;
+    u32* counter = cv.take<u32>(64);                     // 256 bytes, directly before the status words
     u32* status = cv.take<u32>(tiles_max * RADIX);
-    u32* counter = cv.take<u32>(64);
     u64* hist = cv.take<u64>(u64(8) * RADIX);
     u64* base = cv.take<u64>(u64(portions + 1) * 8 * RADIX);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "csa_sort_pairs: workspace too small");
