@@ -6,7 +6,11 @@
 One step = one whole build of the suffix array of the seeded Zipf corpus (BASELINE config 2 at N = 1: 2e9 u16 tokens,
 K = 8 splitters, 64 partitions, everything resident in one GPU's HBM). `value` times the build with the text already
 in HBM (CUDA events on the library's stream); `e2e` times the host-buffer entry point (pinned host text in, 5-byte
-suffix array out, copies inside the timed region). Prints ONE JSON line on rank 0.
+suffix array out, copies inside the timed region). Every array that a number is quoted on is checked in full on the
+device (permutation + order of every neighbouring pair) outside the timed region. Prints ONE JSON line on rank 0.
+
+`--impl reference` times the reference's own CPU builder on the box's host cores, on a bounded sample of the same corpus;
+it loads nothing but the CPU checkers under oracle/.
 """
 import argparse
 import ctypes
@@ -28,10 +32,11 @@ UNIT = "suffixes/s"
 C2_TOKENS = 2_000_000_000
 C2_PARTITIONS = 64
 C2_MEAN_DOC = 1024
+C3_TOKENS = 1_000_000_000
 C5_QUERIES = 4_000_000
-# DRAM read + write of one launch of the digit-pass kernel over 31.25 M records (the partition size of config 2), from the ncu
-# capture summarised in profiles/onesweep_pass_kernel__sort_31m_records.md; the algorithmic bytes of that launch are 750e6.
-ONESWEEP_TRAFFIC = 707.9e6
+# DRAM read + write of one launch of the digit-pass kernel over 31.25 M records (the partition size of config 2), taken from
+# an ncu capture of that launch, not measured by the run that prints it; the algorithmic bytes of that launch are 750e6.
+ONESWEEP_TRAFFIC_FROM_PROFILE = 707.9e6
 
 
 def measured_peak_gbs():
@@ -80,42 +85,88 @@ class ClockSampler:
                 "samples": len(self.rows)}
 
 
-def ref_lib():
-    p = os.path.join(ROOT, "oracle", "_ref", "libcascade_ref.so")
-    if os.path.exists(p):
-        return ctypes.CDLL(p), "reference"
-    subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "liboracle.so"], stdout=subprocess.DEVNULL)
-    return ctypes.CDLL(os.path.join(ROOT, "oracle", "liboracle.so")), "port"
+# ---- the CPU side: the reference's own code (oracle/_ref) or the C restatement (oracle/liboracle.so) -------------------------
+
+def zipf_cdf(vocab=50257, s=1.1):
+    """64-bit inverse-CDF thresholds of Zipf(s) over ranks 1..vocab (the same table as cascade_b200.api.zipf_cdf, kept here
+    so that the CPU arm needs nothing of the product)."""
+    w = np.arange(1, vocab + 1, dtype=np.float64) ** (-s)
+    c = np.cumsum(w)
+    c /= c[-1]
+    t = np.minimum(np.floor(c * 18446744073709551616.0), 18446744073709551615.0)
+    out = np.array([int(x) if x < 18446744073709551615.0 else 0xFFFFFFFFFFFFFFFF for x in t], dtype=np.uint64)
+    out[-1] = np.uint64(0xFFFFFFFFFFFFFFFF)
+    return out
 
 
-def cpu_build_once(L, kind, T, n, out):
-    """One CPU build of the sample with all host threads: the reference's comparator under a parallel sort
-    (oracle/_ref), or the C port's parallel merge sort."""
-    t0 = time.perf_counter()
-    if kind == "reference":
-        L.ref_build_sa40_parallel(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(n), out.ctypes.data_as(ctypes.c_void_p))
-    else:
-        L.orc_build_sa40(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(n), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(0))
-    return time.perf_counter() - t0
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
 
 
-def cpu_threads(L, kind):
-    if kind == "reference":
-        L.ref_thread_count.restype = ctypes.c_uint
-        return int(L.ref_thread_count())
-    L.orc_max_threads.restype = ctypes.c_int
-    return int(L.orc_max_threads())
+class CpuSide:
+    """The CPU checkers, with their thread count set by hand: a launcher such as torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its children, which would leave all but one core idle."""
+
+    def __init__(self):
+        self.threads = host_threads()
+        os.environ["OMP_NUM_THREADS"] = str(self.threads)          # read by the OpenMP runtime when it is first loaded
+        orc = os.path.join(ROOT, "oracle", "liboracle.so")
+        if not os.path.exists(orc):
+            subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "liboracle.so"], stdout=subprocess.DEVNULL)
+        self.orc = ctypes.CDLL(orc)
+        self.orc.orc_set_threads(ctypes.c_int(self.threads))
+        ref = os.path.join(ROOT, "oracle", "_ref", "libcascade_ref.so")
+        self.ref = ctypes.CDLL(ref) if os.path.exists(ref) else None
+        if self.ref is not None:
+            self.ref.ref_set_threads(ctypes.c_int(self.threads))
+        self.kind = "reference" if self.ref is not None else "port"
+
+    def corpus(self, n, mean_doc, seed=0):
+        cdf = zipf_cdf()
+        T = np.zeros(n + 64, dtype=np.uint16)
+        self.orc.orc_gen_corpus(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(0), ctypes.c_uint64(n), ctypes.c_uint64(seed),
+                                ctypes.c_uint32(mean_doc), cdf.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint32(len(cdf)))
+        return T
+
+    def build_once(self, T, n, out):
+        """One CPU build with all host threads: the reference's comparator under a parallel sort (oracle/_ref), or the C
+        port's parallel merge sort."""
+        t0 = time.perf_counter()
+        if self.ref is not None:
+            self.ref.ref_build_sa40_parallel(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(n), out.ctypes.data_as(ctypes.c_void_p))
+        else:
+            self.orc.orc_build_sa40(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(n), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(0))
+        return time.perf_counter() - t0
+
+    def cores(self):
+        if self.ref is not None:
+            self.ref.ref_thread_count.restype = ctypes.c_uint
+            return max(int(self.ref.ref_thread_count()), self.threads)
+        self.orc.orc_max_threads.restype = ctypes.c_int
+        return int(self.orc.orc_max_threads())
+
+    def find(self, T, n, sa40, off, sym, q, itv):
+        vp = ctypes.c_void_p
+        if self.ref is not None:
+            self.ref.ref_host_search_find(T.ctypes.data_as(vp), ctypes.c_uint64(n), sa40.ctypes.data_as(vp), off.ctypes.data_as(vp),
+                                          sym.ctypes.data_as(vp), ctypes.c_uint64(q), itv.ctypes.data_as(vp), ctypes.c_uint(0), ctypes.c_uint(32))
+        else:
+            self.orc.orc_find_batch(T.ctypes.data_as(vp), ctypes.c_uint64(n), sa40.ctypes.data_as(vp), off.ctypes.data_as(vp),
+                                    sym.ctypes.data_as(vp), ctypes.c_uint64(q), itv.ctypes.data_as(vp), ctypes.c_int(0))
 
 
 def cpu_baseline(sample_tokens, mean_doc, queries):
     """Times the reference's CPU paths on a bounded sample of the same corpus: the comparison-sort builder on all host
     threads, then the reference's batched host search over the sample's index."""
     from cascade_b200 import api
-    L, kind = ref_lib()
-    T = api.gen_corpus_host(sample_tokens, 0, mean_doc)
+    cpu = CpuSide()
+    T = cpu.corpus(sample_tokens, mean_doc)
     out = np.zeros(5 * sample_tokens + 128, np.uint8)
-    dt = cpu_build_once(L, kind, T, sample_tokens, out)
-    res = {"value": sample_tokens / dt, "unit": UNIT, "cores": cpu_threads(L, kind), "kind": kind,
+    dt = cpu.build_once(T, sample_tokens, out)
+    res = {"value": sample_tokens / dt, "unit": UNIT, "cores": cpu.cores(), "kind": cpu.kind,
            "sample": f"first {sample_tokens} tokens of the same seeded Zipf corpus, one comparison-sort build ({dt:.2f} s)"}
     if queries:
         off, sym = api.gen_queries("substring", T, sample_tokens, queries // 2, seed=1)
@@ -124,43 +175,11 @@ def cpu_baseline(sample_tokens, mean_doc, queries):
         sym = np.concatenate([sym, sym2, np.zeros(8, np.uint16)])
         itv = np.zeros(2 * queries, np.uint64)
         t0 = time.perf_counter()
-        if kind == "reference":
-            L.ref_host_search_find(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(sample_tokens), out.ctypes.data_as(ctypes.c_void_p),
-                                   off.ctypes.data_as(ctypes.c_void_p), sym.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(queries),
-                                   itv.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint(0), ctypes.c_uint(32))
-        else:
-            L.orc_find_batch(T.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(sample_tokens), out.ctypes.data_as(ctypes.c_void_p),
-                             off.ctypes.data_as(ctypes.c_void_p), sym.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(queries),
-                             itv.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(0))
+        cpu.find(T, sample_tokens, out, off, sym, queries, itv)
         dq = time.perf_counter() - t0
         res["query"] = {"value": queries / dq, "unit": "queries/s (count only, host search)", "queries": queries,
                         "sample": f"index of the {sample_tokens}-token sample"}
     return res
-
-
-def run_reference(args):
-    """The reference arm: the reference's own CPU builder on the box's host cores, on bounded samples of the workload."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    from cascade_b200 import api
-    L, kind = ref_lib()
-    sample = min(args.tokens, args.ref_sample)
-    T = api.gen_corpus_host(sample, 0, C2_MEAN_DOC)
-    out = np.zeros(5 * sample + 128, np.uint8)
-    for _ in range(args.warmup):
-        cpu_build_once(L, kind, T, sample, out)
-    times = [cpu_build_once(L, kind, T, sample, out) for _ in range(args.steps)]
-    ms = 1e3 * sum(times) / len(times)
-    v = sample / (ms * 1e-3)
-    cores = cpu_threads(L, kind)
-    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": workload_config(args, args.gpus),
-            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
-                             "sample": f"each step builds the first {sample} tokens of the workload's corpus with the reference's CPU comparison-sort builder"},
-            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-    print(json.dumps(line))
 
 
 def workload_config(args, n_gpus):
@@ -170,21 +189,145 @@ def workload_config(args, n_gpus):
             "l2": "inputs (4 GB text, 24 GB of sort records per pass at full size) exceed the 126 MB L2; no flush needed"}
 
 
+def run_reference(args):
+    """The reference arm: the reference's own CPU builder on all host cores, each step one build of a bounded sample of the
+    workload's corpus. Under a multi-rank launch rank 0 alone works. Nothing of the product is loaded."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cpu = CpuSide()
+    sample = min(args.tokens, args.ref_sample)
+    T = cpu.corpus(sample, C2_MEAN_DOC)
+    out = np.zeros(5 * sample + 128, np.uint8)
+    for _ in range(args.warmup):
+        cpu.build_once(T, sample, out)
+    times = [cpu.build_once(T, sample, out) for _ in range(args.steps)]
+    ms = 1e3 * sum(times) / len(times)
+    v = sample / (ms * 1e-3)
+    cfg = workload_config(args, args.gpus)
+    cfg["workload"] += f" -- CPU arm: each step sorts a sample, the first {sample} tokens of that corpus"
+    cfg["reference_sample_tokens"] = sample
+    what = "the reference's CPU comparison-sort builder" if cpu.kind == "reference" else "the C port of the reference's CPU builder"
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": cfg,
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cpu.cores(), "kind": cpu.kind,
+                             "sample": f"each step builds the first {sample} tokens of the workload's corpus with {what} on all host threads"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ---- the GPU side -----------------------------------------------------------------------------------------------------
+
+def pass_roofline(ctx, peak, peak_kind, step_ms_total, traffic):
+    from cascade_b200._lib import c_u64
+    pm, pc, pr, pb = ctypes.c_double(0), c_u64(0), c_u64(0), c_u64(0)
+    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr), ctypes.byref(pb))
+    ctx.L.csa_set_pass_timing(ctx.h, 0)
+    # algorithmic bytes: one read and one write of every record of every pass (12-byte key + position records; 8-byte
+    # records in the keys-only passes that order rank updates by address)
+    achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
+    r = {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort)", "achieved": achieved, "peak": peak,
+         "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
+         "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value}
+    if traffic is not None:
+        r["traffic_note"] = "bytes per launch over 31.25 M records (algorithmic: 750e6), from an earlier ncu capture of that launch, not measured by this run"
+    if step_ms_total:
+        r["share_of_step"] = pm.value / step_ms_total
+    return r
+
+
+def sort_baselines(ctx, records=31_250_000, reps=5):
+    """The product's radix sort and the library sort the reference calls (cub::DeviceRadixSort::SortPairs), both on `records`
+    random (u64 key, u32 value) records, all 64 key bits: whole-sort device milliseconds side by side."""
+    import torch
+    from cascade_b200._lib import c_int
+    n = records
+    g = torch.Generator(device="cuda").manual_seed(1)
+    keys0 = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g)
+    keys, ka = keys0.clone(), torch.empty_like(keys0)
+    vals, va = torch.arange(n, device="cuda", dtype=torch.int32), torch.empty(n, device="cuda", dtype=torch.int32)
+    wsb = ctx.L.csa_sort_workspace_bytes(n)
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    ours = []
+    for it in range(reps + 1):
+        keys.copy_(keys0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s = torch.cuda.ExternalStream(ctx.stream())
+        e0.record(s)
+        in_alt = c_int(0)
+        ctx.check(ctx.L.csa_sort_pairs(ctx.h, keys.data_ptr(), ka.data_ptr(), vals.data_ptr(), va.data_ptr(), 4, n, 0, 64, ws.data_ptr(), wsb,
+                                       ctypes.byref(in_alt)))
+        e1.record(s)
+        ctx.sync()
+        if it > 0:
+            ours.append(e0.elapsed_time(e1))
+    del keys, ka, vals, va, ws, keys0
+    torch.cuda.empty_cache()
+    res = {"records": n, "key_bits": 64, "value_bytes": 4, "ours_ms": sum(ours) / len(ours),
+           "ours_gbs_per_pass": 8 * 2 * 12 * n / (sum(ours) / len(ours) * 1e-3) / 1e9}
+    so = os.path.join(ROOT, "bench_cub_sort.so")
+    if os.path.exists(so):
+        L = ctypes.CDLL(so)
+        ms = ctypes.c_double(0)
+        rc = L.cub_sort_pairs_ms(ctypes.c_ulonglong(n), ctypes.c_int(64), ctypes.c_int(reps), ctypes.byref(ms))
+        if rc == 0:
+            res["cub_ms"] = ms.value
+            res["cub_gbs_per_pass"] = 8 * 2 * 12 * n / (ms.value * 1e-3) / 1e9
+            res["ours_over_cub"] = ms.value / res["ours_ms"]
+        else:
+            res["cub_error"] = rc
+    else:
+        res["cub_error"] = "bench_cub_sort.so is not built"
+    res["note"] = ("whole sort, device time; cub::DeviceRadixSort::SortPairs is the call the reference makes, built here for sm_100a as a "
+                   "benchmark-only baseline; the per-pass figure divides 8 passes x 24 B per record by the time")
+    return res
+
+
+def run_config3(ctx, args):
+    """BASELINE config 3, the worst case for prefix doubling: 4096 base documents (geometric, mean 2048, Zipf tokens), then
+    copies of random base documents with 0.1 % of their tokens replaced. Build alone, then the full check of the array."""
+    import torch
+    from cascade_b200 import api
+    n = args.config3_tokens
+    t0 = time.perf_counter()
+    Th = api.gen_repeat_corpus_host(n, seed=0, base_docs=4096, mean_doc=2048, mutate=0.001)
+    T = torch.from_numpy(Th.view(np.int16)).cuda().view(torch.uint16)
+    del Th
+    gen_s = time.perf_counter() - t0
+    out = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8, device="cuda")
+    api.build_sa(ctx, T, n, C2_PARTITIONS, out=out)
+    ms, st = [], None
+    for _ in range(max(1, min(args.steps, 3))):
+        _, st = api.build_sa(ctx, T, n, C2_PARTITIONS, out=out)
+        ms.append(st.ms_total)
+    v = api.validate_sa(ctx, T, n, out)
+    m = sum(ms) / len(ms)
+    res = {"value": n / (m * 1e-3), "unit": UNIT, "ms_per_step": m, "steps": len(ms),
+           "config": {"workload": "repetitive corpus, BASELINE config 3", "tokens": n, "base_docs": 4096, "mean_doc": 2048, "mutate": 0.001,
+                      "partitions": C2_PARTITIONS},
+           "generations": st.generations, "active_per_generation": [int(x) for x in st.active_per_gen[:st.generations]],
+           "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
+           "sort_passes": st.sort_passes, "validated": v["ok"], "validation": v, "host_generation_s": gen_s}
+    del T, out
+    torch.cuda.empty_cache()
+    return res
+
+
+def make_queries(api, tn, n, q):
+    oa, sa_ = api.gen_queries("substring", tn, n, q // 2, seed=1)
+    ob, sb = api.gen_queries("random", None, 0, q - q // 2, seed=2)
+    return np.concatenate([oa, ob[1:] + oa[-1]]), np.concatenate([sa_, sb, np.zeros(8, np.uint16)])
+
+
 def run_ours(args):
     import torch
     from cascade_b200 import api
-    from cascade_b200._lib import c_u64
 
-    rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    if world > 1:
-        from cascade_b200 import multi
-        return multi.bench(args, rank, world, local)
+        return run_ours_multi(args)
 
     torch.cuda.set_device(local)
     ctx = api.Context(local)
@@ -209,38 +352,29 @@ def run_ours(args):
         torch.cuda.synchronize()
         wall_ms = 1e3 * (time.perf_counter() - t0) / args.steps
     ms = sum(step_ms) / len(step_ms)
-    pm, pc, pr, pb = ctypes.c_double(0), c_u64(0), c_u64(0), c_u64(0)
-    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr), ctypes.byref(pb))
-    ctx.L.csa_set_pass_timing(ctx.h, 0)
-    # algorithmic bytes: one read and one write of every record of every pass (12-byte key + position records; 8-byte
-    # records in the keys-only passes that order rank updates by address)
-    achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort)", "achieved": achieved, "peak": peak,
-                "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                "traffic": ONESWEEP_TRAFFIC, "traffic_note": "bytes per launch over 31.25 M records (algorithmic: 750e6), ncu capture in profiles/",
-                "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value, "share_of_step": pm.value / (ms * args.steps)}
+    roofline = pass_roofline(ctx, peak, peak_kind, ms * args.steps, ONESWEEP_TRAFFIC_FROM_PROFILE)
+    validation = api.validate_sa(ctx, T, n, out)         # the whole array, outside the timed region
 
     # ---- end to end through the host-buffer entry point --------------------------------------------------------------
     e2e = None
+    th = None
     if not args.no_e2e:
         th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
         th.copy_(T.cpu())
         oh = torch.empty(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
         api.build_sa_host(ctx, th, n, p, out=oh)      # warm-up (grows the arena)
         ts = []
-        for _ in range(max(1, min(args.steps, 2))):
+        for _ in range(args.steps):
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             api.build_sa_host(ctx, th, n, p, out=oh)
             ts.append(time.perf_counter() - t0)
         e_ms = 1e3 * sum(ts) / len(ts)
         e2e = {"value": n / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 2 * n, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms,
-               "api": "csa_build_sa_host (pinned host text in, sa40 out)"}
+               "steps": len(ts), "api": "csa_build_sa_host (pinned host text in, sa40 out)"}
         # the two entry points must give the same bytes
-        same = bool(torch.equal(oh[:5 * n].cuda(), out[:5 * n]))
-        e2e["matches_device_path"] = same
-    else:
-        th = None
+        e2e["matches_device_path"] = bool(torch.equal(oh[:5 * n].cuda(), out[:5 * n]))
+        del oh
 
     # ---- batched queries on the index just built (BASELINE config 5) ------------------------------------------------
     query = None
@@ -249,10 +383,7 @@ def run_ours(args):
             th = T.cpu()
         tn = th.view(torch.int16).numpy().view(np.uint16)
         q = args.queries
-        oa, sa_ = api.gen_queries("substring", tn, n, q // 2, seed=1)
-        ob, sb = api.gen_queries("random", None, 0, q - q // 2, seed=2)
-        off = np.concatenate([oa, ob[1:] + oa[-1]])
-        sym = np.concatenate([sa_, sb, np.zeros(8, np.uint16)])
+        off, sym = make_queries(api, tn, n, q)
         idx = api.SuffixIndex(ctx, T, out, n, 32)
         od = torch.from_numpy(off.view(np.int64)).cuda()
         sd = torch.from_numpy(sym.view(np.int16)).cuda()
@@ -270,10 +401,14 @@ def run_ours(args):
         bufs = {"itv": torch.empty(2 * q, dtype=torch.int64).pin_memory(), "cnt": torch.empty(q, dtype=torch.int32).pin_memory(),
                 "pos_off": torch.empty(q + 1, dtype=torch.int64).pin_memory(), "pos": torch.empty(q * 100, dtype=torch.int64).pin_memory()}
         idx.query_host(offp, symp, 100, bufs)
-        t0 = time.perf_counter()
-        r = idx.query_host(offp, symp, 100, bufs)
-        dqe = time.perf_counter() - t0
+        tq = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            r = idx.query_host(offp, symp, 100, bufs)
+            tq.append(time.perf_counter() - t0)
+        dqe = min(tq)
         itv_np = bufs["itv"].numpy().view(np.uint64)
+        same_host = bool(np.array_equal(itv_np, itv.cpu().numpy().view(np.uint64)))
         # the same index with the suffix array left in pinned host memory (the device reads it over PCIe)
         pinned = None
         if not args.no_e2e:
@@ -288,23 +423,175 @@ def run_ours(args):
             dqh = time.perf_counter() - t0
             pinned = {"value": q / dqh, "unit": "queries/s (count + locate <= 100, suffix array in pinned host memory, text and table in HBM)",
                       "same_intervals": bool(torch.equal(itv_h, itv))}
+            del sa_pinned, idx_h, pos_h, cnt_h, itv_h
         query = {"value": q / dq, "unit": "queries/s (count + locate <= 100, index in HBM, batch in HBM)", "queries": q,
-                 "e2e": {"value": q / dqe, "unit": "queries/s (host batch in, intervals + positions out)",
-                         "h2d_bytes": int(off.nbytes + sym.nbytes), "d2h_bytes": int(q * 16 + q * 4 + (q + 1) * 8 + r[4] * 8)},
+                 "e2e": {"value": q / dqe, "unit": "queries/s (host batch in, intervals + positions out; best of 3)",
+                         "h2d_bytes": int(off.nbytes + sym.nbytes), "d2h_bytes": int(q * 16 + q * 4 + (q + 1) * 8 + r[4] * 8),
+                         "same_intervals_as_device_path": same_host},
                  "sa_in_pinned_host_memory": pinned, "certificate_failures": fails, "positions": r[4], "counts_hash": f"{api.counts_hash(itv_np):016x}", "table_stride": 32}
+        del idx, od, sd, pos, cnt, itv, bufs
+    del th
+    torch.cuda.empty_cache()
 
     line = {"metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "wall_ms_per_step": wall_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": workload_config(args, 1), "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches),
-            "roofline": roofline,
+            "roofline": roofline, "validated": validation["ok"], "validation": validation,
             "phases_ms": {"partition": stats.ms_partition, "gen0": stats.ms_gen0, "doubling": stats.ms_doubling, "output": stats.ms_output},
             "build": {"partitions": stats.partitions, "generations": stats.generations, "max_partition": stats.max_partition,
-                      "active_after_gen0": stats.active_after_gen0, "sort_passes_per_step": stats.sort_passes},
+                      "active_after_gen0": stats.active_after_gen0, "sort_passes_per_step": stats.sort_passes,
+                      "active_per_generation": [int(x) for x in stats.active_per_gen[:stats.generations]]},
             "query": query}
+    del T, out
+    torch.cuda.empty_cache()
+    if not args.no_sort_baseline:
+        line["sort_baseline"] = sort_baselines(ctx)
+    if args.config3_tokens > 0:
+        line["config3"] = run_config3(ctx, args)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(min(n, args.cpu_sample), C2_MEAN_DOC, min(args.queries, 1_000_000))
     print(json.dumps(line))
     ctx.close()
+
+
+def _max_over_ranks(x, device):
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _sum_over_ranks(x, device):
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def run_ours_multi(args):
+    """N > 1: the same corpus (strong scaling), partitions sharded over the ranks, one process per GPU."""
+    import torch
+    import torch.distributed as dist
+    from cascade_b200 import api, multi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    ctx = api.Context(local)
+    name = [f"/cascade_b200_{os.getpid()}_{int(time.time())}"]
+    dist.broadcast_object_list(name, src=0)            # one name for the job's shared-memory object
+    comm, close_comm = multi.make_shm_comm(rank, world, name[0])
+    n, p = args.tokens, C2_PARTITIONS
+    peak, peak_kind = measured_peak_gbs()
+    T = api.gen_corpus_device(ctx, n, 0, C2_MEAN_DOC)          # every rank makes the same text in its own HBM
+    cap = min(n, n // world + n // 8 + 1024)
+    out = torch.zeros(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8, device=dev)
+    for _ in range(args.warmup):
+        multi.build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+    ctx.L.csa_set_pass_timing(ctx.h, 1)
+    ctx.reset_counters()
+    dist.barrier()
+    torch.cuda.synchronize()
+    step_ms, launches, peer = [], 0, 0
+    with ClockSampler(local) as clocks:
+        for _ in range(args.steps):
+            _, segs, st = multi.build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            step_ms.append(_max_over_ranks(st.ms_total, dev))
+            launches += st.kernel_launches
+            peer += st.peer_bytes
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms = sum(step_ms) / len(step_ms)
+    roofline = pass_roofline(ctx, peak, peak_kind, None, None)
+    roofline["kernel"] += ", rank 0"
+    count = sum(c for _, c in segs)
+    total = _sum_over_ranks(count, dev)
+
+    # The whole array, checked in full on rank 0: every rank lays its segments into a zeroed buffer of the full size, the
+    # buffers are summed over the ranks, and rank 0 runs the device validator on the sum.
+    full = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8, device=dev)
+    at = 0
+    for first, c in segs:
+        full[5 * first:5 * (first + c)] = out[5 * at:5 * (at + c)]
+        at += c
+    dist.all_reduce(full, op=dist.ReduceOp.SUM)
+    validation = api.validate_sa(ctx, T, n, full) if rank == 0 else None
+    del full
+    torch.cuda.empty_cache()
+
+    # end to end: pinned host text in, this rank's slice of the 5-byte array out
+    e2e = None
+    if not args.no_e2e:
+        th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
+        th.copy_(T.cpu())
+        oh = torch.empty(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
+        ts = []
+        scratch = None
+        for it in range(1 + args.steps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            scratch = multi.upload_text_sharded(th, T, scratch)         # 1/world of the text per rank over PCIe, the rest over NVLink
+            _, segs, st = multi.build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
+            count = sum(c for _, c in segs)
+            oh[:5 * count].copy_(out[:5 * count], non_blocking=True)
+            torch.cuda.synchronize()
+            dt = _max_over_ranks(time.perf_counter() - t0, dev)
+            if it > 0:
+                ts.append(dt)
+        e_ms = 1e3 * sum(ts) / len(ts)
+        e2e = {"value": n / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 2 * n, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms, "steps": len(ts),
+               "api": "upload_text_sharded (1/N of the pinned host text per rank, all-gather over NVLink) + csa_build_sa_multi + a pinned copy "
+                      "of the rank's sa40 slice out"}
+        del scratch, th, oh
+        torch.cuda.empty_cache()
+    # ---- batched queries on the index sharded by suffix-array range (BASELINE config 5 over N GPUs) ---------------------
+    query = None
+    if args.queries > 0:
+        comm0, close0 = multi.make_shm_comm(rank, world, name[0] + "_q", policy=0)     # contiguous blocks: one slice of the array per rank
+        sl, segs0, _ = multi.build_sa_multi(ctx, comm0, T, n, p, out=out, capacity=cap)
+        close0()
+        first0, count0 = (segs0[0][0], sum(c for _, c in segs0)) if segs0 else (0, 0)
+        sh = multi.ShardedIndex(ctx, T, sl, n, first0, count0, stride=32)
+        q = args.queries
+        objs = [None, None]
+        if rank == 0:
+            tn = T.cpu().view(torch.int16).numpy().view(np.uint16)
+            objs = list(make_queries(api, tn, n, q))
+        dist.broadcast_object_list(objs, src=0)
+        od = torch.from_numpy(objs[0].view(np.int64)).to(dev)
+        sd = torch.from_numpy(objs[1].view(np.int16)).to(dev)
+        for _ in range(2):
+            itv = sh.find(od, sd, q)
+        dist.barrier(); torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        itv = sh.find(od, sd, q)
+        rows, cnt = sh.locate(itv, q, 100)
+        torch.cuda.synchronize()
+        dq = _max_over_ranks(time.perf_counter() - t0, dev)
+        query = {"value": q / dq, "unit": f"queries/s (count + locate <= 100, suffix array sharded by range over {world} GPUs, text replicated)",
+                 "queries": q, "counts_hash": f"{api.counts_hash(itv.cpu().numpy().view(np.uint64)):016x}", "positions": int(cnt.sum().item())}
+    launches_all = _sum_over_ranks(launches, dev)
+    peer_all = _sum_over_ranks(peer, dev)
+    if rank == 0:
+        line = {"metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                "config": workload_config(args, world), "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches_all),
+                "roofline": roofline,
+                "nvlink": {"peer_bytes_per_step_all_ranks": peer_all / args.steps, "generations": st.generations,
+                           "note": "positions to partition owners + ranks to and from position owners, 4 bytes each, (G-1)/G of them remote"},
+                "phases_ms_rank0": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
+                "query": query, "validated": bool(validation["ok"] and total == n), "validation": validation}
+        print(json.dumps(line))
+    dist.barrier()
+    close_comm()
+    ctx.close()
+    dist.destroy_process_group()
 
 
 def run_micro_sort(args):
@@ -347,47 +634,14 @@ def run_micro_sort(args):
 
 
 def run_repeat(args):
-    """BASELINE config 3, the worst case for prefix doubling: 4096 base documents (geometric, mean 2048, Zipf tokens), then
-    copies of random base documents with 0.1 % of their tokens replaced, 1e9 tokens in all. Reports the build alone."""
-    import torch
+    """BASELINE config 3 alone (it is also a key of the default line)."""
     from cascade_b200 import api
-    n = args.tokens if args.tokens != C2_TOKENS else 1_000_000_000
+    if args.tokens != C2_TOKENS:
+        args.config3_tokens = args.tokens
     ctx = api.Context(0)
-    t0 = time.perf_counter()
-    Th = api.gen_repeat_corpus_host(n, seed=0, base_docs=4096, mean_doc=2048, mutate=0.001)
-    T = torch.from_numpy(Th.view(np.int16)).cuda().view(torch.uint16)
-    gen_s = time.perf_counter() - t0
-    out = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8, device="cuda")
-    for _ in range(max(1, args.warmup - 2)):
-        api.build_sa(ctx, T, n, C2_PARTITIONS, out=out)
-    ms, st = [], None
-    for _ in range(args.steps):
-        _, st = api.build_sa(ctx, T, n, C2_PARTITIONS, out=out)
-        ms.append(st.ms_total)
-    # sampled order check on the device: neighbours compared on their first 64 symbols (undecided pairs count as consistent)
-    g = torch.Generator(device="cuda").manual_seed(0)
-    r = torch.randint(0, n - 1, (1 << 20,), device="cuda", generator=g)
-    b = out[:5 * n].view(n, 5)
-    def entry(idx):
-        e = b[idx].to(torch.int64)
-        return e[:, 0] | (e[:, 1] << 8) | (e[:, 2] << 16) | (e[:, 3] << 24) | (e[:, 4] << 32)
-    pa, pb = entry(r), entry(r + 1)
-    Tl = T.view(torch.int16)
-    undecided = torch.ones_like(pa, dtype=torch.bool)
-    bad = torch.zeros_like(undecided)
-    for k in range(64):
-        xa = torch.where(pa + k < n, Tl[torch.clamp(pa + k, max=n)].to(torch.int64) & 0xFFFF, torch.full_like(pa, -1))
-        xb = torch.where(pb + k < n, Tl[torch.clamp(pb + k, max=n)].to(torch.int64) & 0xFFFF, torch.full_like(pb, -1))
-        bad |= undecided & (xa > xb)
-        undecided &= (xa == xb) & (xa >= 0)
-    m = sum(ms) / len(ms)
-    print(json.dumps({"metric": METRIC, "value": n / (m * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "ms_per_step": m,
-                      "config": {"workload": "repetitive corpus, BASELINE config 3", "tokens": n, "base_docs": 4096, "mean_doc": 2048, "mutate": 0.001,
-                                 "partitions": C2_PARTITIONS}, "generations": st.generations,
-                      "active_per_generation": [int(x) for x in st.active_per_gen[:st.generations]],
-                      "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
-                      "sort_passes": st.sort_passes, "order_violations_in_1M_sampled_neighbours": int(bad.sum().item()),
-                      "host_generation_s": gen_s}))
+    r = run_config3(ctx, args)
+    r.update({"metric": METRIC, "n_gpus": 1})
+    print(json.dumps(r))
     ctx.close()
 
 
@@ -400,24 +654,25 @@ def main():
     ap.add_argument("--tokens", type=int, default=C2_TOKENS)
     ap.add_argument("--queries", type=int, default=C5_QUERIES)
     ap.add_argument("--cpu-sample", type=int, default=1 << 25)
-    ap.add_argument("--ref-sample", type=int, default=1 << 24)
+    ap.add_argument("--ref-sample", type=int, default=1 << 26, help="tokens that one step of the CPU reference arm sorts")
+    ap.add_argument("--config3-tokens", type=int, default=C3_TOKENS, help="size of the repetitive corpus reported under `config3` (0 = skip)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sort-baseline", action="store_true")
     ap.add_argument("--workload", default="zipf", choices=["zipf", "repeat"],
-                    help="zipf: BASELINE config 2; repeat: config 3 (1e9 tokens of near-duplicate documents, build only)")
+                    help="zipf: BASELINE config 2; repeat: config 3 alone (1e9 tokens of near-duplicate documents, build only)")
     ap.add_argument("--micro", default=None, choices=["sort"], help="time one kernel family alone instead of the build")
     ap.add_argument("--records", type=int, default=31_250_000)
     ap.add_argument("--bits", type=int, default=64)
     ap.add_argument("--variant", type=int, default=-1, help="shape of the digit-pass kernel (test hook), -1 = default")
     args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
     if args.micro == "sort":
         return run_micro_sort(args)
     if args.workload == "repeat":
         return run_repeat(args)
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+    run_ours(args)
 
 
 if __name__ == "__main__":

@@ -55,6 +55,8 @@ _SIGS = {
     "csa_build_device_bytes": (ctypes.c_size_t, [c_u64, c_u32]),
     "csa_build_sa": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_build_sa_host": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
+    "csa_validate_workspace_bytes": (ctypes.c_size_t, [c_u64]),
+    "csa_validate_sa": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, ctypes.c_size_t, c_vp]),
     "csa_comm_open_shm": (c_int, [ctypes.c_char_p, c_u32, c_u32, c_u32, c_vp]),
     "csa_comm_close_shm": (None, [c_vp, c_int]),
     "csa_plan_shards": (c_int, [c_vp, c_u32, c_u32, c_u32, c_vp, c_vp, c_vp, c_vp, c_vp]),

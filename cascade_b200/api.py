@@ -64,6 +64,10 @@ class Context:
         if rc != 0:
             raise CascadeError(rc, f"status bits {st.value}: " + self.L.csa_last_error(self.h).decode())
 
+    def stream(self):
+        """The context's cudaStream_t as an integer (for torch.cuda.ExternalStream)."""
+        return int(self.L.csa_ctx_stream(self.h))
+
     @property
     def launches(self):
         return int(self.L.csa_kernel_launches(self.h))
@@ -198,6 +202,21 @@ def build_sa_host(ctx, text_host, n, p=1, seed=0, out=None):
     st = BuildStats()
     ctx.check(ctx.L.csa_build_sa_host(ctx.h, _ptr(text_host), n, p, seed, _ptr(out), ctypes.byref(st)))
     return out, st
+
+
+def validate_sa(ctx, text_dev, n, sa40_dev):
+    """Exact check of a whole suffix array on the device (csa_validate_sa). Returns a dict with the counts of entries out of
+    range, duplicate entries and neighbouring pairs out of order, the first bad rank, and `ok`."""
+    wsb = ctx.L.csa_validate_workspace_bytes(n)
+    ws = torch.empty(wsb, dtype=torch.uint8, device=text_dev.device)
+    res = torch.zeros(4, dtype=torch.int64, device=text_dev.device)
+    torch.cuda.synchronize(text_dev.device)
+    ctx.check(ctx.L.csa_validate_sa(ctx.h, text_dev.data_ptr(), n, sa40_dev.data_ptr(), ws.data_ptr(), wsb, res.data_ptr()))
+    ctx.sync()
+    r = res.cpu().numpy().view(np.uint64)
+    del ws
+    return {"out_of_range": int(r[0]), "duplicates": int(r[1]), "out_of_order": int(r[2]),
+            "first_bad_rank": None if int(r[3]) == 2**64 - 1 else int(r[3]), "ok": int(r[0]) == 0 and int(r[1]) == 0 and int(r[2]) == 0}
 
 
 # ---- queries -------------------------------------------------------------------------------------------------------

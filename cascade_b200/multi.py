@@ -6,16 +6,13 @@ tensors under gloo and on device tensors under NCCL. All bulk data moves inside 
 and stores.
 """
 import ctypes
-import json
-import os
-import time
 
 import numpy as np
 import torch
 import torch.distributed as dist
 
 from . import api
-from ._lib import ALLGATHER_FN, BuildStats, Comm, c_u64
+from ._lib import ALLGATHER_FN, BuildStats, Comm
 
 
 def make_comm(rank, world, device=None, policy=1):
@@ -137,145 +134,3 @@ def upload_text_sharded(text_host, text_dev, scratch=None):
     dist.all_gather_into_tensor(scratch, mine)
     dev_bytes.copy_(scratch[:total])
     return scratch
-
-
-def _max_over_ranks(x, device):
-    t = torch.tensor([x], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def _sum_over_ranks(x, device):
-    t = torch.tensor([x], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.SUM)
-    return float(t.item())
-
-
-def bench(args, rank, world, local):
-    """The N > 1 arm of bench.py: the same corpus (strong scaling), partitions sharded over the ranks."""
-    import bench as B
-    dev = torch.device("cuda", local)
-    ctx = api.Context(local)
-    name = [f"/cascade_b200_{os.getpid()}_{int(time.time())}"]
-    dist.broadcast_object_list(name, src=0)            # one name for the job's shared-memory object
-    comm, close_comm = make_shm_comm(rank, world, name[0])
-    n, p = args.tokens, B.C2_PARTITIONS
-    peak, peak_kind = B.measured_peak_gbs()
-    T = api.gen_corpus_device(ctx, n, 0, B.C2_MEAN_DOC)          # every rank makes the same text in its own HBM
-    cap = min(n, n // world + n // 8 + 1024)
-    out = torch.zeros(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8, device=dev)
-    for _ in range(args.warmup):
-        build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
-    ctx.L.csa_set_pass_timing(ctx.h, 1)
-    ctx.reset_counters()
-    dist.barrier()
-    torch.cuda.synchronize()
-    step_ms, launches, peer = [], 0, 0
-    with B.ClockSampler(local) as clocks:
-        for _ in range(args.steps):
-            _, segs, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
-            count = sum(c for _, c in segs)
-            step_ms.append(_max_over_ranks(st.ms_total, dev))
-            launches += st.kernel_launches
-            peer += st.peer_bytes
-        dist.barrier()
-        torch.cuda.synchronize()
-    ms = sum(step_ms) / len(step_ms)
-    pm, pc, pr, pb = ctypes.c_double(0), c_u64(0), c_u64(0), c_u64(0)
-    ctx.L.csa_get_pass_timing(ctx.h, ctypes.byref(pm), ctypes.byref(pc), ctypes.byref(pr), ctypes.byref(pb))
-    ctx.L.csa_set_pass_timing(ctx.h, 0)
-    achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
-
-    # cheap check of this rank's slice: sizes add up, and sampled neighbours are in order on their first 4 symbols
-    total = _sum_over_ranks(count, dev)
-    ok = 1.0
-    if count > 1:
-        g = torch.Generator(device=dev).manual_seed(rank)
-        r = torch.randint(0, count - 1, (min(count - 1, 1 << 20),), device=dev, generator=g)
-        e = out[:5 * count].view(count, 5)
-        def entry(ix):
-            v = e[ix].to(torch.int64)
-            return v[:, 0] | (v[:, 1] << 8) | (v[:, 2] << 16) | (v[:, 3] << 24) | (v[:, 4] << 32)
-        Ts = T.view(torch.int16)
-        def key4(ps):
-            return sum((Ts[ps + k].to(torch.int64) & 0xFFFF) << (48 - 16 * k) for k in range(4))
-        a, c = key4(entry(r)), key4(entry(r + 1))
-        ok = float(bool(((a >> 1) <= (c >> 1)).all()))      # compare as unsigned through a 63-bit view
-        del a, c, e, Ts
-    torch.cuda.empty_cache()
-    ok_all = _sum_over_ranks(ok, dev) == world and total == n
-
-    # end to end: pinned host text in, this rank's slice of the 5-byte array out
-    e2e = None
-    if not args.no_e2e:
-        th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
-        th.copy_(T.cpu())
-        oh = torch.empty(5 * cap + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
-        ts = []
-        scratch = None
-        for it in range(1 + max(1, min(args.steps, 2))):
-            dist.barrier()
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            scratch = upload_text_sharded(th, T, scratch)         # 1/world of the text per rank over PCIe, the rest over NVLink
-            _, segs, st = build_sa_multi(ctx, comm, T, n, p, out=out, capacity=cap)
-            count = sum(c for _, c in segs)
-            oh[:5 * count].copy_(out[:5 * count], non_blocking=True)
-            torch.cuda.synchronize()
-            dt = _max_over_ranks(time.perf_counter() - t0, dev)
-            if it > 0:
-                ts.append(dt)
-        e_ms = 1e3 * sum(ts) / len(ts)
-        e2e = {"value": n / (e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": 2 * n, "d2h_bytes_per_step": 5 * n, "ms_per_step": e_ms,
-               "api": "upload_text_sharded (1/N of the pinned host text per rank, all-gather over NVLink) + csa_build_sa_multi + a pinned copy "
-                      "of the rank's sa40 slice out"}
-        del scratch
-        torch.cuda.empty_cache()
-    # ---- batched queries on the index sharded by suffix-array range (BASELINE config 5 over N GPUs) ---------------------
-    query = None
-    if args.queries > 0:
-        comm0, close0 = make_shm_comm(rank, world, name[0] + "_q", policy=0)     # contiguous blocks: one slice of the array per rank
-        sl, segs0, _ = build_sa_multi(ctx, comm0, T, n, p, out=out, capacity=cap)
-        close0()
-        first0, count0 = (segs0[0][0], sum(c for _, c in segs0)) if segs0 else (0, 0)
-        sh = ShardedIndex(ctx, T, sl, n, first0, count0, stride=32)
-        q = args.queries
-        qa = [None, None, None, None]
-        if rank == 0:
-            tn = T.cpu().view(torch.int16).numpy().view(np.uint16)
-            oa, sa_ = api.gen_queries("substring", tn, n, q // 2, seed=1)
-            ob, sb = api.gen_queries("random", None, 0, q - q // 2, seed=2)
-            qa = [np.concatenate([oa, ob[1:] + oa[-1]]), np.concatenate([sa_, sb, np.zeros(8, np.uint16)])]
-        objs = [qa[0], qa[1]]
-        dist.broadcast_object_list(objs, src=0)
-        od = torch.from_numpy(objs[0].view(np.int64)).to(dev)
-        sd = torch.from_numpy(objs[1].view(np.int16)).to(dev)
-        for _ in range(2):
-            itv = sh.find(od, sd, q)
-        dist.barrier(); torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        itv = sh.find(od, sd, q)
-        rows, cnt = sh.locate(itv, q, 100)
-        torch.cuda.synchronize()
-        dq = _max_over_ranks(time.perf_counter() - t0, dev)
-        query = {"value": q / dq, "unit": f"queries/s (count + locate <= 100, suffix array sharded by range over {world} GPUs, text replicated)",
-                 "queries": q, "counts_hash": f"{api.counts_hash(itv.cpu().numpy().view(np.uint64)):016x}", "positions": int(cnt.sum().item())}
-    launches_all = _sum_over_ranks(launches, dev)
-    peer_all = _sum_over_ranks(peer, dev)
-    if rank == 0:
-        line = {"metric": B.METRIC, "value": n / (ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-                "config": B.workload_config(args, world), "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches_all),
-                "roofline": {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort), rank 0", "achieved": achieved,
-                             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
-                             "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value},
-                "nvlink": {"peer_bytes_per_step_all_ranks": peer_all / args.steps, "generations": st.generations,
-                           "note": "positions to partition owners + ranks to and from position owners, 4 bytes each, (G-1)/G of them remote"},
-                "phases_ms_rank0": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
-                "query": query,
-                "verified": {"slices_add_up_to_n": total == n, "sampled_neighbours_in_order": ok_all}}
-        print(json.dumps(line))
-    dist.barrier()
-    close_comm()
-    ctx.close()
-    dist.destroy_process_group()

@@ -156,6 +156,19 @@ int csa_build_sa(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint32_t p,
 int csa_build_sa_host(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
                       csa_build_stats* stats);
 
+/* ---- validation -------------------------------------------------------------------------------------------- */
+
+/* Exact check of a whole 5-byte suffix array in device memory against its text: every entry is below n, no entry occurs
+ * twice (so the array is a permutation), and every neighbouring pair is in order: T[x] < T[y], or the symbols are equal
+ * and the suffix at x + 1 ranks before the suffix at y + 1 (the empty suffix at n before all). result_dev receives four
+ * words: entries out of range, duplicate entries, pairs out of order, and the lowest rank i whose pair (i - 1, i) is out
+ * of order (~0 if none); the array is the suffix array exactly when the first three are zero. The work is queued on the
+ * context's stream. workspace_dev holds csa_validate_workspace_bytes(n) bytes (a bit per position and a rank per
+ * position: 4 bytes for n <= 2^32, else 8). Replaces test::is_correct_SA (test/end-to-end.cpp:11-80). */
+size_t csa_validate_workspace_bytes(uint64_t n);
+int csa_validate_sa(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint8_t* sa40_dev, void* workspace_dev,
+                    size_t workspace_bytes, uint64_t* result_dev);
+
 /* ---- build on several GPUs of one box (one process per GPU) ------------------------------------------------ */
 
 /* All-gather of `bytes` bytes per rank between the ranks' HOST buffers: recv holds world * bytes, rank r's part at

@@ -252,3 +252,57 @@ int orc_max_threads(void)
     return 1;
 #endif
 }
+
+void orc_set_threads(int threads)
+{
+#ifdef _OPENMP
+    if(threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}
+
+/* The seeded synthetic corpus of the benchmark, for the CPU arms that must not load the product library. It is not
+ * part of the reference (its corpora are tokenized text, dataset/tokenize-corpus.py:4-7 gives their layout: u16 ids with
+ * 0xFFFF before each document); every symbol is a function of (seed, position): position 0 and every position after a
+ * document's last token hold 0xFFFF, a document ends after each token with probability 1 / mean_doc, tokens are drawn by
+ * inverse CDF from 64-bit thresholds. The product's generators make the same symbols (a CPU test compares them). */
+static uint64_t corpus_hash64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+static int corpus_ends_after(uint64_t seed, uint64_t j, uint32_t mean_doc)
+{
+    return corpus_hash64(seed * 0x9E3779B97F4A7C15ull + 2 * j + 1) % mean_doc == 0;
+}
+
+void orc_gen_corpus(uint16_t* text, uint64_t first, uint64_t count, uint64_t seed, uint32_t mean_doc, const uint64_t* cdf, uint32_t vocab)
+{
+    #pragma omp parallel for schedule(static)
+    for(uint64_t k = 0; k < count; ++k)
+    {
+        const uint64_t i = first + k;
+        int sep;
+        if(i == 0) sep = 1;
+        else
+        {
+            /* a separator follows a document's end unless that end flag belongs to a position that is a separator itself */
+            uint64_t run = 0, j = i;
+            while(j > 0 && corpus_ends_after(seed, j - 1, mean_doc)) { ++run; --j; }
+            sep = (j == 0) ? ((i & 1) == 0) : ((run & 1) == 1);
+        }
+        if(sep) { text[k] = 0xFFFF; continue; }
+        const uint64_t u = corpus_hash64(seed * 0xD1B54A32D192ED03ull + 2 * i);
+        uint32_t a = 0, b = vocab - 1;
+        while(a < b)
+        {
+            const uint32_t mid = (a + b) >> 1;
+            if(u <= cdf[mid]) b = mid; else a = mid + 1;
+        }
+        text[k] = (uint16_t)a;
+    }
+}

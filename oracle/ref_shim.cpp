@@ -21,6 +21,7 @@
 #include "types.hpp"
 
 #include <parallel/algorithm>
+#include <omp.h>
 
 #include <cstdint>
 #include <cstring>
@@ -113,6 +114,13 @@ uint64_t ref_counts_hash(const uint64_t* itv, uint64_t q)
 unsigned ref_thread_count(void)
 {
     return host_search::thread_count(0);
+}
+
+// Sets the OpenMP team size of the calls above (a launcher may have exported OMP_NUM_THREADS=1 for its children).
+void ref_set_threads(int threads)
+{
+    if(threads > 0)
+        omp_set_num_threads(threads);
 }
 
 }
