@@ -58,6 +58,7 @@ _SIGS = {
     "csa_validate_workspace_bytes": (ctypes.c_size_t, [c_u64]),
     "csa_validate_sa": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, ctypes.c_size_t, c_vp]),
     "csa_comm_open_shm": (c_int, [ctypes.c_char_p, c_u32, c_u32, c_u32, c_vp]),
+    "csa_comm_shm_set_timeout": (c_int, [c_vp, ctypes.c_double]),
     "csa_comm_close_shm": (None, [c_vp, c_int]),
     "csa_plan_shards": (c_int, [c_vp, c_u32, c_u32, c_u32, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "csa_build_sa_multi": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, c_vp, c_vp, ctypes.POINTER(c_u32), ctypes.POINTER(BuildStats)]),

@@ -99,18 +99,53 @@ struct Peer_Info
     int device;
 };
 
-int gather(csa_ctx* ctx, const csa_comm* comm, const void* send, void* recv, u64 bytes)
+// Every all-gather of the build carries a status word in front of its payload and has one fixed size, so that a rank which
+// fails on its own (an allocation, a capacity check, a CUDA error) can say so in whichever all-gather its peers reach next:
+// all ranks then leave the build at the same step instead of writing into, or waiting for, a rank that has gone.
+constexpr size_t GATHER_PAYLOAD = size_t(CSA_MAX_PARTITIONS) * 8;
+constexpr size_t GATHER_BYTES = 16 + GATHER_PAYLOAD;
+
+struct Gather_State
 {
-    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));      // a barrier: this rank's queued device work is done first
-    if(comm->allgather(comm->user, send, recv, bytes) != 0) return csa_fail(ctx, CSA_E_COMM, "the caller's all-gather failed");
+    bool comm_failed = false;       // the caller's all-gather itself failed: the ranks can no longer meet
+    bool peers_know = false;        // a non-zero status has crossed: every rank is leaving
+};
+
+int gather(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const void* send, void* recv, u64 bytes, u64 my_status = 0)
+{
+    if(bytes > GATHER_PAYLOAD) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: all-gather payload too large");
+    if(my_status == 0) CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));      // a barrier: this rank's queued device work is done first
+    std::vector<unsigned char> msg(GATHER_BYTES, 0), all(GATHER_BYTES * comm->world);
+    std::memcpy(msg.data(), &my_status, 8);
+    if(bytes) std::memcpy(msg.data() + 16, send, bytes);
+    if(comm->allgather(comm->user, msg.data(), all.data(), GATHER_BYTES) != 0)
+    {
+        gs.comm_failed = true;
+        return csa_fail(ctx, CSA_E_COMM, "the caller's all-gather failed");
+    }
+    for(u32 g = 0; g < comm->world; ++g)
+    {
+        u64 status = 0;
+        std::memcpy(&status, all.data() + size_t(g) * GATHER_BYTES, 8);
+        if(status != 0)
+        {
+            gs.peers_know = true;
+            return csa_fail(ctx, g == comm->rank ? int(status) : CSA_E_COMM,
+                            g == comm->rank ? ctx->err : "multi-GPU build: rank " + std::to_string(g) + " left the build with status " + std::to_string(status));
+        }
+    }
+    if(recv) for(u32 g = 0; g < comm->world; ++g) std::memcpy(static_cast<unsigned char*>(recv) + size_t(g) * bytes, all.data() + size_t(g) * GATHER_BYTES + 16, bytes);
     return CSA_OK;
 }
 
-int barrier(csa_ctx* ctx, const csa_comm* comm)
+int barrier(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs)
 {
     u64 token = comm->rank, all[CSA_MAX_GPUS];
-    return gather(ctx, comm, &token, all, sizeof(u64));
+    return gather(ctx, comm, gs, &token, all, sizeof(u64));
 }
+
+int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const uint16_t* T, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40,
+                     uint64_t capacity_entries, uint64_t* seg_first, uint64_t* seg_count, uint32_t* seg_c, csa_build_stats* stats);
 
 }   // namespace
 
@@ -118,8 +153,31 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
                                   uint64_t capacity_entries, uint64_t* seg_first, uint64_t* seg_count, uint32_t* seg_c, csa_build_stats* stats)
 {
     if(!ctx || !comm || !comm->allgather || !T || !sa40 || !seg_first || !seg_count || !seg_c) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: null argument");
+    if(comm->world == 0 || comm->world > CSA_MAX_GPUS || comm->rank >= comm->world) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: bad rank or world size");
+    Gather_State gs;
+    int rc = build_multi_body(ctx, comm, gs, T, n, p, seed, sa40, capacity_entries, seg_first, seg_count, seg_c, stats);
+    const std::string why = ctx->err;
+    // A rank that failed on its own tells the others in the all-gather they reach next; then every rank, failed or not, drains
+    // its stream and passes one last barrier, so that no arena is reused or freed while a peer's copy into it is in flight.
+    if(rc != CSA_OK && !gs.comm_failed && !gs.peers_know) gather(ctx, comm, gs, nullptr, nullptr, 0, u64(rc));
+    cudaStreamSynchronize(ctx->stream);
+    if(!gs.comm_failed)
+    {
+        Gather_State last;
+        const int brc = barrier(ctx, comm, last);
+        if(rc == CSA_OK) rc = brc;
+    }
+    if(rc != CSA_OK && !why.empty()) ctx->err = why;
+    return rc;
+}
+
+namespace
+{
+
+int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const uint16_t* T, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40,
+                     uint64_t capacity_entries, uint64_t* seg_first, uint64_t* seg_count, uint32_t* seg_c, csa_build_stats* stats)
+{
     const u32 G = comm->world, me = comm->rank;
-    if(G == 0 || G > CSA_MAX_GPUS || me >= G) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: bad rank or world size");
     if(n == 0 || p == 0 || p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: n or partition count out of range");
     if(n >= (u64(1) << 32) - (u64(1) << 26)) return csa_fail(ctx, CSA_E_LIMIT, "multi-GPU build: this build addresses fewer than 2^32 - 2^26 suffixes");
     if((reinterpret_cast<uintptr_t>(T) & 15) || (reinterpret_cast<uintptr_t>(sa40) & 15)) return csa_fail(ctx, CSA_E_INVALID, "multi-GPU build: text and output must be 16-byte aligned");
@@ -198,7 +256,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
 
     // ---- plan: the same on every rank ------------------------------------------------------------------------------
     std::vector<u64> hist_all(size_t(G) * p_eff), send_hist(my_hist.begin(), my_hist.begin() + p_eff);
-    CSA_TRY(gather(ctx, comm, send_hist.data(), hist_all.data(), size_t(p_eff) * 8));
+    CSA_TRY(gather(ctx, comm, gs, send_hist.data(), hist_all.data(), size_t(p_eff) * 8));
     std::vector<u64> part_off(p_eff + 1), local_first(p_eff), local_count(G), cursor_all(size_t(G) * p_eff);
     std::vector<u32> owner(p_eff);
     if(csa_plan_shards(reinterpret_cast<const uint64_t*>(hist_all.data()), p_eff, G, comm->policy, reinterpret_cast<uint64_t*>(part_off.data()), owner.data(),
@@ -270,7 +328,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     mine.arena_address = reinterpret_cast<u64>(ctx->arena);
     mine.device = ctx->device;
     std::vector<Peer_Info> peers(G);
-    CSA_TRY(gather(ctx, comm, &mine, peers.data(), sizeof(Peer_Info)));
+    CSA_TRY(gather(ctx, comm, gs, &mine, peers.data(), sizeof(Peer_Info)));
     u8* peer_arena[CSA_MAX_GPUS];
     for(u32 g = 0; g < G; ++g)
     {
@@ -322,7 +380,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 16, counts_dev, G * 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         for(u32 g = 0; g < G; ++g) mine_c[g] = ctx->h_scalars[16 + g];
-        CSA_TRY(gather(ctx, comm, mine_c, C.data(), G * 8));
+        CSA_TRY(gather(ctx, comm, gs, mine_c, C.data(), G * 8));
         u64 off = 0;
         for(u32 d = 0; d < G; ++d) { ctx->h_scalars[24 + d] = off; off += C[size_t(me) * G + d]; }
         CSA_CUDA(ctx, cudaMemcpyAsync(cursor_dev, ctx->h_scalars + 24, G * 8, cudaMemcpyHostToDevice, ctx->stream));
@@ -368,7 +426,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
                 mine_c[g] += hist_host[bkt];
             }
         }
-        CSA_TRY(gather(ctx, comm, mine_c, C.data(), G * 8));
+        CSA_TRY(gather(ctx, comm, gs, mine_c, C.data(), G * 8));
         if(inbox_total() > shard) return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: more rank updates than positions in a shard");
         {
             void* dsts[CSA_MAX_GPUS]; const void* srcs[CSA_MAX_GPUS]; u64 bytes[CSA_MAX_GPUS];
@@ -382,7 +440,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
             }
             CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
-        CSA_TRY(barrier(ctx, comm));                                   // every inbox is complete
+        CSA_TRY(barrier(ctx, comm, gs));                                   // every inbox is complete
         CSA_TRY(launch_apply_updates(ctx, isa, reinterpret_cast<const u64*>(xin), inbox_total(), u64(me) * shard));
         return CSA_OK;
     };
@@ -408,7 +466,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
             }
             CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
-        CSA_TRY(barrier(ctx, comm));                                   // every request has arrived
+        CSA_TRY(barrier(ctx, comm, gs));                                   // every request has arrived
         CSA_TRY(launch_serve_requests(ctx, isa, req_in, inbox_total(), resp_out));
         {
             void* dsts[CSA_MAX_GPUS]; const void* srcs[CSA_MAX_GPUS]; u64 bytes[CSA_MAX_GPUS];
@@ -423,7 +481,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
             CSA_TRY(launch_copy_segments(ctx, dsts, srcs, bytes, G));
         }
         CSA_TRY(launch_keys_init(ctx, heads, poss, count, n, h, sec_bits, keys));
-        CSA_TRY(barrier(ctx, comm));                                   // every response has arrived
+        CSA_TRY(barrier(ctx, comm, gs));                                   // every response has arrived
         u64 asked = 0;
         for(u32 d = 0; d < G; ++d) asked += C[size_t(me) * G + d];
         CSA_TRY(launch_keys_add(ctx, perm, resp_in, asked, h, keys));
@@ -456,7 +514,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     }
     CSA_CUDA(ctx, cudaEventRecord(ev[1], ctx->stream));
     lap("ids + scatter");
-    CSA_TRY(barrier(ctx, comm));        // every position has reached its owner
+    CSA_TRY(barrier(ctx, comm, gs));        // every position has reached its owner
     lap("barrier");
 
     // ---- generation 0 over this rank's partitions -------------------------------------------------------------------
@@ -489,7 +547,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     u64 active = ctx->h_scalars[0];
     u64 counts[CSA_MAX_GPUS];
-    CSA_TRY(gather(ctx, comm, &active, counts, sizeof(u64)));     // also the barrier after generation 0's rank writes
+    CSA_TRY(gather(ctx, comm, gs, &active, counts, sizeof(u64)));     // also the barrier after generation 0's rank writes
     u64 total_active = 0;
     for(u32 g = 0; g < G; ++g) total_active += counts[g];
     st.active_after_gen0 = total_active;
@@ -524,7 +582,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
         CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 1, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         u64 mine2[2] = {ctx->h_scalars[0], ctx->h_scalars[1]}, all2[2 * CSA_MAX_GPUS];
-        CSA_TRY(gather(ctx, comm, mine2, all2, sizeof(mine2)));    // the barrier after this generation's rank writes
+        CSA_TRY(gather(ctx, comm, gs, mine2, all2, sizeof(mine2)));    // the barrier after this generation's rank writes
         u64 next_total = 0, any_status = 0;
         for(u32 g = 0; g < G; ++g) { next_total += all2[2 * g]; any_status |= all2[2 * g + 1]; }
         if(any_status != 0) { u64 b = 0; csa_sync(ctx, reinterpret_cast<uint64_t*>(&b)); return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: a rank reported a device status"); }
@@ -543,8 +601,7 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     CSA_TRY(launch_pack_sa40(ctx, sa, n_local, sa40));
     CSA_CUDA(ctx, cudaEventRecord(ev[4], ctx->stream));
     u64 bits = 0;
-    CSA_TRY(csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits)));
-    CSA_TRY(barrier(ctx, comm));        // no rank leaves (and reuses its arena) while another may still read it
+    CSA_TRY(csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits)));     // the caller of this body passes the last barrier
 
     float ms = 0;
     cudaEventElapsedTime(&ms, ev[0], ev[1]); st.ms_partition = ms;
@@ -558,3 +615,5 @@ extern "C" int csa_build_sa_multi(csa_ctx* ctx, const csa_comm* comm, const uint
     st.peer_bytes = peer_bytes + route_bytes;
     return CSA_OK;
 }
+
+}   // namespace

@@ -15,6 +15,7 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <chrono>
 #include <cstdlib>
 #include <random>
@@ -87,42 +88,58 @@ int main(int argc, char** argv)
         if(gpus > CSA_MAX_GPUS) { std::fprintf(stderr, "error: CASCADE_GPUS is at most %d\n", CSA_MAX_GPUS); return EXIT_FAILURE; }
         int present = 0;
         if(cudaGetDeviceCount(&present) != cudaSuccess || present < 1) { std::fprintf(stderr, "error: no CUDA device\n"); return EXIT_FAILURE; }
-        const std::string shm = "/cascade_b200_cli_" + std::to_string(getpid());
+        // a name of this run alone: process id and start time
+        const std::string shm = "/cascade_b200_cli_" + std::to_string(getpid()) + "_" +
+                                std::to_string(std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::system_clock::now().time_since_epoch()).count());
         std::vector<int> rcs(gpus, CSA_OK);
         std::vector<std::string> errs(gpus);
         std::vector<csa_build_stats> sts(gpus);
         std::vector<std::thread> pool;
+        std::atomic<uint32_t> ready{0}, broken{0};      // ranks that have finished their set-up, and how many of them failed it
         for(uint32_t r = 0; r < gpus; ++r)
             pool.emplace_back([&, r]
             {
                 const int dev = (device + int(r)) % present;
-                auto fail = [&](int rc, const std::string& why) { rcs[r] = rc; errs[r] = why; };
-                if(cudaSetDevice(dev) != cudaSuccess) return fail(CSA_E_CUDA, "cudaSetDevice");
                 csa_comm comm{};
-                if(csa_comm_open_shm(shm.c_str(), r, gpus, 1, &comm) != CSA_OK) return fail(CSA_E_COMM, "csa_comm_open_shm");
                 csa_ctx* c = nullptr;
-                if(csa_ctx_create(dev, &c) != CSA_OK) return fail(CSA_E_CUDA, "csa_ctx_create");
                 uint16_t* T_d = nullptr; uint8_t* out_d = nullptr;
                 const uint64_t cap = n;     // room for any deal of the partitions
-                if(cudaMalloc(&T_d, (n + CSA_TEXT_PAD) * 2) != cudaSuccess || cudaMalloc(&out_d, 5 * cap + CSA_SA_PAD_BYTES) != cudaSuccess)
-                    return fail(CSA_E_NOMEM, "device memory for the text and the output");
-                cudaMemcpy(T_d, T, (n + CSA_TEXT_PAD) * 2, cudaMemcpyHostToDevice);
-                std::vector<uint64_t> seg_first(p), seg_count(p);
-                uint32_t seg_c = 0;
-                const int rc = csa_build_sa_multi(c, &comm, T_d, n, p, 0, out_d, cap, seg_first.data(), seg_count.data(), &seg_c, &sts[r]);
-                if(rc != CSA_OK) fail(rc, csa_last_error(c));
-                else
+                bool comm_open = false;
+                // Set-up first, on every rank; the ranks then meet, and nobody starts the build unless all of them can: a rank
+                // that entered the build alone would wait for the others until its all-gather gave up.
+                if(cudaSetDevice(dev) != cudaSuccess) { rcs[r] = CSA_E_CUDA; errs[r] = "cudaSetDevice"; }
+                else if(csa_ctx_create(dev, &c) != CSA_OK) { rcs[r] = CSA_E_CUDA; errs[r] = "csa_ctx_create"; }
+                else if(cudaMalloc(&T_d, (n + CSA_TEXT_PAD) * 2) != cudaSuccess || cudaMalloc(&out_d, 5 * cap + CSA_SA_PAD_BYTES) != cudaSuccess)
+                { rcs[r] = CSA_E_NOMEM; errs[r] = "device memory for the text and the output"; }
+                else if(cudaMemcpy(T_d, T, (n + CSA_TEXT_PAD) * 2, cudaMemcpyHostToDevice) != cudaSuccess) { rcs[r] = CSA_E_CUDA; errs[r] = "copy of the text"; }
+                if(rcs[r] != CSA_OK) broken.fetch_add(1);
+                ready.fetch_add(1);
+                while(ready.load() < gpus) std::this_thread::yield();
+                if(broken.load() == 0)
                 {
-                    uint64_t at = 0;
-                    for(uint32_t k = 0; k < seg_c; ++k)
+                    if(csa_comm_open_shm(shm.c_str(), r, gpus, 1, &comm) != CSA_OK) { rcs[r] = CSA_E_COMM; errs[r] = "csa_comm_open_shm"; }
+                    else
                     {
-                        cudaMemcpy(SA + 5 * seg_first[k], out_d + 5 * at, 5 * seg_count[k], cudaMemcpyDeviceToHost);
-                        at += seg_count[k];
+                        comm_open = true;
+                        std::vector<uint64_t> seg_first(p), seg_count(p);
+                        uint32_t seg_c = 0;
+                        const int rc = csa_build_sa_multi(c, &comm, T_d, n, p, 0, out_d, cap, seg_first.data(), seg_count.data(), &seg_c, &sts[r]);
+                        if(rc != CSA_OK) { rcs[r] = rc; errs[r] = csa_last_error(c); }
+                        else
+                        {
+                            uint64_t at = 0;
+                            for(uint32_t k = 0; k < seg_c; ++k)
+                            {
+                                cudaMemcpy(SA + 5 * seg_first[k], out_d + 5 * at, 5 * seg_count[k], cudaMemcpyDeviceToHost);
+                                at += seg_count[k];
+                            }
+                        }
                     }
                 }
+                else if(rcs[r] == CSA_OK) { rcs[r] = CSA_E_COMM; errs[r] = "another rank could not be set up"; }
                 cudaFree(T_d); cudaFree(out_d);
-                csa_ctx_destroy(c);
-                csa_comm_close_shm(&comm, r == 0);
+                if(c) csa_ctx_destroy(c);
+                if(comm_open) csa_comm_close_shm(&comm, r == 0);
             });
         for(auto& t : pool) t.join();
         for(uint32_t r = 0; r < gpus; ++r)

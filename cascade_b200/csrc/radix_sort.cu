@@ -23,7 +23,11 @@ constexpr u32 FLAG_AGGREGATE = 1u << FLAG_SHIFT;
 constexpr u32 FLAG_PREFIX = 2u << FLAG_SHIFT;
 u64 PORTION = 1ull << 29;                   // records per launch of a pass: tile counts stay below 2^30 (tests may lower it)
 constexpr u32 LOOKBACK_SPIN_LIMIT = 1u << 22;
+// The limit that the kernels read (a test lowers it through csa_debug_set so that a wait which cannot succeed ends at once).
+__device__ u32 g_lookback_spin_limit = LOOKBACK_SPIN_LIMIT;
+u32 g_first_tile = 0;                        // test hook: value that a pass's tile counter starts from (0 in every real run)
 constexpr int LOOKBACK_BATCH = 8;
+constexpr int GAVE_UP_WORD = 32;           // word of a block's scratch words in shared memory that says a look-back wait ran out
 constexpr int HIST_UNROLL = 4;             // 16-byte loads in flight per thread of the histogram kernel
 
 // The digit of a pass that starts at bit `shift` holds min(8, end_bit - shift) bits.
@@ -298,6 +302,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
             // The status words of LOOKBACK_BATCH earlier tiles are requested at once, so that a long walk costs one memory
             // round trip per batch instead of one per tile; a word that is still empty is polled (with a bound) in place.
             bool gave_up = false, done = false;
+            const u32 spin_limit = g_lookback_spin_limit;
             long long t = (long long)tile - 1;
             while(t >= 0 && !done && !gave_up)
             {
@@ -313,7 +318,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
                     u32 spins = 0;
                     while((v >> FLAG_SHIFT) == 0)
                     {
-                        if(++spins > LOOKBACK_SPIN_LIMIT || ((spins & 255u) == 0 && (ld_relaxed_u64(dev_status) & CSA_ST_LOOKBACK_TIMEOUT)))
+                        if(++spins > spin_limit || ((spins & 255u) == 0 && (ld_relaxed_u64(dev_status) & CSA_ST_LOOKBACK_TIMEOUT)))
                         {
                             gave_up = true;
                             break;
@@ -327,7 +332,8 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
                 }
                 t -= LOOKBACK_BATCH;
             }
-            if(gave_up) atomicOr(dev_status, (u64)CSA_ST_LOOKBACK_TIMEOUT);
+            if(gave_up) { atomicOr(dev_status, (u64)CSA_ST_LOOKBACK_TIMEOUT); misc[GAVE_UP_WORD] = 1; }
+            // published even then, so that the tiles after this one end their waits too
             st_relaxed_u32(status + u64(tile) * RADIX + tid, FLAG_PREFIX | ((before + count) & COUNT_MASK));
         }
         const u64 db = digit_base[tid];
@@ -335,6 +341,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
         g_off[tid] = db + before - tile_excl[tid];
     }
     __syncthreads();
+    if(misc[GAVE_UP_WORD]) return;      // a wait ran out: the offsets are not known, nothing is written (the status word tells the host)
 
     // Stage the records in digit order.
     #pragma unroll
@@ -378,7 +385,7 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
     u32* const misc = reinterpret_cast<u32*>(smem_raw + size_t(TILE) * 8 + size_t(TILE) * sizeof(V) + size_t(WARPS) * RADIX * 4 + RADIX * 4 + RADIX * 8);
 
     // Tiles are taken in launch order of the blocks that run, so that every tile a block waits on is already running.
-    if(threadIdx.x == 0) misc[0] = atomicAdd(tile_counter, 1u);
+    if(threadIdx.x == 0) { misc[0] = atomicAdd(tile_counter, 1u); misc[GAVE_UP_WORD] = 0; }
     for(int i = threadIdx.x; i < WARPS * RADIX; i += BLOCK) warp_hist[i] = 0;
     __syncthreads();
     const u32 tile = misc[0];
@@ -410,6 +417,12 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
     {
         CSA_CUDA(ctx, cudaMemsetAsync(status, 0, tiles * RADIX * sizeof(u32), ctx->stream));
         CSA_CUDA(ctx, cudaMemsetAsync(counter, 0, sizeof(u32), ctx->stream));
+    }
+    if(g_first_tile != 0)       // test hook only
+    {
+        static u32 start_value;
+        start_value = g_first_tile;
+        CSA_CUDA(ctx, cudaMemcpyAsync(counter, &start_value, sizeof(u32), cudaMemcpyHostToDevice, ctx->stream));
     }
     kern<<<unsigned(tiles), BLOCK, S::bytes, ctx->stream>>>(kin, kout, vin, vout, n, shift, dmask, digit_base, next_base, status, counter, ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
@@ -568,6 +581,12 @@ extern "C" int csa_debug_set(int key, uint64_t value)
 {
     if(key == 0 && value >= 12 && value <= 29) { PORTION = 1ull << value; return CSA_OK; }
     if(key == 1 && value <= 5) { g_variant = int(value); return CSA_OK; }
+    if(key == 2 && value >= 1 && value <= LOOKBACK_SPIN_LIMIT)     // on the current device
+    {
+        const u32 v = u32(value);
+        return cudaMemcpyToSymbol(g_lookback_spin_limit, &v, sizeof(v)) == cudaSuccess ? CSA_OK : CSA_E_CUDA;
+    }
+    if(key == 3 && value <= 1) { g_first_tile = u32(value); return CSA_OK; }
     return CSA_E_INVALID;
 }
 

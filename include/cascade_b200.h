@@ -87,8 +87,12 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, voi
  * threads) race on it, so keep them one after another per device. */
 int csa_sort_pairs_static(void* stream, uint64_t* keys_dev, uint64_t* keys_alt_dev, uint32_t* vals_dev, uint32_t* vals_alt_dev,
                           uint64_t n, int begin_bit, int end_bit, int* in_alt);
-/* Test hook. key 0: log2 of the most records one launch of a digit pass takes (12..29, default 29); larger sorts run
- * as several launches per pass. */
+/* Test hooks. key 0: log2 of the most records one launch of a digit pass takes (12..29, default 29); larger sorts run
+ * as several launches per pass. key 2: polls after which a tile of a digit pass gives up waiting for the tile before it
+ * (1..2^22, default 2^22), on the current device. key 3: 1 makes the tile numbering of csa_sort_pairs' passes start at 1,
+ * so that tile 0 never comes and every wait of the pass runs out (0 restores it): the sort then returns normally, nothing
+ * of the failed pass is written, and csa_sync reports CSA_E_DEVICE with bit 0 (a look-back wait ran out) in its status
+ * word. No device fault is involved. */
 int csa_debug_set(int key, uint64_t value);
 /* Average device time of the digit passes of the sorts run on ctx since the last csa_reset_counters, measured
  * with CUDA events on the context's stream when pass timing is on (csa_set_pass_timing): total milliseconds,
@@ -185,8 +189,11 @@ typedef struct csa_comm
 /* A ready-made communicator for ranks that run on one box: the all-gather goes through a POSIX shared-memory object
  * called `name` (the same string on every rank, unique to the job; at most 48 KB per rank and call). Every rank calls
  * csa_comm_open_shm before the first build and csa_comm_close_shm after the last (one rank passes unlink_name = 1).
- * Waits are bounded (two minutes): a missing rank makes the others fail with CSA_E_COMM. */
+ * Rank 0 makes the object, replacing a leftover of the same name; the other ranks wait for it. Waits are bounded (two
+ * minutes unless the environment variable CASCADE_COMM_TIMEOUT_S or csa_comm_shm_set_timeout says otherwise): a rank that
+ * never arrives makes the others fail with CSA_E_COMM. */
 int csa_comm_open_shm(const char* name, uint32_t rank, uint32_t world, uint32_t policy, csa_comm* out);
+int csa_comm_shm_set_timeout(csa_comm* comm, double seconds);
 void csa_comm_close_shm(csa_comm* comm, int unlink_name);
 
 /* Host-side plan of a sharded build, the same on every rank: from every rank's partition sizes over its share of the

@@ -161,3 +161,95 @@ def test_shared_memory_allgather_between_processes():
     for rank, out in res:
         for rnd, row in enumerate(out):
             assert row == [r * 1000 + rnd for r in range(world)]
+
+
+def _open(lib, name, rank, world):
+    from cascade_b200._lib import Comm
+    comm = Comm()
+    rc = lib.csa_comm_open_shm(name.encode(), rank, world, 1, ctypes.byref(comm))
+    return rc, comm
+
+
+def test_a_leftover_object_of_the_same_name_is_replaced_not_reused():
+    """A finished or crashed job may leave its object behind (its round counters are far ahead, its payloads are old). The
+    next job with that name must start from a fresh object: rank 0 replaces it, the other ranks refuse the old one."""
+    import threading
+    from multiprocessing import shared_memory
+    from cascade_b200._lib import lib
+    L = lib()
+    name, world = f"/cascade_b200_stale_{os.getpid()}", 2
+    # the old job's object: same size, marked live, every rank 57 rounds in, payloads full of junk
+    slot = 64 + 2 * 48 * 1024
+    size = 64 + world * slot
+    old = shared_memory.SharedMemory(name=name.lstrip("/"), create=True, size=size)
+    buf = np.frombuffer(old.buf, dtype=np.uint8)
+    buf[:] = 0xAB
+    np.frombuffer(old.buf, dtype=np.uint64, count=2)[:] = (0x4353415F4C495645, world)
+    for g in range(world):
+        np.frombuffer(old.buf, dtype=np.uint64, count=1, offset=64 + g * slot)[:] = 57
+    res = {}
+
+    def rank_body(rank, delay):
+        import time
+        time.sleep(delay)
+        rc, comm = _open(L, name, rank, world)
+        assert rc == 0
+        got = []
+        for rnd in range(3):
+            mine = np.full(4, 100 * rank + rnd, np.uint64)
+            allv = np.zeros(4 * world, np.uint64)
+            got.append((comm.allgather(comm.user, mine.ctypes.data, allv.ctypes.data, mine.nbytes), allv.reshape(world, 4)[:, 0].tolist()))
+        res[rank] = got
+        L.csa_comm_close_shm(ctypes.byref(comm), 1 if rank == 0 else 0)
+
+    # rank 1 arrives first and finds only the leftover; it must wait for rank 0's fresh object
+    ts = [threading.Thread(target=rank_body, args=(1, 0.0)), threading.Thread(target=rank_body, args=(0, 0.3))]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(timeout=60)
+    del buf
+    old.close()
+    try:
+        old.unlink()
+    except FileNotFoundError:
+        pass
+    for rank in range(world):
+        assert res[rank] == [(0, [rnd, 100 + rnd]) for rnd in range(3)], res
+
+
+def test_a_missing_rank_makes_the_others_fail_within_the_limit():
+    import threading
+    import time
+    from cascade_b200._lib import lib
+    L = lib()
+    name, world = f"/cascade_b200_missing_{os.getpid()}", 3
+    out = {}
+
+    def rank_body(rank):
+        rc, comm = _open(L, name, rank, world)
+        assert rc == 0
+        assert L.csa_comm_shm_set_timeout(ctypes.byref(comm), 1.0) == 0
+        mine = np.full(2, rank, np.uint64)
+        allv = np.zeros(2 * world, np.uint64)
+        t0 = time.perf_counter()
+        rc = comm.allgather(comm.user, mine.ctypes.data, allv.ctypes.data, mine.nbytes)
+        out[rank] = (rc, time.perf_counter() - t0)
+        L.csa_comm_close_shm(ctypes.byref(comm), 1 if rank == 0 else 0)
+
+    ts = [threading.Thread(target=rank_body, args=(r,)) for r in (0, 1)]        # rank 2 never comes
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(timeout=60)
+    for r in (0, 1):
+        rc, dt = out[r]
+        assert rc != 0 and 0.9 < dt < 10.0, out
+    # a rank other than 0 that finds no object at all gives up too
+    os.environ["CASCADE_COMM_TIMEOUT_S"] = "0.5"
+    try:
+        t0 = time.perf_counter()
+        rc, _ = _open(L, name + "_nobody", 1, 2)
+        assert rc == 6 and time.perf_counter() - t0 < 10.0
+    finally:
+        del os.environ["CASCADE_COMM_TIMEOUT_S"]

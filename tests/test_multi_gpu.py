@@ -100,3 +100,78 @@ def test_sharded_build_equals_the_single_gpu_build(world, n, p, kind, policy):
     if kind == "repeat":
         assert res[0][4] >= 5
     assert sum(r[5] for r in res) > 0      # ranks and positions did cross between the GPUs' memories
+
+
+def test_a_failing_all_gather_ends_the_build_with_a_comm_error_and_the_context_stays_usable():
+    from cascade_b200 import api, multi
+    from cascade_b200._lib import ALLGATHER_FN, Comm
+    ctx = api.Context(0)
+    try:
+        n = 500_000
+        T = api.gen_corpus_device(ctx, n, 3, 512)
+        calls = []
+
+        def broken(user, send, recv, nbytes):
+            calls.append(int(nbytes))
+            return 1 if len(calls) >= 2 else multi.make_comm(0, 1, None)[0].allgather(user, send, recv, nbytes)
+        fn = ALLGATHER_FN(broken)
+        with pytest.raises(api.CascadeError) as e:
+            multi.build_sa_multi(ctx, Comm(0, 1, 1, fn, None), T, n, 8)
+        assert e.value.code == 6 and len(calls) == 2          # CSA_E_COMM at the second all-gather; no further calls on a dead communicator
+        assert len(set(calls)) == 1, "every all-gather of a build has one size"
+        comm, keep = multi.make_comm(0, 1, None)
+        out, segs, st = multi.build_sa_multi(ctx, comm, T, n, 8)
+        ref, _ = api.build_sa(ctx, T, n, 8)
+        assert torch.equal(out[:5 * n], ref[:5 * n])
+    finally:
+        ctx.close()
+
+
+def _failing_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import time
+    import torch.distributed as dist
+    from cascade_b200 import api, multi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    ctx = api.Context(dev)
+    n, p = 1_000_000, 8
+    T = api.gen_corpus_device(ctx, n, 7, 512)
+    comm, close = multi.make_shm_comm(rank, world, f"/cascade_b200_f{port}")
+    # rank 1's output buffer is too small for its slice: it alone can tell, yet both ranks must leave the build, and soon
+    code = 0
+    t0 = time.perf_counter()
+    try:
+        multi.build_sa_multi(ctx, comm, T, n, p, capacity=(1000 if rank == 1 else n))
+    except api.CascadeError as e:
+        code = e.code
+    dt = time.perf_counter() - t0
+    out, segs, st = multi.build_sa_multi(ctx, comm, T, n, p)           # the same contexts and communicator build normally afterwards
+    ref, _ = api.build_sa(ctx, T, n, p)
+    at, same = 0, True
+    for first, count in segs:
+        same = same and bool(torch.equal(out[5 * at:5 * (at + count)], ref[5 * first:5 * (first + count)]))
+        at += count
+    q.put((rank, code, dt, same))
+    dist.barrier()
+    close()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+def test_a_rank_that_fails_alone_takes_every_rank_out_of_the_build():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted(q.get(timeout=600) for _ in range(world))
+    for pr in procs:
+        pr.join(timeout=120)
+        assert pr.exitcode == 0
+    assert res[1][1] == 3 and res[0][1] == 6, res          # CSA_E_NOMEM where it happened, CSA_E_COMM on the peer
+    assert all(r[2] < 30 and r[3] for r in res), res

@@ -89,3 +89,24 @@ def test_sort_in_several_launches_per_pass(ctx):
         _check(ctx, keys, torch.arange(n, device="cuda", dtype=torch.int32), 0, 20)
     finally:
         assert lib().csa_debug_set(0, 29) == 0
+
+
+def test_a_wait_that_cannot_succeed_runs_out_and_is_reported_without_a_fault(ctx):
+    """With the test hooks on, the tiles of a pass are numbered from 1: tile 0, on which tile 1 waits, never comes. Every
+    bounded wait of the pass must run out, the kernels must return, nothing of the failed passes may be written, the host
+    must get CSA_E_DEVICE with the look-back bit from csa_sync, and the context must sort correctly afterwards."""
+    from cascade_b200 import api
+    from cascade_b200._lib import lib
+    L = lib()
+    n = 200_000
+    g = torch.Generator(device="cuda").manual_seed(5)
+    keys = torch.randint(-(1 << 62), 1 << 62, (n,), device="cuda", dtype=torch.int64, generator=g)
+    vals = torch.arange(n, device="cuda", dtype=torch.int32)
+    assert L.csa_debug_set(2, 64) == 0 and L.csa_debug_set(3, 1) == 0
+    try:
+        with pytest.raises(api.CascadeError) as e:
+            api.sort_pairs(ctx, keys.clone(), vals.clone(), 0, 16)
+        assert e.value.code == 5 and "status bits 1" in str(e.value)
+    finally:
+        assert L.csa_debug_set(3, 0) == 0 and L.csa_debug_set(2, 1 << 22) == 0
+    _check(ctx, keys, vals, 0, 64)
