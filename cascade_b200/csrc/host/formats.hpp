@@ -9,9 +9,11 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <cerrno>
+#include <cstdlib>
 #include <ctime>
 #include <fstream>
-#include <map>
+#include <utility>
 #include <sstream>
 #include <string>
 #include <sys/stat.h>
@@ -73,54 +75,122 @@ struct Index_Meta
     long long sep = 65535;
 };
 
+// index.meta is a list of key=value lines (schema: include/Index_Meta.hpp:207-241 of the reference). The two helpers
+// below keep the schema in ONE table of rows, used for writing and for reading.
+class Meta_Lines
+{
+    std::vector<std::pair<std::string, std::string>> rows_;
+    std::string problem_;
+public:
+    void put(const std::string& key, const std::string& value) { rows_.emplace_back(key, value); }
+    void put(const std::string& key, unsigned long long value) { rows_.emplace_back(key, std::to_string(value)); }
+    void put_signed(const std::string& key, long long value) { rows_.emplace_back(key, std::to_string(value)); }
+    std::string text() const
+    {
+        std::string out;
+        for(const auto& r : rows_) out += r.first + "=" + r.second + "\n";
+        return out;
+    }
+    // Reads `path`; comment lines (#) and empty lines are skipped.
+    bool load(const std::string& path)
+    {
+        std::ifstream is(path);
+        if(!is) { problem_ = "cannot open index metadata: " + path; return false; }
+        for(std::string line; std::getline(is, line); )
+        {
+            if(line.empty() || line[0] == '#') continue;
+            const size_t eq = line.find('=');
+            if(eq == std::string::npos) { problem_ = "index.meta: a line without `=`: " + line; return false; }
+            rows_.emplace_back(line.substr(0, eq), line.substr(eq + 1));
+        }
+        return true;
+    }
+    const std::string* find(const std::string& key) const
+    {
+        for(auto it = rows_.rbegin(); it != rows_.rend(); ++it) if(it->first == key) return &it->second;     // a later line wins
+        return nullptr;
+    }
+    // The accessors note the first key that is missing or unreadable and return a neutral value; `problem()` tells.
+    std::string str(const std::string& key)
+    {
+        const std::string* v = find(key);
+        if(!v && problem_.empty()) problem_ = "index.meta: no `" + key + "`";
+        return v ? *v : std::string();
+    }
+    unsigned long long num(const std::string& key)
+    {
+        const std::string v = str(key);
+        char* stop = nullptr;
+        errno = 0;
+        const unsigned long long x = v.empty() ? 0 : std::strtoull(v.c_str(), &stop, 10);
+        if((v.empty() || errno != 0 || (stop && *stop)) && problem_.empty()) problem_ = "index.meta: `" + key + "` is not a number";
+        return x;
+    }
+    const std::string& problem() const { return problem_; }
+};
+
 inline bool write_index_meta(const std::string& dir, const Index_Meta& m, std::string& err)
 {
-    std::ostringstream o;
-    o << "format=gpu_saca_query_index\nformat_version=1\nn=" << m.n << "\nsym_bytes=" << m.sym_bytes << "\nsa_width=" << m.sa_width
-      << "\nsa_order=" << m.sa_order << "\ntext=" << m.text << "\nsa_part_c=" << m.sa_part.size() << "\n";
-    for(size_t i = 0; i < m.sa_part.size(); ++i) o << "sa_part_" << i << "=" << m.sa_part[i] << "\nsa_part_off_" << i << "=" << m.sa_part_off[i] << "\n";
-    char when[32] = "";
-    const std::time_t t = std::time(nullptr);
-    std::strftime(when, sizeof(when), "%Y-%m-%dT%H:%M:%SZ", std::gmtime(&t));
-    o << "sep=" << m.sep << "\nsa_source=" << m.sa_source << "\ncreated_utc=" << (m.created_utc.empty() ? when : m.created_utc) << "\n";
-    const std::string path = dir + "/index.meta", tmp = path + ".tmp";
-    { std::ofstream os(tmp); os << o.str(); if(!os) { err = "cannot write " + tmp; return false; } }
-    if(std::rename(tmp.c_str(), path.c_str()) != 0) { err = "cannot rename " + tmp; return false; }
+    std::string when = m.created_utc;
+    if(when.empty())
+    {
+        char buf[32] = "";
+        const std::time_t t = std::time(nullptr);
+        std::strftime(buf, sizeof(buf), "%Y-%m-%dT%H:%M:%SZ", std::gmtime(&t));
+        when = buf;
+    }
+    Meta_Lines L;
+    L.put("format", "gpu_saca_query_index");
+    L.put("format_version", 1ull);
+    L.put("n", m.n);
+    L.put("sym_bytes", m.sym_bytes);
+    L.put("sa_width", m.sa_width);
+    L.put("sa_order", m.sa_order);
+    L.put("text", m.text);
+    L.put("sa_part_c", m.sa_part.size());
+    for(size_t i = 0; i < m.sa_part.size(); ++i)
+    {
+        L.put("sa_part_" + std::to_string(i), m.sa_part[i]);
+        L.put("sa_part_off_" + std::to_string(i), m.sa_part_off[i]);
+    }
+    L.put_signed("sep", m.sep);
+    L.put("sa_source", m.sa_source);
+    L.put("created_utc", when);
+    // written beside its final name and moved there, so that a reader never sees half a file
+    const std::string final_path = dir + "/index.meta", draft = final_path + ".tmp";
+    std::ofstream os(draft, std::ios::trunc);
+    os << L.text();
+    os.close();
+    if(!os) { err = "cannot write " + draft; return false; }
+    if(std::rename(draft.c_str(), final_path.c_str()) != 0) { err = "cannot move " + draft + " to " + final_path; return false; }
     return true;
 }
 
 inline bool read_index_meta(const std::string& dir, Index_Meta& m, std::string& err)
 {
-    std::ifstream is(dir + "/index.meta");
-    if(!is) { err = "cannot open index metadata: " + dir + "/index.meta"; return false; }
-    std::map<std::string, std::string> kv;
-    for(std::string line; std::getline(is, line); )
+    Meta_Lines L;
+    if(!L.load(dir + "/index.meta")) { err = L.problem(); return false; }
+    if(L.str("format") != "gpu_saca_query_index") { err = L.problem().empty() ? "index.meta: not a query index" : L.problem(); return false; }
+    if(L.num("format_version") != 1) { err = L.problem().empty() ? "index.meta: only format_version 1 is understood" : L.problem(); return false; }
+    m.n = L.num("n");
+    m.sym_bytes = uint32_t(L.num("sym_bytes"));
+    m.sa_width = uint32_t(L.num("sa_width"));
+    m.sa_order = L.str("sa_order");
+    m.text = join(dir, L.str("text"));
+    const unsigned long long parts = L.num("sa_part_c");
+    m.sa_part.clear();
+    m.sa_part_off.clear();
+    for(unsigned long long i = 0; i < parts && L.problem().empty(); ++i)
     {
-        if(line.empty() || line[0] == '#') continue;
-        const auto eq = line.find('=');
-        if(eq == std::string::npos) { err = "malformed line in index.meta: `" + line + "`"; return false; }
-        kv[line.substr(0, eq)] = line.substr(eq + 1);
+        m.sa_part.push_back(join(dir, L.str("sa_part_" + std::to_string(i))));
+        m.sa_part_off.push_back(L.num("sa_part_off_" + std::to_string(i)));
     }
-    try
-    {
-        if(kv["format"] != "gpu_saca_query_index") { err = "not a query-index metadata file"; return false; }
-        if(std::stoul(kv.at("format_version")) != 1) { err = "unsupported index-metadata version"; return false; }
-        m.n = std::stoull(kv.at("n"));
-        m.sym_bytes = uint32_t(std::stoul(kv.at("sym_bytes")));
-        m.sa_width = uint32_t(std::stoul(kv.at("sa_width")));
-        m.sa_order = kv.at("sa_order");
-        m.text = join(dir, kv.at("text"));
-        const uint64_t c = std::stoull(kv.at("sa_part_c"));
-        m.sa_part.clear(); m.sa_part_off.clear();
-        for(uint64_t i = 0; i < c; ++i)
-        {
-            m.sa_part.push_back(join(dir, kv.at("sa_part_" + std::to_string(i))));
-            m.sa_part_off.push_back(std::stoull(kv.at("sa_part_off_" + std::to_string(i))));
-        }
-        m.sep = kv.count("sep") ? std::stoll(kv["sep"]) : -1;
-        m.sa_source = kv["sa_source"]; m.created_utc = kv["created_utc"];
-    }
-    catch(const std::exception&) { err = "missing or malformed field in index.meta"; return false; }
+    if(!L.problem().empty()) { err = L.problem(); return false; }
+    // optional keys
+    const std::string* sep = L.find("sep");
+    m.sep = sep ? std::atoll(sep->c_str()) : -1;
+    if(const std::string* v = L.find("sa_source")) m.sa_source = *v; else m.sa_source.clear();
+    if(const std::string* v = L.find("created_utc")) m.created_utc = *v; else m.created_utc.clear();
     if(m.sa_width != 5 || m.sa_order != "numeric_eot_smallest") { err = "index.meta: only 5-byte entries in numeric order are supported"; return false; }
     return true;
 }

@@ -29,9 +29,12 @@ namespace
 
 constexpr uint64_t ENTRY = 5, PAGE = 4096, MAX_N = 1ull << 40;
 
+enum class Mode { convert, meta_only, widen };
+
 struct Args
 {
-    std::string mode = "convert", in, out, sa, text, index_dir, source, check = "perm";
+    Mode mode = Mode::convert;
+    std::string in, out, sa, text, index_dir, source, check = "perm";
     std::vector<std::string> part_dirs;
     uint32_t sym_bytes = 0;
     uint64_t parts = 1, spot = 100000;
@@ -47,53 +50,79 @@ const char* USAGE =
     "             [--spot N] [--sep S] [--source STR]\n"
     "  sa_convert --widen --in SA.u40 --out SA.u64\n";
 
+std::vector<std::string> split(const std::string& v, char at)
+{
+    std::vector<std::string> out(1);
+    for(const char c : v) { if(c == at) out.emplace_back(); else out.back().push_back(c); }
+    return out;
+}
+
+// One row per option: its name, whether a value follows, and what to do with it. The flags are the reference tool's
+// (tools/sa_convert.cpp:38-58); how they are read is this file's own.
+struct Option
+{
+    const char* name;
+    bool takes_value;
+    void (*apply)(Args&, const std::string&);
+};
+
+const Option OPTIONS[] = {
+    {"--meta-only", false, [](Args& a, const std::string&) { a.mode = Mode::meta_only; }},
+    {"--widen", false, [](Args& a, const std::string&) { a.mode = Mode::widen; }},
+    {"--in", true, [](Args& a, const std::string& v) { a.in = v; }},
+    {"--out", true, [](Args& a, const std::string& v) { a.out = v; }},
+    {"--sa", true, [](Args& a, const std::string& v) { a.sa = v; }},
+    {"--text", true, [](Args& a, const std::string& v) { a.text = v; }},
+    {"--index-dir", true, [](Args& a, const std::string& v) { a.index_dir = v; }},
+    {"--source", true, [](Args& a, const std::string& v) { a.source = v; }},
+    {"--check", true, [](Args& a, const std::string& v) { a.check = v; }},
+    {"--part-dirs", true, [](Args& a, const std::string& v) { a.part_dirs = split(v, ':'); }},
+    {"--sym-bytes", true, [](Args& a, const std::string& v) { a.sym_bytes = uint32_t(std::stoul(v)); }},
+    {"--parts", true, [](Args& a, const std::string& v) { a.parts = std::stoull(v); }},
+    {"--spot", true, [](Args& a, const std::string& v) { a.spot = std::stoull(v); }},
+    {"--sep", true, [](Args& a, const std::string& v) { a.sep = std::stoll(v); }},
+};
+
+// What must hold between the options once all are read; the first rule that fails names the problem.
+std::string first_broken_rule(const Args& a)
+{
+    if(a.mode == Mode::widen) return (a.in.empty() || a.out.empty()) ? "widening needs both --in and --out" : "";
+    const bool width_ok = a.sym_bytes == 1 || a.sym_bytes == 2 || a.sym_bytes == 4;
+    const bool check_ok = a.check == "none" || a.check == "range" || a.check == "perm";
+    const struct { bool broken; const char* why; } rules[] = {
+        {a.text.empty() || a.index_dir.empty() || a.sym_bytes == 0, "give --text, --index-dir and --sym-bytes"},
+        {!width_ok, "symbols are 1, 2 or 4 bytes wide (--sym-bytes)"},
+        {a.mode == Mode::convert && a.in.empty(), "a conversion reads its 64-bit entries from --in"},
+        {a.mode == Mode::meta_only && a.sa.empty(), "--meta-only describes the 5-byte array given by --sa"},
+        {a.parts == 0, "--parts counts from 1"},
+        {a.parts > 1 && a.part_dirs.size() != a.parts, "--part-dirs must list one directory per part"},
+        {a.parts > 1 && a.mode != Mode::convert, "only a conversion can cut the array into parts"},
+        {!check_ok, "--check is one of none, range, perm"},
+    };
+    for(const auto& r : rules) if(r.broken) return r.why;
+    return "";
+}
+
 bool parse(int argc, char** argv, Args& a, std::string& err)
 {
     for(int i = 1; i < argc; ++i)
     {
-        const std::string k = argv[i];
-        const auto val = [&]() -> std::string { if(i + 1 >= argc) { err = "missing value after " + k; return ""; } return argv[++i]; };
-        try
+        const std::string key = argv[i];
+        if(key == "-h" || key == "--help") { err.clear(); return false; }
+        const Option* opt = nullptr;
+        for(const Option& o : OPTIONS) if(key == o.name) opt = &o;
+        if(!opt) { err = "unknown option " + key; return false; }
+        std::string value;
+        if(opt->takes_value)
         {
-            if(k == "--meta-only") a.mode = "meta-only";
-            else if(k == "--widen") a.mode = "widen";
-            else if(k == "--in") a.in = val();
-            else if(k == "--out") a.out = val();
-            else if(k == "--sa") a.sa = val();
-            else if(k == "--text") a.text = val();
-            else if(k == "--index-dir") a.index_dir = val();
-            else if(k == "--source") a.source = val();
-            else if(k == "--sym-bytes") a.sym_bytes = uint32_t(std::stoul(val()));
-            else if(k == "--parts") a.parts = std::stoull(val());
-            else if(k == "--check") a.check = val();
-            else if(k == "--spot") a.spot = std::stoull(val());
-            else if(k == "--sep") a.sep = std::stoll(val());
-            else if(k == "--part-dirs")
-            {
-                const std::string v = val();
-                size_t b = 0;
-                while(b <= v.size()) { const size_t e = v.find(':', b); a.part_dirs.push_back(v.substr(b, e == std::string::npos ? e : e - b)); if(e == std::string::npos) break; b = e + 1; }
-            }
-            else if(k == "-h" || k == "--help") { err = ""; return false; }
-            else { err = "unknown option " + k; return false; }
+            if(i + 1 >= argc) { err = key + " needs a value"; return false; }
+            value = argv[++i];
         }
-        catch(const std::exception&) { err = "malformed value for " + k; return false; }
-        if(!err.empty()) return false;
+        try { opt->apply(a, value); }
+        catch(const std::exception&) { err = "cannot read the value of " + key + ": " + value; return false; }
     }
-    if(a.mode == "widen")
-    {
-        if(a.in.empty() || a.out.empty()) { err = "--widen requires --in and --out"; return false; }
-        return true;
-    }
-    if(a.text.empty() || a.index_dir.empty() || a.sym_bytes == 0) { err = "--text, --index-dir, and --sym-bytes are required"; return false; }
-    if(a.sym_bytes != 1 && a.sym_bytes != 2 && a.sym_bytes != 4) { err = "--sym-bytes must be 1, 2, or 4"; return false; }
-    if(a.mode == "convert" && a.in.empty()) { err = "conversion requires --in"; return false; }
-    if(a.mode == "meta-only" && a.sa.empty()) { err = "--meta-only requires --sa"; return false; }
-    if(a.parts == 0) { err = "--parts must be positive"; return false; }
-    if(a.parts > 1 && a.part_dirs.size() != a.parts) { err = "--parts K requires K --part-dirs"; return false; }
-    if(a.parts > 1 && a.mode != "convert") { err = "--parts is supported only for conversion"; return false; }
-    if(a.check != "none" && a.check != "range" && a.check != "perm") { err = "--check must be none, range, or perm"; return false; }
-    return true;
+    err = first_broken_rule(a);
+    return err.empty();
 }
 
 std::string absolute(const std::string& p)
@@ -118,27 +147,30 @@ bool make_dirs(const std::string& dir)
     return true;
 }
 
-// A file mapped read-only.
-struct Mapping
+// A whole file mapped for reading; empty files and files that cannot be opened give a null view.
+class Mapping
 {
-    void* p = MAP_FAILED;
+    const uint8_t* base_ = nullptr;
+public:
     size_t len = 0;
     Mapping() = default;
     Mapping(const Mapping&) = delete;
     Mapping& operator=(const Mapping&) = delete;
-    ~Mapping() { if(p != MAP_FAILED) ::munmap(p, len); }
+    ~Mapping() { if(base_) ::munmap(const_cast<uint8_t*>(base_), len); }
     bool map(const std::string& path)
     {
-        const int fd = ::open(path.c_str(), O_RDONLY);
+        uint64_t bytes = 0;
+        if(!file_size(path, bytes) || bytes == 0) return false;
+        const int fd = ::open(path.c_str(), O_RDONLY | O_CLOEXEC);
         if(fd < 0) return false;
-        struct stat st;
-        if(::fstat(fd, &st) != 0 || st.st_size == 0) { ::close(fd); return false; }
-        len = size_t(st.st_size);
-        p = ::mmap(nullptr, len, PROT_READ, MAP_SHARED, fd, 0);
+        void* const at = ::mmap(nullptr, size_t(bytes), PROT_READ, MAP_PRIVATE, fd, 0);
         ::close(fd);
-        return p != MAP_FAILED;
+        if(at == MAP_FAILED) return false;
+        base_ = static_cast<const uint8_t*>(at);
+        len = size_t(bytes);
+        return true;
     }
-    const uint8_t* data() const { return static_cast<const uint8_t*>(p); }
+    const uint8_t* data() const { return base_; }
 };
 
 uint64_t text_length(const std::string& path, uint32_t sym_bytes, std::string& err)
@@ -386,7 +418,7 @@ int main(int argc, char** argv)
         std::fputs(USAGE, stderr);
         return err.empty() ? 0 : 2;
     }
-    if(a.mode == "widen") return widen(a);
-    if(a.mode == "meta-only") return meta_only(a);
+    if(a.mode == Mode::widen) return widen(a);
+    if(a.mode == Mode::meta_only) return meta_only(a);
     return convert(a);
 }

@@ -49,7 +49,7 @@ int launch_keys_gen(csa_ctx* ctx, const u32* head, const u32* pos, u64 count, u6
 // scratch holds 3 words per tile of RANK_TILE records.
 constexpr int RANK_BLOCK = 256, RANK_ITEMS = 8, RANK_TILE = RANK_BLOCK * RANK_ITEMS;
 // If `updates` is non-null the new ranks are not written into the inverse array but listed there, record i of the sorted
-// list as (rank << 32) | position, for a bulk exchange between GPUs.
+// list as (position << 32) | rank, for a bulk exchange between GPUs.
 int launch_rank_and_compact(csa_ctx* ctx, const u64* keys, const u32* pos, u64 count, int prim_shift, u32 fixed_head, Isa_View isa,
                             Slot_Map map, u32* sa, u32* next_head, u32* next_pos, u64* act_count, u32* scratch, u64* updates = nullptr);
 

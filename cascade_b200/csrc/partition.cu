@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <utility>
+#include <atomic>
 #include <vector>
 
 namespace
@@ -611,7 +612,7 @@ int launch_scatter_with_keys(csa_ctx* ctx, const u16* T, u64 text_limit, const u
     constexpr int SB = 256, SI = 16, TILE = SB * SI;
     constexpr size_t smem = size_t(TILE) * 8 + 256 * 8 + size_t(TILE) * 4 + size_t(SB / 32) * 256 * 4 + 8 * 4 + size_t(TILE + 8) * 2 + TILE;
     auto kern = scatter_keys_ranked_kernel<SB, SI>;
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     if(!configured[ctx->device & 63])
     {
         CSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));

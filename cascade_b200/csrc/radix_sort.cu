@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "sort.cuh"
 
+#include <atomic>
 #include <vector>
 
 namespace
@@ -402,7 +403,7 @@ template <int BLOCK, int ITEMS, typename V, int MATCH_BITS>
 int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, u64 n, int shift, u32 dmask, const u64* digit_base, u64* next_base, u32* status, u32* counter)
 {
     using S = Pass_Smem<BLOCK, ITEMS, V>;
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];      // several host threads (one per GPU) may come here at once; setting the attribute twice is harmless
     auto kern = onesweep_pass_kernel<BLOCK, ITEMS, V, MATCH_BITS>;
     if(!configured[ctx->device & 63])
     {
@@ -528,7 +529,7 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
 
 int launch_first_pass(csa_ctx* ctx, const u64* kin, u64* kout, const u32* vin, u32* vout, u64 n, int shift, u32 dmask, u64* cursor)
 {
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     if(!configured[ctx->device & 63])
     {
         CSA_CUDA(ctx, cudaFuncSetAttribute(first_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(FP_SMEM)));
@@ -677,7 +678,7 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "csa_sort_pairs: workspace too small");
 
     {
-        static bool hist_configured[64] = {false};
+        static std::atomic<bool> hist_configured[64];
         if(!hist_configured[ctx->device & 63])
         {
             CSA_CUDA(ctx, cudaFuncSetAttribute(histogram_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8 * RADIX * 4));

@@ -116,7 +116,7 @@ def test_sa_convert_modes_without_a_gpu(tmp_path, oracle):
     r = subprocess.run([tool, "--in", os.path.join(tmp, "swap.u64"), "--index-dir", os.path.join(tmp, "x3"), "--spot", str(n)] + common, capture_output=True, text=True)
     assert r.returncode == 1 and "order violated" in r.stderr and not os.path.exists(os.path.join(tmp, "x3", "index.meta"))
     r = subprocess.run([tool, "--meta-only", "--text", os.path.join(tmp, "text.u16"), "--sym-bytes", "2", "--index-dir", tmp], capture_output=True, text=True)
-    assert r.returncode == 2 and "--meta-only requires --sa" in r.stderr
+    assert r.returncode == 2 and "--sa" in r.stderr and "usage" in r.stderr
 
 
 @pytest.mark.gpu
