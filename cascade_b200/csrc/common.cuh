@@ -43,6 +43,10 @@ struct csa_ctx
     const u32* symbol_range = nullptr;     // optional first-symbol table of csa_partition_ids (see partition_install_symbol_ranges)
     bool ties_in_any_order = false;        // set by callers whose sorts may leave records of equal keys in any order (see radix_sort.cu)
     void* pass_timer = nullptr;            // digit-pass event timing of the sorts on this context (owned by radix_sort.cu)
+    // Extra streams ("lanes") of the chunked host-batch pipelines, each with an event; made on first use.
+    static constexpr int LANES = 3;
+    cudaStream_t lane[LANES] = {nullptr, nullptr, nullptr};
+    cudaEvent_t lane_event[LANES] = {nullptr, nullptr, nullptr};
     // Mappings of other GPUs' arenas opened through CUDA IPC (multi-GPU builds), kept while the peers' handles stay the same.
     void* peer_base[CSA_MAX_GPUS] = {nullptr};
     unsigned char peer_handle[CSA_MAX_GPUS][64] = {{0}};
@@ -93,6 +97,20 @@ static inline int csa_fail(csa_ctx* ctx, int code, const std::string& why)
     if(ctx) ctx->err = why;
     return code;
 }
+
+// Makes the context's lanes (streams and events) if they do not exist yet.
+int csa_lanes(csa_ctx* ctx);
+
+// While one of these lives, the context's calls are queued on another stream than its own.
+struct On_Stream
+{
+    csa_ctx* ctx;
+    cudaStream_t saved;
+    On_Stream(csa_ctx* c, cudaStream_t s) : ctx(c), saved(c->stream) { c->stream = s; }
+    ~On_Stream() { ctx->stream = saved; }
+    On_Stream(const On_Stream&) = delete;
+    On_Stream& operator=(const On_Stream&) = delete;
+};
 
 // Returns in *out a scratch pointer of at least `bytes` bytes from the context's grow-only arena.
 int csa_arena(csa_ctx* ctx, size_t bytes, void** out);

@@ -39,6 +39,11 @@ extern "C" void csa_ctx_destroy(csa_ctx* ctx)
     if(ctx->d_status) cudaFree(ctx->d_status);
     if(ctx->d_scalars) cudaFree(ctx->d_scalars);
     if(ctx->h_scalars) cudaFreeHost(ctx->h_scalars);
+    for(int l = 0; l < csa_ctx::LANES; ++l)
+    {
+        if(ctx->lane_event[l]) cudaEventDestroy(ctx->lane_event[l]);
+        if(ctx->lane[l]) { cudaStreamSynchronize(ctx->lane[l]); cudaStreamDestroy(ctx->lane[l]); }
+    }
     if(ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -70,6 +75,16 @@ extern "C" void csa_reset_counters(csa_ctx* ctx)
     if(!ctx) return;
     for(auto& c : ctx->counters) c = 0;
     sort_reset_timing(ctx);
+}
+
+int csa_lanes(csa_ctx* ctx)
+{
+    for(int l = 0; l < csa_ctx::LANES; ++l)
+    {
+        if(!ctx->lane[l]) CSA_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->lane[l], cudaStreamNonBlocking));
+        if(!ctx->lane_event[l]) CSA_CUDA(ctx, cudaEventCreateWithFlags(&ctx->lane_event[l], cudaEventDisableTiming));
+    }
+    return CSA_OK;
 }
 
 int csa_arena(csa_ctx* ctx, size_t bytes, void** out)

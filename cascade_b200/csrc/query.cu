@@ -483,6 +483,28 @@ extern "C" int csa_certify(csa_ctx* ctx, const csa_index* index, const uint64_t*
     return CSA_OK;
 }
 
+namespace
+{
+
+__global__ void add_base_kernel(u64* __restrict__ off, const u64 count, const u64 base)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) off[i] += base;
+}
+
+constexpr u64 HOST_CHUNK_QUERIES = u64(1) << 18;     // the reference's chunk of a host batch (include/Query_Engine.hpp:94-100)
+
+// Device buffers of one lane of the host-batch pipeline.
+struct Lane_Buffers
+{
+    u64* off; u16* sym; u64* itv; u32* cnt; u64* poff; u64* sums; u64* pos;
+};
+
+}   // namespace
+
+// The host batch runs as chunks of 2^18 queries over three streams, as Query_Engine::find does (src/Query_Engine.cu:1355-1516):
+// while one chunk's results cross PCIe to the host, the next chunk's search runs and the one after is on its way in. A
+// chunk's positions are copied out once the host knows how many there are, one chunk behind the searches.
 extern "C" int csa_query_host(csa_ctx* ctx, const csa_index* index, const uint64_t* off_host, const uint16_t* sym_host, uint64_t q, uint32_t max_pos,
                               uint64_t* itv_host, uint32_t* cnt_host, uint64_t* pos_off_host, uint64_t* pos_host, uint64_t pos_capacity,
                               uint64_t* pos_total)
@@ -493,40 +515,108 @@ extern "C" int csa_query_host(csa_ctx* ctx, const csa_index* index, const uint64
     if(!off_host || !itv_host) return csa_fail(ctx, CSA_E_INVALID, "csa_query_host: null buffer");
     const bool want_pos = max_pos > 0 && pos_host && cnt_host && pos_off_host;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    const u64 sym_c = off_host[q] - off_host[0];
-    const size_t b_off = align_up256((q + 1) * 8), b_sym = align_up256(sym_c * 2 + 16), b_itv = align_up256(q * 16), b_cnt = align_up256(q * 4),
-                 b_poff = align_up256((q + 1) * 8), b_sums = align_up256((div_up(q, SCAN_TILE) + 1) * 8),
-                 b_pos = want_pos ? align_up256(size_t(q) * max_pos * 8) : 0;
+    CSA_TRY(csa_lanes(ctx));
+    // With the suffix array in host memory the search itself uses the context's one window buffer: one lane then.
+    cudaPointerAttributes attr;
+    const bool sa_on_host = cudaPointerGetAttributes(&attr, index->sa40) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    const u64 chunks = div_up(q, HOST_CHUNK_QUERIES);
+    const int lanes = sa_on_host ? 1 : int(chunks < u64(csa_ctx::LANES) ? chunks : u64(csa_ctx::LANES));
+    const u64 cq_max = q < HOST_CHUNK_QUERIES ? q : HOST_CHUNK_QUERIES;
+    u64 sym_max = 0;
+    for(u64 c = 0; c < chunks; ++c)
+    {
+        const u64 first = c * HOST_CHUNK_QUERIES, cq = (q - first < HOST_CHUNK_QUERIES ? q - first : HOST_CHUNK_QUERIES);
+        if(off_host[first + cq] < off_host[first]) return csa_fail(ctx, CSA_E_INVALID, "csa_query_host: offsets must not decrease");
+        const u64 sc = off_host[first + cq] - off_host[first];
+        if(sc > sym_max) sym_max = sc;
+    }
+    const size_t b_off = align_up256((cq_max + 1) * 8), b_sym = align_up256(sym_max * 2 + 16), b_itv = align_up256(cq_max * 16), b_cnt = align_up256(cq_max * 4),
+                 b_poff = align_up256((cq_max + 1) * 8), b_sums = align_up256((div_up(cq_max, SCAN_TILE) + 1) * 8),
+                 b_pos = want_pos ? align_up256(size_t(cq_max) * max_pos * 8) : 0;
+    const size_t per_lane = b_off + b_sym + b_itv + b_cnt + b_poff + b_sums + b_pos;
     void* ws = nullptr;
-    CSA_TRY(csa_arena(ctx, b_off + b_sym + b_itv + b_cnt + b_poff + b_sums + b_pos + 4096, &ws));
-    u8* p = static_cast<u8*>(ws);
-    u64* off_d = reinterpret_cast<u64*>(p); p += b_off;
-    u16* sym_d = reinterpret_cast<u16*>(p); p += b_sym;
-    u64* itv_d = reinterpret_cast<u64*>(p); p += b_itv;
-    u32* cnt_d = reinterpret_cast<u32*>(p); p += b_cnt;
-    u64* poff_d = reinterpret_cast<u64*>(p); p += b_poff;
-    u64* sums_d = reinterpret_cast<u64*>(p); p += b_sums;
-    u64* pos_d = reinterpret_cast<u64*>(p);
-    CSA_CUDA(ctx, cudaMemcpyAsync(off_d, off_host, (q + 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
-    if(sym_c) CSA_CUDA(ctx, cudaMemcpyAsync(sym_d, sym_host, sym_c * 2, cudaMemcpyHostToDevice, ctx->stream));
-    CSA_TRY(csa_find(ctx, index, reinterpret_cast<uint64_t*>(off_d), sym_d, q, reinterpret_cast<uint64_t*>(itv_d)));
-    CSA_CUDA(ctx, cudaMemcpyAsync(itv_host, itv_d, q * 16, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_TRY(csa_arena(ctx, per_lane * lanes + 4096, &ws));
+    Lane_Buffers L[csa_ctx::LANES];
+    for(int l = 0; l < lanes; ++l)
+    {
+        u8* p = static_cast<u8*>(ws) + per_lane * l;
+        L[l].off = reinterpret_cast<u64*>(p); p += b_off;
+        L[l].sym = reinterpret_cast<u16*>(p); p += b_sym;
+        L[l].itv = reinterpret_cast<u64*>(p); p += b_itv;
+        L[l].cnt = reinterpret_cast<u32*>(p); p += b_cnt;
+        L[l].poff = reinterpret_cast<u64*>(p); p += b_poff;
+        L[l].sums = reinterpret_cast<u64*>(p); p += b_sums;
+        L[l].pos = reinterpret_cast<u64*>(p);
+    }
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // whatever the caller queued on the context's own stream comes first
+
+    // search of chunk c: batch in, intervals out, counts, offsets inside the chunk, positions packed in the lane's buffer
+    auto search = [&](u64 c) -> int
+    {
+        const int l = int(c % u64(lanes));
+        const u64 first = c * HOST_CHUNK_QUERIES, cq = (q - first < HOST_CHUNK_QUERIES ? q - first : HOST_CHUNK_QUERIES);
+        const u64 sc = off_host[first + cq] - off_host[first];
+        const On_Stream on(ctx, ctx->lane[l]);
+        CSA_CUDA(ctx, cudaMemcpyAsync(L[l].off, off_host + first, (cq + 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
+        if(sc) CSA_CUDA(ctx, cudaMemcpyAsync(L[l].sym, sym_host + (off_host[first] - off_host[0]), sc * 2, cudaMemcpyHostToDevice, ctx->stream));
+        CSA_TRY(csa_find(ctx, index, reinterpret_cast<uint64_t*>(L[l].off), L[l].sym, cq, reinterpret_cast<uint64_t*>(L[l].itv)));
+        CSA_CUDA(ctx, cudaMemcpyAsync(itv_host + 2 * first, L[l].itv, cq * 16, cudaMemcpyDeviceToHost, ctx->stream));
+        if(want_pos)
+        {
+            counts_kernel<<<unsigned(div_up(cq, 256)), 256, 0, ctx->stream>>>(L[l].itv, cq, max_pos, L[l].cnt);
+            CSA_LAUNCH_CHECK(ctx);
+            u64* total_d = ctx->d_scalars + 8 + l;
+            CSA_TRY(exclusive_sum(ctx, L[l].cnt, cq, L[l].poff, L[l].sums, total_d));
+            locate_packed_kernel<<<unsigned(div_up(cq * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, L[l].itv, cq, max_pos, L[l].poff, L[l].pos);
+            CSA_LAUNCH_CHECK(ctx);
+            CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 8 + l, total_d, 8, cudaMemcpyDeviceToHost, ctx->stream));
+            CSA_CUDA(ctx, cudaMemcpyAsync(cnt_host + first, L[l].cnt, cq * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        }
+        CSA_CUDA(ctx, cudaEventRecord(ctx->lane_event[l], ctx->stream));
+        return CSA_OK;
+    };
+    // delivery of chunk c, once its search is over: its positions go behind those of the chunks before it
+    u64 base = 0;
+    bool overflow = false;
+    auto deliver = [&](u64 c) -> int
+    {
+        if(!want_pos) return CSA_OK;
+        const int l = int(c % u64(lanes));
+        const u64 first = c * HOST_CHUNK_QUERIES, cq = (q - first < HOST_CHUNK_QUERIES ? q - first : HOST_CHUNK_QUERIES);
+        CSA_CUDA(ctx, cudaEventSynchronize(ctx->lane_event[l]));
+        const u64 total = ctx->h_scalars[8 + l];
+        const On_Stream on(ctx, ctx->lane[l]);
+        if(base)
+        {
+            add_base_kernel<<<unsigned(div_up(cq, 256)), 256, 0, ctx->stream>>>(L[l].poff, cq, base);
+            CSA_LAUNCH_CHECK(ctx);
+        }
+        CSA_CUDA(ctx, cudaMemcpyAsync(pos_off_host + first, L[l].poff, cq * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        if(base + total > pos_capacity) overflow = true;
+        else if(total) CSA_CUDA(ctx, cudaMemcpyAsync(pos_host + base, L[l].pos, total * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        base += total;
+        return CSA_OK;
+    };
+    // With two or more lanes the delivery of a chunk is issued after the search of the next one (which runs on another lane);
+    // one lane takes the chunks one by one.
+    const bool pipelined = lanes >= 2;
+    int rc = CSA_OK;
+    for(u64 c = 0; c < chunks && rc == CSA_OK; ++c)
+    {
+        rc = search(c);
+        if(rc != CSA_OK) break;
+        if(!pipelined) rc = deliver(c);
+        else if(c >= 1) rc = deliver(c - 1);
+    }
+    if(rc == CSA_OK && pipelined) rc = deliver(chunks - 1);
+    for(int l = 0; l < lanes; ++l) cudaStreamSynchronize(ctx->lane[l]);      // on every path: the lanes' buffers are the arena's
+    CSA_TRY(rc);
     if(want_pos)
     {
-        counts_kernel<<<unsigned(div_up(q, 256)), 256, 0, ctx->stream>>>(itv_d, q, max_pos, cnt_d);
-        CSA_LAUNCH_CHECK(ctx);
-        u64* total_d = ctx->d_scalars + 8;
-        CSA_TRY(exclusive_sum(ctx, cnt_d, q, poff_d, sums_d, total_d));
-        locate_packed_kernel<<<unsigned(div_up(q * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, itv_d, q, max_pos, poff_d, pos_d);
-        CSA_LAUNCH_CHECK(ctx);
-        CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 8, total_d, 8, cudaMemcpyDeviceToHost, ctx->stream));
-        CSA_CUDA(ctx, cudaMemcpyAsync(cnt_host, cnt_d, q * 4, cudaMemcpyDeviceToHost, ctx->stream));
-        CSA_CUDA(ctx, cudaMemcpyAsync(pos_off_host, poff_d, (q + 1) * 8, cudaMemcpyDeviceToHost, ctx->stream));
-        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        const u64 total = ctx->h_scalars[8];
-        if(pos_total) *pos_total = total;
-        if(total > pos_capacity) return csa_fail(ctx, CSA_E_NOMEM, "csa_query_host: the positions buffer is too small");
-        if(total) CSA_CUDA(ctx, cudaMemcpyAsync(pos_host, pos_d, total * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        pos_off_host[q] = base;
+        if(pos_total) *pos_total = base;
+        if(overflow) return csa_fail(ctx, CSA_E_NOMEM, "csa_query_host: the positions buffer is too small");
     }
     u64 bits = 0;
     return csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits));

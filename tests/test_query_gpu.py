@@ -185,3 +185,47 @@ def test_index_sharded_by_suffix_array_range(ctx, oracle):
     rn = rows.view(600, 100).cpu().numpy().view(np.uint64)
     for i in range(600):
         assert np.array_equal(rn[i, :wc[i]], wp[i, :wc[i]]), i
+
+
+def test_host_batches_of_several_chunks_over_the_lanes(ctx, oracle):
+    """A host batch larger than one chunk (2^18 queries) runs as a pipeline of chunks over three streams; its intervals,
+    counts, offsets and packed positions must be those of the device path and of the oracle. The same with the suffix array
+    in pinned host memory (one lane), and with a positions buffer that is too small."""
+    from cascade_b200 import api
+    n = 1 << 20
+    Td = api.gen_corpus_device(ctx, n, 2, 256)
+    sa, _ = api.build_sa(ctx, Td, n, 4)
+    Th = Td.cpu().view(torch.int16).numpy().view(np.uint16)
+    sa_h = sa.cpu().numpy()
+    idx = api.SuffixIndex(ctx, Td, sa, n, 32)
+    q = 700_001                                                  # two full chunks and a ragged third
+    oa, sa_ = api.gen_queries("substring", Th, n, q // 2, seed=5)
+    ob, sb = api.gen_queries("random", None, 0, q - q // 2, seed=6)
+    off = np.concatenate([oa, ob[1:] + oa[-1]])
+    sym = np.concatenate([sa_, sb, np.zeros(8, np.uint16)])
+    o, s = _dev(off, sym)
+    itv_d = idx.find(o, s, q)
+    pos_d, cnt_d = idx.locate(itv_d, q, 20)
+    want_itv = itv_d.cpu().numpy().view(np.uint64)
+    want_cnt = cnt_d.cpu().numpy().view(np.uint32)
+    want_pos = pos_d.cpu().numpy().view(np.uint64)
+    sample = np.arange(0, q, 1013)
+    sub_off = np.zeros(len(sample) + 1, np.uint64)
+    sub_off[1:] = np.cumsum(off[sample + 1] - off[sample])
+    sub_sym = np.concatenate([sym[int(off[i]):int(off[i + 1])] for i in sample])
+    assert np.array_equal(want_itv.reshape(q, 2)[sample].ravel(), oracle.find_batch(Th[:n], sa_h, sub_off, sub_sym))
+    for index in (idx, api.SuffixIndex(ctx, Td, sa.cpu().pin_memory(), n, 32, table=idx.table)):
+        itv_h, cnt_h, poff_h, pos_h, total = index.query_host(off, sym, 20)
+        assert np.array_equal(itv_h, want_itv)
+        assert np.array_equal(cnt_h, want_cnt) and total == int(want_cnt.sum()) and int(poff_h[-1]) == total
+        assert np.array_equal(poff_h[:-1], np.concatenate([[0], np.cumsum(want_cnt.astype(np.uint64))[:-1]]))
+        for i in list(range(0, q, 4999)) + [262143, 262144, 524287, 524288, q - 1]:
+            assert np.array_equal(pos_h[int(poff_h[i]):int(poff_h[i + 1])], want_pos[i, :want_cnt[i]]), i
+    # counts only
+    itv_h, _, _, _, total = idx.query_host(off, sym, 0)
+    assert np.array_equal(itv_h, want_itv) and total == 0
+    # a positions buffer that is too small: refused, and the caller learns how many words are needed
+    small = {"pos": np.zeros(1000, np.uint64)}
+    with pytest.raises(api.CascadeError) as e:
+        idx.query_host(off, sym, 20, small)
+    assert e.value.code == 3
