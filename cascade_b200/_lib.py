@@ -29,6 +29,14 @@ class Comm(ctypes.Structure):
     _fields_ = [("rank", c_u32), ("world", c_u32), ("policy", c_u32), ("allgather", ALLGATHER_FN), ("user", c_vp)]
 
 
+class Part(ctypes.Structure):
+    _fields_ = [("lanes", c_vp), ("ranks", c_vp), ("count", c_u64), ("part", c_u32)]
+
+
+class PartResult(ctypes.Structure):
+    _fields_ = [("lanes", c_vp), ("ranks", c_vp), ("active", c_u64), ("messages", c_u64)]
+
+
 class Index(ctypes.Structure):
     _fields_ = [("text", c_vp), ("sa40", c_vp), ("table", c_vp), ("n", c_u64), ("stride", c_u64), ("sa_entries", c_u64), ("sa_first", c_u64)]
 
@@ -55,6 +63,16 @@ _SIGS = {
     "csa_build_device_bytes": (ctypes.c_size_t, [c_u64, c_u32]),
     "csa_build_sa": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_build_sa_host": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
+    "csa_store_create": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, c_u32, ctypes.POINTER(c_vp)]),
+    "csa_store_drop_partition_ids": (None, [c_vp]),
+    "csa_store_destroy": (None, [c_vp]),
+    "csa_store_reserve_messages": (c_int, [c_vp, c_vp, c_u64]),
+    "csa_part_workspace_bytes": (ctypes.c_size_t, [c_u64]),
+    "csa_rank_gen0": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), ctypes.POINTER(PartResult)]),
+    "csa_rank_gen": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_u64, ctypes.POINTER(PartResult)]),
+    "csa_exchange_messages": (c_int, [c_vp, c_vp, ctypes.POINTER(c_u64)]),
+    "csa_rank_order": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),
+    "csa_build_sa_streamed": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, ctypes.POINTER(BuildStats)]),
     "csa_validate_workspace_bytes": (ctypes.c_size_t, [c_u64]),
     "csa_validate_sa": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, ctypes.c_size_t, c_vp]),
     "csa_comm_open_shm": (c_int, [ctypes.c_char_p, c_u32, c_u32, c_u32, c_vp]),

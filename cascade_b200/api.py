@@ -204,6 +204,16 @@ def build_sa_host(ctx, text_host, n, p=1, seed=0, out=None):
     return out, st
 
 
+def build_sa_streamed(ctx, text_host, n, p=64, seed=0, out=None, part_suffixes=0):
+    """The build driven part by part (csa_build_sa_streamed): text and output in host memory (numpy arrays or pinned torch
+    tensors), suffix lists streamed through the device, positions up to 2^40. Returns (sa40, stats)."""
+    if out is None:
+        out = np.zeros(5 * n + SA_PAD_BYTES, dtype=np.uint8)
+    st = BuildStats()
+    ctx.check(ctx.L.csa_build_sa_streamed(ctx.h, _ptr(text_host), n, p, seed, _ptr(out), part_suffixes, ctypes.byref(st)))
+    return out, st
+
+
 def validate_sa(ctx, text_dev, n, sa40_dev):
     """Exact check of a whole suffix array on the device (csa_validate_sa). Returns a dict with the counts of entries out of
     range, duplicate entries and neighbouring pairs out of order, the first bad rank, and `ok`."""

@@ -588,6 +588,7 @@ extern "C" int csa_debug_set(int key, uint64_t value)
         return cudaMemcpyToSymbol(g_lookback_spin_limit, &v, sizeof(v)) == cudaSuccess ? CSA_OK : CSA_E_CUDA;
     }
     if(key == 3 && value <= 1) { g_first_tile = u32(value); return CSA_OK; }
+    if(key == 4 && value < (1ull << 40)) { stream_set_position_offset(value); return CSA_OK; }
     return CSA_E_INVALID;
 }
 

@@ -1,0 +1,761 @@
+// The build with the partition as the unit of device work, for texts whose suffix lists do not fit the device and for
+// positions beyond 32 bits (up to 2^40, 5-byte lanes as in the reference, include/lane.hpp:22-26).
+//
+// What stays on the device for the whole build is small and position-indexed: the text (2 bytes per position) and the rank
+// store R (4 bytes per position: the rank of the suffix inside its part). What is large and rank-ordered, the parts' suffix
+// lists (5-byte lanes and 4-byte ranks, 9 bytes per suffix), lives in host memory and streams through the device one part
+// at a time, as the reference streams partitions through its three dispatcher threads (src/GPU_SACA.cu:1334-1608):
+//
+//   generation 0 of a part   (sort_and_init_rank_and_filter, src/GPU_SACA.cu:1111-1331)   csa_rank_gen0
+//   generation t of a part   (sort_and_re_rank_and_filter,   src/GPU_SACA.cu:1714-1995)   csa_rank_gen
+//   the exchange between two generations (messages, include/message.hpp:22-61)              csa_exchange_messages
+//   the final order of a part (scatter_to_rank_order, src/GPU_SACA.cu:2106-2164)           csa_rank_order
+//
+// Ranks are local to a part (below 2^31, include/bit-layout.hpp:51-68), so a (rank, rank of the suffix h further on)
+// pair fits one 64-bit sort key whatever the text's length. That needs the reference's invariant: suffixes that are
+// still tied always take their second rank from one and the same part. It holds because the sort key of generation 0
+// ends in a tag, the part of the suffix 3 symbols further on (the reference's forward tag, include/bit-layout.hpp:92-106):
+// two suffixes that tie on (3 symbols, tag) have their successors in one part, and by induction so have suffixes that
+// tie on (rank, second rank) later. The tag of a suffix that ends within 3 symbols is 0, 1 or 2 by its length, below every
+// part's tag, so short suffixes are alone in their group from the start and a tied suffix always has h symbols left.
+//
+// Where the reference pushes (target, rank) messages into the host inboxes of other partitions and joins them by search,
+// a part here writes its new ranks as (position, rank) messages into an outbox on the device, and the exchange applies
+// them to R after the generation's last part: every read of a generation sees the ranks of the generation before.
+#include "common.cuh"
+#include "part.cuh"
+
+#include "sort.cuh"
+
+#include <atomic>
+#include <chrono>
+#include <cstdlib>
+#include <new>
+#include <thread>
+#include <vector>
+
+struct csa_store
+{
+    int device = 0;
+    const u16* text = nullptr;      // borrowed: n symbols + CSA_TEXT_PAD zeros
+    u64 n = 0;
+    u32* rank = nullptr;            // R: n words, owned
+    const u16* pid = nullptr;       // borrowed: partition id of every position (generation 0 only)
+    u16* part_of_pid = nullptr;     // owned: p entries
+    u32 p = 0;
+    u64 position_offset = 0;        // test hook: lanes carry position + offset
+    // the outbox of one generation: 5-byte positions and 4-byte ranks
+    u8* box_lanes = nullptr;
+    u32* box_ranks = nullptr;
+    u64 box_capacity = 0;
+    std::atomic<u64> box_count{0};
+};
+
+namespace
+{
+
+u64 g_position_offset = 0;          // test hook (csa_debug_set key 4): what new stores add to every position in a lane
+
+constexpr int SR_BLOCK = 256, SR_ITEMS = 8, SR_TILE = SR_BLOCK * SR_ITEMS;
+
+__device__ __forceinline__ void lane_store(u8* lanes, u64 i, u64 v)
+{
+    u8* d = lanes + 5 * i;
+    d[0] = u8(v); d[1] = u8(v >> 8); d[2] = u8(v >> 16); d[3] = u8(v >> 24); d[4] = u8(v >> 32);
+}
+
+__global__ void unpack_lanes_kernel(const u8* __restrict__ lanes, const u64 count, const u64 offset, u64* __restrict__ pos)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) pos[i] = sa40_load(lanes, i) - offset;
+}
+
+// Generation 0: key = 3 symbols, most significant first, then the 16-bit tag of the suffix 3 symbols on.
+__global__ void stream_keys0_kernel(const u16* __restrict__ T, const u64 n, const u16* __restrict__ pid, const u16* __restrict__ part_of_pid,
+                                    const u64* __restrict__ pos, const u64 count, u64* __restrict__ keys, u32* __restrict__ idx, u64* __restrict__ dev_status)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= count) return;
+    const u64 x = pos[i];
+    if(x >= n) { atomicOr(dev_status, (u64)CSA_ST_RANGE); keys[i] = 0; idx[i] = u32(i); return; }
+    const u64 next = x + 3;
+    const u64 tag = next < n ? u64(part_of_pid[pid[next]]) + 3 : (n + 2 - next);
+    keys[i] = (u64(T[x]) << 48) | (u64(T[x + 1]) << 32) | (u64(T[x + 2]) << 16) | tag;
+    idx[i] = u32(i);
+}
+
+// Generation t: key = (rank, rank of the suffix h symbols on), both local to their parts.
+__global__ void stream_keys_kernel(const u32* __restrict__ R, const u64 n, const u64 h, const u64* __restrict__ pos, const u32* __restrict__ ranks,
+                                   const u64 count, u64* __restrict__ keys, u32* __restrict__ idx, u64* __restrict__ dev_status)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= count) return;
+    const u64 x = pos[i] + h;
+    u32 sec = 0;
+    if(x < n) sec = R[x];
+    else atomicOr(dev_status, (u64)CSA_ST_UNSERVED);       // a tied suffix has h symbols left: see the head of this file
+    keys[i] = (u64(ranks[i]) << 32) | sec;
+    idx[i] = u32(i);
+}
+
+__device__ __forceinline__ u32 sr_warp_max(u32 v)
+{
+    #pragma unroll
+    for(int o = 1; o < 32; o <<= 1) { const u32 t = __shfl_up_sync(0xFFFFFFFFu, v, o); if(int(lane_id()) >= o) v = max(v, t); }
+    return v;
+}
+__device__ __forceinline__ u32 sr_warp_sum(u32 v)
+{
+    #pragma unroll
+    for(int o = 1; o < 32; o <<= 1) { const u32 t = __shfl_up_sync(0xFFFFFFFFu, v, o); if(int(lane_id()) >= o) v += t; }
+    return v;
+}
+
+struct Sr_Flags { u32 prim_head, full_head, active; };
+
+// Flags of a thread's SR_ITEMS consecutive records of the sorted list. prim_shift = 64: the whole list is one group.
+__device__ __forceinline__ Sr_Flags sr_flags(const u64* __restrict__ keys, const u64 count, const u64 first, const int prim_shift, u64 (&k)[SR_ITEMS])
+{
+    Sr_Flags f{0, 0, 0};
+    if(first >= count) return f;
+    const u64 prev = first > 0 ? keys[first - 1] : 0;
+    #pragma unroll
+    for(int i = 0; i < SR_ITEMS; ++i) k[i] = (first + i < count) ? keys[first + i] : 0;
+    const u64 after = (first + SR_ITEMS < count) ? keys[first + SR_ITEMS] : 0;
+    #pragma unroll
+    for(int i = 0; i < SR_ITEMS; ++i)
+    {
+        if(first + i >= count) break;
+        const u64 p = i == 0 ? prev : k[i - 1];
+        const bool is_first = first + i == 0;
+        const bool fh = is_first || k[i] != p;
+        const bool ph = is_first || (prim_shift < 64 && (k[i] >> prim_shift) != (p >> prim_shift));
+        const bool has_next = first + i + 1 < count;
+        const u64 nx = i + 1 < SR_ITEMS ? k[i + 1] : after;
+        const bool next_head = !has_next || nx != k[i];
+        if(fh) f.full_head |= 1u << i;
+        if(ph) f.prim_head |= 1u << i;
+        if(!(fh && next_head)) f.active |= 1u << i;
+    }
+    return f;
+}
+
+// Step 1: per tile, the last heads (as index + 1, 0 = none) and the number of tied records.
+__global__ void __launch_bounds__(SR_BLOCK) stream_rank_tile_kernel(const u64* __restrict__ keys, const u64 count, const int prim_shift, u32* __restrict__ agg)
+{
+    __shared__ u32 s_p[SR_BLOCK / 32], s_f[SR_BLOCK / 32], s_a[SR_BLOCK / 32];
+    const u64 first = u64(blockIdx.x) * SR_TILE + u64(threadIdx.x) * SR_ITEMS;
+    u64 k[SR_ITEMS];
+    const Sr_Flags f = sr_flags(keys, count, first, prim_shift, k);
+    u32 lp = f.prim_head ? u32(first) + (31 - __clz(f.prim_head)) + 1 : 0;
+    u32 lf = f.full_head ? u32(first) + (31 - __clz(f.full_head)) + 1 : 0;
+    u32 ac = __popc(f.active);
+    #pragma unroll
+    for(int o = 16; o > 0; o >>= 1)
+    {
+        lp = max(lp, __shfl_xor_sync(0xFFFFFFFFu, lp, o));
+        lf = max(lf, __shfl_xor_sync(0xFFFFFFFFu, lf, o));
+        ac += __shfl_xor_sync(0xFFFFFFFFu, ac, o);
+    }
+    if(lane_id() == 0) { s_p[threadIdx.x >> 5] = lp; s_f[threadIdx.x >> 5] = lf; s_a[threadIdx.x >> 5] = ac; }
+    __syncthreads();
+    if(threadIdx.x == 0)
+    {
+        u32 a = 0, b = 0, c = 0;
+        for(int w = 0; w < SR_BLOCK / 32; ++w) { a = max(a, s_p[w]); b = max(b, s_f[w]); c += s_a[w]; }
+        agg[3 * u64(blockIdx.x)] = a; agg[3 * u64(blockIdx.x) + 1] = b; agg[3 * u64(blockIdx.x) + 2] = c;
+    }
+}
+
+// Step 2: one block makes the tiles' carries: exclusive running maxima of the heads, exclusive running sum of the tied counts,
+// and the total of the tied records.
+__global__ void __launch_bounds__(1024) stream_rank_carry_kernel(u32* __restrict__ agg, const u64 tiles, u64* __restrict__ total_active)
+{
+    __shared__ u32 s_a[32], s_b[32], s_c[32];
+    __shared__ u32 carry_a, carry_b, carry_c;
+    if(threadIdx.x == 0) { carry_a = 0; carry_b = 0; carry_c = 0; }
+    __syncthreads();
+    for(u64 base = 0; base < tiles; base += 1024)
+    {
+        const u64 t = base + threadIdx.x;
+        u32 a = 0, b = 0, c = 0;
+        if(t < tiles) { a = agg[3 * t]; b = agg[3 * t + 1]; c = agg[3 * t + 2]; }
+        const u32 ia = sr_warp_max(a), ib = sr_warp_max(b), ic = sr_warp_sum(c);
+        if(lane_id() == 31) { s_a[threadIdx.x >> 5] = ia; s_b[threadIdx.x >> 5] = ib; s_c[threadIdx.x >> 5] = ic; }
+        __syncthreads();
+        u32 pa = carry_a, pb = carry_b, pc = carry_c;
+        for(u32 w = 0; w < (threadIdx.x >> 5); ++w) { pa = max(pa, s_a[w]); pb = max(pb, s_b[w]); pc += s_c[w]; }
+        const u32 ua = __shfl_up_sync(0xFFFFFFFFu, ia, 1), ub = __shfl_up_sync(0xFFFFFFFFu, ib, 1);
+        const u32 ea = lane_id() > 0 ? max(pa, ua) : pa, eb = lane_id() > 0 ? max(pb, ub) : pb;
+        const u32 ec = pc + (ic - c);
+        __syncthreads();
+        if(threadIdx.x == 1023) { carry_a = max(pa, ia); carry_b = max(pb, ib); carry_c = pc + ic; }
+        if(t < tiles) { agg[3 * t] = ea; agg[3 * t + 1] = eb; agg[3 * t + 2] = ec; }
+        __syncthreads();
+    }
+    if(threadIdx.x == 0) *total_active = carry_c;
+}
+
+// Step 3: every record gets its new rank and its place in the part's reordered list (tied records first, in rank order, then
+// the records that retire now); its (position, rank) goes straight into R (generation 0, when nothing reads R yet) or into the
+// outbox (later generations).
+__global__ void __launch_bounds__(SR_BLOCK) stream_rank_apply_kernel(const u64* __restrict__ keys, const u32* __restrict__ idx, const u64* __restrict__ pos,
+                                                                    const u64 count, const int prim_shift, const u64 offset, const u32* __restrict__ agg,
+                                                                    const u64* __restrict__ total_active, u8* __restrict__ out_lanes, u32* __restrict__ out_ranks,
+                                                                    u32* __restrict__ R, u8* __restrict__ box_lanes, u32* __restrict__ box_ranks, const u64 box_first)
+{
+    __shared__ u32 s_p[SR_BLOCK / 32], s_f[SR_BLOCK / 32], s_a[SR_BLOCK / 32];
+    const u64 first = u64(blockIdx.x) * SR_TILE + u64(threadIdx.x) * SR_ITEMS;
+    const u32 carry_p = agg[3 * u64(blockIdx.x)], carry_f = agg[3 * u64(blockIdx.x) + 1], tile_act = agg[3 * u64(blockIdx.x) + 2];
+    const u64 total = *total_active;
+    u64 k[SR_ITEMS];
+    const Sr_Flags f = sr_flags(keys, count, first, prim_shift, k);
+    const u32 lp = f.prim_head ? u32(first) + (31 - __clz(f.prim_head)) + 1 : 0;
+    const u32 lf = f.full_head ? u32(first) + (31 - __clz(f.full_head)) + 1 : 0;
+    const u32 ac = __popc(f.active);
+    const u32 ip = sr_warp_max(lp), ifl = sr_warp_max(lf), ia = sr_warp_sum(ac);
+    if(lane_id() == 31) { s_p[threadIdx.x >> 5] = ip; s_f[threadIdx.x >> 5] = ifl; s_a[threadIdx.x >> 5] = ia; }
+    __syncthreads();
+    u32 run_p = carry_p, run_f = carry_f, act_before = tile_act;
+    for(u32 w = 0; w < (threadIdx.x >> 5); ++w) { run_p = max(run_p, s_p[w]); run_f = max(run_f, s_f[w]); act_before += s_a[w]; }
+    {
+        const u32 up = __shfl_up_sync(0xFFFFFFFFu, ip, 1), uf = __shfl_up_sync(0xFFFFFFFFu, ifl, 1);
+        if(lane_id() > 0) { run_p = max(run_p, up); run_f = max(run_f, uf); }
+        act_before += ia - ac;
+    }
+    if(first >= count) return;
+    #pragma unroll
+    for(int i = 0; i < SR_ITEMS; ++i)
+    {
+        const u64 j = first + i;
+        if(j >= count) break;
+        if(f.prim_head & (1u << i)) run_p = u32(j) + 1;
+        if(f.full_head & (1u << i)) run_f = u32(j) + 1;
+        const u32 old_rank = prim_shift < 64 ? u32(k[i] >> prim_shift) : 0;
+        const u32 new_rank = old_rank + ((run_f - 1) - (run_p - 1));
+        const bool tied = (f.active >> i) & 1u;
+        const u64 slot = tied ? u64(act_before) : total + (j - act_before);
+        if(tied) ++act_before;
+        const u64 x = pos[idx[j]];
+        lane_store(out_lanes, slot, x + offset);
+        out_ranks[slot] = new_rank;
+        if(box_lanes) { lane_store(box_lanes, box_first + j, x); box_ranks[box_first + j] = new_rank; }
+        else R[x] = new_rank;
+    }
+}
+
+__global__ void apply_messages_kernel(const u8* __restrict__ box_lanes, const u32* __restrict__ box_ranks, const u64 count, const u64 n, u32* __restrict__ R,
+                                      u64* __restrict__ dev_status)
+{
+    const u64 stride = u64(gridDim.x) * blockDim.x;
+    for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+    {
+        const u64 x = sa40_load(box_lanes, i);
+        if(x < n) R[x] = box_ranks[i];
+        else atomicOr(dev_status, (u64)CSA_ST_RANGE);
+    }
+}
+
+__global__ void rank_order_kernel(const u8* __restrict__ lanes, const u32* __restrict__ ranks, const u64 count, u8* __restrict__ out, u64* __restrict__ dev_status)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= count) return;
+    const u64 r = ranks[i];
+    if(r >= count) { atomicOr(dev_status, (u64)CSA_ST_RANGE); return; }
+    lane_store(out, r, sa40_load(lanes, i));
+}
+
+// Histogram of the parts over a stretch of partition ids, and the scatter of the stretch's positions into per-part runs of a
+// staging buffer (5-byte lanes). part_first: where each part's run starts in the staging buffer; cursor: running fill.
+__global__ void count_parts_kernel(const u16* __restrict__ pid, const u64 count, const u16* __restrict__ part_of_pid, const u32 parts, u64* __restrict__ hist)
+{
+    extern __shared__ u32 s_cnt[];
+    for(u32 i = threadIdx.x; i < parts; i += blockDim.x) s_cnt[i] = 0;
+    __syncthreads();
+    const u64 stride = u64(gridDim.x) * blockDim.x;
+    for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) atomicAdd(&s_cnt[part_of_pid[pid[i]]], 1u);
+    __syncthreads();
+    for(u32 i = threadIdx.x; i < parts; i += blockDim.x) if(s_cnt[i]) atomicAdd(reinterpret_cast<unsigned long long*>(hist + i), (unsigned long long)s_cnt[i]);
+}
+
+__global__ void scatter_parts_kernel(const u16* __restrict__ pid, const u64 first, const u64 count, const u64 offset, const u16* __restrict__ part_of_pid,
+                                     const u64* __restrict__ part_first, u64* __restrict__ cursor, u8* __restrict__ staging)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    const bool live = i < count;
+    const u32 part = live ? u32(part_of_pid[pid[i]]) : 0xFFFFFFFFu;
+    // the lanes of a warp that go to one part take their places with one atomic
+    const u32 peers = __match_any_sync(0xFFFFFFFFu, part);
+    u64 base = 0;
+    if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + part), (unsigned long long)__popc(peers));
+    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(peers) - 1);
+    if(live) lane_store(staging, part_first[part] + base + __popc(peers & lanemask_lt()), first + i + offset);
+}
+
+size_t part_workspace_bytes(u64 count)
+{
+    const u64 c = count ? count : 1;
+    return align_up256(5 * c + 64) * 2 + align_up256(4 * c + 64) * 4 + align_up256(8 * c + 64) * 3 + align_up256(csa_sort_workspace_bytes(c))
+         + align_up256(div_up(c, SR_TILE) * 12 + 256) + 4096;
+}
+
+bool is_host_pointer(const void* p)
+{
+    cudaPointerAttributes attr;
+    const bool ok = cudaPointerGetAttributes(&attr, p) == cudaSuccess;
+    cudaGetLastError();
+    return !ok || attr.type == cudaMemoryTypeHost || attr.type == cudaMemoryTypeUnregistered;
+}
+
+// The common body of csa_rank_gen0 (h = 0) and csa_rank_gen.
+int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_result* out)
+{
+    if(!ctx || !st || !in || !out) return csa_fail(ctx, CSA_E_INVALID, "part job: null argument");
+    out->active = 0; out->messages = 0;
+    const u64 S = in->count;
+    if(S == 0) return CSA_OK;
+    if(S >= (u64(1) << 31)) return csa_fail(ctx, CSA_E_LIMIT, "part job: a part holds fewer than 2^31 suffixes");
+    if(!in->lanes || !out->lanes || !out->ranks || (h > 0 && !in->ranks)) return csa_fail(ctx, CSA_E_INVALID, "part job: null buffer");
+    if(h == 0 && !st->pid) return csa_fail(ctx, CSA_E_INVALID, "part job: generation 0 needs the store's partition ids");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t need = part_workspace_bytes(S);
+    void* ws = nullptr;
+    CSA_TRY(csa_arena(ctx, need, &ws));
+    Carver cv(ws, ctx->arena_bytes);
+    u8* lanes_in = cv.take<u8>(5 * S + 64);
+    u8* lanes_out = cv.take<u8>(5 * S + 64);
+    u32* ranks_in = cv.take<u32>(S + 16);
+    u32* ranks_out = cv.take<u32>(S + 16);
+    u32* idxA = cv.take<u32>(S + 16);
+    u32* idxB = cv.take<u32>(S + 16);
+    u64* pos = cv.take<u64>(S + 8);
+    u64* keysA = cv.take<u64>(S + 8);
+    u64* keysB = cv.take<u64>(S + 8);
+    const size_t sort_ws_bytes = csa_sort_workspace_bytes(S);
+    void* sort_ws = cv.take<u8>(sort_ws_bytes);
+    u32* agg = cv.take<u32>(div_up(S, SR_TILE) * 3 + 64);
+    if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "part job: workspace too small");
+
+    // in: lanes (and ranks) from wherever the caller keeps them
+    CSA_CUDA(ctx, cudaMemcpyAsync(lanes_in, in->lanes, 5 * S, cudaMemcpyDefault, ctx->stream));
+    CSA_CUDA(ctx, cudaMemsetAsync(lanes_in + 5 * S, 0, 8, ctx->stream));
+    if(h > 0) CSA_CUDA(ctx, cudaMemcpyAsync(ranks_in, in->ranks, 4 * S, cudaMemcpyDefault, ctx->stream));
+    const unsigned blocks = unsigned(div_up(S, 256));
+    unpack_lanes_kernel<<<blocks, 256, 0, ctx->stream>>>(lanes_in, S, st->position_offset, pos);
+    CSA_LAUNCH_CHECK(ctx);
+    int bits = 64, prim_shift = 64;
+    if(h == 0)
+        stream_keys0_kernel<<<blocks, 256, 0, ctx->stream>>>(st->text, st->n, st->pid, st->part_of_pid, pos, S, keysA, idxA, ctx->d_status);
+    else
+    {
+        stream_keys_kernel<<<blocks, 256, 0, ctx->stream>>>(st->rank, st->n, h, pos, ranks_in, S, keysA, idxA, ctx->d_status);
+        bits = 64; prim_shift = 32;
+    }
+    CSA_LAUNCH_CHECK(ctx);
+    int in_alt = 0;
+    {
+        const Ties_In_Any_Order free_ties(ctx);       // ties are what the next generation sorts
+        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), idxA, idxB, 4, S, 0, bits, sort_ws, sort_ws_bytes, &in_alt));
+    }
+    const u64* ks = in_alt ? keysB : keysA;
+    const u32* is = in_alt ? idxB : idxA;
+
+    // messages: generation 0 writes R itself (nothing reads R before generation 1); later generations fill the outbox
+    u64 box_first = 0;
+    const bool boxed = h > 0;
+    if(boxed)
+    {
+        box_first = st->box_count.fetch_add(S);
+        if(box_first + S > st->box_capacity) return csa_fail(ctx, CSA_E_NOMEM, "part job: the store's outbox is full (csa_store_reserve_messages)");
+    }
+    const u64 tiles = div_up(S, SR_TILE);
+    u64* total_d = ctx->d_scalars + 12;
+    stream_rank_tile_kernel<<<unsigned(tiles), SR_BLOCK, 0, ctx->stream>>>(ks, S, prim_shift, agg);
+    CSA_LAUNCH_CHECK(ctx);
+    stream_rank_carry_kernel<<<1, 1024, 0, ctx->stream>>>(agg, tiles, total_d);
+    CSA_LAUNCH_CHECK(ctx);
+    stream_rank_apply_kernel<<<unsigned(tiles), SR_BLOCK, 0, ctx->stream>>>(ks, is, pos, S, prim_shift, st->position_offset, agg, total_d, lanes_out, ranks_out, st->rank,
+                                                                          boxed ? st->box_lanes : nullptr, boxed ? st->box_ranks : nullptr, box_first);
+    CSA_LAUNCH_CHECK(ctx);
+    CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 12, total_d, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 13, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if(ctx->h_scalars[13] != 0) { u64 b = 0; return csa_sync(ctx, reinterpret_cast<uint64_t*>(&b)); }
+    out->active = ctx->h_scalars[12];
+    out->messages = boxed ? S : 0;
+    // out: queued behind the job; complete after csa_sync
+    CSA_CUDA(ctx, cudaMemcpyAsync(out->lanes, lanes_out, 5 * S, cudaMemcpyDefault, ctx->stream));
+    CSA_CUDA(ctx, cudaMemcpyAsync(out->ranks, ranks_out, 4 * S, cudaMemcpyDefault, ctx->stream));
+    return CSA_OK;
+}
+
+}   // namespace
+
+void stream_set_position_offset(u64 offset) { g_position_offset = offset; }
+
+extern "C" size_t csa_part_workspace_bytes(uint64_t count) { return part_workspace_bytes(count); }
+
+extern "C" int csa_store_create(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint16_t* pid_dev, const uint16_t* part_of_pid_host, uint32_t p,
+                                csa_store** out)
+{
+    if(!ctx || !text_dev || !out || n == 0 || p == 0 || p > CSA_MAX_PARTITIONS || !part_of_pid_host) return csa_fail(ctx, CSA_E_INVALID, "csa_store_create: bad argument");
+    if(n + g_position_offset >= (u64(1) << 40)) return csa_fail(ctx, CSA_E_LIMIT, "csa_store_create: positions must fit 40 bits");
+    *out = nullptr;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    csa_store* st = new(std::nothrow) csa_store();
+    if(!st) return CSA_E_NOMEM;
+    st->device = ctx->device; st->text = text_dev; st->n = n; st->pid = pid_dev; st->p = p; st->position_offset = g_position_offset;
+    if(cudaMalloc(&st->rank, n * 4 + 64) != cudaSuccess || cudaMalloc(&st->part_of_pid, size_t(p) * 2 + 64) != cudaSuccess)
+    {
+        cudaGetLastError();
+        if(st->rank) cudaFree(st->rank);
+        delete st;
+        return csa_fail(ctx, CSA_E_NOMEM, "csa_store_create: no device memory for the rank store");
+    }
+    CSA_CUDA(ctx, cudaMemcpyAsync(st->part_of_pid, part_of_pid_host, size_t(p) * 2, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    *out = st;
+    return CSA_OK;
+}
+
+extern "C" void csa_store_destroy(csa_store* st)
+{
+    if(!st) return;
+    cudaSetDevice(st->device);
+    if(st->rank) cudaFree(st->rank);
+    if(st->part_of_pid) cudaFree(st->part_of_pid);
+    if(st->box_lanes) cudaFree(st->box_lanes);
+    if(st->box_ranks) cudaFree(st->box_ranks);
+    delete st;
+}
+
+extern "C" void csa_store_drop_partition_ids(csa_store* st) { if(st) st->pid = nullptr; }
+
+extern "C" int csa_store_reserve_messages(csa_ctx* ctx, csa_store* st, uint64_t messages)
+{
+    if(!ctx || !st) return csa_fail(ctx, CSA_E_INVALID, "csa_store_reserve_messages: null argument");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    st->box_count.store(0);
+    if(messages > st->box_capacity)
+    {
+        CSA_CUDA(ctx, cudaDeviceSynchronize());
+        if(st->box_lanes) cudaFree(st->box_lanes);
+        if(st->box_ranks) cudaFree(st->box_ranks);
+        st->box_lanes = nullptr; st->box_ranks = nullptr; st->box_capacity = 0;
+        if(cudaMalloc(&st->box_lanes, messages * 5 + 64) != cudaSuccess || cudaMalloc(&st->box_ranks, messages * 4 + 64) != cudaSuccess)
+        {
+            cudaGetLastError();
+            if(st->box_lanes) { cudaFree(st->box_lanes); st->box_lanes = nullptr; }
+            return csa_fail(ctx, CSA_E_NOMEM, "csa_store_reserve_messages: no device memory for the outbox");
+        }
+        st->box_capacity = messages;
+    }
+    return CSA_OK;
+}
+
+extern "C" int csa_rank_gen0(csa_ctx* ctx, csa_store* st, const csa_part* in, csa_part_result* out) { return rank_part(ctx, st, in, 0, out); }
+
+extern "C" int csa_rank_gen(csa_ctx* ctx, csa_store* st, const csa_part* in, uint64_t h, csa_part_result* out)
+{
+    if(h == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_rank_gen: h must be positive");
+    return rank_part(ctx, st, in, h, out);
+}
+
+extern "C" int csa_exchange_messages(csa_ctx* ctx, csa_store* st, uint64_t* applied)
+{
+    if(!ctx || !st) return csa_fail(ctx, CSA_E_INVALID, "csa_exchange_messages: null argument");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const u64 c = st->box_count.load();
+    if(applied) *applied = c;
+    if(c == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaMemsetAsync(st->box_lanes + 5 * c, 0, 8, ctx->stream));
+    const unsigned blocks = unsigned(div_up(c, 256) < 148 * 16 ? div_up(c, 256) : 148 * 16);
+    apply_messages_kernel<<<blocks, 256, 0, ctx->stream>>>(st->box_lanes, st->box_ranks, c, st->n, st->rank, ctx->d_status);
+    CSA_LAUNCH_CHECK(ctx);
+    st->box_count.store(0);
+    u64 bits = 0;
+    return csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits));
+}
+
+extern "C" int csa_rank_order(csa_ctx* ctx, const uint8_t* lanes, const uint32_t* ranks, uint64_t count, uint8_t* sa40_out)
+{
+    if(!ctx || !lanes || !ranks || !sa40_out) return csa_fail(ctx, CSA_E_INVALID, "csa_rank_order: null argument");
+    if(count == 0) return CSA_OK;
+    if(count >= (u64(1) << 31)) return csa_fail(ctx, CSA_E_LIMIT, "csa_rank_order: a part holds fewer than 2^31 suffixes");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* ws = nullptr;
+    CSA_TRY(csa_arena(ctx, align_up256(5 * count + 64) * 2 + align_up256(4 * count + 64) + 1024, &ws));
+    Carver cv(ws, ctx->arena_bytes);
+    u8* lanes_in = cv.take<u8>(5 * count + 64);
+    u8* lanes_out = cv.take<u8>(5 * count + 64);
+    u32* ranks_in = cv.take<u32>(count + 16);
+    if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "csa_rank_order: workspace too small");
+    CSA_CUDA(ctx, cudaMemcpyAsync(lanes_in, lanes, 5 * count, cudaMemcpyDefault, ctx->stream));
+    CSA_CUDA(ctx, cudaMemsetAsync(lanes_in + 5 * count, 0, 8, ctx->stream));
+    CSA_CUDA(ctx, cudaMemcpyAsync(ranks_in, ranks, 4 * count, cudaMemcpyDefault, ctx->stream));
+    rank_order_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(lanes_in, ranks_in, count, lanes_out, ctx->d_status);
+    CSA_LAUNCH_CHECK(ctx);
+    CSA_CUDA(ctx, cudaMemcpyAsync(sa40_out, lanes_out, 5 * count, cudaMemcpyDefault, ctx->stream));
+    return CSA_OK;
+}
+
+// ---- the host pipeline: the whole build, parts streamed through the device --------------------------------------------------
+
+namespace
+{
+
+struct Dev_Buffer
+{
+    void* p = nullptr;
+    ~Dev_Buffer() { if(p) cudaFree(p); }
+    int alloc(csa_ctx* ctx, size_t bytes)
+    {
+        if(cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); p = nullptr; return csa_fail(ctx, CSA_E_NOMEM, "streamed build: device allocation of " + std::to_string(bytes) + " bytes failed"); }
+        return CSA_OK;
+    }
+};
+
+struct Host_Buffer
+{
+    void* p = nullptr;
+    ~Host_Buffer() { if(p) cudaFreeHost(p); }
+    int alloc(csa_ctx* ctx, size_t bytes)
+    {
+        if(cudaMallocHost(&p, bytes) != cudaSuccess) { cudaGetLastError(); p = nullptr; return csa_fail(ctx, CSA_E_NOMEM, "streamed build: pinned host allocation of " + std::to_string(bytes) + " bytes failed"); }
+        return CSA_OK;
+    }
+};
+
+double ms_since(const std::chrono::steady_clock::time_point& t0)
+{
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+}
+
+}   // namespace
+
+extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
+                                     uint64_t part_suffixes, csa_build_stats* stats)
+{
+    if(!ctx || !text_host || !sa40_host) return csa_fail(ctx, CSA_E_INVALID, "streamed build: null argument");
+    if(n == 0) return csa_fail(ctx, CSA_E_INVALID, "streamed build: empty text");
+    if(p == 0 || p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "streamed build: partition count out of range");
+    if(n + g_position_offset >= (u64(1) << 40)) return csa_fail(ctx, CSA_E_LIMIT, "streamed build: positions must fit 40 bits");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    csa_build_stats local_stats;
+    csa_build_stats& bs = stats ? *stats : local_stats;
+    std::memset(&bs, 0, sizeof(bs));
+    bs.n = n;
+    const u64 launches_before = ctx->counters[0], passes_before = ctx->counters[1], records_before = ctx->counters[2];
+    const auto t_start = std::chrono::steady_clock::now();
+    const u64 offset = g_position_offset;
+
+    // ---- text and partition ids on the device ------------------------------------------------------------------------------
+    Dev_Buffer text_b, pid_b, small_b, stage_b;
+    CSA_TRY(text_b.alloc(ctx, (n + CSA_TEXT_PAD) * 2 + 256));
+    CSA_TRY(pid_b.alloc(ctx, n * 2 + 256));
+    u16* T = static_cast<u16*>(text_b.p);
+    u16* pid = static_cast<u16*>(pid_b.p);
+    CSA_CUDA(ctx, cudaMemcpyAsync(T, text_host, n * 2, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaMemsetAsync(T + n, 0, CSA_TEXT_PAD * 2, ctx->stream));
+    constexpr u64 MAX_SAMPLES = 1u << 19;
+    const size_t split_bytes = align_up256(pick_splitters_scratch_bytes(MAX_SAMPLES));
+    CSA_TRY(small_b.alloc(ctx, split_bytes + align_up256(size_t(2) * p * 8) + 3 * align_up256(size_t(CSA_MAX_PARTITIONS) * 8) + align_up256(65536 * 4) + 4096));
+    Carver sc(small_b.p, split_bytes + align_up256(size_t(2) * p * 8) + 3 * align_up256(size_t(CSA_MAX_PARTITIONS) * 8) + align_up256(65536 * 4) + 4096);
+    void* split_scratch = sc.take<u8>(split_bytes);
+    u64* pivots_dev = sc.take<u64>(2 * u64(p));
+    u64* hist_dev = sc.take<u64>(CSA_MAX_PARTITIONS);
+    u64* part_first_dev = sc.take<u64>(CSA_MAX_PARTITIONS);
+    u64* cursor_dev = sc.take<u64>(CSA_MAX_PARTITIONS);
+    u32* symbol_range = sc.take<u32>(65536);
+    if(!sc.ok) return csa_fail(ctx, CSA_E_NOMEM, "streamed build: scratch too small");
+
+    u32 p_eff = 1;
+    std::vector<u64> pivots(2 * size_t(p));
+    if(p > 1)
+    {
+        u64 n_samples = u64(32) * p * u64(bits_for(n));
+        if(n_samples > MAX_SAMPLES) n_samples = MAX_SAMPLES;
+        if(n_samples < 1024) n_samples = 1024;
+        CSA_TRY(pick_splitters(ctx, T, n, p, seed, n_samples, split_scratch, pick_splitters_scratch_bytes(MAX_SAMPLES), pivots.data(), &p_eff));
+        if(p_eff > 1) CSA_CUDA(ctx, cudaMemcpyAsync(pivots_dev, pivots.data(), size_t(2) * (p_eff - 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    bs.partitions = p_eff;
+    CSA_CUDA(ctx, cudaMemsetAsync(hist_dev, 0, size_t(p_eff) * 8, ctx->stream));
+    if(p_eff > 1) CSA_TRY(partition_install_symbol_ranges(ctx, pivots.data(), p_eff, symbol_range));
+    constexpr u64 PID_CHUNK = u64(1) << 28;
+    int pid_rc = CSA_OK;
+    for(u64 first = 0; first < n && pid_rc == CSA_OK; first += PID_CHUNK)
+        pid_rc = csa_partition_ids(ctx, T, n, first, n - first < PID_CHUNK ? n - first : PID_CHUNK, reinterpret_cast<const uint64_t*>(pivots_dev), p_eff, pid + first,
+                                   reinterpret_cast<uint64_t*>(hist_dev));
+    partition_install_symbol_ranges(ctx, nullptr, 0, nullptr);
+    CSA_TRY(pid_rc);
+    std::vector<u64> part_size(p_eff);
+    CSA_CUDA(ctx, cudaMemcpyAsync(part_size.data(), hist_dev, size_t(p_eff) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+
+    // ---- parts: runs of whole partitions, each below the size asked for (and below 2^31) -----------------------------------
+    if(part_suffixes == 0) part_suffixes = u64(1) << 27;
+    if(part_suffixes >= (u64(1) << 31)) part_suffixes = (u64(1) << 31) - 1;
+    std::vector<u16> part_of_pid(p_eff);
+    std::vector<u64> part_off(1, 0);
+    {
+        u64 cur = 0, total = 0;
+        for(u32 q = 0; q < p_eff; ++q)
+        {
+            if(part_size[q] >= (u64(1) << 31)) return csa_fail(ctx, CSA_E_LIMIT, "streamed build: a partition holds 2^31 suffixes or more; ask for more partitions");
+            if(cur > 0 && cur + part_size[q] > part_suffixes) { part_off.push_back(total); cur = 0; }
+            part_of_pid[q] = u16(part_off.size() - 1);
+            cur += part_size[q];
+            total += part_size[q];
+            if(part_size[q] > bs.max_partition) bs.max_partition = part_size[q];
+        }
+        part_off.push_back(total);
+        if(total != n) return csa_fail(ctx, CSA_E_DEVICE, "streamed build: partition sizes do not add up to n");
+    }
+    const u32 parts = u32(part_off.size() - 1);
+    u64 largest_part = 0;
+    for(u32 u = 0; u < parts; ++u) if(part_off[u + 1] - part_off[u] > largest_part) largest_part = part_off[u + 1] - part_off[u];
+
+    csa_store* st = nullptr;
+    CSA_TRY(csa_store_create(ctx, T, n, pid, part_of_pid.data(), p_eff, &st));
+    struct Store_Guard { csa_store* s; ~Store_Guard() { csa_store_destroy(s); } } store_guard{st};
+
+    // ---- the parts' lanes go to the host: part u owns the bytes from 5 part_off[u] on of the output array ------------------
+    Host_Buffer ranks_b;
+    CSA_TRY(ranks_b.alloc(ctx, n * 4 + 64));
+    u32* ranks_host = static_cast<u32*>(ranks_b.p);
+    {
+        constexpr u64 CHUNK = u64(1) << 26;
+        CSA_TRY(stage_b.alloc(ctx, 5 * (n < CHUNK ? n : CHUNK) + 256));
+        u8* staging = static_cast<u8*>(stage_b.p);
+        std::vector<u64> filled(parts, 0), chunk_hist(parts), chunk_first(parts);
+        for(u64 first = 0; first < n; first += CHUNK)
+        {
+            const u64 c = n - first < CHUNK ? n - first : CHUNK;
+            CSA_CUDA(ctx, cudaMemsetAsync(hist_dev, 0, size_t(parts) * 8, ctx->stream));
+            count_parts_kernel<<<148 * 4, 256, size_t(parts) * 4, ctx->stream>>>(pid + first, c, st->part_of_pid, parts, hist_dev);
+            CSA_LAUNCH_CHECK(ctx);
+            CSA_CUDA(ctx, cudaMemcpyAsync(chunk_hist.data(), hist_dev, size_t(parts) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            u64 at = 0;
+            for(u32 u = 0; u < parts; ++u) { chunk_first[u] = at; at += chunk_hist[u]; }
+            CSA_CUDA(ctx, cudaMemcpyAsync(part_first_dev, chunk_first.data(), size_t(parts) * 8, cudaMemcpyHostToDevice, ctx->stream));
+            CSA_CUDA(ctx, cudaMemsetAsync(cursor_dev, 0, size_t(parts) * 8, ctx->stream));
+            scatter_parts_kernel<<<unsigned(div_up(c, 256)), 256, 0, ctx->stream>>>(pid + first, first, c, offset, st->part_of_pid, part_first_dev, cursor_dev, staging);
+            CSA_LAUNCH_CHECK(ctx);
+            for(u32 u = 0; u < parts; ++u)
+            {
+                if(chunk_hist[u] == 0) continue;
+                CSA_CUDA(ctx, cudaMemcpyAsync(sa40_host + 5 * (part_off[u] + filled[u]), staging + 5 * chunk_first[u], 5 * chunk_hist[u], cudaMemcpyDeviceToHost, ctx->stream));
+                filled[u] += chunk_hist[u];
+            }
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // the staging buffer is reused by the next stretch
+        }
+        for(u32 u = 0; u < parts; ++u) if(filled[u] != part_off[u + 1] - part_off[u]) return csa_fail(ctx, CSA_E_DEVICE, "streamed build: a part's lanes do not add up");
+    }
+    cudaFree(stage_b.p); stage_b.p = nullptr;
+    bs.ms_partition = ms_since(t_start);
+
+    // ---- three workers, each with its own context (stream and scratch), take the parts one by one ---------------------------
+    constexpr int WORKERS = 3;
+    csa_ctx* wctx[WORKERS] = {ctx, nullptr, nullptr};
+    struct Ctx_Guard { csa_ctx** c; ~Ctx_Guard() { for(int i = 1; i < WORKERS; ++i) if(c[i]) csa_ctx_destroy(c[i]); } } ctx_guard{wctx};
+    const int workers = parts < u32(WORKERS) ? int(parts) : WORKERS;
+    for(int w = 1; w < workers; ++w)
+        if(csa_ctx_create(ctx->device, &wctx[w]) != CSA_OK) return csa_fail(ctx, CSA_E_CUDA, "streamed build: cannot create a worker context");
+    std::vector<u64> active(parts);
+    // Runs job(context, part) over all parts on the workers; returns the first error.
+    auto over_parts = [&](auto job) -> int
+    {
+        std::atomic<u32> next{0};
+        std::atomic<int> first_rc{CSA_OK};
+        std::string why[WORKERS];
+        auto body = [&](int w)
+        {
+            cudaSetDevice(ctx->device);
+            for(;;)
+            {
+                const u32 u = next.fetch_add(1);
+                if(u >= parts || first_rc.load() != CSA_OK) break;
+                int rc = job(wctx[w], u);
+                if(rc == CSA_OK) { u64 b = 0; rc = csa_sync(wctx[w], reinterpret_cast<uint64_t*>(&b)); }
+                if(rc != CSA_OK) { int expected = CSA_OK; if(first_rc.compare_exchange_strong(expected, rc)) why[w] = wctx[w]->err; break; }
+            }
+        };
+        std::vector<std::thread> pool;
+        for(int w = 1; w < workers; ++w) pool.emplace_back(body, w);
+        body(0);
+        for(auto& t : pool) t.join();
+        if(first_rc.load() != CSA_OK) for(int w = 0; w < WORKERS; ++w) if(!why[w].empty()) ctx->err = why[w];
+        return first_rc.load();
+    };
+
+    // ---- generation 0 ----------------------------------------------------------------------------------------------------------
+    const auto t_gen0 = std::chrono::steady_clock::now();
+    CSA_TRY(over_parts([&](csa_ctx* c, u32 u) -> int
+    {
+        const u64 S = part_off[u + 1] - part_off[u];
+        csa_part in{sa40_host + 5 * part_off[u], nullptr, S, u};
+        csa_part_result out{sa40_host + 5 * part_off[u], ranks_host + part_off[u], 0, 0};
+        const int rc = csa_rank_gen0(c, st, &in, &out);
+        active[u] = out.active;
+        return rc;
+    }));
+    csa_store_drop_partition_ids(st);
+    cudaFree(pid_b.p); pid_b.p = nullptr;
+    u64 total_active = 0;
+    for(u32 u = 0; u < parts; ++u) total_active += active[u];
+    bs.active_after_gen0 = total_active;
+    bs.ms_gen0 = ms_since(t_gen0);
+    const bool debug = std::getenv("CSA_DEBUG") != nullptr;
+    if(debug) std::fprintf(stderr, "[csa streamed] n=%llu partitions=%u parts=%u largest part=%llu active after generation 0: %llu\n", (unsigned long long)n, p_eff, parts,
+                           (unsigned long long)largest_part, (unsigned long long)total_active);
+
+    // ---- doubling generations ------------------------------------------------------------------------------------------------
+    const auto t_dbl = std::chrono::steady_clock::now();
+    u64 h = 3;
+    u32 gen = 0;
+    while(total_active > 0)
+    {
+        if(gen < 48) bs.active_per_gen[gen] = total_active;
+        CSA_TRY(csa_store_reserve_messages(ctx, st, total_active));
+        CSA_TRY(over_parts([&](csa_ctx* c, u32 u) -> int
+        {
+            if(active[u] == 0) return CSA_OK;
+            csa_part in{sa40_host + 5 * part_off[u], ranks_host + part_off[u], active[u], u};
+            csa_part_result out{sa40_host + 5 * part_off[u], ranks_host + part_off[u], 0, 0};
+            const int rc = csa_rank_gen(c, st, &in, h, &out);
+            active[u] = out.active;
+            return rc;
+        }));
+        uint64_t applied = 0;
+        CSA_TRY(csa_exchange_messages(ctx, st, &applied));
+        u64 next_total = 0;
+        for(u32 u = 0; u < parts; ++u) next_total += active[u];
+        if(debug) std::fprintf(stderr, "[csa streamed] generation %u: h=%llu active %llu -> %llu (%llu messages)\n", gen + 1, (unsigned long long)h,
+                               (unsigned long long)total_active, (unsigned long long)next_total, (unsigned long long)applied);
+        total_active = next_total;
+        ++gen;
+        if(h > (u64(1) << 41)) return csa_fail(ctx, CSA_E_DEVICE, "streamed build: doubling did not terminate");
+        h *= 2;
+    }
+    bs.generations = gen;
+    bs.ms_doubling = ms_since(t_dbl);
+
+    // ---- every part into its final order, in place in the output array ------------------------------------------------------------
+    const auto t_out = std::chrono::steady_clock::now();
+    CSA_TRY(over_parts([&](csa_ctx* c, u32 u) -> int
+    {
+        const u64 S = part_off[u + 1] - part_off[u];
+        return csa_rank_order(c, sa40_host + 5 * part_off[u], ranks_host + part_off[u], S, sa40_host + 5 * part_off[u]);
+    }));
+    bs.ms_output = ms_since(t_out);
+    bs.ms_total = ms_since(t_start);
+    for(int w = 0; w < workers; ++w)
+    {
+        bs.kernel_launches += wctx[w]->counters[0] - (w == 0 ? launches_before : 0);
+        bs.sort_passes += wctx[w]->counters[1] - (w == 0 ? passes_before : 0);
+        bs.sort_records += wctx[w]->counters[2] - (w == 0 ? records_before : 0);
+    }
+    return CSA_OK;
+}

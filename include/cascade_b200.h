@@ -92,7 +92,9 @@ int csa_sort_pairs_static(void* stream, uint64_t* keys_dev, uint64_t* keys_alt_d
  * (1..2^22, default 2^22), on the current device. key 3: 1 makes the tile numbering of csa_sort_pairs' passes start at 1,
  * so that tile 0 never comes and every wait of the pass runs out (0 restores it): the sort then returns normally, nothing
  * of the failed pass is written, and csa_sync reports CSA_E_DEVICE with bit 0 (a look-back wait ran out) in its status
- * word. No device fault is involved. */
+ * word. No device fault is involved. key 4: an offset that stores created afterwards (csa_store_create,
+ * csa_build_sa_streamed) add to every position they put into a lane and take off again when they read one, so that a small
+ * text exercises lanes above 2^32; the suffix array of such a build holds position + offset. */
 int csa_debug_set(int key, uint64_t value);
 /* Average device time of the digit passes of the sorts run on ctx since the last csa_reset_counters, measured
  * with CUDA events on the context's stream when pass timing is on (csa_set_pass_timing): total milliseconds,
@@ -159,6 +161,70 @@ int csa_build_sa(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint32_t p,
  * stands for `cascade <text> <sa>` (src/main.cu:12-46) once the files are in memory. */
 int csa_build_sa_host(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
                       csa_build_stats* stats);
+
+/* ---- build, one part at a time (suffix lists in host memory, positions up to 2^40) ---------------------------------- */
+
+/* A part is a run of whole partitions, i.e. one contiguous range of the suffix array, small enough to be ranked on the
+ * device in one go (fewer than 2^31 suffixes). Its suffix list travels as 5-byte little-endian position lanes
+ * (include/lane.hpp:22-26) with 4-byte ranks that are local to the part (include/bit-layout.hpp:51-68). The device keeps,
+ * for the whole build, only what is indexed by text position: the text and the store of every position's rank. */
+typedef struct csa_store csa_store;
+
+typedef struct csa_part
+{
+    const uint8_t* lanes;   /* count lanes; device memory, or host memory (pinned makes the copies asynchronous) */
+    const uint32_t* ranks;  /* the suffixes' ranks of the generation before (null at generation 0) */
+    uint64_t count;         /* generation 0: the whole part; later: its still-tied suffixes, which lead the part's list */
+    uint32_t part;          /* number of the part, in suffix order */
+} csa_part;
+
+typedef struct csa_part_result
+{
+    uint8_t* lanes;         /* count lanes, reordered: the suffixes that are still tied, in rank order, then those that retired now */
+    uint32_t* ranks;        /* their new ranks inside the part (final for the retired ones) */
+    uint64_t active;        /* out: how many are still tied */
+    uint64_t messages;      /* out: (position, rank) messages left in the store's outbox for csa_exchange_messages */
+} csa_part_result;
+
+/* The store of one build on ctx's device: text_dev (n symbols + CSA_TEXT_PAD zeros) and pid_dev (the partition id of every
+ * position, from csa_partition_ids; needed until generation 0 is over, then csa_store_drop_partition_ids lets the caller
+ * free it) are borrowed; part_of_pid_host[p] gives the part of every partition (non-decreasing). The rank store (4 n bytes)
+ * is allocated here. Part jobs of different contexts may run on one store at the same time. */
+int csa_store_create(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint16_t* pid_dev, const uint16_t* part_of_pid_host,
+                     uint32_t p, csa_store** out);
+void csa_store_drop_partition_ids(csa_store* store);
+void csa_store_destroy(csa_store* store);
+/* Empties the outbox and makes room for `messages` messages (9 bytes each): call before the part jobs of a generation >= 1
+ * with the number of suffixes that are still tied over all parts. */
+int csa_store_reserve_messages(csa_ctx* ctx, csa_store* store, uint64_t messages);
+/* Device bytes of ctx's scratch that a part job of `count` suffixes takes (about 55 bytes per suffix). */
+size_t csa_part_workspace_bytes(uint64_t count);
+/* Generation 0 of one part: sorts its suffixes by their first 3 symbols and the part of the suffix that follows those,
+ * ranks them (rank = index of the group's first suffix in the sorted part), writes every rank into the store and returns
+ * the list with the tied suffixes first. `active` is valid on return; the lists are complete after csa_sync(ctx).
+ * in and out may name the same memory. Replaces sort_and_init_rank_and_filter (src/GPU_SACA.cu:1111-1331). */
+int csa_rank_gen0(csa_ctx* ctx, csa_store* store, const csa_part* in, csa_part_result* out);
+/* Generation t >= 1 of one part, h = 3 * 2^(t-1): sorts the tied suffixes by (rank, stored rank of the suffix h symbols on),
+ * refines the ranks, and leaves one (position, new rank) message per suffix in the outbox; the store itself is not changed,
+ * so every part of a generation reads the ranks of the generation before. Replaces sort_and_re_rank_and_filter
+ * (src/GPU_SACA.cu:1714-1995) with its message emission (include/GPU_SACA.cuh:291-353). */
+int csa_rank_gen(csa_ctx* ctx, csa_store* store, const csa_part* in, uint64_t h, csa_part_result* out);
+/* After the last part of a generation: applies the outbox to the rank store and empties it; *applied = messages applied.
+ * Stands where the reference routes messages to the inboxes of their target partitions between two generations
+ * (src/Partition_Backend.cpp:516-553, include/message.hpp:22-61). */
+int csa_exchange_messages(csa_ctx* ctx, csa_store* store, uint64_t* applied);
+/* The final order of a part: sa40_out[5 ranks[i], +5) = lanes[i] for i < count (ranks must be a permutation of [0, count)).
+ * Input and output may be host or device memory and may be the same. Replaces scatter_to_rank_order
+ * (src/GPU_SACA.cu:2106-2164). Complete after csa_sync(ctx). */
+int csa_rank_order(csa_ctx* ctx, const uint8_t* lanes, const uint32_t* ranks, uint64_t count, uint8_t* sa40_out);
+/* The whole build driven part by part, as the reference's drive_pipeline does (src/GPU_SACA.cu:1334-1608): text_host[0, n)
+ * goes to the device, positions are grouped by part into sa40_host itself (5 bytes per suffix, the part's range of the output),
+ * three worker threads with a context each stream the parts through csa_rank_gen0 / csa_rank_gen / csa_rank_order, and
+ * sa40_host ends as the suffix array. n up to 2^40 - 1; device memory: 8 n bytes (text, rank store, partition ids until
+ * generation 0 is over) + 9 bytes per tied suffix of a generation + three part workspaces; host memory: 4 n bytes pinned for
+ * the ranks besides the caller's buffers. part_suffixes bounds a part's size (0: 2^27). */
+int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
+                          uint64_t part_suffixes, csa_build_stats* stats);
 
 /* ---- validation -------------------------------------------------------------------------------------------- */
 
