@@ -633,6 +633,49 @@ def run_micro_sort(args):
     ctx.close()
 
 
+def run_c4(args):
+    """A scaled-down stand-in for BASELINE config 4 on ONE GPU: the part-at-a-time build (suffix lists in pinned host memory,
+    5-byte lanes, 4096 partitions) on a corpus of more than 2^32 tokens, so that every position-carrying path runs beyond 32
+    bits for real. Wall time of the whole call, PCIe included; the array is then checked in full on the device."""
+    import torch
+    from cascade_b200 import api
+    n = args.tokens if args.tokens != C2_TOKENS else 4_500_000_000
+    p = 4096
+    ctx = api.Context(0)
+    t0 = time.perf_counter()
+    T = api.gen_corpus_device(ctx, n, 0, C2_MEAN_DOC)
+    th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
+    th.copy_(T)
+    del T
+    torch.cuda.empty_cache()
+    oh = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
+    setup_s = time.perf_counter() - t0
+    times, st = [], None
+    for _ in range(max(1, min(args.steps, 2))):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        _, st = api.build_sa_streamed(ctx, th, n, p, out=oh, part_suffixes=args.part_suffixes)
+        times.append(time.perf_counter() - t0)
+    ctx.close()                                   # gives the build's scratch back before the check
+    ctx = api.Context(0)
+    Td = th.cuda()
+    sd = oh.cuda()
+    v = api.validate_sa(ctx, Td, n, sd)
+    sec = min(times)
+    print(json.dumps({"metric": METRIC, "value": n / sec, "unit": UNIT, "n_gpus": 1, "steps": len(times), "ms_per_step": 1e3 * sec,
+                      "config": {"workload": "part-at-a-time build with the suffix lists in pinned host memory: a one-GPU, scaled-down stand-in for BASELINE "
+                                             "config 4 (64e9 tokens over 8 GPUs with NVMe spill, which is not built)", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
+                                 "partitions_asked": p, "part_suffixes": args.part_suffixes or (1 << 27), "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0},
+                      "timed": "wall clock of csa_build_sa_streamed: text upload, lanes to the host, every generation's lists over PCIe both ways, final order",
+                      "partitions": st.partitions, "generations": st.generations, "active_per_generation": [int(x) for x in st.active_per_gen[:st.generations]],
+                      "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
+                      "sort_passes": st.sort_passes, "gpu_launches": st.kernel_launches, "validated": v["ok"], "validation": v,
+                      "pcie_bytes_per_step": {"h2d": 2 * n + 5 * n + 9 * sum(int(x) for x in st.active_per_gen[:st.generations]) + 9 * n,
+                                              "d2h": 5 * n + 9 * n + 9 * sum(int(x) for x in st.active_per_gen[:st.generations]) + 5 * n},
+                      "setup_s": setup_s}))
+    ctx.close()
+
+
 def run_repeat(args):
     """BASELINE config 3 alone (it is also a key of the default line)."""
     from cascade_b200 import api
@@ -659,8 +702,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sort-baseline", action="store_true")
-    ap.add_argument("--workload", default="zipf", choices=["zipf", "repeat"],
-                    help="zipf: BASELINE config 2; repeat: config 3 alone (1e9 tokens of near-duplicate documents, build only)")
+    ap.add_argument("--workload", default="zipf", choices=["zipf", "repeat", "c4"],
+                    help="zipf: BASELINE config 2; repeat: config 3 alone (1e9 tokens of near-duplicate documents, build only); "
+                         "c4: the part-at-a-time build on more than 2^32 tokens (one-GPU stand-in for config 4)")
+    ap.add_argument("--part-suffixes", type=int, default=0, help="c4: most suffixes of a part (0 = the library's default, 2^27)")
     ap.add_argument("--micro", default=None, choices=["sort"], help="time one kernel family alone instead of the build")
     ap.add_argument("--records", type=int, default=31_250_000)
     ap.add_argument("--bits", type=int, default=64)
@@ -672,6 +717,8 @@ def main():
         return run_micro_sort(args)
     if args.workload == "repeat":
         return run_repeat(args)
+    if args.workload == "c4":
+        return run_c4(args)
     run_ours(args)
 
 

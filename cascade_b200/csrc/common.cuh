@@ -38,6 +38,8 @@ struct csa_ctx
     size_t arena_bytes = 0;
     void* aux = nullptr;           // a second grow-only buffer, for data that must survive a regrowth of the arena
     size_t aux_bytes = 0;
+    void* host_aux = nullptr;      // grow-only pinned host scratch (pinning gigabytes takes seconds: kept between builds)
+    size_t host_aux_bytes = 0;
     std::string err;
     u64 counters[16] = {0};        // launch and byte counters for the benchmark
     const u32* symbol_range = nullptr;     // optional first-symbol table of csa_partition_ids (see partition_install_symbol_ranges)
@@ -115,6 +117,7 @@ struct On_Stream
 // Returns in *out a scratch pointer of at least `bytes` bytes from the context's grow-only arena.
 int csa_arena(csa_ctx* ctx, size_t bytes, void** out);
 int csa_aux(csa_ctx* ctx, size_t bytes, void** out);
+int csa_host_aux(csa_ctx* ctx, size_t bytes, void** out);
 
 static inline size_t align_up256(size_t b) { return (b + 255) & ~size_t(255); }
 static inline u64 div_up(u64 a, u64 b) { return (a + b - 1) / b; }

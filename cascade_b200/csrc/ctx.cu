@@ -39,6 +39,7 @@ extern "C" void csa_ctx_destroy(csa_ctx* ctx)
     if(ctx->d_status) cudaFree(ctx->d_status);
     if(ctx->d_scalars) cudaFree(ctx->d_scalars);
     if(ctx->h_scalars) cudaFreeHost(ctx->h_scalars);
+    if(ctx->host_aux) cudaFreeHost(ctx->host_aux);
     for(int l = 0; l < csa_ctx::LANES; ++l)
     {
         if(ctx->lane_event[l]) cudaEventDestroy(ctx->lane_event[l]);
@@ -127,5 +128,24 @@ int csa_aux(csa_ctx* ctx, size_t bytes, void** out)
         ctx->aux_bytes = bytes;
     }
     *out = ctx->aux;
+    return CSA_OK;
+}
+
+int csa_host_aux(csa_ctx* ctx, size_t bytes, void** out)
+{
+    if(bytes > ctx->host_aux_bytes)
+    {
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if(ctx->host_aux) { cudaFreeHost(ctx->host_aux); ctx->host_aux = nullptr; ctx->host_aux_bytes = 0; }
+        const cudaError_t e = cudaMallocHost(&ctx->host_aux, bytes);
+        if(e != cudaSuccess)
+        {
+            cudaGetLastError();
+            ctx->err = "pinned host allocation of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e);
+            return CSA_E_NOMEM;
+        }
+        ctx->host_aux_bytes = bytes;
+    }
+    *out = ctx->host_aux;
     return CSA_OK;
 }

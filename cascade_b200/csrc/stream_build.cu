@@ -515,17 +515,6 @@ struct Dev_Buffer
     }
 };
 
-struct Host_Buffer
-{
-    void* p = nullptr;
-    ~Host_Buffer() { if(p) cudaFreeHost(p); }
-    int alloc(csa_ctx* ctx, size_t bytes)
-    {
-        if(cudaMallocHost(&p, bytes) != cudaSuccess) { cudaGetLastError(); p = nullptr; return csa_fail(ctx, CSA_E_NOMEM, "streamed build: pinned host allocation of " + std::to_string(bytes) + " bytes failed"); }
-        return CSA_OK;
-    }
-};
-
 double ms_since(const std::chrono::steady_clock::time_point& t0)
 {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
@@ -621,17 +610,27 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     struct Store_Guard { csa_store* s; ~Store_Guard() { csa_store_destroy(s); } } store_guard{st};
 
     // ---- the parts' lanes go to the host: part u owns the bytes from 5 part_off[u] on of the output array ------------------
-    Host_Buffer ranks_b;
-    CSA_TRY(ranks_b.alloc(ctx, n * 4 + 64));
-    u32* ranks_host = static_cast<u32*>(ranks_b.p);
+    void* ranks_p = nullptr;
+    CSA_TRY(csa_host_aux(ctx, n * 4 + 64, &ranks_p));      // kept by the context: a second build of this size pins nothing
+    u32* ranks_host = static_cast<u32*>(ranks_p);
+    const double ms_pinned = ms_since(t_start);
     {
-        constexpr u64 CHUNK = u64(1) << 26;
-        CSA_TRY(stage_b.alloc(ctx, 5 * (n < CHUNK ? n : CHUNK) + 256));
-        u8* staging = static_cast<u8*>(stage_b.p);
+        // Stretch by stretch: count the stretch's positions by part, scatter them into per-part runs of a staging buffer, and
+        // copy every run to its part's place on the host. Two staging buffers and a second stream let the copies of one
+        // stretch run under the scatter of the next.
+        constexpr u64 CHUNK = u64(1) << 27;
+        const u64 chunk_cap = n < CHUNK ? n : CHUNK;
+        CSA_TRY(stage_b.alloc(ctx, 2 * align_up256(5 * chunk_cap + 256)));
+        u8* const staging[2] = {static_cast<u8*>(stage_b.p), static_cast<u8*>(stage_b.p) + align_up256(5 * chunk_cap + 256)};
+        CSA_TRY(csa_lanes(ctx));
+        cudaStream_t copy_stream = ctx->lane[0];
+        cudaEvent_t scattered = ctx->lane_event[0], copied[2] = {ctx->lane_event[1], ctx->lane_event[2]};
         std::vector<u64> filled(parts, 0), chunk_hist(parts), chunk_first(parts);
-        for(u64 first = 0; first < n; first += CHUNK)
+        u64 k = 0;
+        for(u64 first = 0; first < n; first += CHUNK, ++k)
         {
             const u64 c = n - first < CHUNK ? n - first : CHUNK;
+            u8* const stage = staging[k & 1];
             CSA_CUDA(ctx, cudaMemsetAsync(hist_dev, 0, size_t(parts) * 8, ctx->stream));
             count_parts_kernel<<<148 * 4, 256, size_t(parts) * 4, ctx->stream>>>(pid + first, c, st->part_of_pid, parts, hist_dev);
             CSA_LAUNCH_CHECK(ctx);
@@ -641,16 +640,21 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
             for(u32 u = 0; u < parts; ++u) { chunk_first[u] = at; at += chunk_hist[u]; }
             CSA_CUDA(ctx, cudaMemcpyAsync(part_first_dev, chunk_first.data(), size_t(parts) * 8, cudaMemcpyHostToDevice, ctx->stream));
             CSA_CUDA(ctx, cudaMemsetAsync(cursor_dev, 0, size_t(parts) * 8, ctx->stream));
-            scatter_parts_kernel<<<unsigned(div_up(c, 256)), 256, 0, ctx->stream>>>(pid + first, first, c, offset, st->part_of_pid, part_first_dev, cursor_dev, staging);
+            if(k >= 2) CSA_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, copied[k & 1], 0));       // the copies out of this staging buffer, two stretches ago
+            scatter_parts_kernel<<<unsigned(div_up(c, 256)), 256, 0, ctx->stream>>>(pid + first, first, c, offset, st->part_of_pid, part_first_dev, cursor_dev, stage);
             CSA_LAUNCH_CHECK(ctx);
+            CSA_CUDA(ctx, cudaEventRecord(scattered, ctx->stream));
+            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // chunk_first is a host array that the next stretch rewrites
+            CSA_CUDA(ctx, cudaStreamWaitEvent(copy_stream, scattered, 0));
             for(u32 u = 0; u < parts; ++u)
             {
                 if(chunk_hist[u] == 0) continue;
-                CSA_CUDA(ctx, cudaMemcpyAsync(sa40_host + 5 * (part_off[u] + filled[u]), staging + 5 * chunk_first[u], 5 * chunk_hist[u], cudaMemcpyDeviceToHost, ctx->stream));
+                CSA_CUDA(ctx, cudaMemcpyAsync(sa40_host + 5 * (part_off[u] + filled[u]), stage + 5 * chunk_first[u], 5 * chunk_hist[u], cudaMemcpyDeviceToHost, copy_stream));
                 filled[u] += chunk_hist[u];
             }
-            CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // the staging buffer is reused by the next stretch
+            CSA_CUDA(ctx, cudaEventRecord(copied[k & 1], copy_stream));
         }
+        CSA_CUDA(ctx, cudaStreamSynchronize(copy_stream));
         for(u32 u = 0; u < parts; ++u) if(filled[u] != part_off[u + 1] - part_off[u]) return csa_fail(ctx, CSA_E_DEVICE, "streamed build: a part's lanes do not add up");
     }
     cudaFree(stage_b.p); stage_b.p = nullptr;
@@ -708,8 +712,9 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     bs.active_after_gen0 = total_active;
     bs.ms_gen0 = ms_since(t_gen0);
     const bool debug = std::getenv("CSA_DEBUG") != nullptr;
-    if(debug) std::fprintf(stderr, "[csa streamed] n=%llu partitions=%u parts=%u largest part=%llu active after generation 0: %llu\n", (unsigned long long)n, p_eff, parts,
-                           (unsigned long long)largest_part, (unsigned long long)total_active);
+    if(debug) std::fprintf(stderr, "[csa streamed] n=%llu partitions=%u parts=%u largest part=%llu active after generation 0: %llu; text, ids and pinned ranks after %.0f ms, "
+                           "lanes on the host after %.0f ms\n", (unsigned long long)n, p_eff, parts, (unsigned long long)largest_part, (unsigned long long)total_active,
+                           ms_pinned, bs.ms_partition);
 
     // ---- doubling generations ------------------------------------------------------------------------------------------------
     const auto t_dbl = std::chrono::steady_clock::now();
