@@ -634,46 +634,86 @@ def run_micro_sort(args):
 
 
 def run_c4(args):
-    """A scaled-down stand-in for BASELINE config 4 on ONE GPU: the part-at-a-time build (suffix lists in pinned host memory,
-    5-byte lanes, 4096 partitions) on a corpus of more than 2^32 tokens, so that every position-carrying path runs beyond 32
-    bits for real. Wall time of the whole call, PCIe included; the array is then checked in full on the device."""
+    """A scaled-down stand-in for BASELINE config 4: the part-at-a-time build (suffix lists in pinned host memory, 5-byte
+    lanes, 4096 partitions) on a corpus of more than 2^32 tokens, so that every position-carrying path runs beyond 32 bits for
+    real, on N GPUs of one box (strong scaling: the same corpus at every N). Each rank owns the parts u with u mod N == rank and
+    streams their lists over its own PCIe link; ranks cross NVLink between generations. Wall time of the whole build with
+    the text resident on the devices, max over ranks; the array is then put together and checked in full on rank 0's device."""
     import torch
-    from cascade_b200 import api
+    import torch.distributed as dist
+    from cascade_b200 import api, multi
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     n = args.tokens if args.tokens != C2_TOKENS else 4_500_000_000
     p = 4096
-    ctx = api.Context(0)
-    t0 = time.perf_counter()
-    T = api.gen_corpus_device(ctx, n, 0, C2_MEAN_DOC)
-    th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
-    th.copy_(T)
-    del T
+    ps = args.part_suffixes or (1 << 27)
+    ctx = api.Context(local)
+    T = api.gen_corpus_device(ctx, n, 0, C2_MEAN_DOC)            # every rank makes the same text in its own HBM
+    host, times, infos = {}, [], []
+    with ClockSampler(local) as clocks:
+        for it in range(1 + max(1, min(args.steps, 3))):            # the first build pins the host lists and is not counted
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            segs, info = multi.build_sa_streamed_multi(ctx, T, n, p, part_suffixes=ps, host=host)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            if world > 1:
+                dt = _max_over_ranks(dt, dev)
+            if it > 0:
+                times.append(dt)
+                infos.append(info)
+    info = infos[-1]
+    sec = sum(times) / len(times)
+    # the whole array on rank 0's device, checked in full
+    full = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8, device=dev)
+    for first, count, lanes in segs:
+        full[5 * first:5 * (first + count)].copy_(lanes, non_blocking=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.all_reduce(full)
+    v = api.validate_sa(ctx, T, n, full) if rank == 0 else None
+    del full
     torch.cuda.empty_cache()
-    oh = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8).pin_memory()
-    setup_s = time.perf_counter() - t0
-    times, st = [], None
-    for _ in range(max(1, min(args.steps, 2))):
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        _, st = api.build_sa_streamed(ctx, th, n, p, out=oh, part_suffixes=args.part_suffixes)
-        times.append(time.perf_counter() - t0)
-    ctx.close()                                   # gives the build's scratch back before the check
-    ctx = api.Context(0)
-    Td = th.cuda()
-    sd = oh.cuda()
-    v = api.validate_sa(ctx, Td, n, sd)
-    sec = min(times)
-    print(json.dumps({"metric": METRIC, "value": n / sec, "unit": UNIT, "n_gpus": 1, "steps": len(times), "ms_per_step": 1e3 * sec,
-                      "config": {"workload": "part-at-a-time build with the suffix lists in pinned host memory: a one-GPU, scaled-down stand-in for BASELINE "
-                                             "config 4 (64e9 tokens over 8 GPUs with NVMe spill, which is not built)", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
-                                 "partitions_asked": p, "part_suffixes": args.part_suffixes or (1 << 27), "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0},
-                      "timed": "wall clock of csa_build_sa_streamed: text upload, lanes to the host, every generation's lists over PCIe both ways, final order",
-                      "partitions": st.partitions, "generations": st.generations, "active_per_generation": [int(x) for x in st.active_per_gen[:st.generations]],
-                      "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
-                      "sort_passes": st.sort_passes, "gpu_launches": st.kernel_launches, "validated": v["ok"], "validation": v,
-                      "pcie_bytes_per_step": {"h2d": 2 * n + 5 * n + 9 * sum(int(x) for x in st.active_per_gen[:st.generations]) + 9 * n,
-                                              "d2h": 5 * n + 9 * n + 9 * sum(int(x) for x in st.active_per_gen[:st.generations]) + 5 * n},
-                      "setup_s": setup_s}))
+    c_driver = None
+    if world == 1 and not args.no_e2e:
+        # the same build through the one-call C entry point, host text in (its own pinned rank list is kept by the context)
+        th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
+        th.copy_(T)
+        oh = host["lanes"]                                          # 5 n + 64 bytes, pinned: the output array
+        ts = []
+        for it in range(2):
+            t0 = time.perf_counter()
+            _, st = api.build_sa_streamed(ctx, th, n, p, out=oh, part_suffixes=ps)
+            ts.append(time.perf_counter() - t0)
+        c_driver = {"value": n / ts[-1], "unit": UNIT, "ms_per_step": 1e3 * ts[-1], "api": "csa_build_sa_streamed (pinned host text in, sa40 out in pinned host memory)",
+                    "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output}}
+    own_active = info["active_per_generation"]
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": n / sec, "unit": UNIT, "n_gpus": world, "steps": len(times), "warmup": 1, "ms_per_step": 1e3 * sec,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                          "config": {"workload": "part-at-a-time build with the suffix lists in pinned host memory: a scaled-down stand-in for BASELINE config 4 "
+                                                 "(64e9 tokens with NVMe spill, which is not built)", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
+                                     "partitions_asked": p, "part_suffixes": ps, "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0, "gpus": world},
+                          "timed": "wall clock of the whole build, text resident on every device: partition ids, lanes to the host, every generation's lists over "
+                                   "PCIe both ways, rank exchange over NVLink, final order; max over ranks",
+                          "clocks": clocks.summary(), "partitions": info["partitions"], "parts": info["parts"], "generations": info["generations"],
+                          "active_per_generation": own_active, "phases_ms_rank0": info["ms"], "gpu_launches": info["launches"],
+                          "nvlink_bytes_received_rank0": info["nvlink_bytes_received"],
+                          "pcie_bytes_rank0": {"h2d": 5 * info["own_suffixes"] + 9 * info["own_suffixes"] + 9 * sum(own_active) // world,
+                                               "d2h": 5 * info["own_suffixes"] + 9 * info["own_suffixes"] + 9 * sum(own_active) // world + 5 * info["own_suffixes"]},
+                          "validated": bool(v["ok"]), "validation": v, "one_call_entry_point": c_driver}))
+    if world > 1:
+        dist.barrier()
     ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_repeat(args):
@@ -715,10 +755,10 @@ def main():
         return run_reference(args)
     if args.micro == "sort":
         return run_micro_sort(args)
-    if args.workload == "repeat":
-        return run_repeat(args)
     if args.workload == "c4":
         return run_c4(args)
+    if args.workload == "repeat":
+        return run_repeat(args)
     run_ours(args)
 
 

@@ -49,6 +49,7 @@ struct csa_store
     u32* box_ranks = nullptr;
     u64 box_capacity = 0;
     std::atomic<u64> box_count{0};
+    bool owns_rank = true, owns_box = true;     // false where the caller lent the memory
 };
 
 namespace
@@ -396,7 +397,7 @@ void stream_set_position_offset(u64 offset) { g_position_offset = offset; }
 extern "C" size_t csa_part_workspace_bytes(uint64_t count) { return part_workspace_bytes(count); }
 
 extern "C" int csa_store_create(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint16_t* pid_dev, const uint16_t* part_of_pid_host, uint32_t p,
-                                csa_store** out)
+                                uint32_t* rank_store_dev, csa_store** out)
 {
     if(!ctx || !text_dev || !out || n == 0 || p == 0 || p > CSA_MAX_PARTITIONS || !part_of_pid_host) return csa_fail(ctx, CSA_E_INVALID, "csa_store_create: bad argument");
     if(n + g_position_offset >= (u64(1) << 40)) return csa_fail(ctx, CSA_E_LIMIT, "csa_store_create: positions must fit 40 bits");
@@ -405,10 +406,11 @@ extern "C" int csa_store_create(csa_ctx* ctx, const uint16_t* text_dev, uint64_t
     csa_store* st = new(std::nothrow) csa_store();
     if(!st) return CSA_E_NOMEM;
     st->device = ctx->device; st->text = text_dev; st->n = n; st->pid = pid_dev; st->p = p; st->position_offset = g_position_offset;
-    if(cudaMalloc(&st->rank, n * 4 + 64) != cudaSuccess || cudaMalloc(&st->part_of_pid, size_t(p) * 2 + 64) != cudaSuccess)
+    if(rank_store_dev) { st->rank = rank_store_dev; st->owns_rank = false; }
+    if((!rank_store_dev && cudaMalloc(&st->rank, n * 4 + 64) != cudaSuccess) || cudaMalloc(&st->part_of_pid, size_t(p) * 2 + 64) != cudaSuccess)
     {
         cudaGetLastError();
-        if(st->rank) cudaFree(st->rank);
+        if(st->rank && st->owns_rank) cudaFree(st->rank);
         delete st;
         return csa_fail(ctx, CSA_E_NOMEM, "csa_store_create: no device memory for the rank store");
     }
@@ -422,10 +424,10 @@ extern "C" void csa_store_destroy(csa_store* st)
 {
     if(!st) return;
     cudaSetDevice(st->device);
-    if(st->rank) cudaFree(st->rank);
+    if(st->rank && st->owns_rank) cudaFree(st->rank);
     if(st->part_of_pid) cudaFree(st->part_of_pid);
-    if(st->box_lanes) cudaFree(st->box_lanes);
-    if(st->box_ranks) cudaFree(st->box_ranks);
+    if(st->box_lanes && st->owns_box) cudaFree(st->box_lanes);
+    if(st->box_ranks && st->owns_box) cudaFree(st->box_ranks);
     delete st;
 }
 
@@ -436,6 +438,7 @@ extern "C" int csa_store_reserve_messages(csa_ctx* ctx, csa_store* st, uint64_t 
     if(!ctx || !st) return csa_fail(ctx, CSA_E_INVALID, "csa_store_reserve_messages: null argument");
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
     st->box_count.store(0);
+    if(!st->owns_box && messages > st->box_capacity) return csa_fail(ctx, CSA_E_NOMEM, "csa_store_reserve_messages: the outbox lent by the caller is too small");
     if(messages > st->box_capacity)
     {
         CSA_CUDA(ctx, cudaDeviceSynchronize());
@@ -450,6 +453,57 @@ extern "C" int csa_store_reserve_messages(csa_ctx* ctx, csa_store* st, uint64_t 
         }
         st->box_capacity = messages;
     }
+    return CSA_OK;
+}
+
+extern "C" int csa_store_use_outbox(csa_store* st, uint8_t* lanes_dev, uint32_t* ranks_dev, uint64_t capacity)
+{
+    if(!st || ((lanes_dev == nullptr) != (ranks_dev == nullptr))) return CSA_E_INVALID;
+    cudaSetDevice(st->device);
+    if(st->owns_box)
+    {
+        cudaDeviceSynchronize();
+        if(st->box_lanes) cudaFree(st->box_lanes);
+        if(st->box_ranks) cudaFree(st->box_ranks);
+    }
+    st->box_lanes = lanes_dev; st->box_ranks = ranks_dev;
+    st->box_capacity = lanes_dev ? capacity : 0;
+    st->owns_box = lanes_dev == nullptr;
+    st->box_count.store(0);
+    return CSA_OK;
+}
+
+extern "C" uint64_t csa_store_outbox_count(const csa_store* st) { return st ? st->box_count.load() : 0; }
+
+extern "C" int csa_store_apply_messages(csa_ctx* ctx, csa_store* st, const uint8_t* lanes_dev, const uint32_t* ranks_dev, uint64_t count)
+{
+    if(!ctx || !st || (count && (!lanes_dev || !ranks_dev))) return csa_fail(ctx, CSA_E_INVALID, "csa_store_apply_messages: null argument");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const unsigned blocks = unsigned(div_up(count, 256) < 148 * 16 ? div_up(count, 256) : 148 * 16);
+    apply_messages_kernel<<<blocks, 256, 0, ctx->stream>>>(lanes_dev, ranks_dev, count, st->n, st->rank, ctx->d_status);
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_part_sizes(csa_ctx* ctx, csa_store* st, uint64_t first, uint64_t count, uint32_t parts, uint64_t* hist_dev)
+{
+    if(!ctx || !st || !st->pid || !hist_dev || parts == 0 || parts > CSA_MAX_PARTITIONS || first + count > st->n) return csa_fail(ctx, CSA_E_INVALID, "csa_part_sizes: bad argument");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    count_parts_kernel<<<148 * 4, 256, size_t(parts) * 4, ctx->stream>>>(st->pid + first, count, st->part_of_pid, parts, reinterpret_cast<u64*>(hist_dev));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_scatter_lanes(csa_ctx* ctx, csa_store* st, uint64_t first, uint64_t count, const uint64_t* part_first_dev, uint64_t* cursor_dev, uint8_t* lanes_dev)
+{
+    if(!ctx || !st || !st->pid || !part_first_dev || !cursor_dev || !lanes_dev || first + count > st->n) return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_lanes: bad argument");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    scatter_parts_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(st->pid + first, first, count, st->position_offset, st->part_of_pid,
+                                                                                reinterpret_cast<const u64*>(part_first_dev), reinterpret_cast<u64*>(cursor_dev), lanes_dev);
+    CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
 
@@ -606,7 +660,7 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     for(u32 u = 0; u < parts; ++u) if(part_off[u + 1] - part_off[u] > largest_part) largest_part = part_off[u + 1] - part_off[u];
 
     csa_store* st = nullptr;
-    CSA_TRY(csa_store_create(ctx, T, n, pid, part_of_pid.data(), p_eff, &st));
+    CSA_TRY(csa_store_create(ctx, T, n, pid, part_of_pid.data(), p_eff, nullptr, &st));
     struct Store_Guard { csa_store* s; ~Store_Guard() { csa_store_destroy(s); } } store_guard{st};
 
     // ---- the parts' lanes go to the host: part u owns the bytes from 5 part_off[u] on of the output array ------------------

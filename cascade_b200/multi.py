@@ -134,3 +134,264 @@ def upload_text_sharded(text_host, text_dev, scratch=None):
     dist.all_gather_into_tensor(scratch, mine)
     dev_bytes.copy_(scratch[:total])
     return scratch
+
+
+def group_partitions_into_parts(sizes, part_suffixes):
+    """Runs of whole partitions, each run below part_suffixes suffixes (a partition larger than that is a part of its own).
+    Returns (part_of_pid uint16[p], part_off int list of parts + 1 entries), as csa_build_sa_streamed groups them."""
+    part_of_pid = np.zeros(len(sizes), np.uint16)
+    part_off, cur, total = [0], 0, 0
+    for q, s in enumerate(int(x) for x in sizes):
+        if s >= 1 << 31:
+            raise api.CascadeError(4, "a partition holds 2^31 suffixes or more; ask for more partitions")
+        if cur > 0 and cur + s > part_suffixes:
+            part_off.append(total)
+            cur = 0
+        part_of_pid[q] = len(part_off) - 1
+        cur += s
+        total += s
+    part_off.append(total)
+    return part_of_pid, part_off
+
+
+def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 << 27, workers=3, host=None):
+    """The part-at-a-time build over the GPUs of a process group (one process per GPU; also works alone), written on the
+    library's part jobs: every rank holds the whole text and a replica of the rank store on its device, owns the parts u with
+    u mod world == rank, keeps their suffix lists (5-byte lanes + 4-byte ranks) in its own pinned host memory and streams them
+    through its GPU over its own PCIe link on `workers` contexts. Between generations the ranks exchange their (position, rank)
+    messages: after generation 0 the replicas (zero where a rank wrote nothing) are added up by one all-reduce; after a later
+    generation every rank's outbox is all-gathered (NCCL over NVLink) and applied to every replica.
+    Returns (segments, info): segments = [(first global rank, count, pinned uint8 tensor of 5 * count bytes)] for the
+    rank's parts in the order of their ranks, info = timings and counts. `host` may be a dict that keeps the pinned list
+    buffers between calls (pinning gigabytes takes seconds)."""
+    import threading
+    import time
+    from ._lib import Part, PartResult, c_u64, c_vp
+    L = ctx.L
+    dev = text_dev.device
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    info = {"ms": {}}
+
+    def sync_all():
+        ctx.sync()
+        torch.cuda.synchronize(dev)
+
+    def mark(name, t0):
+        sync_all()
+        info["ms"][name] = info["ms"].get(name, 0.0) + 1e3 * (time.perf_counter() - t0)
+
+    def total_over_ranks(x):
+        if world == 1:
+            return int(x)
+        t = torch.tensor([int(x)], dtype=torch.int64, device=dev)
+        dist.all_reduce(t)
+        return int(t.item())
+
+    t_all = time.perf_counter()
+    # ---- splitters and partition ids: the same on every rank (the same samples of the same text) ------------------------------
+    t0 = time.perf_counter()
+    pe, piv = 1, None
+    if p > 1:
+        ns = min(1 << 19, max(1024, 32 * p * max(1, int(n).bit_length())))
+        samples = torch.empty(2 * ns, dtype=torch.int64, device=dev)
+        torch.cuda.synchronize(dev)
+        ctx.check(L.csa_sample_kgrams(ctx.h, text_dev.data_ptr(), n, ns, seed, samples.data_ptr()))
+        ctx.sync()
+        sh = samples.cpu().numpy().view(np.uint64)
+        piv = np.zeros(2 * (p - 1), np.uint64)
+        p_out = ctypes.c_uint32(0)
+        rc = L.csa_select_pivots(sh.ctypes.data, ns, p, piv.ctypes.data, ctypes.byref(p_out))
+        if rc != 0:
+            raise api.CascadeError(rc, "csa_select_pivots")
+        pe = p_out.value
+        del samples
+    pivd = torch.from_numpy(piv.view(np.int64)).to(dev) if pe > 1 else None
+    pid = torch.empty(n + 64, dtype=torch.int16, device=dev)
+    hist = torch.zeros(max(pe, 1), dtype=torch.int64, device=dev)
+    torch.cuda.synchronize(dev)
+    step = 1 << 28
+    for first in range(0, n, step):
+        c = min(step, n - first)
+        ctx.check(L.csa_partition_ids(ctx.h, text_dev.data_ptr(), n, first, c, pivd.data_ptr() if pivd is not None else None, pe,
+                                      pid.data_ptr() + 2 * first, hist.data_ptr()))
+    ctx.sync()
+    sizes = hist.cpu().numpy()
+    part_of_pid, part_off = group_partitions_into_parts(sizes, part_suffixes)
+    parts = len(part_off) - 1
+    if part_off[-1] != n:
+        raise api.CascadeError(5, "partition sizes do not add up to n")
+    own = [u for u in range(parts) if u % world == rank]
+    size = [part_off[u + 1] - part_off[u] for u in range(parts)]
+    mark("partition_ids", t0)
+
+    # ---- the store (a replica of the rank store on every GPU) and this rank's lists in pinned host memory --------------------
+    t0 = time.perf_counter()
+    R = torch.zeros(n + 16, dtype=torch.int32, device=dev)
+    store = c_vp()
+    torch.cuda.synchronize(dev)
+    ctx.check(L.csa_store_create(ctx.h, text_dev.data_ptr(), n, pid.data_ptr(), part_of_pid.ctypes.data, pe, R.data_ptr(), ctypes.byref(store)))
+    ctxs = [ctx]
+    try:
+        own_first, at = {}, 0
+        for u in own:
+            own_first[u] = at
+            at += size[u]
+        own_total = at
+        host = host if host is not None else {}
+        if host.get("lanes") is None or host["lanes"].numel() < 5 * own_total + 64:
+            host["lanes"] = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+            host["ranks"] = torch.empty(own_total + 16, dtype=torch.int32).pin_memory()
+        lanes_h, ranks_h = host["lanes"], host["ranks"]
+        mark("pinned_lists", t0)
+        t0 = time.perf_counter()
+        chunk = min(n, 1 << 27)
+        staging = torch.empty(5 * chunk + 64, dtype=torch.uint8, device=dev)
+        hist_c = torch.zeros(parts, dtype=torch.int64, device=dev)
+        first_d = torch.zeros(parts, dtype=torch.int64, device=dev)
+        cursor_d = torch.zeros(parts, dtype=torch.int64, device=dev)
+        filled = {u: 0 for u in own}
+        for first in range(0, n, chunk):
+            c = min(chunk, n - first)
+            hist_c.zero_()
+            cursor_d.zero_()
+            torch.cuda.synchronize(dev)
+            ctx.check(L.csa_part_sizes(ctx.h, store, first, c, parts, hist_c.data_ptr()))
+            ctx.sync()
+            hc = hist_c.cpu().numpy()
+            cf = np.concatenate([[0], np.cumsum(hc)[:-1]]).astype(np.int64)
+            first_d.copy_(torch.from_numpy(cf))
+            torch.cuda.synchronize(dev)
+            ctx.check(L.csa_scatter_lanes(ctx.h, store, first, c, first_d.data_ptr(), cursor_d.data_ptr(), staging.data_ptr()))
+            ctx.sync()
+            for u in own:
+                k = int(hc[u])
+                if k:
+                    o = 5 * (own_first[u] + filled[u])
+                    lanes_h[o:o + 5 * k].copy_(staging[5 * int(cf[u]):5 * (int(cf[u]) + k)], non_blocking=True)
+                    filled[u] += k
+            torch.cuda.synchronize(dev)
+        del staging
+        assert all(filled[u] == size[u] for u in own)
+        mark("lanes_to_host", t0)
+
+        # ---- the part jobs, on `workers` contexts (streams and scratch), one host thread each ---------------------------------
+        ctxs += [api.Context(dev.index) for _ in range(max(0, min(workers, len(own)) - 1))]
+        active = {u: size[u] for u in own}
+
+        def over_parts(todo, job):
+            it, lock, errors = iter(todo), threading.Lock(), []
+
+            def body(c):
+                torch.cuda.set_device(dev)
+                while not errors:
+                    with lock:
+                        u = next(it, None)
+                    if u is None:
+                        return
+                    try:
+                        job(c, u)
+                        c.sync()
+                    except Exception as e:        # noqa: BLE001 - reported after the workers have joined
+                        errors.append(e)
+            ts = [threading.Thread(target=body, args=(c,)) for c in ctxs[1:]]
+            for t in ts:
+                t.start()
+            body(ctxs[0])
+            for t in ts:
+                t.join()
+            if errors:
+                raise errors[0]
+
+        def lists(u):
+            return lanes_h.data_ptr() + 5 * own_first[u], ranks_h.data_ptr() + 4 * own_first[u]
+
+        def gen0(c, u):
+            lp, rp = lists(u)
+            pin, pout = Part(lp, None, size[u], u), PartResult(lp, rp, 0, 0)
+            c.check(L.csa_rank_gen0(c.h, store, ctypes.byref(pin), ctypes.byref(pout)))
+            active[u] = int(pout.active)
+
+        t0 = time.perf_counter()
+        torch.cuda.synchronize(dev)
+        over_parts(own, gen0)
+        L.csa_store_drop_partition_ids(store)
+        del pid
+        if world > 1:
+            dist.all_reduce(R)          # every position was ranked by exactly one GPU; the others hold zero there
+        total_active = total_over_ranks(sum(active.values()))
+        info["active_after_gen0"] = total_active
+        mark("gen0", t0)
+
+        # ---- doubling generations --------------------------------------------------------------------------------------------------
+        t0 = time.perf_counter()
+        h, gens, exchanged = 3, 0, 0
+        info["active_per_generation"] = []
+        while total_active > 0:
+            info["active_per_generation"].append(total_active)
+            a_own = sum(active.values())
+            box_l = torch.empty(5 * a_own + 64, dtype=torch.uint8, device=dev)
+            box_r = torch.empty(a_own + 16, dtype=torch.int32, device=dev)
+            torch.cuda.synchronize(dev)
+            ctx.check(L.csa_store_use_outbox(store, box_l.data_ptr(), box_r.data_ptr(), a_own))
+
+            def gen(c, u, h=h):
+                lp, rp = lists(u)
+                pin, pout = Part(lp, rp, active[u], u), PartResult(lp, rp, 0, 0)
+                c.check(L.csa_rank_gen(c.h, store, ctypes.byref(pin), h, ctypes.byref(pout)))
+                active[u] = int(pout.active)
+            over_parts([u for u in own if active[u] > 0], gen)
+            sent = int(L.csa_store_outbox_count(store))
+            assert sent == a_own
+            if world == 1:
+                ctx.check(L.csa_store_apply_messages(ctx.h, store, box_l.data_ptr(), box_r.data_ptr(), sent))
+                ctx.sync()
+            else:
+                counts = torch.zeros(world, dtype=torch.int64, device=dev)
+                counts[rank] = sent
+                dist.all_reduce(counts)
+                cs = [int(x) for x in counts.cpu()]
+                m = max(cs)
+                row_l, row_r = (5 * m + 64 + 15) // 16 * 16, (m + 16 + 3) // 4 * 4
+                snd_l = torch.zeros(row_l, dtype=torch.uint8, device=dev)
+                snd_r = torch.zeros(row_r, dtype=torch.int32, device=dev)
+                snd_l[:5 * sent] = box_l[:5 * sent]
+                snd_r[:sent] = box_r[:sent]
+                all_l = torch.empty(world * row_l, dtype=torch.uint8, device=dev)
+                all_r = torch.empty(world * row_r, dtype=torch.int32, device=dev)
+                dist.all_gather([all_l[g * row_l:(g + 1) * row_l] for g in range(world)], snd_l)
+                dist.all_gather([all_r[g * row_r:(g + 1) * row_r] for g in range(world)], snd_r)
+                torch.cuda.synchronize(dev)
+                for g in range(world):
+                    ctx.check(L.csa_store_apply_messages(ctx.h, store, all_l.data_ptr() + g * row_l, all_r.data_ptr() + 4 * g * row_r, cs[g]))
+                ctx.sync()
+                exchanged += 9 * sum(cs[g] for g in range(world) if g != rank)
+                del snd_l, snd_r, all_l, all_r
+            ctx.check(L.csa_store_use_outbox(store, None, None, 0))
+            del box_l, box_r
+            total_active = total_over_ranks(sum(active.values()))
+            h *= 2
+            gens += 1
+            if gens > 45:
+                raise api.CascadeError(5, "doubling did not terminate")
+        info["generations"] = gens
+        info["nvlink_bytes_received"] = exchanged + (4 * n * (world - 1) // world if world > 1 else 0)
+        mark("doubling", t0)
+
+        # ---- every part into its final order, in place -------------------------------------------------------------------------------
+        t0 = time.perf_counter()
+
+        def order(c, u):
+            lp, rp = lists(u)
+            c.check(L.csa_rank_order(c.h, lp, rp, size[u], lp))
+        over_parts(own, order)
+        mark("output", t0)
+    finally:
+        for c in ctxs[1:]:
+            c.close()
+        L.csa_store_destroy(store)
+    info["ms"]["total"] = 1e3 * (time.perf_counter() - t_all)
+    info.update({"partitions": pe, "parts": parts, "own_parts": len(own), "own_suffixes": own_total,
+                 "launches": sum(c.launches for c in ctxs[:1])})
+    segments = [(part_off[u], size[u], lanes_h[5 * own_first[u]:5 * (own_first[u] + size[u])]) for u in own]
+    return segments, info

@@ -189,14 +189,31 @@ typedef struct csa_part_result
 /* The store of one build on ctx's device: text_dev (n symbols + CSA_TEXT_PAD zeros) and pid_dev (the partition id of every
  * position, from csa_partition_ids; needed until generation 0 is over, then csa_store_drop_partition_ids lets the caller
  * free it) are borrowed; part_of_pid_host[p] gives the part of every partition (non-decreasing). The rank store (4 n bytes)
- * is allocated here. Part jobs of different contexts may run on one store at the same time. */
+ * is allocated here unless rank_store_dev lends n words (a caller that shares the ranks between GPUs keeps them in memory that
+ * its collectives can name). Part jobs of different contexts may run on one store at the same time. */
 int csa_store_create(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, const uint16_t* pid_dev, const uint16_t* part_of_pid_host,
-                     uint32_t p, csa_store** out);
+                     uint32_t p, uint32_t* rank_store_dev, csa_store** out);
 void csa_store_drop_partition_ids(csa_store* store);
 void csa_store_destroy(csa_store* store);
 /* Empties the outbox and makes room for `messages` messages (9 bytes each): call before the part jobs of a generation >= 1
  * with the number of suffixes that are still tied over all parts. */
 int csa_store_reserve_messages(csa_ctx* ctx, csa_store* store, uint64_t messages);
+/* Several GPUs, one store each (every GPU holds the whole text and a replica of the rank store, and ranks the parts it
+ * owns): the caller lends the outbox (5 capacity + 8 bytes of lanes, 4 capacity bytes of ranks; null takes it back), so that
+ * after a generation it can gather all GPUs' outboxes with its own collective (NCCL over NVLink) and apply each of them to
+ * its replica with csa_store_apply_messages (queued on ctx's stream); csa_store_outbox_count tells how many messages the
+ * GPU's own jobs left. Generation 0 writes the replica directly: the replicas, zero before it, are then added up by the
+ * caller (every position is written by exactly one GPU). */
+int csa_store_use_outbox(csa_store* store, uint8_t* lanes_dev, uint32_t* ranks_dev, uint64_t capacity);
+uint64_t csa_store_outbox_count(const csa_store* store);
+int csa_store_apply_messages(csa_ctx* ctx, csa_store* store, const uint8_t* lanes_dev, const uint32_t* ranks_dev, uint64_t count);
+/* The positions [first, first + count) grouped by part, from the store's partition ids: csa_part_sizes adds the number of
+ * positions of every part into hist_dev[parts]; csa_scatter_lanes writes the positions as lanes into lanes_dev, part u's from
+ * lane part_first_dev[u] + cursor_dev[u] on (the cursors are advanced; the order inside a part is arbitrary). Replaces the host
+ * scatter of GPU_SACA::partition (src/GPU_SACA.cu:795-826, Suffix_Buffer::add include/Suffix_Buffer.hpp:80-93) for 5-byte lanes. */
+int csa_part_sizes(csa_ctx* ctx, csa_store* store, uint64_t first, uint64_t count, uint32_t parts, uint64_t* hist_dev);
+int csa_scatter_lanes(csa_ctx* ctx, csa_store* store, uint64_t first, uint64_t count, const uint64_t* part_first_dev,
+                      uint64_t* cursor_dev, uint8_t* lanes_dev);
 /* Device bytes of ctx's scratch that a part job of `count` suffixes takes (about 55 bytes per suffix). */
 size_t csa_part_workspace_bytes(uint64_t count);
 /* Generation 0 of one part: sorts its suffixes by their first 3 symbols and the part of the suffix that follows those,

@@ -175,3 +175,51 @@ def test_a_rank_that_fails_alone_takes_every_rank_out_of_the_build():
         assert pr.exitcode == 0
     assert res[1][1] == 3 and res[0][1] == 6, res          # CSA_E_NOMEM where it happened, CSA_E_COMM on the peer
     assert all(r[2] < 30 and r[3] for r in res), res
+
+
+def _streamed_worker(rank, world, port, n, p, part_suffixes, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from cascade_b200 import api, multi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    ctx = api.Context(dev)
+    T = api.gen_corpus_device(ctx, n, 11, 256)
+    segs, info = multi.build_sa_streamed_multi(ctx, T, n, p, part_suffixes=part_suffixes, workers=2)
+    ref = None
+    if rank == 0:
+        r, _ = api.build_sa(ctx, T, n, 16)
+        ref = r[:5 * n].cpu().numpy()
+    q.put((rank, [(f, c, t.numpy().copy()) for f, c, t in segs], ref, info["generations"], info["parts"]))
+    dist.barrier()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_part_at_a_time_build_over_several_ranks(world):
+    """Every rank ranks the parts it owns with its lists in its own host memory; the rank stores are replicas kept equal by
+    an all-reduce after generation 0 and an all-gather of the outboxes after every later generation. The ranks' parts,
+    put together, are the resident build's array."""
+    n, p, part_suffixes = 700_001, 64, 50_000
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_streamed_worker, args=(r, world, port, n, p, part_suffixes, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted((q.get(timeout=600) for _ in range(world)), key=lambda x: x[0])
+    for pr in procs:
+        pr.join(timeout=120)
+        assert pr.exitcode == 0
+    ref = res[0][2]
+    covered = np.zeros(n, np.uint8)
+    for rank, segs, _, gens, parts in res:
+        assert parts >= 10 and gens >= 1
+        for first, count, lanes in segs:
+            assert np.array_equal(lanes, ref[5 * first:5 * (first + count)]), f"rank {rank}'s part at {first} differs"
+            covered[first:first + count] += 1
+    assert np.all(covered == 1)

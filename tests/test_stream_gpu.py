@@ -121,7 +121,7 @@ def test_part_jobs_called_one_by_one(ctx, oracle):
     pid_h = pid[:n].cpu().numpy().view(np.uint16)
     part_of_pos = part_of_pid[pid_h]
     store = c_vp()
-    ctx.check(L.csa_store_create(ctx.h, Td.data_ptr(), n, pid.data_ptr(), part_of_pid.ctypes.data, pe, ctypes.byref(store)))
+    ctx.check(L.csa_store_create(ctx.h, Td.data_ptr(), n, pid.data_ptr(), part_of_pid.ctypes.data, pe, None, ctypes.byref(store)))
     try:
         lanes, ranks, active = [], [], []
         for u in range(parts):
