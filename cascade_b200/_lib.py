@@ -64,9 +64,10 @@ _SIGS = {
     "csa_build_sa": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_build_sa_host": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_store_create": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, c_u32, c_vp, ctypes.POINTER(c_vp)]),
-    "csa_store_use_outbox": (c_int, [c_vp, c_vp, c_vp, c_u64]),
+    "csa_store_use_outbox": (c_int, [c_vp, c_vp, c_vp, c_vp, c_u64]),
     "csa_store_outbox_count": (c_u64, [c_vp]),
-    "csa_store_apply_messages": (c_int, [c_vp, c_vp, c_vp, c_vp, c_u64]),
+    "csa_store_apply_messages": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_u64]),
+    "csa_install_pivots": (c_int, [c_vp, c_vp, c_u32]),
     "csa_part_sizes": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u32, c_vp]),
     "csa_scatter_lanes": (c_int, [c_vp, c_vp, c_u64, c_u64, c_vp, c_vp, c_vp]),
     "csa_store_drop_partition_ids": (None, [c_vp]),

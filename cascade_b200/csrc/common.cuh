@@ -43,6 +43,7 @@ struct csa_ctx
     std::string err;
     u64 counters[16] = {0};        // launch and byte counters for the benchmark
     const u32* symbol_range = nullptr;     // optional first-symbol table of csa_partition_ids (see partition_install_symbol_ranges)
+    u32* symbol_table = nullptr;           // the table's memory where csa_install_pivots made it (65536 words, owned)
     bool ties_in_any_order = false;        // set by callers whose sorts may leave records of equal keys in any order (see radix_sort.cu)
     void* pass_timer = nullptr;            // digit-pass event timing of the sorts on this context (owned by radix_sort.cu)
     // Extra streams ("lanes") of the chunked host-batch pipelines, each with an event; made on first use.

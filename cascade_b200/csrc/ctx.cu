@@ -40,6 +40,7 @@ extern "C" void csa_ctx_destroy(csa_ctx* ctx)
     if(ctx->d_scalars) cudaFree(ctx->d_scalars);
     if(ctx->h_scalars) cudaFreeHost(ctx->h_scalars);
     if(ctx->host_aux) cudaFreeHost(ctx->host_aux);
+    if(ctx->symbol_table) cudaFree(ctx->symbol_table);
     for(int l = 0; l < csa_ctx::LANES; ++l)
     {
         if(ctx->lane_event[l]) cudaEventDestroy(ctx->lane_event[l]);

@@ -556,6 +556,15 @@ int partition_install_symbol_ranges(csa_ctx* ctx, const u64* pivots_host, u32 p,
     return CSA_OK;
 }
 
+extern "C" int csa_install_pivots(csa_ctx* ctx, const uint64_t* pivots_host, uint32_t p)
+{
+    if(!ctx || p > CSA_MAX_PARTITIONS || (p > 1 && !pivots_host)) return csa_fail(ctx, CSA_E_INVALID, "csa_install_pivots: bad argument");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    if(p <= 1) return partition_install_symbol_ranges(ctx, nullptr, 0, nullptr);
+    if(!ctx->symbol_table) CSA_CUDA(ctx, cudaMalloc(&ctx->symbol_table, 65536 * sizeof(u32)));
+    return partition_install_symbol_ranges(ctx, reinterpret_cast<const u64*>(pivots_host), p, ctx->symbol_table);
+}
+
 extern "C" int csa_partition_ids(csa_ctx* ctx, const uint16_t* text, uint64_t n, uint64_t first, uint64_t count, const uint64_t* pivots,
                                  uint32_t p, uint16_t* pid, uint64_t* hist)
 {

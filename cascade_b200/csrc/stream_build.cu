@@ -44,8 +44,9 @@ struct csa_store
     u16* part_of_pid = nullptr;     // owned: p entries
     u32 p = 0;
     u64 position_offset = 0;        // test hook: lanes carry position + offset
-    // the outbox of one generation: 5-byte positions and 4-byte ranks
-    u8* box_lanes = nullptr;
+    // the outbox of one generation: positions (low 32 bits and high 8 bits apart, so that every store is aligned) and ranks
+    u32* box_lo = nullptr;
+    u8* box_hi = nullptr;
     u32* box_ranks = nullptr;
     u64 box_capacity = 0;
     std::atomic<u64> box_count{0};
@@ -202,8 +203,9 @@ __global__ void __launch_bounds__(1024) stream_rank_carry_kernel(u32* __restrict
 // outbox (later generations).
 __global__ void __launch_bounds__(SR_BLOCK) stream_rank_apply_kernel(const u64* __restrict__ keys, const u32* __restrict__ idx, const u64* __restrict__ pos,
                                                                     const u64 count, const int prim_shift, const u64 offset, const u32* __restrict__ agg,
-                                                                    const u64* __restrict__ total_active, u8* __restrict__ out_lanes, u32* __restrict__ out_ranks,
-                                                                    u32* __restrict__ R, u8* __restrict__ box_lanes, u32* __restrict__ box_ranks, const u64 box_first)
+                                                                    const u64* __restrict__ total_active, u64* __restrict__ out_pos, u32* __restrict__ out_ranks,
+                                                                    u32* __restrict__ R, u32* __restrict__ box_lo, u8* __restrict__ box_hi, u32* __restrict__ box_ranks,
+                                                                    const u64 box_first)
 {
     __shared__ u32 s_p[SR_BLOCK / 32], s_f[SR_BLOCK / 32], s_a[SR_BLOCK / 32];
     const u64 first = u64(blockIdx.x) * SR_TILE + u64(threadIdx.x) * SR_ITEMS;
@@ -238,20 +240,20 @@ __global__ void __launch_bounds__(SR_BLOCK) stream_rank_apply_kernel(const u64* 
         const u64 slot = tied ? u64(act_before) : total + (j - act_before);
         if(tied) ++act_before;
         const u64 x = pos[idx[j]];
-        lane_store(out_lanes, slot, x + offset);
+        out_pos[slot] = x + offset;
         out_ranks[slot] = new_rank;
-        if(box_lanes) { lane_store(box_lanes, box_first + j, x); box_ranks[box_first + j] = new_rank; }
+        if(box_lo) { box_lo[box_first + j] = u32(x); box_hi[box_first + j] = u8(x >> 32); box_ranks[box_first + j] = new_rank; }
         else R[x] = new_rank;
     }
 }
 
-__global__ void apply_messages_kernel(const u8* __restrict__ box_lanes, const u32* __restrict__ box_ranks, const u64 count, const u64 n, u32* __restrict__ R,
-                                      u64* __restrict__ dev_status)
+__global__ void apply_messages_kernel(const u32* __restrict__ box_lo, const u8* __restrict__ box_hi, const u32* __restrict__ box_ranks, const u64 count, const u64 n,
+                                      u32* __restrict__ R, u64* __restrict__ dev_status)
 {
     const u64 stride = u64(gridDim.x) * blockDim.x;
     for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
     {
-        const u64 x = sa40_load(box_lanes, i);
+        const u64 x = (u64(box_hi[i]) << 32) | box_lo[i];
         if(x < n) R[x] = box_ranks[i];
         else atomicOr(dev_status, (u64)CSA_ST_RANGE);
     }
@@ -264,6 +266,32 @@ __global__ void rank_order_kernel(const u8* __restrict__ lanes, const u32* __res
     const u64 r = ranks[i];
     if(r >= count) { atomicOr(dev_status, (u64)CSA_ST_RANGE); return; }
     lane_store(out, r, sa40_load(lanes, i));
+}
+
+// 5-byte lanes from 64-bit positions: a thread packs 16 entries = 80 bytes = five 16-byte stores (out is 16-byte aligned).
+__global__ void pack_lanes_kernel(const u64* __restrict__ pos, const u64 count, u8* __restrict__ out)
+{
+    const u64 first = (u64(blockIdx.x) * blockDim.x + threadIdx.x) * 16;
+    if(first >= count) return;
+    if(first + 16 <= count)
+    {
+        u32 w[20];
+        #pragma unroll
+        for(int j = 0; j < 20; ++j) w[j] = 0;
+        #pragma unroll
+        for(int e = 0; e < 16; ++e)
+        {
+            const u64 v = pos[first + e] & 0xFFFFFFFFFFull;
+            const int b = 5 * e, wi = b >> 2, sh = (b & 3) * 8;        // 40 bits from bit sh of word wi on
+            w[wi] |= u32(v << sh);
+            w[wi + 1] |= u32(v >> (32 - sh));
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + first * 5);
+        #pragma unroll
+        for(int i = 0; i < 5; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    }
+    else
+        for(u64 r = first; r < count; ++r) lane_store(out, r, pos[r]);
 }
 
 // Histogram of the parts over a stretch of partition ids, and the scatter of the stretch's positions into per-part runs of a
@@ -283,8 +311,9 @@ __global__ void scatter_parts_kernel(const u16* __restrict__ pid, const u64 firs
                                      const u64* __restrict__ part_first, u64* __restrict__ cursor, u8* __restrict__ staging)
 {
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    const bool live = i < count;
-    const u32 part = live ? u32(part_of_pid[pid[i]]) : 0xFFFFFFFFu;
+    u32 part = i < count ? u32(part_of_pid[pid[i]]) : 0xFFFFFFFFu;
+    if(part != 0xFFFFFFFFu && part_first[part] == ~0ull) part = 0xFFFFFFFFu;       // a part that the caller does not want now
+    const bool live = part != 0xFFFFFFFFu;
     // the lanes of a warp that go to one part take their places with one atomic
     const u32 peers = __match_any_sync(0xFFFFFFFFu, part);
     u64 base = 0;
@@ -296,7 +325,7 @@ __global__ void scatter_parts_kernel(const u16* __restrict__ pid, const u64 firs
 size_t part_workspace_bytes(u64 count)
 {
     const u64 c = count ? count : 1;
-    return align_up256(5 * c + 64) * 2 + align_up256(4 * c + 64) * 4 + align_up256(8 * c + 64) * 3 + align_up256(csa_sort_workspace_bytes(c))
+    return align_up256(5 * c + 64) * 2 + align_up256(4 * c + 64) * 4 + align_up256(8 * c + 64) * 4 + align_up256(csa_sort_workspace_bytes(c))
          + align_up256(div_up(c, SR_TILE) * 12 + 256) + 4096;
 }
 
@@ -332,6 +361,7 @@ int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_r
     u64* pos = cv.take<u64>(S + 8);
     u64* keysA = cv.take<u64>(S + 8);
     u64* keysB = cv.take<u64>(S + 8);
+    u64* pos_out = cv.take<u64>(S + 8);
     const size_t sort_ws_bytes = csa_sort_workspace_bytes(S);
     void* sort_ws = cv.take<u8>(sort_ws_bytes);
     u32* agg = cv.take<u32>(div_up(S, SR_TILE) * 3 + 64);
@@ -375,8 +405,10 @@ int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_r
     CSA_LAUNCH_CHECK(ctx);
     stream_rank_carry_kernel<<<1, 1024, 0, ctx->stream>>>(agg, tiles, total_d);
     CSA_LAUNCH_CHECK(ctx);
-    stream_rank_apply_kernel<<<unsigned(tiles), SR_BLOCK, 0, ctx->stream>>>(ks, is, pos, S, prim_shift, st->position_offset, agg, total_d, lanes_out, ranks_out, st->rank,
-                                                                          boxed ? st->box_lanes : nullptr, boxed ? st->box_ranks : nullptr, box_first);
+    stream_rank_apply_kernel<<<unsigned(tiles), SR_BLOCK, 0, ctx->stream>>>(ks, is, pos, S, prim_shift, st->position_offset, agg, total_d, pos_out, ranks_out, st->rank,
+                                                                          boxed ? st->box_lo : nullptr, boxed ? st->box_hi : nullptr, boxed ? st->box_ranks : nullptr, box_first);
+    CSA_LAUNCH_CHECK(ctx);
+    pack_lanes_kernel<<<unsigned(div_up(div_up(S, 16), 256)), 256, 0, ctx->stream>>>(pos_out, S, lanes_out);
     CSA_LAUNCH_CHECK(ctx);
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 12, total_d, 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 13, ctx->d_status, 8, cudaMemcpyDeviceToHost, ctx->stream));
@@ -426,8 +458,7 @@ extern "C" void csa_store_destroy(csa_store* st)
     cudaSetDevice(st->device);
     if(st->rank && st->owns_rank) cudaFree(st->rank);
     if(st->part_of_pid) cudaFree(st->part_of_pid);
-    if(st->box_lanes && st->owns_box) cudaFree(st->box_lanes);
-    if(st->box_ranks && st->owns_box) cudaFree(st->box_ranks);
+    if(st->owns_box) { if(st->box_lo) cudaFree(st->box_lo); if(st->box_hi) cudaFree(st->box_hi); if(st->box_ranks) cudaFree(st->box_ranks); }
     delete st;
 }
 
@@ -442,13 +473,16 @@ extern "C" int csa_store_reserve_messages(csa_ctx* ctx, csa_store* st, uint64_t 
     if(messages > st->box_capacity)
     {
         CSA_CUDA(ctx, cudaDeviceSynchronize());
-        if(st->box_lanes) cudaFree(st->box_lanes);
+        if(st->box_lo) cudaFree(st->box_lo);
+        if(st->box_hi) cudaFree(st->box_hi);
         if(st->box_ranks) cudaFree(st->box_ranks);
-        st->box_lanes = nullptr; st->box_ranks = nullptr; st->box_capacity = 0;
-        if(cudaMalloc(&st->box_lanes, messages * 5 + 64) != cudaSuccess || cudaMalloc(&st->box_ranks, messages * 4 + 64) != cudaSuccess)
+        st->box_lo = nullptr; st->box_hi = nullptr; st->box_ranks = nullptr; st->box_capacity = 0;
+        if(cudaMalloc(&st->box_lo, messages * 4 + 64) != cudaSuccess || cudaMalloc(&st->box_hi, messages + 64) != cudaSuccess ||
+           cudaMalloc(&st->box_ranks, messages * 4 + 64) != cudaSuccess)
         {
             cudaGetLastError();
-            if(st->box_lanes) { cudaFree(st->box_lanes); st->box_lanes = nullptr; }
+            if(st->box_lo) { cudaFree(st->box_lo); st->box_lo = nullptr; }
+            if(st->box_hi) { cudaFree(st->box_hi); st->box_hi = nullptr; }
             return csa_fail(ctx, CSA_E_NOMEM, "csa_store_reserve_messages: no device memory for the outbox");
         }
         st->box_capacity = messages;
@@ -456,32 +490,34 @@ extern "C" int csa_store_reserve_messages(csa_ctx* ctx, csa_store* st, uint64_t 
     return CSA_OK;
 }
 
-extern "C" int csa_store_use_outbox(csa_store* st, uint8_t* lanes_dev, uint32_t* ranks_dev, uint64_t capacity)
+extern "C" int csa_store_use_outbox(csa_store* st, uint32_t* pos_lo_dev, uint8_t* pos_hi_dev, uint32_t* ranks_dev, uint64_t capacity)
 {
-    if(!st || ((lanes_dev == nullptr) != (ranks_dev == nullptr))) return CSA_E_INVALID;
+    const int given = (pos_lo_dev != nullptr) + (pos_hi_dev != nullptr) + (ranks_dev != nullptr);
+    if(!st || (given != 0 && given != 3)) return CSA_E_INVALID;
     cudaSetDevice(st->device);
     if(st->owns_box)
     {
         cudaDeviceSynchronize();
-        if(st->box_lanes) cudaFree(st->box_lanes);
+        if(st->box_lo) cudaFree(st->box_lo);
+        if(st->box_hi) cudaFree(st->box_hi);
         if(st->box_ranks) cudaFree(st->box_ranks);
     }
-    st->box_lanes = lanes_dev; st->box_ranks = ranks_dev;
-    st->box_capacity = lanes_dev ? capacity : 0;
-    st->owns_box = lanes_dev == nullptr;
+    st->box_lo = pos_lo_dev; st->box_hi = pos_hi_dev; st->box_ranks = ranks_dev;
+    st->box_capacity = given ? capacity : 0;
+    st->owns_box = given == 0;
     st->box_count.store(0);
     return CSA_OK;
 }
 
 extern "C" uint64_t csa_store_outbox_count(const csa_store* st) { return st ? st->box_count.load() : 0; }
 
-extern "C" int csa_store_apply_messages(csa_ctx* ctx, csa_store* st, const uint8_t* lanes_dev, const uint32_t* ranks_dev, uint64_t count)
+extern "C" int csa_store_apply_messages(csa_ctx* ctx, csa_store* st, const uint32_t* pos_lo_dev, const uint8_t* pos_hi_dev, const uint32_t* ranks_dev, uint64_t count)
 {
-    if(!ctx || !st || (count && (!lanes_dev || !ranks_dev))) return csa_fail(ctx, CSA_E_INVALID, "csa_store_apply_messages: null argument");
+    if(!ctx || !st || (count && (!pos_lo_dev || !pos_hi_dev || !ranks_dev))) return csa_fail(ctx, CSA_E_INVALID, "csa_store_apply_messages: null argument");
     if(count == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
     const unsigned blocks = unsigned(div_up(count, 256) < 148 * 16 ? div_up(count, 256) : 148 * 16);
-    apply_messages_kernel<<<blocks, 256, 0, ctx->stream>>>(lanes_dev, ranks_dev, count, st->n, st->rank, ctx->d_status);
+    apply_messages_kernel<<<blocks, 256, 0, ctx->stream>>>(pos_lo_dev, pos_hi_dev, ranks_dev, count, st->n, st->rank, ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
@@ -522,9 +558,8 @@ extern "C" int csa_exchange_messages(csa_ctx* ctx, csa_store* st, uint64_t* appl
     const u64 c = st->box_count.load();
     if(applied) *applied = c;
     if(c == 0) return CSA_OK;
-    CSA_CUDA(ctx, cudaMemsetAsync(st->box_lanes + 5 * c, 0, 8, ctx->stream));
     const unsigned blocks = unsigned(div_up(c, 256) < 148 * 16 ? div_up(c, 256) : 148 * 16);
-    apply_messages_kernel<<<blocks, 256, 0, ctx->stream>>>(st->box_lanes, st->box_ranks, c, st->n, st->rank, ctx->d_status);
+    apply_messages_kernel<<<blocks, 256, 0, ctx->stream>>>(st->box_lo, st->box_hi, st->box_ranks, c, st->n, st->rank, ctx->d_status);
     CSA_LAUNCH_CHECK(ctx);
     st->box_count.store(0);
     u64 bits = 0;

@@ -6,6 +6,7 @@ tensors under gloo and on device tensors under NCCL. All bulk data moves inside 
 and stores.
 """
 import ctypes
+import os
 
 import numpy as np
 import torch
@@ -154,7 +155,7 @@ def group_partitions_into_parts(sizes, part_suffixes):
     return part_of_pid, part_off
 
 
-def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 << 27, workers=3, host=None):
+def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 << 27, workers=3, host=None, window_bytes=8 << 30):
     """The part-at-a-time build over the GPUs of a process group (one process per GPU; also works alone), written on the
     library's part jobs: every rank holds the whole text and a replica of the rank store on its device, owns the parts u with
     u mod world == rank, keeps their suffix lists (5-byte lanes + 4-byte ranks) in its own pinned host memory and streams them
@@ -207,15 +208,27 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
         pe = p_out.value
         del samples
     pivd = torch.from_numpy(piv.view(np.int64)).to(dev) if pe > 1 else None
-    pid = torch.empty(n + 64, dtype=torch.int16, device=dev)
+    # every rank computes the ids of its own stretch of positions; the stretches meet by one all-gather (NVLink)
+    stretch = (-(-n // world) + 4095) // 4096 * 4096               # equal stretches, whole 4096 positions
+    pid = torch.empty(world * stretch + 64, dtype=torch.int16, device=dev)
     hist = torch.zeros(max(pe, 1), dtype=torch.int64, device=dev)
     torch.cuda.synchronize(dev)
+    my_first, my_end = min(n, rank * stretch), min(n, (rank + 1) * stretch)
     step = 1 << 28
-    for first in range(0, n, step):
-        c = min(step, n - first)
-        ctx.check(L.csa_partition_ids(ctx.h, text_dev.data_ptr(), n, first, c, pivd.data_ptr() if pivd is not None else None, pe,
-                                      pid.data_ptr() + 2 * first, hist.data_ptr()))
-    ctx.sync()
+    if pe > 1:
+        ctx.check(L.csa_install_pivots(ctx.h, piv.ctypes.data, pe))
+    try:
+        for first in range(my_first, my_end, step):
+            c = min(step, my_end - first)
+            ctx.check(L.csa_partition_ids(ctx.h, text_dev.data_ptr(), n, first, c, pivd.data_ptr() if pivd is not None else None, pe,
+                                          pid.data_ptr() + 2 * first, hist.data_ptr()))
+        ctx.sync()
+    finally:
+        L.csa_install_pivots(ctx.h, None, 0)
+    if world > 1:
+        pb = pid.view(torch.uint8)             # the collective libraries take bytes, not 16-bit integers
+        dist.all_gather([pb[2 * g * stretch:2 * (g + 1) * stretch] for g in range(world)], pb[2 * rank * stretch:2 * (rank + 1) * stretch].clone())
+        dist.all_reduce(hist)
     sizes = hist.cpu().numpy()
     part_of_pid, part_off = group_partitions_into_parts(sizes, part_suffixes)
     parts = len(part_off) - 1
@@ -244,43 +257,12 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
             host["ranks"] = torch.empty(own_total + 16, dtype=torch.int32).pin_memory()
         lanes_h, ranks_h = host["lanes"], host["ranks"]
         mark("pinned_lists", t0)
-        t0 = time.perf_counter()
-        chunk = min(n, 1 << 27)
-        staging = torch.empty(5 * chunk + 64, dtype=torch.uint8, device=dev)
-        hist_c = torch.zeros(parts, dtype=torch.int64, device=dev)
-        first_d = torch.zeros(parts, dtype=torch.int64, device=dev)
-        cursor_d = torch.zeros(parts, dtype=torch.int64, device=dev)
-        filled = {u: 0 for u in own}
-        for first in range(0, n, chunk):
-            c = min(chunk, n - first)
-            hist_c.zero_()
-            cursor_d.zero_()
-            torch.cuda.synchronize(dev)
-            ctx.check(L.csa_part_sizes(ctx.h, store, first, c, parts, hist_c.data_ptr()))
-            ctx.sync()
-            hc = hist_c.cpu().numpy()
-            cf = np.concatenate([[0], np.cumsum(hc)[:-1]]).astype(np.int64)
-            first_d.copy_(torch.from_numpy(cf))
-            torch.cuda.synchronize(dev)
-            ctx.check(L.csa_scatter_lanes(ctx.h, store, first, c, first_d.data_ptr(), cursor_d.data_ptr(), staging.data_ptr()))
-            ctx.sync()
-            for u in own:
-                k = int(hc[u])
-                if k:
-                    o = 5 * (own_first[u] + filled[u])
-                    lanes_h[o:o + 5 * k].copy_(staging[5 * int(cf[u]):5 * (int(cf[u]) + k)], non_blocking=True)
-                    filled[u] += k
-            torch.cuda.synchronize(dev)
-        del staging
-        assert all(filled[u] == size[u] for u in own)
-        mark("lanes_to_host", t0)
-
         # ---- the part jobs, on `workers` contexts (streams and scratch), one host thread each ---------------------------------
         ctxs += [api.Context(dev.index) for _ in range(max(0, min(workers, len(own)) - 1))]
         active = {u: size[u] for u in own}
 
         def over_parts(todo, job):
-            it, lock, errors = iter(todo), threading.Lock(), []
+            it, lock, errors, job_s = iter(todo), threading.Lock(), [], []
 
             def body(c):
                 torch.cuda.set_device(dev)
@@ -290,8 +272,11 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
                     if u is None:
                         return
                     try:
+                        t1 = time.perf_counter()
                         job(c, u)
+                        t2 = time.perf_counter()
                         c.sync()
+                        job_s.append((t2 - t1, time.perf_counter() - t2))
                     except Exception as e:        # noqa: BLE001 - reported after the workers have joined
                         errors.append(e)
             ts = [threading.Thread(target=body, args=(c,)) for c in ctxs[1:]]
@@ -302,19 +287,47 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
                 t.join()
             if errors:
                 raise errors[0]
+            if os.environ.get("CSA_DEBUG") and job_s:
+                print(f"[csa multi {rank}/{world}] {job.__name__}: {len(job_s)} jobs, in the call {1e3 * sum(a for a, _ in job_s) / len(job_s):.1f} ms, "
+                      f"waiting for the lists to be out {1e3 * sum(b for _, b in job_s) / len(job_s):.1f} ms on average", flush=True)
 
         def lists(u):
             return lanes_h.data_ptr() + 5 * own_first[u], ranks_h.data_ptr() + 4 * own_first[u]
 
+        # ---- generation 0, a window of parts at a time: the window's lanes are picked out of the partition ids into a device
+        # buffer (one sweep over the ids per window; the parts' sizes are known, so every lane has its place), and the parts are
+        # ranked from there; only their ranked lists travel to the host.
+        t0 = time.perf_counter()
+        largest = max([size[u] for u in own], default=1)
+        window = max(1, min(len(own), int(window_bytes // (5 * largest + 64)))) if own else 1
+        win_buf = torch.empty(5 * sum(sorted((size[u] for u in own), reverse=True)[:window]) + 256, dtype=torch.uint8, device=dev)
+        first_d = torch.empty(parts, dtype=torch.int64, device=dev)
+        cursor_d = torch.zeros(parts, dtype=torch.int64, device=dev)
+        win_first = {}
+
         def gen0(c, u):
             lp, rp = lists(u)
-            pin, pout = Part(lp, None, size[u], u), PartResult(lp, rp, 0, 0)
+            pin, pout = Part(win_buf.data_ptr() + 5 * win_first[u], None, size[u], u), PartResult(lp, rp, 0, 0)
             c.check(L.csa_rank_gen0(c.h, store, ctypes.byref(pin), ctypes.byref(pout)))
             active[u] = int(pout.active)
 
-        t0 = time.perf_counter()
-        torch.cuda.synchronize(dev)
-        over_parts(own, gen0)
+        for w0 in range(0, len(own), window):
+            wparts = own[w0:w0 + window]
+            pf = np.full(parts, -1, np.int64)
+            at = 0
+            for u in wparts:
+                win_first[u] = at
+                pf[u] = at
+                at += size[u]
+            first_d.copy_(torch.from_numpy(pf))
+            cursor_d.zero_()
+            torch.cuda.synchronize(dev)
+            sweep = 1 << 30
+            for first in range(0, n, sweep):
+                ctx.check(L.csa_scatter_lanes(ctx.h, store, first, min(sweep, n - first), first_d.data_ptr(), cursor_d.data_ptr(), win_buf.data_ptr()))
+            ctx.sync()
+            over_parts(wparts, gen0)
+        del win_buf
         L.csa_store_drop_partition_ids(store)
         del pid
         if world > 1:
@@ -330,10 +343,11 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
         while total_active > 0:
             info["active_per_generation"].append(total_active)
             a_own = sum(active.values())
-            box_l = torch.empty(5 * a_own + 64, dtype=torch.uint8, device=dev)
-            box_r = torch.empty(a_own + 16, dtype=torch.int32, device=dev)
+            box_l = torch.empty(a_own + 16, dtype=torch.int32, device=dev)     # positions: low 32 bits
+            box_h = torch.empty(a_own + 16, dtype=torch.uint8, device=dev)     #            high 8 bits
+            box_r = torch.empty(a_own + 16, dtype=torch.int32, device=dev)     # ranks
             torch.cuda.synchronize(dev)
-            ctx.check(L.csa_store_use_outbox(store, box_l.data_ptr(), box_r.data_ptr(), a_own))
+            ctx.check(L.csa_store_use_outbox(store, box_l.data_ptr(), box_h.data_ptr(), box_r.data_ptr(), a_own))
 
             def gen(c, u, h=h):
                 lp, rp = lists(u)
@@ -344,31 +358,30 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
             sent = int(L.csa_store_outbox_count(store))
             assert sent == a_own
             if world == 1:
-                ctx.check(L.csa_store_apply_messages(ctx.h, store, box_l.data_ptr(), box_r.data_ptr(), sent))
+                ctx.check(L.csa_store_apply_messages(ctx.h, store, box_l.data_ptr(), box_h.data_ptr(), box_r.data_ptr(), sent))
                 ctx.sync()
             else:
                 counts = torch.zeros(world, dtype=torch.int64, device=dev)
                 counts[rank] = sent
                 dist.all_reduce(counts)
                 cs = [int(x) for x in counts.cpu()]
-                m = max(cs)
-                row_l, row_r = (5 * m + 64 + 15) // 16 * 16, (m + 16 + 3) // 4 * 4
-                snd_l = torch.zeros(row_l, dtype=torch.uint8, device=dev)
-                snd_r = torch.zeros(row_r, dtype=torch.int32, device=dev)
-                snd_l[:5 * sent] = box_l[:5 * sent]
-                snd_r[:sent] = box_r[:sent]
-                all_l = torch.empty(world * row_l, dtype=torch.uint8, device=dev)
-                all_r = torch.empty(world * row_r, dtype=torch.int32, device=dev)
-                dist.all_gather([all_l[g * row_l:(g + 1) * row_l] for g in range(world)], snd_l)
-                dist.all_gather([all_r[g * row_r:(g + 1) * row_r] for g in range(world)], snd_r)
+                row = (max(cs) + 16 + 15) // 16 * 16          # messages per rank in the gathered arrays, padded
+                gathered = []
+                for box, dt in ((box_l, torch.int32), (box_h, torch.uint8), (box_r, torch.int32)):
+                    snd = torch.zeros(row, dtype=dt, device=dev)
+                    snd[:sent] = box[:sent]
+                    allb = torch.empty(world * row, dtype=dt, device=dev)
+                    dist.all_gather([allb[g * row:(g + 1) * row] for g in range(world)], snd)
+                    gathered.append(allb)
                 torch.cuda.synchronize(dev)
+                al, ah, ar = gathered
                 for g in range(world):
-                    ctx.check(L.csa_store_apply_messages(ctx.h, store, all_l.data_ptr() + g * row_l, all_r.data_ptr() + 4 * g * row_r, cs[g]))
+                    ctx.check(L.csa_store_apply_messages(ctx.h, store, al.data_ptr() + 4 * g * row, ah.data_ptr() + g * row, ar.data_ptr() + 4 * g * row, cs[g]))
                 ctx.sync()
                 exchanged += 9 * sum(cs[g] for g in range(world) if g != rank)
-                del snd_l, snd_r, all_l, all_r
-            ctx.check(L.csa_store_use_outbox(store, None, None, 0))
-            del box_l, box_r
+                del gathered, al, ah, ar
+            ctx.check(L.csa_store_use_outbox(store, None, None, None, 0))
+            del box_l, box_h, box_r
             total_active = total_over_ranks(sum(active.values()))
             h *= 2
             gens += 1

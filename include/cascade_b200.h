@@ -118,6 +118,10 @@ int csa_select_pivots(const uint64_t* samples_host, uint64_t n_samples, uint32_t
  * (include/GPU_SACA.cuh:23-73, launched at src/GPU_SACA.cu:939). pivots_dev holds 2 (p-1) words. */
 int csa_partition_ids(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint64_t first, uint64_t count,
                       const uint64_t* pivots_dev, uint32_t p, uint16_t* pid_dev, uint64_t* hist_dev);
+/* Optional, before csa_partition_ids: from the same pivots in host memory, a table in the context that gives, for every
+ * first symbol, the range of partitions a K-gram starting with it can fall into; the search of csa_partition_ids then starts
+ * from that range (most symbols allow one partition only). p = 0 removes the table; pivots of another build need another call. */
+int csa_install_pivots(csa_ctx* ctx, const uint64_t* pivots_host, uint32_t p);
 /* Scatters the positions [first, first + count) into their partitions: position i goes to
  * part_base_dev[pid] [ cursor_dev[pid]++ ], 4 bytes each. part_base_dev holds p device pointers (they may
  * point into another GPU's memory); cursor_dev holds p running offsets. Replaces the host scatter of
@@ -199,17 +203,19 @@ void csa_store_destroy(csa_store* store);
  * with the number of suffixes that are still tied over all parts. */
 int csa_store_reserve_messages(csa_ctx* ctx, csa_store* store, uint64_t messages);
 /* Several GPUs, one store each (every GPU holds the whole text and a replica of the rank store, and ranks the parts it
- * owns): the caller lends the outbox (5 capacity + 8 bytes of lanes, 4 capacity bytes of ranks; null takes it back), so that
- * after a generation it can gather all GPUs' outboxes with its own collective (NCCL over NVLink) and apply each of them to
- * its replica with csa_store_apply_messages (queued on ctx's stream); csa_store_outbox_count tells how many messages the
- * GPU's own jobs left. Generation 0 writes the replica directly: the replicas, zero before it, are then added up by the
- * caller (every position is written by exactly one GPU). */
-int csa_store_use_outbox(csa_store* store, uint8_t* lanes_dev, uint32_t* ranks_dev, uint64_t capacity);
+ * owns): the caller lends the outbox, `capacity` messages as three arrays (the low 32 bits of the positions, their high 8
+ * bits, the ranks; all null takes it back), so that after a generation it can gather all GPUs' outboxes with its own
+ * collective (NCCL over NVLink) and apply each of them to its replica with csa_store_apply_messages (queued on ctx's
+ * stream); csa_store_outbox_count tells how many messages the GPU's own jobs left. Generation 0 writes the replica directly:
+ * the replicas, zero before it, are then added up by the caller (every position is written by exactly one GPU). */
+int csa_store_use_outbox(csa_store* store, uint32_t* pos_lo_dev, uint8_t* pos_hi_dev, uint32_t* ranks_dev, uint64_t capacity);
 uint64_t csa_store_outbox_count(const csa_store* store);
-int csa_store_apply_messages(csa_ctx* ctx, csa_store* store, const uint8_t* lanes_dev, const uint32_t* ranks_dev, uint64_t count);
+int csa_store_apply_messages(csa_ctx* ctx, csa_store* store, const uint32_t* pos_lo_dev, const uint8_t* pos_hi_dev,
+                             const uint32_t* ranks_dev, uint64_t count);
 /* The positions [first, first + count) grouped by part, from the store's partition ids: csa_part_sizes adds the number of
  * positions of every part into hist_dev[parts]; csa_scatter_lanes writes the positions as lanes into lanes_dev, part u's from
- * lane part_first_dev[u] + cursor_dev[u] on (the cursors are advanced; the order inside a part is arbitrary). Replaces the host
+ * lane part_first_dev[u] + cursor_dev[u] on (the cursors are advanced; the order inside a part is arbitrary; parts whose
+ * part_first_dev entry is all ones are left out, so that a caller can fill a buffer with a few parts at a time). Replaces the host
  * scatter of GPU_SACA::partition (src/GPU_SACA.cu:795-826, Suffix_Buffer::add include/Suffix_Buffer.hpp:80-93) for 5-byte lanes. */
 int csa_part_sizes(csa_ctx* ctx, csa_store* store, uint64_t first, uint64_t count, uint32_t parts, uint64_t* hist_dev);
 int csa_scatter_lanes(csa_ctx* ctx, csa_store* store, uint64_t first, uint64_t count, const uint64_t* part_first_dev,

@@ -81,7 +81,7 @@ def test_sharded_build_equals_the_single_gpu_build(world, n, p, kind, policy):
     procs = [ctx.Process(target=_worker, args=(r, world, port, n, p, kind, policy, q)) for r in range(world)]
     for pr in procs:
         pr.start()
-    res = sorted((q.get(timeout=600) for _ in range(world)), key=lambda x: x[0])
+    res = sorted((q.get(timeout=240) for _ in range(world)), key=lambda x: x[0])
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
@@ -169,7 +169,7 @@ def test_a_rank_that_fails_alone_takes_every_rank_out_of_the_build():
     procs = [ctx.Process(target=_failing_worker, args=(r, world, port, q)) for r in range(world)]
     for pr in procs:
         pr.start()
-    res = sorted(q.get(timeout=600) for _ in range(world))
+    res = sorted(q.get(timeout=240) for _ in range(world))
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
@@ -211,7 +211,7 @@ def test_part_at_a_time_build_over_several_ranks(world):
     procs = [ctx.Process(target=_streamed_worker, args=(r, world, port, n, p, part_suffixes, q)) for r in range(world)]
     for pr in procs:
         pr.start()
-    res = sorted((q.get(timeout=600) for _ in range(world)), key=lambda x: x[0])
+    res = sorted((q.get(timeout=240) for _ in range(world)), key=lambda x: x[0])
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
