@@ -37,6 +37,12 @@ class PartResult(ctypes.Structure):
     _fields_ = [("lanes", c_vp), ("ranks", c_vp), ("active", c_u64), ("messages", c_u64)]
 
 
+class QueryPlacement(ctypes.Structure):
+    _fields_ = [("plan", c_u32), ("key_words", c_u32), ("stride", c_u64), ("table_bytes", c_u64), ("device_bytes", c_u64), ("host_bytes", c_u64),
+                ("device_budget", c_u64), ("host_budget", c_u64), ("device_margin", c_u64), ("host_margin", c_u64),
+                ("chunk_queries", c_u64), ("chunk_symbols", c_u64), ("why", ctypes.c_char * 512)]
+
+
 class Index(ctypes.Structure):
     _fields_ = [("text", c_vp), ("sa40", c_vp), ("table", c_vp), ("n", c_u64), ("stride", c_u64), ("sa_entries", c_u64), ("sa_first", c_u64)]
 
@@ -93,6 +99,7 @@ _SIGS = {
     "csa_locate": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp, c_vp]),
     "csa_certify": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp, c_vp]),
     "csa_query_host": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_u32, c_vp, c_vp, c_vp, c_vp, c_u64, ctypes.POINTER(c_u64)]),
+    "csa_query_plan": (c_int, [c_u64, c_u64, c_u64, c_u64, c_int, ctypes.POINTER(QueryPlacement)]),
     "csa_gen_corpus_dev": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u32, c_vp, c_u32]),
     "csa_gen_queries_host": (c_int, [c_int, c_vp, c_u64, c_u64, c_vp, c_u32, c_u64, c_u64, c_vp, c_vp, c_u64]),
     "csa_counts_hash": (c_u64, [c_vp, c_u64]),

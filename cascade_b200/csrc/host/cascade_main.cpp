@@ -3,8 +3,15 @@
 // builds without writing (include/GPU_SACA.hpp:301-304).
 //
 // Environment, names as in the reference where they apply:
-//   GPU_SACA_P_TARGET     partitions to form (default 64)
-//   GPU_SACA_SCRATCH      accepted for compatibility; the in-HBM build spills nothing
+//   GPU_SACA_P_TARGET     partitions to form (default 64; src/GPU_SACA.cu:413)
+//   GPU_SACA_RAM_BUDGET   bytes of host memory the build may take (src/GPU_SACA.cu:50); default: 90 % of what is available.
+//                         A build that needs more is refused before it starts, as the reference refuses (Host_Budget_Refusal)
+//   GPU_SACA_FORCE_SPILL  if set and not 0: the suffix lists leave the device even where they would fit, i.e. the build runs
+//                         part by part with its lists in host memory (the reference forces its lower tier the same way,
+//                         src/Residency_Plan.cpp:44-45). Without it that build is chosen when the resident one does not fit the device
+//   GPU_SACA_CHUNK_CAP    most suffixes of a part of that build (the reference's test knob for small slabs, src/GPU_SACA.cu:660)
+//   GPU_SACA_SCRATCH      spill directories of the reference (src/GPU_SACA.cu:718-731). Accepted; no tier below host memory is
+//                         built here, so nothing is written there (said once on stderr)
 //   CASCADE_DEVICE        CUDA device (default 0)
 //   CASCADE_GPUS          GPUs to shard the build over (default 1): one host thread per GPU, devices CASCADE_DEVICE + i modulo
 //                         the number of devices present
@@ -31,6 +38,19 @@ static int cmp_suffixes(const uint16_t* T, uint64_t n, uint64_t i, uint64_t j, u
     for(uint64_t k = 0; k < lim; ++k) if(T[i + k] != T[j + k]) return T[i + k] < T[j + k] ? -1 : 1;
     if(lim == max_cmp && len > max_cmp) return 0;
     return li < lj ? -1 : 1;
+}
+
+// MemAvailable of /proc/meminfo in bytes (0 if it cannot be read).
+static uint64_t available_host_bytes()
+{
+    std::ifstream is("/proc/meminfo");
+    for(std::string key; is >> key; )
+    {
+        uint64_t kb = 0;
+        if(key == "MemAvailable:" && (is >> kb)) return kb * 1024;
+        is.ignore(4096, '\n');
+    }
+    return 0;
 }
 
 int main(int argc, char** argv)
@@ -68,14 +88,35 @@ int main(int argc, char** argv)
     std::fprintf(stderr, "Loaded the text of %llu symbols. Time taken: %.3f s.\n", (unsigned long long)n, since());
 
     const uint32_t gpus = uint32_t(env_u64("CASCADE_GPUS", 1));
+    if(std::getenv("GPU_SACA_SCRATCH")) std::fprintf(stderr, "note: GPU_SACA_SCRATCH is accepted, but no tier below host memory is built: nothing is written there.\n");
+    // Which build: the resident one keeps every list on the device; the part-by-part one keeps them in host memory.
+    size_t dev_free = 0, dev_total = 0;
+    cudaMemGetInfo(&dev_free, &dev_total);
+    const uint64_t resident_need = csa_build_device_bytes(n, p) + (n + CSA_TEXT_PAD) * 2 + 5 * n + CSA_SA_PAD_BYTES;
+    const bool forced = env_u64("GPU_SACA_FORCE_SPILL", 0) != 0;
+    const bool by_parts = gpus <= 1 && (forced || resident_need > dev_free || n >= (1ull << 32) - (1ull << 26));
+    if(by_parts)
+    {
+        // host memory of that build: the text and the output (held already) and 4 bytes per suffix of ranks
+        uint64_t budget = env_u64("GPU_SACA_RAM_BUDGET", 0);
+        if(budget == 0) budget = uint64_t(0.9 * double(available_host_bytes()));
+        const uint64_t need = 4 * n;
+        if(budget != 0 && need > budget)
+        {
+            std::fprintf(stderr, "error: the build would take %.1f GB more of host memory, past the budget of %.1f GB (GPU_SACA_RAM_BUDGET)\n", double(need) / 1e9,
+                         double(budget) / 1e9);
+            return EXIT_FAILURE;
+        }
+    }
     csa_ctx* ctx = nullptr;
     const double b0 = since();
     if(gpus <= 1)
     {
         if(csa_ctx_create(device, &ctx) != CSA_OK) { std::fprintf(stderr, "error: cannot create a device context\n"); return EXIT_FAILURE; }
         csa_build_stats st{};
-        const int rc = csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
+        const int rc = by_parts ? csa_build_sa_streamed(ctx, T, n, p, 0, SA, env_u64("GPU_SACA_CHUNK_CAP", 0), &st) : csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
         if(rc != CSA_OK) { std::fprintf(stderr, "error: build failed (%d): %s\n", rc, csa_last_error(ctx)); return EXIT_FAILURE; }
+        if(by_parts) std::fprintf(stderr, "Built part by part with the suffix lists in host memory (%s).\n", forced ? "GPU_SACA_FORCE_SPILL" : "the resident build does not fit the device");
         std::fprintf(stderr, "Built the suffix array: %u partitions (largest %llu), %u doubling generations, %llu digit passes.\n", st.partitions,
                      (unsigned long long)st.max_partition, st.generations, (unsigned long long)st.sort_passes);
         std::fprintf(stderr, "Device time: partition %.1f ms, initial ranking %.1f ms, doubling %.1f ms, output %.1f ms.\n", st.ms_partition, st.ms_gen0,

@@ -1,7 +1,8 @@
 // `query info | plan | find | gen`: the query engine's command line with the reference's flags and key=value output
-// (src/query.cu:43-112, 536-541) for the part this engine implements: text and suffix array resident in device memory,
-// a sample table of packed K-grams, count and (an extension) locate. Flags of the reference that select other residency
-// tiers or pipeline shapes are accepted and reported as not applicable.
+// (src/query.cu:43-112, 536-541) for the part this engine implements: search on the device, text in device memory, suffix
+// array in device or pinned host memory as the planner (csa_query_plan) or --sa-res places it, a sample table of packed
+// K-grams, count and (an extension) locate. The reference's host-search tiers (--text-res/--sa-res pageable, mapped) are
+// refused with the reason; flags that only shape its host search are read and listed as `not_applicable=` lines.
 #include "../../../include/cascade_b200.h"
 #include "formats.hpp"
 
@@ -21,9 +22,9 @@ namespace
 const char* const USAGE =
     "Usage:\n"
     "  query info --index DIR\n"
-    "  query plan --index DIR [--stride S]\n"
-    "  query find --index DIR --queries Q1.qry[,Q2.qry,...] [--q N] [--stride S] [--reps K] [--locate M] [--itv-out F] [--cnt-out F]\n"
-    "             [--pos-out F] [--cnt-dir D] [--validate] [--device D]\n"
+    "  query plan --index DIR [--stride S|auto] [--sa-res device|pinned|auto] [--device-budget BYTES] [--host-budget BYTES]\n"
+    "  query find --index DIR --queries Q1.qry[,Q2.qry,...] [--q N] [--stride S|auto] [--sa-res device|pinned|auto] [--reps K] [--locate M]\n"
+    "             [--itv-out F] [--cnt-out F] [--pos-out F] [--cnt-dir D] [--validate] [--device D] [--device-budget BYTES] [--host-budget BYTES]\n"
     "  query gen --index DIR --out Q.qry --kind substring|random [--q N --len L1[,L2,...]] [--source F] [--vocab V] [--seed S]\n";
 
 struct Args
@@ -70,19 +71,64 @@ std::string stem(const std::string& p)
 #define CK(call) do { const int r_ = (call); if(r_ != CSA_OK) { std::fprintf(stderr, "error: %s failed (%d): %s\n", #call, r_, csa_last_error(ctx)); return 1; } } while(0)
 #define CU(call) do { const cudaError_t e_ = (call); if(e_ != cudaSuccess) { std::fprintf(stderr, "error: %s: %s\n", #call, cudaGetErrorString(e_)); return 1; } } while(0)
 
+uint64_t available_host_bytes()
+{
+    std::ifstream is("/proc/meminfo");
+    for(std::string key; is >> key; )
+    {
+        uint64_t kb = 0;
+        if(key == "MemAvailable:" && (is >> kb)) return kb * 1024;
+        is.ignore(4096, '\n');
+    }
+    return 0;
+}
+
+// The placement of the index for the options given: budgets as set or else measured, the suffix array's tier as named or
+// else the planner's choice, the stride as given or else the finest that fits (`--stride auto`, the default of `plan`).
+bool place(const Args& a, uint64_t n, uint64_t stride_default, csa_query_placement& pl, std::string& err)
+{
+    for(const char* k : {"stride", "sa-res", "text-res"})
+        if(a.get(k).find(',') != std::string::npos) { err = std::string("--") + k + " takes one value here, not a list"; return false; }
+    const std::string sa_res = a.get("sa-res", "auto"), text_res = a.get("text-res", "auto");
+    if(text_res != "auto" && text_res != "device") { err = "--text-res " + text_res + ": this engine searches on the device and keeps the text there (device, auto)"; return false; }
+    int tier = 0;
+    if(sa_res == "device") tier = 1;
+    else if(sa_res == "pinned") tier = 2;
+    else if(sa_res != "auto") { err = "--sa-res " + sa_res + ": this engine searches on the device; the suffix array is in device or pinned memory (device, pinned, auto)"; return false; }
+    uint64_t dev_budget = a.u64("device-budget", 0), host_budget = a.u64("host-budget", 0);
+    if(dev_budget == 0)
+    {
+        size_t free_b = 0, total_b = 0;
+        if(cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) { cudaGetLastError(); err = "cannot measure the device's free memory; set --device-budget"; return false; }
+        dev_budget = free_b;
+    }
+    if(host_budget == 0) host_budget = available_host_bytes();
+    const std::string st = a.get("stride", stride_default ? std::to_string(stride_default) : "auto");
+    const uint64_t stride = st == "auto" ? 0 : std::strtoull(st.c_str(), nullptr, 10);
+    if(st != "auto" && stride == 0) { err = "--stride must be a positive number or auto"; return false; }
+    if(csa_query_plan(n, dev_budget, host_budget, stride, tier, &pl) != CSA_OK) { err = "the planner refused its arguments"; return false; }
+    if(pl.plan == 0) { err = pl.why; return false; }
+    return true;
+}
+
+void print_placement(const csa_query_placement& pl)
+{
+    std::printf("plan=%c\ntext_res=device\nsa_res=%s\nstride=%" PRIu64 "\nkey_words=%u\ntable_bytes=%" PRIu64 "\ndevice_bytes=%" PRIu64 "\nhost_bytes=%" PRIu64
+                "\ndevice_budget=%" PRIu64 "\nhost_budget=%" PRIu64 "\nchunk_queries=%" PRIu64 "\nchunk_symbols=%" PRIu64 "\nlanes=3\n",
+                char(pl.plan), pl.plan == 'A' ? "device" : "pinned", pl.stride, pl.key_words, pl.table_bytes, pl.device_bytes, pl.host_bytes, pl.device_budget,
+                pl.host_budget, pl.chunk_queries, pl.chunk_symbols);
+}
+
 int run_info(const Args& a, bool plan)
 {
     Index_Meta m; std::string err;
     if(!read_index_meta(a.get("index"), m, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
-    const uint64_t stride = a.u64("stride", 32);
-    const uint64_t table = ((m.n + stride - 1) / stride) * 16, need = 2 * m.n + 5 * m.n + table + 256;
-    size_t free_b = 0, total_b = 0;
-    const bool have = cudaMemGetInfo(&free_b, &total_b) == cudaSuccess;
     std::printf("n=%" PRIu64 "\nsym_bytes=%u\nsa_width=%u\nsa_order=%s\ntext=%s\nsa_part_c=%zu\nsep=%lld\n", m.n, m.sym_bytes, m.sa_width, m.sa_order.c_str(),
                 m.text.c_str(), m.sa_part.size(), m.sep);
-    if(plan) std::printf("plan=A\ntext_res=device\nsa_res=device\nstride=%" PRIu64 "\nkey_words=2\ntable_bytes=%" PRIu64 "\n", stride, table);
-    std::printf("device_bytes_needed=%" PRIu64 "\n", need);
-    if(have) std::printf("device_free=%zu\nfits_device=%d\n", free_b, int(need <= free_b));
+    if(!plan) return 0;
+    csa_query_placement pl;
+    if(!place(a, m.n, 0, pl, err)) { std::printf("plan=none\nwhy=%s\n", err.c_str()); return 1; }
+    print_placement(pl);
     return 0;
 }
 
@@ -91,7 +137,11 @@ int run_gen(const Args& a)
     Index_Meta m; std::string err;
     if(!read_index_meta(a.get("index"), m, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
     const std::string kind = a.get("kind", "substring");
-    if(kind != "substring" && kind != "random") { std::fprintf(stderr, "error: --kind %s is not supported here (substring, random)\n", kind.c_str()); return 1; }
+    if(kind != "substring" && kind != "random")
+    {
+        std::fprintf(stderr, "error: --kind %s is not supported: this generator makes the kinds substring and random (the reference also has mutated and unigram)\n", kind.c_str());
+        return 1;
+    }
     const uint64_t q = a.u64("q", 1000), seed = a.u64("seed", 1), vocab = a.u64("vocab", 65536);
     std::vector<uint32_t> lens;
     for(const auto& t : split(a.get("len", "8"), ',')) lens.push_back(uint32_t(std::strtoul(t.c_str(), nullptr, 10)));
@@ -117,15 +167,20 @@ int run_gen(const Args& a)
 
 int run_find(const Args& a)
 {
-    for(const char* k : {"text-res", "sa-res", "key-words", "sort", "gather", "gather-queries", "chunk-queries", "chunk-symbols", "host-threads", "host-lanes",
-                         "host-prefetch", "sa-cold", "phase-times", "device-budget", "host-budget", "spot"})
-        if(a.has(k)) std::fprintf(stderr, "note: --%s is accepted but not applicable: the index is kept whole in device memory\n", k);
+    // flags of the reference that shape its host search or its own pipeline: read, named on stdout, without effect here
+    for(const char* k : {"key-words", "sort", "gather", "gather-queries", "chunk-queries", "chunk-symbols", "host-threads", "host-lanes", "host-prefetch", "sa-cold",
+                         "phase-times", "spot"})
+        if(a.has(k)) std::printf("not_applicable=--%s\n", k);
     Index_Meta m; std::string err;
     if(!read_index_meta(a.get("index"), m, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
-    const uint64_t n = m.n, stride = std::max<uint64_t>(1, a.u64("stride", 32)), reps = std::max<uint64_t>(1, a.u64("reps", 3));
+    const uint64_t n = m.n, reps = std::max<uint64_t>(1, a.u64("reps", 3));
     const uint32_t max_pos = uint32_t(a.u64("locate", 0));
     const int device = int(a.u64("device", 0));
     CU(cudaSetDevice(device));
+    csa_query_placement pl;
+    if(!place(a, n, 32, pl, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
+    const uint64_t stride = pl.stride;
+    const bool sa_pinned = pl.plan == 'B';
     csa_ctx* ctx = nullptr;
     if(csa_ctx_create(device, &ctx) != CSA_OK) { std::fprintf(stderr, "error: cannot create a device context\n"); return 1; }
 
@@ -154,13 +209,17 @@ int run_find(const Args& a)
     if(at != 5 * n) { std::fprintf(stderr, "error: the suffix-array parts hold %" PRIu64 " bytes, expected %" PRIu64 "\n", at, 5 * n); return 1; }
     uint16_t* T_d = nullptr; uint8_t* SA_d = nullptr; uint64_t* tab_d = nullptr;
     const uint64_t entries = (n + stride - 1) / stride;
-    CU(cudaMalloc(&T_d, T.size() * 2)); CU(cudaMalloc(&SA_d, SA.size())); CU(cudaMalloc(&tab_d, entries * 16));
+    CU(cudaMalloc(&T_d, T.size() * 2)); CU(cudaMalloc(&tab_d, entries * 16));
+    if(sa_pinned) CU(cudaMallocHost(&SA_d, SA.size()));        // plan B: the device reads the array across the bus
+    else CU(cudaMalloc(&SA_d, SA.size()));
     CU(cudaMemcpy(T_d, T.data(), T.size() * 2, cudaMemcpyHostToDevice));
-    CU(cudaMemcpy(SA_d, SA.data(), SA.size(), cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(SA_d, SA.data(), SA.size(), sa_pinned ? cudaMemcpyHostToHost : cudaMemcpyHostToDevice));
     CK(csa_table_build(ctx, T_d, n, SA_d, stride, tab_d));
     CK(csa_sync(ctx, nullptr));
     const csa_index idx{T_d, SA_d, tab_d, n, stride};
-    std::printf("n=%" PRIu64 "\nplan=A\ntext_res=device\nsa_res=device\nstride=%" PRIu64 "\nkey_words=2\nload_s=%.6f\n", n, stride, since());
+    std::printf("n=%" PRIu64 "\n", n);
+    print_placement(pl);
+    std::printf("load_s=%.6f\n", since());
 
     for(const auto& qpath : split(a.get("queries"), ','))
     {
@@ -231,7 +290,8 @@ int run_find(const Args& a)
         cudaEventDestroy(e0); cudaEventDestroy(e1);
     }
     csa_ctx_destroy(ctx);
-    cudaFree(T_d); cudaFree(SA_d); cudaFree(tab_d);
+    cudaFree(T_d); cudaFree(tab_d);
+    if(sa_pinned) cudaFreeHost(SA_d); else cudaFree(SA_d);
     return 0;
 }
 

@@ -358,6 +358,22 @@ int csa_query_host(csa_ctx* ctx, const csa_index* index, const uint64_t* off_hos
                    uint32_t max_pos, uint64_t* itv_host, uint32_t* cnt_host, uint64_t* pos_off_host, uint64_t* pos_host,
                    uint64_t pos_capacity, uint64_t* pos_total);
 
+/* Where an index of n symbols goes, by the rules of the reference's planner (Query_Engine::plan / ::fit,
+ * src/Query_Engine.cu:822-1006): the first plan that fits the budgets less their margins (a sixteenth, at least 1 GiB), with the
+ * finest table stride from 32 on that the device still holds when stride is 0. Plans: 'A' text and suffix array in device
+ * memory; 'B' text in device memory, suffix array in pinned host memory (brackets gathered over PCIe; strides up to 64). The
+ * reference's plans C and D search on the host and are not offered. sa_tier: 0 any, 1 device, 2 pinned. plan = 0 and `why`
+ * say so when nothing fits. Host code only. */
+typedef struct csa_query_placement
+{
+    uint32_t plan, key_words;
+    uint64_t stride, table_bytes, device_bytes, host_bytes;
+    uint64_t device_budget, host_budget, device_margin, host_margin;
+    uint64_t chunk_queries, chunk_symbols;      /* a lane's chunk of a host batch (csa_query_host runs three lanes) */
+    char why[512];
+} csa_query_placement;
+int csa_query_plan(uint64_t n, uint64_t device_budget, uint64_t host_budget, uint64_t stride, int sa_tier, csa_query_placement* out);
+
 /* ---- synthetic workloads (seeded; the same integers on host and device) -------------------------------- */
 
 /* Fills text[0, n) with the Zipf corpus: separators 0xFFFF before documents of geometric length (mean mean_doc),

@@ -141,6 +141,17 @@ def test_cascade_and_query_find_against_the_oracle(tmp_path, oracle):
         assert r.returncode == 0, r.stderr
         assert np.array_equal(np.fromfile(out2, dtype=np.uint8), want[:5 * n]), gpus
 
+    # the reference's knobs: the lower tier forced (the build then runs part by part with its lists in host memory, parts capped
+    # as the reference's test knob caps its slabs), and a host budget that the build would pass, which refuses it before it starts
+    out3 = os.path.join(tmp, "text.parts.sa40")
+    r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), out3], capture_output=True, text=True,
+                       env=dict(env, GPU_SACA_FORCE_SPILL="1", GPU_SACA_CHUNK_CAP="70000", GPU_SACA_SCRATCH="/tmp"))
+    assert r.returncode == 0 and "part by part" in r.stderr and "GPU_SACA_SCRATCH" in r.stderr, r.stderr
+    assert np.array_equal(np.fromfile(out3, dtype=np.uint8), want[:5 * n])
+    r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), out3], capture_output=True, text=True,
+                       env=dict(env, GPU_SACA_FORCE_SPILL="1", GPU_SACA_RAM_BUDGET="100000"))
+    assert r.returncode != 0 and "GPU_SACA_RAM_BUDGET" in r.stderr
+
     q = os.path.join(tmp, "a.qry")
     assert subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", q, "--kind", "substring", "--q", "5000", "--len", "1,2,4,8,16",
                            "--seed", "1"], capture_output=True).returncode == 0
