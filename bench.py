@@ -661,7 +661,8 @@ def run_c4(args):
                 dist.barrier()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            segs, info = multi.build_sa_streamed_multi(ctx, T, n, p, part_suffixes=ps, host=host)
+            segs, info = multi.build_sa_streamed_multi(ctx, T, n, p, part_suffixes=ps, host=host,
+                                                       list_budget_bytes=None if args.list_budget_gb < 0 else int(args.list_budget_gb * 1e9))
             torch.cuda.synchronize()
             dt = time.perf_counter() - t0
             if world > 1:
@@ -700,7 +701,9 @@ def run_c4(args):
                           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
                           "config": {"workload": "part-at-a-time build with the suffix lists in pinned host memory: a scaled-down stand-in for BASELINE config 4 "
                                                  "(64e9 tokens with NVMe spill, which is not built)", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
-                                     "partitions_asked": p, "part_suffixes": ps, "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0, "gpus": world},
+                                     "partitions_asked": p, "part_suffixes": ps, "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0, "gpus": world,
+                                     "lists_on_device_rank0": info["lists_on_device"], "lists_on_host_rank0": info["lists_on_host"],
+                                     "list_budget_gb": "what is free" if args.list_budget_gb < 0 else args.list_budget_gb},
                           "timed": "wall clock of the whole build, text resident on every device: partition ids, lanes to the host, every generation's lists over "
                                    "PCIe both ways, rank exchange over NVLink, final order; max over ranks",
                           "clocks": clocks.summary(), "partitions": info["partitions"], "parts": info["parts"], "generations": info["generations"],
@@ -746,6 +749,8 @@ def main():
                     help="zipf: BASELINE config 2; repeat: config 3 alone (1e9 tokens of near-duplicate documents, build only); "
                          "c4: the part-at-a-time build on more than 2^32 tokens (one-GPU stand-in for config 4)")
     ap.add_argument("--part-suffixes", type=int, default=0, help="c4: most suffixes of a part (0 = the library's default, 2^27)")
+    ap.add_argument("--list-budget-gb", type=float, default=-1.0,
+                    help="c4: device memory (GB) that may hold parts' suffix lists; 0 keeps every list in pinned host memory, -1 (default) takes what is free")
     ap.add_argument("--micro", default=None, choices=["sort"], help="time one kernel family alone instead of the build")
     ap.add_argument("--records", type=int, default=31_250_000)
     ap.add_argument("--bits", type=int, default=64)

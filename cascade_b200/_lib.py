@@ -58,6 +58,8 @@ _SIGS = {
     "csa_version": (ctypes.c_char_p, []),
     "csa_sort_workspace_bytes": (ctypes.c_size_t, [c_u64]),
     "csa_sort_pairs": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_u32, c_u64, c_int, c_int, c_vp, ctypes.c_size_t, ctypes.POINTER(c_int)]),
+    "csa_sort_segments_workspace_bytes": (ctypes.c_size_t, [c_u64, c_u32]),
+    "csa_sort_segments": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_u32, c_int, c_int, c_vp, ctypes.c_size_t, ctypes.POINTER(c_int)]),
     "csa_sort_pairs_static": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_u64, c_int, c_int, ctypes.POINTER(c_int)]),
     "csa_debug_set": (c_int, [c_int, c_u64]),
     "csa_set_pass_timing": (c_int, [c_vp, c_int]),

@@ -7,6 +7,7 @@
 // (:1052), exponentiate_prefix (:1998) and concatenate_partitions (:2167), for a text that fits the device.
 #include "common.cuh"
 #include "part.cuh"
+#include "sort.cuh"
 
 #include <cstdlib>
 #include <vector>
@@ -36,7 +37,8 @@ Build_Layout layout_for(u64 n, u32 p)
     L.head = align256(cap * 4);
     L.isa = align256(n * 4);
     L.sa = align256(n * 4 + 64);
-    L.sort_ws = align256(csa_sort_workspace_bytes(n));
+    const size_t one = csa_sort_workspace_bytes(n), many = sort_segments_workspace_bytes(n, p ? p : 1);
+    L.sort_ws = align256(one > many ? one : many);
     L.scratch = align256(div_up(n, RANK_TILE) * 3 * 4 + 256);
     L.small = align256(size_t(p) * 8) * 3 + align256(size_t(2) * p * 8) + align256(pick_splitters_scratch_bytes(size_t(1) << 19)) + align256(65536 * 4) + 4096;   // hist, cursors, bases, pivots, splitter scratch, first-symbol table
     L.upd = align256(cap * 8);     // (position, rank) updates of one step, applied to `isa` in address order
@@ -135,7 +137,20 @@ int build_core(csa_ctx* ctx, const u16* T, const u64 n, u32 p, const u64 seed, u
     const Slot_Map whole{nullptr, nullptr, 0, 0};      // one GPU: local slots are global ranks
     u64* act_count = ctx->d_scalars;       // running length of the next active list
     CSA_CUDA(ctx, cudaMemsetAsync(act_count, 0, 8, ctx->stream));
-    for(u32 q = 0; q < p_eff; ++q)
+    // All partitions go through every digit pass together (one launch per pass, no read-back) unless one of them is too large
+    // for the segmented sort's tile counts; CSA_GEN0_BY_PARTITION=1 asks for the one-by-one form.
+    bool together = max_part < (u64(1) << 30) && n < (u64(1) << 32);
+    if(const char* e = std::getenv("CSA_GEN0_BY_PARTITION")) together = together && std::atoi(e) == 0;
+    if(together)
+    {
+        if(!keys_from_scatter) CSA_TRY(launch_keys_gen0(ctx, T, sa, n, keysA));
+        int in_alt = 0;
+        CSA_TRY(sort_segments(ctx, keysA, keysB, sa, posB, part_off.data(), p_eff, 0, 64, sort_ws, L.sort_ws, &in_alt));
+        // Ranked as one list: the partitions follow one another in suffix order, so the whole array is in key order; a group
+        // of equal keys that meets a partition's border is one group (as in a build with fewer partitions).
+        CSA_TRY(launch_rank_and_compact(ctx, in_alt ? keysB : keysA, in_alt ? posB : sa, n, 64, 0, iv, whole, sa, head, posA, act_count, scratch, upd));
+    }
+    for(u32 q = 0; q < p_eff && !together; ++q)
     {
         const u64 S = part_size[q], first = part_off[q];
         if(S == 0) continue;

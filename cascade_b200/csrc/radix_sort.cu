@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "sort.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <vector>
 
@@ -40,8 +41,8 @@ __host__ __device__ __forceinline__ u32 digit_mask(int shift, int end_bit)
 
 // Digit histograms of every pass in one read of the keys. hist holds [passes][RADIX] 64-bit counts of the whole array.
 template <int BLOCK>
-__global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict__ keys, const u64 n, const int begin_bit, const int end_bit, const int passes,
-                                                         u64* __restrict__ hist)
+__device__ __forceinline__ void histogram_body(const u64* __restrict__ keys, const u64 n, const int begin_bit, const int end_bit, const int passes,
+                                               u64* __restrict__ hist, const u64 pass_stride, const u32 block_index, const u32 block_count)
 {
     // One private histogram per warp keeps the shared-memory atomics of different warps apart; lanes of a warp that
     // hold the same digit still meet, and when all 32 do (a digit that is constant over long stretches, as the high bytes
@@ -63,9 +64,9 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
     const int width = end_bit - begin_bit;
     const u64 width_mask = width >= 64 ? ~0ull : ((1ull << width) - 1);
     const u64 chunk = u64(BLOCK) * HIST_UNROLL;
-    const u64 stride = u64(gridDim.x) * chunk;
+    const u64 stride = u64(block_count) * chunk;
     const u64 rounds = (pairs + stride - 1) / stride;       // whole warps take part in every round: the votes see a full mask
-    u64 i = u64(blockIdx.x) * chunk + threadIdx.x;
+    u64 i = u64(block_index) * chunk + threadIdx.x;
     for(u64 r = 0; r < rounds; ++r, i += stride)
     {
         u64 k[2 * HIST_UNROLL];
@@ -110,7 +111,7 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
             }
         }
     }
-    if(blockIdx.x == 0 && threadIdx.x == 0)
+    if(block_index == 0 && threadIdx.x == 0)
     {
         // the keys outside the 16-byte pairs: the first of an odd start, the last of an odd remainder
         u64 rest[2];
@@ -127,8 +128,26 @@ __global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict_
         u32 t = 0;
         #pragma unroll
         for(int w = 0; w < WARPS; ++w) t += h[w * per_warp + i2];
-        if(t != 0) atomicAdd(&hist[i2], u64(t));
+        if(t != 0) atomicAdd(&hist[u64(i2 / RADIX) * pass_stride + (i2 % RADIX)], u64(t));
     }
+}
+
+template <int BLOCK>
+__global__ void __launch_bounds__(BLOCK) histogram_kernel(const u64* __restrict__ keys, const u64 n, const int begin_bit, const int end_bit, const int passes,
+                                                         u64* __restrict__ hist)
+{
+    histogram_body<BLOCK>(keys, n, begin_bit, end_bit, passes, hist, RADIX, blockIdx.x, gridDim.x);
+}
+
+// The same for many segments of one array in one launch: blockIdx.y is the segment, hist is [passes][segments][RADIX].
+template <int BLOCK>
+__global__ void __launch_bounds__(BLOCK) seg_histogram_kernel(const u64* __restrict__ keys, const u64* __restrict__ seg_off, const u32 segs, const int begin_bit,
+                                                             const int end_bit, const int passes, u64* __restrict__ hist)
+{
+    const u32 s = blockIdx.y;
+    const u64 first = seg_off[s], count = seg_off[s + 1] - first;
+    if(count == 0) return;
+    histogram_body<BLOCK>(keys + first, count, begin_bit, end_bit, passes, hist + u64(s) * RADIX, u64(segs) * RADIX, blockIdx.x, gridDim.x);
 }
 
 // From the histograms: for every pass the global offset of each digit's first record (what the first launch of the pass
@@ -174,8 +193,11 @@ template <int BLOCK, int ITEMS, typename V, int MATCH_BITS, bool FULL>
 __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const V* __restrict__ vals_in,
                                               V* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
                                               const u64* __restrict__ digit_base, u64* __restrict__ next_base, u32* __restrict__ status,
-                                              u64* __restrict__ dev_status, const u32 tile, const u32 valid_records)
+                                              u64* __restrict__ dev_status, const u32 tile, const u32 valid_records, const u32 first_tile, const u64 tile_base)
 {
+    // tile: the tile's index among the status words; first_tile: the index of the first tile of the run of records that this
+    // tile belongs to (0 for a sort of one array; a segment's first tile in a segmented sort: nothing before it is looked at);
+    // tile_base: the tile's first record; n: the end of the run.
     constexpr int TILE = BLOCK * ITEMS;
     constexpr int WARPS = BLOCK / 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -187,7 +209,6 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
     u32* const misc = reinterpret_cast<u32*>(g_off + RADIX);   // [0] tile id, [1..] warp totals of the digit scan
 
     const u32 tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const u64 tile_base = u64(tile) * TILE;
     const u32 valid = FULL ? u32(TILE) : valid_records;     // a full tile needs no bounds checks
 
     // Warp-striped load: a warp owns 32 * ITEMS consecutive records; item i of lane l is record i * 32 + l of them.
@@ -266,7 +287,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
         #pragma unroll
         for(int w = 0; w < WARPS; ++w) { wcount[w] = warp_hist[w * RADIX + tid]; count += wcount[w]; }
         if(!FULL && tid == dmask) count -= (u32(TILE) - valid);      // dmask is the digit of the all-ones filler key
-        st_relaxed_u32(status + u64(tile) * RADIX + tid, (tile == 0 ? FLAG_PREFIX : FLAG_AGGREGATE) | count);
+        st_relaxed_u32(status + u64(tile) * RADIX + tid, (tile == first_tile ? FLAG_PREFIX : FLAG_AGGREGATE) | count);
     }
     {
         u32 inc = count;
@@ -298,23 +319,24 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
     if(tid < RADIX)
     {
         u32 before = 0;
-        if(tile > 0)
+        if(tile > first_tile)
         {
             // The status words of LOOKBACK_BATCH earlier tiles are requested at once, so that a long walk costs one memory
             // round trip per batch instead of one per tile; a word that is still empty is polled (with a bound) in place.
             bool gave_up = false, done = false;
             const u32 spin_limit = g_lookback_spin_limit;
+            const long long t_first = (long long)first_tile;
             long long t = (long long)tile - 1;
-            while(t >= 0 && !done && !gave_up)
+            while(t >= t_first && !done && !gave_up)
             {
                 u32 s[LOOKBACK_BATCH];
                 #pragma unroll
                 for(int j = 0; j < LOOKBACK_BATCH; ++j)
-                    s[j] = (t - j >= 0) ? ld_relaxed_u32(status + u64(t - j) * RADIX + tid) : FLAG_PREFIX;
+                    s[j] = (t - j >= t_first) ? ld_relaxed_u32(status + u64(t - j) * RADIX + tid) : FLAG_PREFIX;
                 #pragma unroll
                 for(int j = 0; j < LOOKBACK_BATCH; ++j)
                 {
-                    if(done || gave_up || t - j < 0) break;
+                    if(done || gave_up || t - j < t_first) break;
                     u32 v = s[j];
                     u32 spins = 0;
                     while((v >> FLAG_SHIFT) == 0)
@@ -338,7 +360,7 @@ __device__ __forceinline__ void onesweep_tile(const u64* __restrict__ keys_in, u
             st_relaxed_u32(status + u64(tile) * RADIX + tid, FLAG_PREFIX | ((before + count) & COUNT_MASK));
         }
         const u64 db = digit_base[tid];
-        if(tile_base + TILE >= n) next_base[tid] = db + before + count;     // the last tile has seen every record of the launch
+        if(next_base != nullptr && tile_base + TILE >= n) next_base[tid] = db + before + count;     // the last tile has seen every record of the launch
         g_off[tid] = db + before - tile_excl[tid];
     }
     __syncthreads();
@@ -393,10 +415,101 @@ __global__ void __launch_bounds__(BLOCK) onesweep_pass_kernel(const u64* __restr
     const u64 tile_base = u64(tile) * TILE;
     if(tile_base >= n) return;
     if(n - tile_base >= u64(TILE))
-        onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, true>(keys_in, keys_out, vals_in, vals_out, n, shift, dmask, digit_base, next_base, status, dev_status, tile, u32(TILE));
+        onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, true>(keys_in, keys_out, vals_in, vals_out, n, shift, dmask, digit_base, next_base, status, dev_status, tile, u32(TILE),
+                                                         0u, tile_base);
     else
         onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, false>(keys_in, keys_out, vals_in, vals_out, n, shift, dmask, digit_base, next_base, status, dev_status, tile,
-                                                          u32(n - tile_base));
+                                                          u32(n - tile_base), 0u, tile_base);
+}
+
+// The segment that holds tile `t`: the last s with seg_tile0[s] <= t (seg_tile0 has segs + 1 ascending entries).
+__device__ __forceinline__ u32 segment_of_tile(const u32* __restrict__ seg_tile0, const u32 segs, const u32 t)
+{
+    u32 a = 0, b = segs - 1;
+    while(a < b)
+    {
+        const u32 mid = (a + b + 1) >> 1;
+        if(__ldg(seg_tile0 + mid) <= t) a = mid; else b = mid - 1;
+    }
+    return a;
+}
+
+// One digit pass over MANY segments of one array in one launch: every segment is sorted on its own (its tiles look back no
+// further than its first tile, its records stay inside its range). digit_base: [segments][RADIX] offsets in the whole array;
+// skip: [segments], non-zero where the digit is the same for all of a segment's records: its tiles then copy their records
+// over unchanged, so that all segments change buffers together.
+template <int BLOCK, int ITEMS, typename V, int MATCH_BITS>
+__global__ void __launch_bounds__(BLOCK) onesweep_seg_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const V* __restrict__ vals_in,
+                                                                 V* __restrict__ vals_out, const u64* __restrict__ seg_off, const u32* __restrict__ seg_tile0,
+                                                                 const u32 segs, const int shift, const u32 dmask, const u64* __restrict__ digit_base,
+                                                                 const u32* __restrict__ skip, u32* __restrict__ status, u32* __restrict__ tile_counter,
+                                                                 u64* __restrict__ dev_status)
+{
+    constexpr int TILE = BLOCK * ITEMS;
+    constexpr int WARPS = BLOCK / 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    u32* const warp_hist = reinterpret_cast<u32*>(smem_raw + size_t(TILE) * 8 + size_t(TILE) * sizeof(V));
+    u32* const misc = reinterpret_cast<u32*>(smem_raw + size_t(TILE) * 8 + size_t(TILE) * sizeof(V) + size_t(WARPS) * RADIX * 4 + RADIX * 4 + RADIX * 8);
+    if(threadIdx.x == 0)
+    {
+        const u32 t = atomicAdd(tile_counter, 1u);
+        misc[0] = t;
+        misc[GAVE_UP_WORD] = 0;
+        misc[GAVE_UP_WORD + 1] = t < __ldg(seg_tile0 + segs) ? segment_of_tile(seg_tile0, segs, t) : 0xFFFFFFFFu;
+    }
+    for(int i = threadIdx.x; i < WARPS * RADIX; i += BLOCK) warp_hist[i] = 0;
+    __syncthreads();
+    const u32 tile = misc[0], s = misc[GAVE_UP_WORD + 1];
+    if(s == 0xFFFFFFFFu) return;
+    const u32 first_tile = __ldg(seg_tile0 + s);
+    const u64 seg_first = seg_off[s], seg_end = seg_off[s + 1];
+    const u64 tile_base = seg_first + u64(tile - first_tile) * TILE;
+    if(tile_base >= seg_end) return;
+    const u32 valid = seg_end - tile_base >= u64(TILE) ? u32(TILE) : u32(seg_end - tile_base);
+    if(__ldg(skip + s))
+    {
+        for(u32 i = threadIdx.x; i < valid; i += BLOCK)
+        {
+            keys_out[tile_base + i] = keys_in[tile_base + i];
+            if(vals_in != nullptr) vals_out[tile_base + i] = vals_in[tile_base + i];
+        }
+        return;
+    }
+    const u64* const db = digit_base + u64(s) * RADIX;
+    if(valid == u32(TILE))
+        onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, true>(keys_in, keys_out, vals_in, vals_out, seg_end, shift, dmask, db, nullptr, status, dev_status, tile, u32(TILE),
+                                                         first_tile, tile_base);
+    else
+        onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, false>(keys_in, keys_out, vals_in, vals_out, seg_end, shift, dmask, db, nullptr, status, dev_status, tile, valid,
+                                                          first_tile, tile_base);
+}
+
+// Digit offsets and skip flags of a segmented sort. hist: [passes][segments][RADIX]; base likewise, offsets in the whole array;
+// skip: [passes][segments].
+__global__ void __launch_bounds__(RADIX) seg_digit_base_kernel(const u64* __restrict__ hist, const u64* __restrict__ seg_off, const u32 segs, u64* __restrict__ base,
+                                                              u32* __restrict__ skip)
+{
+    __shared__ u64 warp_tot[RADIX / 32];
+    __shared__ int s_skip;
+    const u32 p = blockIdx.x, s = blockIdx.y, d = threadIdx.x;
+    if(d == 0) s_skip = 0;
+    __syncthreads();
+    const u64 n = seg_off[s + 1] - seg_off[s];
+    const u64 at = (u64(p) * segs + s) * RADIX;
+    const u64 total = hist[at + d];
+    if(total == n) s_skip = 1;
+    u64 inc = total;
+    for(int o = 1; o < 32; o <<= 1)
+    {
+        const u64 t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if(int(lane_id()) >= o) inc += t;
+    }
+    if(lane_id() == 31) warp_tot[d >> 5] = inc;
+    __syncthreads();
+    u64 pre = seg_off[s];
+    for(u32 w = 0; w < (d >> 5); ++w) pre += warp_tot[w];
+    base[at + d] = pre + inc - total;
+    if(d == 0) skip[u64(p) * segs + s] = u32(s_skip);
 }
 
 template <int BLOCK, int ITEMS, typename V, int MATCH_BITS>
@@ -439,9 +552,9 @@ int launch_pass(csa_ctx* ctx, const u64* kin, u64* kout, const V* vin, V* vout, 
 constexpr int FP_BLOCK = 256, FP_ITEMS = 16, FP_TILE = FP_BLOCK * FP_ITEMS;
 constexpr int FP_COPIES = 4;     // counters per digit, taken by lane: a digit that many records share (the low byte of a frequent token id) then serialises a quarter as many lanes of an atomic instruction
 constexpr size_t FP_SMEM = size_t(FP_TILE) * 12 + RADIX * 8 + RADIX * FP_COPIES * 4 + 64;
-__global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const u32* __restrict__ vals_in,
-                                                             u32* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
-                                                             u64* __restrict__ cursor)
+__device__ __forceinline__ void first_pass_tile(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const u32* __restrict__ vals_in,
+                                                u32* __restrict__ vals_out, const u64 tile_first, const u32 valid, const int shift, const u32 dmask,
+                                                u64* __restrict__ cursor)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     u64* const stage_keys = reinterpret_cast<u64*>(smem_raw);
@@ -451,8 +564,6 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
     u32* const warp_tot = cnt + RADIX * FP_COPIES;
     static_assert(FP_BLOCK == RADIX, "one thread per digit");
     const u32 tid = threadIdx.x, copy = tid & (FP_COPIES - 1);
-    const u64 tile_first = u64(blockIdx.x) * FP_TILE;
-    const u32 valid = (n - tile_first < u64(FP_TILE)) ? u32(n - tile_first) : u32(FP_TILE);
     #pragma unroll
     for(int j = 0; j < FP_COPIES; ++j) cnt[tid * FP_COPIES + j] = 0;
     __syncthreads();
@@ -525,6 +636,31 @@ __global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restr
             if(vals_in != nullptr) vals_out[dst] = stage_vals[j];
         }
     }
+}
+
+__global__ void __launch_bounds__(FP_BLOCK) first_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const u32* __restrict__ vals_in,
+                                                             u32* __restrict__ vals_out, const u64 n, const int shift, const u32 dmask,
+                                                             u64* __restrict__ cursor)
+{
+    const u64 tile_first = u64(blockIdx.x) * FP_TILE;
+    const u32 valid = (n - tile_first < u64(FP_TILE)) ? u32(n - tile_first) : u32(FP_TILE);
+    first_pass_tile(keys_in, keys_out, vals_in, vals_out, tile_first, valid, shift, dmask, cursor);
+}
+
+// The same over many segments in one launch: a block's tile lies inside one segment and uses that segment's cursors
+// (cursor: [segments][RADIX], each segment's digit offsets in the whole array).
+__global__ void __launch_bounds__(FP_BLOCK) first_pass_seg_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const u32* __restrict__ vals_in,
+                                                                 u32* __restrict__ vals_out, const u64* __restrict__ seg_off, const u32* __restrict__ seg_tile0,
+                                                                 const u32 segs, const int shift, const u32 dmask, u64* __restrict__ cursor)
+{
+    __shared__ u32 s_seg;
+    if(threadIdx.x == 0) s_seg = segment_of_tile(seg_tile0, segs, blockIdx.x);
+    __syncthreads();
+    const u32 s = s_seg;
+    const u64 tile_first = seg_off[s] + u64(blockIdx.x - __ldg(seg_tile0 + s)) * FP_TILE, seg_end = seg_off[s + 1];
+    if(tile_first >= seg_end) return;
+    const u32 valid = (seg_end - tile_first < u64(FP_TILE)) ? u32(seg_end - tile_first) : u32(FP_TILE);
+    first_pass_tile(keys_in, keys_out, vals_in, vals_out, tile_first, valid, shift, dmask, cursor + u64(s) * RADIX);
 }
 
 int launch_first_pass(csa_ctx* ctx, const u64* kin, u64* kout, const u32* vin, u32* vout, u64 n, int shift, u32 dmask, u64* cursor)
@@ -748,6 +884,141 @@ int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, void* vals,
     }
     *in_alt = flips & 1;
     return CSA_OK;
+}
+
+// ---- many segments of one array, sorted in one set of launches ----------------------------------------------------------------
+// Generation 0 of a build sorts every partition on its own; done one partition at a time that is a dozen launches and one
+// read-back per partition. Here all partitions go through each digit pass together: one histogram launch, one launch for the
+// digit offsets, one launch per pass, no read-back. A pass whose digit is constant inside a segment copies that segment's
+// records over unchanged instead of being skipped, so that all segments change buffers together.
+
+namespace
+{
+
+constexpr int SEG_BLOCK = 256, SEG_ITEMS = 24, SEG_MATCH = 3, SEG_TILE = SEG_BLOCK * SEG_ITEMS;
+
+}   // namespace
+
+size_t sort_segments_workspace_bytes(u64 n, u32 segs)
+{
+    const u64 tiles = n / SEG_TILE + segs + 2;
+    return align_up256(tiles * RADIX * 4) + 256                                   // tile counter, then the tile status words
+         + 2 * align_up256(size_t(8) * segs * RADIX * 8)                          // histograms and digit offsets of every pass and segment
+         + align_up256(size_t(8) * segs * 4)                                      // skip flags
+         + align_up256(size_t(segs + 1) * 8) + 2 * align_up256(size_t(segs + 1) * 4) + 4096;
+}
+
+int sort_segments(csa_ctx* ctx, u64* keys, u64* keys_alt, u32* vals, u32* vals_alt, const u64* seg_off_host, u32 segs, int begin_bit, int end_bit, void* workspace,
+                  size_t workspace_bytes, int* in_alt)
+{
+    *in_alt = 0;
+    if(segs == 0 || begin_bit < 0 || end_bit > 64 || begin_bit >= end_bit) return csa_fail(ctx, CSA_E_INVALID, "segmented sort: bad argument");
+    const u64 n = seg_off_host[segs];
+    if(n == 0) return CSA_OK;
+    if(workspace_bytes < sort_segments_workspace_bytes(n, segs)) return csa_fail(ctx, CSA_E_NOMEM, "segmented sort: workspace too small");
+    const int passes = (end_bit - begin_bit + RADIX_BITS - 1) / RADIX_BITS;
+    std::vector<u32> tile0(segs + 1), tile0_fp(segs + 1);
+    u64 t = 0, tf = 0;
+    for(u32 s = 0; s < segs; ++s)
+    {
+        const u64 c = seg_off_host[s + 1] - seg_off_host[s];
+        if(c >= (u64(1) << 30)) return csa_fail(ctx, CSA_E_LIMIT, "segmented sort: a segment holds 2^30 records or more");
+        tile0[s] = u32(t); tile0_fp[s] = u32(tf);
+        t += div_up(c, SEG_TILE); tf += div_up(c, FP_TILE);
+    }
+    if(t >= (u64(1) << 31) || tf >= (u64(1) << 31)) return csa_fail(ctx, CSA_E_LIMIT, "segmented sort: too many tiles");
+    tile0[segs] = u32(t); tile0_fp[segs] = u32(tf);
+
+    Carver cv(workspace, workspace_bytes);
+    u32* counter = cv.take<u32>(64);
+    u32* status = cv.take<u32>((t + 1) * RADIX);
+    u64* hist = cv.take<u64>(u64(8) * segs * RADIX);
+    u64* base = cv.take<u64>(u64(8) * segs * RADIX);
+    u32* skip = cv.take<u32>(u64(8) * segs);
+    u64* seg_off = cv.take<u64>(segs + 1);
+    u32* seg_tile0 = cv.take<u32>(segs + 1);
+    u32* seg_tile0_fp = cv.take<u32>(segs + 1);
+    if(!cv.ok || reinterpret_cast<unsigned char*>(counter) + 256 != reinterpret_cast<unsigned char*>(status)) return csa_fail(ctx, CSA_E_NOMEM, "segmented sort: workspace too small");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    // the tables go up from pageable memory: the copies are done when the calls return
+    CSA_CUDA(ctx, cudaMemcpyAsync(seg_off, seg_off_host, size_t(segs + 1) * 8, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaMemcpyAsync(seg_tile0, tile0.data(), size_t(segs + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaMemcpyAsync(seg_tile0_fp, tile0_fp.data(), size_t(segs + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CSA_CUDA(ctx, cudaMemsetAsync(hist, 0, u64(passes) * segs * RADIX * 8, ctx->stream));
+
+    using S = Pass_Smem<SEG_BLOCK, SEG_ITEMS, u32>;
+    auto pass_kern = onesweep_seg_pass_kernel<SEG_BLOCK, SEG_ITEMS, u32, SEG_MATCH>;
+    {
+        static std::atomic<bool> configured[64];
+        if(!configured[ctx->device & 63])
+        {
+            CSA_CUDA(ctx, cudaFuncSetAttribute(pass_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::bytes)));
+            CSA_CUDA(ctx, cudaFuncSetAttribute(seg_histogram_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8 * RADIX * 4));
+            CSA_CUDA(ctx, cudaFuncSetAttribute(first_pass_seg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(FP_SMEM)));
+            configured[ctx->device & 63] = true;
+        }
+    }
+    // blocks per segment of the histogram: enough to fill the device over all segments
+    const unsigned hx = unsigned(std::max<u64>(1, std::min<u64>(148 * 4 / segs + 1, div_up(n / segs + 1, 2 * 256 * HIST_UNROLL))));
+    seg_histogram_kernel<256><<<dim3(hx, segs), 256, size_t(8) * passes * RADIX * 4, ctx->stream>>>(keys, seg_off, segs, begin_bit, end_bit, passes, hist);
+    CSA_LAUNCH_CHECK(ctx);
+    seg_digit_base_kernel<<<dim3(passes, segs), RADIX, 0, ctx->stream>>>(hist, seg_off, segs, base, skip);
+    CSA_LAUNCH_CHECK(ctx);
+
+    Pass_Timer& timer = timer_of(ctx);
+    u64* kin = keys; u64* kout = keys_alt;
+    u32* vin = vals; u32* vout = vals_alt;
+    for(int p = 0; p < passes; ++p)
+    {
+        const int shift = begin_bit + p * RADIX_BITS;
+        const u32 dmask = digit_mask(shift, end_bit);
+        const bool unordered = p == 0 && ctx->ties_in_any_order;
+        if(unordered)
+        {
+            first_pass_seg_kernel<<<unsigned(tf), FP_BLOCK, FP_SMEM, ctx->stream>>>(kin, kout, vin, vout, seg_off, seg_tile0_fp, segs, shift, dmask, base);
+            CSA_LAUNCH_CHECK(ctx);
+        }
+        else
+        {
+            cudaEvent_t e0 = nullptr, e1 = nullptr;
+            if(timer.on)
+            {
+                CSA_CUDA(ctx, cudaEventCreate(&e0));
+                CSA_CUDA(ctx, cudaEventCreate(&e1));
+                CSA_CUDA(ctx, cudaEventRecord(e0, ctx->stream));
+            }
+            CSA_CUDA(ctx, cudaMemsetAsync(counter, 0, 256 + t * RADIX * sizeof(u32), ctx->stream));
+            pass_kern<<<unsigned(t), SEG_BLOCK, S::bytes, ctx->stream>>>(kin, kout, vin, vout, seg_off, seg_tile0, segs, shift, dmask, base + u64(p) * segs * RADIX,
+                                                                        skip + u64(p) * segs, status, counter, ctx->d_status);
+            CSA_LAUNCH_CHECK(ctx);
+            if(timer.on)
+            {
+                CSA_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
+                timer.ev.push_back(e0); timer.ev.push_back(e1);
+                timer.passes++; timer.records += n; timer.bytes += 2 * n * (8 + (vin ? 4 : 0));
+            }
+        }
+        ctx->counters[1]++;
+        ctx->counters[2] += n;
+        u64* tk = kin; kin = kout; kout = tk;
+        u32* tv = vin; vin = vout; vout = tv;
+    }
+    *in_alt = passes & 1;
+    return CSA_OK;
+}
+
+extern "C" size_t csa_sort_segments_workspace_bytes(uint64_t n, uint32_t segments) { return sort_segments_workspace_bytes(n, segments ? segments : 1); }
+
+extern "C" int csa_sort_segments(csa_ctx* ctx, uint64_t* keys, uint64_t* keys_alt, uint32_t* vals, uint32_t* vals_alt, const uint64_t* seg_off_host, uint32_t segments,
+                                 int begin_bit, int end_bit, void* workspace, size_t workspace_bytes, int* in_alt)
+{
+    if(!ctx || !in_alt || !keys || !keys_alt || !seg_off_host || !workspace || ((vals == nullptr) != (vals_alt == nullptr)))
+        return csa_fail(ctx, CSA_E_INVALID, "csa_sort_segments: null argument");
+    for(uint32_t s = 0; s < segments; ++s)
+        if(seg_off_host[s + 1] < seg_off_host[s]) return csa_fail(ctx, CSA_E_INVALID, "csa_sort_segments: offsets must not decrease");
+    if(segments && seg_off_host[0] != 0) return csa_fail(ctx, CSA_E_INVALID, "csa_sort_segments: the first segment starts at record 0");
+    return sort_segments(ctx, reinterpret_cast<u64*>(keys), reinterpret_cast<u64*>(keys_alt), vals, vals_alt, reinterpret_cast<const u64*>(seg_off_host), segments,
+                         begin_bit, end_bit, workspace, workspace_bytes, in_alt);
 }
 
 // ---- the sort for callers that must not allocate ---------------------------------------------------------------------

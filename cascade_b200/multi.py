@@ -155,7 +155,8 @@ def group_partitions_into_parts(sizes, part_suffixes):
     return part_of_pid, part_off
 
 
-def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 << 27, workers=3, host=None, window_bytes=8 << 30):
+def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 << 27, workers=3, host=None, window_bytes=8 << 30,
+                            list_budget_bytes=None):
     """The part-at-a-time build over the GPUs of a process group (one process per GPU; also works alone), written on the
     library's part jobs: every rank holds the whole text and a replica of the rank store on its device, owns the parts u with
     u mod world == rank, keeps their suffix lists (5-byte lanes + 4-byte ranks) in its own pinned host memory and streams them
@@ -164,7 +165,11 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
     generation every rank's outbox is all-gathered (NCCL over NVLink) and applied to every replica.
     Returns (segments, info): segments = [(first global rank, count, pinned uint8 tensor of 5 * count bytes)] for the
     rank's parts in the order of their ranks, info = timings and counts. `host` may be a dict that keeps the pinned list
-    buffers between calls (pinning gigabytes takes seconds)."""
+    buffers between calls (pinning gigabytes takes seconds).
+    Residency of the lists (the reference plans its tiers likewise, src/Residency_Plan.cpp): a part's list stays in device
+    memory while the device has room for it (list_budget_bytes, or what is free after the text, the rank store, the job
+    workspaces and the largest outboxes), and lives in pinned host memory otherwise; list_budget_bytes = 0 keeps every list on
+    the host. The final order always lands in the pinned host segments."""
     import threading
     import time
     from ._lib import Part, PartResult, c_u64, c_vp
@@ -291,14 +296,36 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
                 print(f"[csa multi {rank}/{world}] {job.__name__}: {len(job_s)} jobs, in the call {1e3 * sum(a for a, _ in job_s) / len(job_s):.1f} ms, "
                       f"waiting for the lists to be out {1e3 * sum(b for _, b in job_s) / len(job_s):.1f} ms on average", flush=True)
 
+        # which lists stay on the device
+        largest = max([size[u] for u in own], default=1)
+        if list_budget_bytes is None:
+            free_b, _ = torch.cuda.mem_get_info(dev)
+            reserve = 3 * int(L.csa_part_workspace_bytes(largest)) + window_bytes + 2 * 9 * int(0.7 * n) + (6 << 30)
+            budget = max(0, free_b - reserve)
+        else:
+            budget = int(list_budget_bytes)
+        res_first, used = {}, 0
+        for u in own:
+            if 9 * (used + size[u]) + 256 <= budget:
+                res_first[u] = used
+                used += size[u]
+        dev_lanes = torch.empty(5 * used + 64, dtype=torch.uint8, device=dev)
+        dev_ranks = torch.empty(used + 16, dtype=torch.int32, device=dev)
+        info["lists_on_device"] = len(res_first)
+        info["lists_on_host"] = len(own) - len(res_first)
+
+        def host_segment(u):
+            return lanes_h.data_ptr() + 5 * own_first[u]
+
         def lists(u):
-            return lanes_h.data_ptr() + 5 * own_first[u], ranks_h.data_ptr() + 4 * own_first[u]
+            if u in res_first:
+                return dev_lanes.data_ptr() + 5 * res_first[u], dev_ranks.data_ptr() + 4 * res_first[u]
+            return host_segment(u), ranks_h.data_ptr() + 4 * own_first[u]
 
         # ---- generation 0, a window of parts at a time: the window's lanes are picked out of the partition ids into a device
         # buffer (one sweep over the ids per window; the parts' sizes are known, so every lane has its place), and the parts are
         # ranked from there; only their ranked lists travel to the host.
         t0 = time.perf_counter()
-        largest = max([size[u] for u in own], default=1)
         window = max(1, min(len(own), int(window_bytes // (5 * largest + 64)))) if own else 1
         win_buf = torch.empty(5 * sum(sorted((size[u] for u in own), reverse=True)[:window]) + 256, dtype=torch.uint8, device=dev)
         first_d = torch.empty(parts, dtype=torch.int64, device=dev)
@@ -396,9 +423,10 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
 
         def order(c, u):
             lp, rp = lists(u)
-            c.check(L.csa_rank_order(c.h, lp, rp, size[u], lp))
+            c.check(L.csa_rank_order(c.h, lp, rp, size[u], host_segment(u)))
         over_parts(own, order)
         mark("output", t0)
+        del dev_lanes, dev_ranks
     finally:
         for c in ctxs[1:]:
             c.close()

@@ -74,6 +74,15 @@ size_t csa_sort_workspace_bytes(uint64_t n);
 int csa_sort_pairs(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, void* vals_dev, void* vals_alt_dev,
                    uint32_t val_bytes, uint64_t n, int begin_bit, int end_bit, void* workspace_dev, size_t workspace_bytes,
                    int* in_alt);
+/* Many segments of one record array, each sorted on its own (stable, 32-bit values or none), in one set of launches and
+ * without a read-back: segment s holds the records [seg_off_host[s], seg_off_host[s + 1]) (seg_off_host[0] = 0, fewer than 2^30
+ * records per segment). Every pass runs (a pass whose digit is constant inside a segment copies that segment over), so
+ * *in_alt = number of passes & 1. This is how a build's generation 0 sorts all its partitions at once; it stands where the
+ * reference sorts partition after partition (src/GPU_SACA.cu:1175, 1203). */
+size_t csa_sort_segments_workspace_bytes(uint64_t n, uint32_t segments);
+int csa_sort_segments(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, uint32_t* vals_dev, uint32_t* vals_alt_dev,
+                      const uint64_t* seg_off_host, uint32_t segments, int begin_bit, int end_bit, void* workspace_dev,
+                      size_t workspace_bytes, int* in_alt);
 /* Most records of one csa_sort_pairs_static call. */
 #define CSA_STATIC_SORT_MAX_RECORDS (1ull << 22)
 /* The same sort for callers that cannot allocate device memory (no counterpart in the reference). It takes no context
@@ -220,7 +229,7 @@ int csa_store_apply_messages(csa_ctx* ctx, csa_store* store, const uint32_t* pos
 int csa_part_sizes(csa_ctx* ctx, csa_store* store, uint64_t first, uint64_t count, uint32_t parts, uint64_t* hist_dev);
 int csa_scatter_lanes(csa_ctx* ctx, csa_store* store, uint64_t first, uint64_t count, const uint64_t* part_first_dev,
                       uint64_t* cursor_dev, uint8_t* lanes_dev);
-/* Device bytes of ctx's scratch that a part job of `count` suffixes takes (about 55 bytes per suffix). */
+/* Device bytes of ctx's scratch that a part job of `count` suffixes takes (about 63 bytes per suffix). */
 size_t csa_part_workspace_bytes(uint64_t count);
 /* Generation 0 of one part: sorts its suffixes by their first 3 symbols and the part of the suffix that follows those,
  * ranks them (rank = index of the group's first suffix in the sorted part), writes every rank into the store and returns

@@ -188,7 +188,10 @@ def _streamed_worker(rank, world, port, n, p, part_suffixes, q):
     torch.cuda.set_device(dev)
     ctx = api.Context(dev)
     T = api.gen_corpus_device(ctx, n, 11, 256)
-    segs, info = multi.build_sa_streamed_multi(ctx, T, n, p, part_suffixes=part_suffixes, workers=2)
+    # where the parts' lists live: wherever the device has room (one rank), all in host memory (two), some of each (three)
+    budget = {1: None, 2: 0, 3: 9 * 130_000}[world]
+    segs, info = multi.build_sa_streamed_multi(ctx, T, n, p, part_suffixes=part_suffixes, workers=2, list_budget_bytes=budget)
+    assert (info["lists_on_host"] == 0) if world == 1 else (info["lists_on_device"] == 0) if world == 2 else (info["lists_on_device"] > 0 and info["lists_on_host"] > 0)
     ref = None
     if rank == 0:
         r, _ = api.build_sa(ctx, T, n, 16)
