@@ -299,6 +299,7 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
         # which lists stay on the device
         largest = max([size[u] for u in own], default=1)
         if list_budget_bytes is None:
+            torch.cuda.empty_cache()                # what an earlier build left in the allocator's cache counts as free
             free_b, _ = torch.cuda.mem_get_info(dev)
             reserve = 3 * int(L.csa_part_workspace_bytes(largest)) + window_bytes + 2 * 9 * int(0.7 * n) + (6 << 30)
             budget = max(0, free_b - reserve)
@@ -311,6 +312,7 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
                 used += size[u]
         dev_lanes = torch.empty(5 * used + 64, dtype=torch.uint8, device=dev)
         dev_ranks = torch.empty(used + 16, dtype=torch.int32, device=dev)
+        info["list_budget_bytes"] = int(budget)
         info["lists_on_device"] = len(res_first)
         info["lists_on_host"] = len(own) - len(res_first)
 
