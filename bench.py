@@ -568,13 +568,16 @@ def run_ours_multi(args):
         sd = torch.from_numpy(objs[1].view(np.int16)).to(dev)
         for _ in range(2):
             itv = sh.find(od, sd, q)
+            pos, poff, cnt = sh.locate_packed(itv, q, 100)
+        del pos, poff, cnt
         dist.barrier(); torch.cuda.synchronize()
         t0 = time.perf_counter()
         itv = sh.find(od, sd, q)
-        rows, cnt = sh.locate(itv, q, 100)
+        pos, poff, cnt = sh.locate_packed(itv, q, 100)
         torch.cuda.synchronize()
         dq = _max_over_ranks(time.perf_counter() - t0, dev)
-        query = {"value": q / dq, "unit": f"queries/s (count + locate <= 100, suffix array sharded by range over {world} GPUs, text replicated)",
+        query = {"value": q / dq, "unit": f"queries/s (count + locate <= 100 into packed positions, suffix array sharded by range over {world} GPUs, text replicated; each shard answers at once the "
+                                           f"patterns outside its range, one all-reduce of the intervals and one of the packed positions)",
                  "queries": q, "counts_hash": f"{api.counts_hash(itv.cpu().numpy().view(np.uint64)):016x}", "positions": int(cnt.sum().item())}
     launches_all = _sum_over_ranks(launches, dev)
     peer_all = _sum_over_ranks(peer, dev)

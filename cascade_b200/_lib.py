@@ -97,6 +97,7 @@ _SIGS = {
     "csa_table_build": (c_int, [c_vp, c_vp, c_u64, c_vp, c_u64, c_vp]),
     "csa_table_build_slice": (c_int, [c_vp, c_vp, c_u64, c_vp, c_u64, c_u64, c_vp]),
     "csa_locate_window": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp]),
+    "csa_locate_window_packed": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp, c_vp, c_vp, c_vp]),
     "csa_find": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp]),
     "csa_locate": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_u64, c_u32, c_vp, c_vp]),
     "csa_certify": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_vp, c_vp]),

@@ -80,7 +80,8 @@ Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
     L.head = align_up256(cap * 4);
     L.isa = align_up256(shard * 4 + 64);
     L.sa = align_up256(cap * 4 + 64);
-    L.sort_ws = align_up256(csa_sort_workspace_bytes(cap > shard ? cap : shard));
+    const size_t one = csa_sort_workspace_bytes(cap > shard ? cap : shard), many = sort_segments_workspace_bytes(cap, p);
+    L.sort_ws = align_up256(one > many ? one : many);
     L.scratch = align_up256(div_up(cap, RANK_TILE) * 3 * 4 + 256);
     L.pid = 0;
     L.small = align_up256(size_t(p) * 8) * 5 + align_up256(size_t(2) * p * 8) + 4096;
@@ -94,7 +95,7 @@ Multi_Layout multi_layout(u64 n_local, u64 shard, u32 p)
 struct Peer_Info
 {
     unsigned char handle[64];
-    u64 off_isa, off_sa, off_xin, off_resp, arena_bytes;
+    u64 off_isa, off_sa, off_xin, off_resp, off_keys, arena_bytes;
     u64 process, arena_address;     // ranks that are threads of one process reach one another's arenas directly
     int device;
 };
@@ -323,6 +324,7 @@ int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const
     mine.off_sa = reinterpret_cast<u8*>(sa) - static_cast<u8*>(ctx->arena);
     mine.off_xin = xin - static_cast<u8*>(ctx->arena);
     mine.off_resp = reinterpret_cast<u8*>(resp_in) - static_cast<u8*>(ctx->arena);
+    mine.off_keys = reinterpret_cast<u8*>(keysA) - static_cast<u8*>(ctx->arena);
     mine.arena_bytes = ctx->arena_bytes;
     mine.process = u64(getpid());
     mine.arena_address = reinterpret_cast<u64>(ctx->arena);
@@ -490,6 +492,7 @@ int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const
 
     // ---- partition ids of this rank's positions, then the scatter to the partitions' owners ------------------------
     u64 peer_bytes = 0;
+    const bool keys_travel = p_eff <= 256;
     {
         // Positions are first grouped by partition in a local buffer (one run per partition), then every run crosses to the
         // partition's owner as one contiguous copy: long coalesced transfers instead of scattered peer stores.
@@ -497,18 +500,35 @@ int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const
         std::vector<u32*> bases(p_eff);
         std::vector<u64> local_off(p_eff + 1, 0);
         for(u32 q = 0; q < p_eff; ++q) { local_off[q + 1] = local_off[q] + hist_all[size_t(me) * p_eff + q]; bases[q] = local + local_off[q]; }
-        CSA_CUDA(ctx, cudaMemcpyAsync(part_base, bases.data(), size_t(p_eff) * sizeof(u32*), cudaMemcpyHostToDevice, ctx->stream));
         CSA_CUDA(ctx, cudaMemsetAsync(cursor, 0, size_t(p_eff) * 8, ctx->stream));
-        if(my_count) CSA_TRY(csa_scatter_by_pid(ctx, pid, my_first, my_count, p_eff, part_base, reinterpret_cast<uint64_t*>(cursor)));
+        u64* const local_keys = reinterpret_cast<u64*>(xin);       // the inbox is idle until the first rank exchange
+        if(keys_travel)
+        {
+            // The rank that scans a stretch of the text packs every suffix's generation-0 key from the text window it has in
+            // shared memory anyway; (position, key) cross together, and the owner never reads the text at random.
+            CSA_CUDA(ctx, cudaMemcpyAsync(hist, local_off.data(), size_t(p_eff) * 8, cudaMemcpyHostToDevice, ctx->stream));
+            if(my_count) CSA_TRY(launch_scatter_with_keys(ctx, T, n + CSA_TEXT_PAD, pid, my_first, my_count, p_eff, hist, cursor, local, local_keys));
+        }
+        else
+        {
+            CSA_CUDA(ctx, cudaMemcpyAsync(part_base, bases.data(), size_t(p_eff) * sizeof(u32*), cudaMemcpyHostToDevice, ctx->stream));
+            if(my_count) CSA_TRY(csa_scatter_by_pid(ctx, pid, my_first, my_count, p_eff, part_base, reinterpret_cast<uint64_t*>(cursor)));
+        }
         for(u32 k = 0; k < p_eff; ++k)
         {
             const u32 q = (k + me) % p_eff;     // every rank starts with another partition, so the copies of one moment go to different GPUs
             const u64 c = hist_all[size_t(me) * p_eff + q];
             if(c == 0) continue;
             const u32 o = owner[q];
-            u32* dst = reinterpret_cast<u32*>(peer_arena[o] + peers[o].off_sa) + local_first[q] + cursor_all[size_t(me) * p_eff + q];
+            const u64 slot = local_first[q] + cursor_all[size_t(me) * p_eff + q];
+            u32* dst = reinterpret_cast<u32*>(peer_arena[o] + peers[o].off_sa) + slot;
             CSA_CUDA(ctx, cudaMemcpyAsync(dst, local + local_off[q], c * 4, cudaMemcpyDefault, ctx->stream));
-            if(o != me) peer_bytes += c * 4;
+            if(keys_travel)
+            {
+                u64* kdst = reinterpret_cast<u64*>(peer_arena[o] + peers[o].off_keys) + slot;
+                CSA_CUDA(ctx, cudaMemcpyAsync(kdst, local_keys + local_off[q], c * 8, cudaMemcpyDefault, ctx->stream));
+            }
+            if(o != me) peer_bytes += c * (keys_travel ? 12 : 4);
         }
         CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
@@ -526,17 +546,35 @@ int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const
         CSA_CUDA(ctx, cudaMemcpyAsync(seg_delta_dev, seg_delta.data(), seg_delta.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
     }
     const Slot_Map slot_map{seg_first_dev, seg_delta_dev, u32(seg_delta.size()), 0};
+    // This rank's partitions are sorted together (one launch per digit pass, no read-back) and then ranked one by one: they are
+    // not neighbours in the suffix array, so a group of equal keys must not run across the border of two of them.
+    std::vector<u64> seg_off_local;
+    for(u32 q = 0; q < p_eff; ++q) if(owner[q] == me) seg_off_local.push_back(local_first[q]);
+    seg_off_local.push_back(n_local);
+    const bool together = max_part < (u64(1) << 30) && n_local > 0;
+    int all_in_alt = 0;
+    if(together)
+    {
+        if(!keys_travel) CSA_TRY(launch_keys_gen0(ctx, T, sa, n_local, keysA));
+        CSA_TRY(sort_segments(ctx, keysA, keysB, sa, posB, seg_off_local.data(), u32(seg_off_local.size() - 1), 0, 64, sort_ws, L.sort_ws, &all_in_alt));
+    }
     for(u32 q = 0; q < p_eff; ++q)
     {
         if(owner[q] != me) continue;
         const u64 S = part_off[q + 1] - part_off[q], first = local_first[q];
         if(S == 0) continue;
-        CSA_TRY(launch_keys_gen0(ctx, T, sa + first, S, keysA));
-        int in_alt = 0;
-        CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(keysA), reinterpret_cast<uint64_t*>(keysB), sa + first, posB, 4, S, 0, 64, sort_ws,
-                               L.sort_ws, &in_alt));
-        const u64* ks = in_alt ? keysB : keysA;
-        const u32* ps = in_alt ? posB : sa + first;
+        const u64* ks; const u32* ps;
+        if(together) { ks = (all_in_alt ? keysB : keysA) + first; ps = (all_in_alt ? posB : sa) + first; }
+        else
+        {
+            u64* const kq = keys_travel ? keysA + first : keysA;
+            if(!keys_travel) CSA_TRY(launch_keys_gen0(ctx, T, sa + first, S, kq));
+            int in_alt = 0;
+            CSA_TRY(csa_sort_pairs(ctx, reinterpret_cast<uint64_t*>(kq), reinterpret_cast<uint64_t*>(keysB), sa + first, posB, 4, S, 0, 64, sort_ws,
+                                   L.sort_ws, &in_alt));
+            ks = in_alt ? keysB : kq;
+            ps = in_alt ? posB : sa + first;
+        }
         CSA_TRY(launch_rank_and_compact(ctx, ks, ps, S, 64, u32(first), iv, Slot_Map{nullptr, nullptr, 0, part_off[q] - first}, sa, head, posA, act_count, scratch, G > 1 ? upd + first : nullptr));
     }
     lap("generation 0 sorts + ranks");

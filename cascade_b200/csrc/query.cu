@@ -143,6 +143,14 @@ __global__ void find_kernel(const csa_index idx, const u64* __restrict__ off, co
     const u64 m = off[i + 1] - off[i];
     const u16* const P = sym + (off[i] - off[0]);
     if(m == 0) { itv[2 * i] = 0; itv[2 * i + 1] = idx.sa_entries ? idx.sa_entries : idx.n; return; }
+    if(idx.sa_entries != 0 && idx.sa_entries < idx.n)
+    {
+        // One slice of a sharded array: most patterns lie wholly before or wholly after it, which its first and last suffix
+        // tell with two comparisons; only a pattern that falls inside the slice's range is searched for.
+        const u64 e = idx.sa_entries;
+        if(cmp_suffix_pattern(idx.text, idx.n, sa40_load(idx.sa40, 0), P, m) > 0) { itv[2 * i] = 0; itv[2 * i + 1] = 0; return; }
+        if(cmp_suffix_pattern(idx.text, idx.n, sa40_load(idx.sa40, e - 1), P, m) < 0) { itv[2 * i] = e; itv[2 * i + 1] = e; return; }
+    }
     const Brackets br = table_brackets(idx, P, m);
     u64 lo, hi;
     search_brackets(idx, br, P, m, idx.sa40, idx.sa40, lo, hi);
@@ -248,6 +256,25 @@ __global__ void locate_window_kernel(const u8* __restrict__ sa40, const u64 sa_f
     {
         const u64 r = lo + k;
         if(r >= sa_first && r < sa_first + sa_entries) pos[w * max_pos + k] = sa40_load(sa40, r - sa_first);
+    }
+}
+
+// Sharded locate into ONE packed array: the entries of a global interval's first max_pos ranks that fall into this slice go to
+// pos[pos_off[i] + k] (rank lo + k); the other entries are left as they are, so packed arrays that all shards write into, starting
+// from zeros, add up to the packed positions of the whole index.
+__global__ void locate_window_packed_kernel(const u8* __restrict__ sa40, const u64 sa_first, const u64 sa_entries, const u64* __restrict__ itv, const u64 q,
+                                            const u32 max_pos, const u64* __restrict__ pos_off, u64* __restrict__ pos)
+{
+    const u64 w = (u64(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if(w >= q) return;
+    const u64 lo = itv[2 * w], hi = itv[2 * w + 1];
+    const u64 c = (hi - lo < max_pos) ? hi - lo : max_pos;
+    if(c == 0 || lo + c <= sa_first || lo >= sa_first + sa_entries) return;
+    const u64 o = pos_off[w];
+    for(u64 k = lane_id(); k < c; k += 32)
+    {
+        const u64 r = lo + k;
+        if(r >= sa_first && r < sa_first + sa_entries) pos[o + k] = sa40_load(sa40, r - sa_first);
     }
 }
 
@@ -402,6 +429,25 @@ extern "C" int csa_locate_window(csa_ctx* ctx, const csa_index* index, const uin
     const u64 ne = index->sa_entries ? index->sa_entries : index->n;
     locate_window_kernel<<<unsigned(div_up(q * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, index->sa_first, ne, reinterpret_cast<const u64*>(itv), q, max_pos,
                                                                                  reinterpret_cast<u64*>(pos));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_locate_window_packed(csa_ctx* ctx, const csa_index* index, const uint64_t* itv, uint64_t q, uint32_t max_pos, uint32_t* cnt, uint64_t* pos_off,
+                                        uint64_t* pos, uint64_t* total)
+{
+    CSA_TRY(check_index(ctx, index));
+    if(q == 0) return CSA_OK;
+    if(!itv || !cnt || !pos_off || !pos || !total || max_pos == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_locate_window_packed: bad argument");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* ws = nullptr;
+    CSA_TRY(csa_aux(ctx, align_up256((div_up(q, SCAN_TILE) + 1) * 8), &ws));
+    counts_kernel<<<unsigned(div_up(q, 256)), 256, 0, ctx->stream>>>(reinterpret_cast<const u64*>(itv), q, max_pos, cnt);
+    CSA_LAUNCH_CHECK(ctx);
+    CSA_TRY(exclusive_sum(ctx, cnt, q, reinterpret_cast<u64*>(pos_off), static_cast<u64*>(ws), reinterpret_cast<u64*>(total)));
+    const u64 ne = index->sa_entries ? index->sa_entries : index->n;
+    locate_window_packed_kernel<<<unsigned(div_up(q * 32, 256)), 256, 0, ctx->stream>>>(index->sa40, index->sa_first, ne, reinterpret_cast<const u64*>(itv), q, max_pos,
+                                                                                        reinterpret_cast<const u64*>(pos_off), reinterpret_cast<u64*>(pos));
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }

@@ -118,6 +118,30 @@ class ShardedIndex:
         return rows.view(q, max_pos), cnt
 
 
+def _locate_packed(self, itv_global_dev, q, max_pos=100, reduce=True):
+    """Packed positions of global intervals: (pos, pos_off, cnt) with query i's positions at pos[pos_off[i]:pos_off[i + 1]], in
+    rank order. Every shard fills in the entries whose ranks it holds; one all-reduce of the packed array (a ninth of the
+    q x max_pos rows on the benchmark's queries) puts them together."""
+    dev = itv_global_dev.device
+    cnt_t = torch.clamp(itv_global_dev[1::2] - itv_global_dev[0::2], max=max_pos)
+    total = int(cnt_t.sum().item())
+    pos = torch.zeros(max(1, total), dtype=torch.int64, device=dev)
+    cnt = torch.empty(q, dtype=torch.int32, device=dev)
+    poff = torch.empty(q + 1, dtype=torch.int64, device=dev)
+    tot = torch.zeros(1, dtype=torch.int64, device=dev)
+    loc = self.local
+    torch.cuda.synchronize(dev)
+    loc.ctx.check(loc.ctx.L.csa_locate_window_packed(loc.ctx.h, ctypes.byref(loc.c), itv_global_dev.data_ptr(), q, max_pos, cnt.data_ptr(), poff.data_ptr(),
+                                                     pos.data_ptr(), tot.data_ptr()))
+    loc.ctx.sync()
+    if reduce and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(pos, op=dist.ReduceOp.SUM)
+    return pos[:total], poff, cnt
+
+
+ShardedIndex.locate_packed = _locate_packed
+
+
 def upload_text_sharded(text_host, text_dev, scratch=None):
     """Fills this rank's device copy of the text from host memory with every rank copying only its own 1/world share over
     PCIe; the shares then meet by one all-gather over NVLink (NCCL). text_host: pinned uint16 tensor, text_dev: device uint16

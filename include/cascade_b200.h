@@ -354,6 +354,13 @@ int csa_table_build_slice(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, co
                           uint64_t stride, uint64_t* table_dev);
 int csa_locate_window(csa_ctx* ctx, const csa_index* index, const uint64_t* itv_global_dev, uint64_t q, uint32_t max_pos,
                       uint64_t* pos_dev);
+/* The same into one packed array, which is what should cross between GPUs (the rows are mostly empty): cnt_dev[i] =
+ * min(max_pos, hi - lo), pos_off_dev[q + 1] = their exclusive sums (the same on every shard, being made from the global
+ * intervals), *total_dev = their sum; this slice's share of query i's positions goes to pos_dev[pos_off[i] + k]. pos_dev must
+ * hold the total (at most q max_pos words) and be zero before the first shard writes. csa_find on a slice first compares the
+ * pattern with the slice's first and last suffix and answers at once when the pattern lies outside the slice's range. */
+int csa_locate_window_packed(csa_ctx* ctx, const csa_index* index, const uint64_t* itv_global_dev, uint64_t q, uint32_t max_pos,
+                             uint32_t* cnt_dev, uint64_t* pos_off_dev, uint64_t* pos_dev, uint64_t* total_dev);
 /* Interval certificate of ref::certify (include/CPU_Reference.hpp:79-101) for every query: result_dev[0] = number
  * of failing queries, result_dev[1] = first failing query (or ~0). Replaces certify_kernel (src/Query_Engine.cu:665-686). */
 int csa_certify(csa_ctx* ctx, const csa_index* index, const uint64_t* off_dev, const uint16_t* sym_dev, uint64_t q,

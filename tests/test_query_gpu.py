@@ -178,6 +178,16 @@ def test_index_sharded_by_suffix_array_range(ctx, oracle):
         shards.append(sh)
         total += sh.find(o, s_, 600, reduce=False)
     assert np.array_equal(total.cpu().numpy().view(np.uint64), want)
+    # the packed form: every shard adds its entries to one packed array (here one after another into the same array)
+    packed = None
+    for sh in shards:
+        pos, poff, cnt = sh.locate_packed(total, 600, 100, reduce=False)
+        packed = pos.clone() if packed is None else packed + pos
+    wp0, wc0 = oracle.locate_batch(sa, want, 100)
+    pk, po = packed.cpu().numpy().view(np.uint64), poff.cpu().numpy()
+    assert np.array_equal(cnt.cpu().numpy().view(np.uint32), wc0) and int(po[-1]) == int(wc0.sum())
+    for i in range(600):
+        assert np.array_equal(pk[int(po[i]):int(po[i + 1])], wp0[i, :wc0[i]]), i
     rows = torch.zeros(600 * 100, dtype=torch.int64, device="cuda")
     for sh in shards:
         sh.local.locate_window(total, 600, 100, rows)

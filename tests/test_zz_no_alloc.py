@@ -50,6 +50,31 @@ def test_static_sort_matches_the_workspace_sort_twice_in_a_row():
         ctx.close()
 
 
+def test_static_sort_edges_against_a_comparison_sort():
+    """The sizes around a tile and at the limit, a list that starts on an odd 8-byte boundary, a caller's own stream; checked
+    against a stable comparison sort of the same records, not against the library's other sort."""
+    from cascade_b200._lib import lib
+    L = lib()
+    g = torch.Generator(device="cuda").manual_seed(23)
+    stream = torch.cuda.Stream()
+    for n in (1, 2, 4095, 4096, 4097, 1 << 22):
+        base_k = torch.randint(-(1 << 62), 1 << 62, (n + 1,), device="cuda", dtype=torch.int64, generator=g)
+        base_v = torch.arange(n + 1, device="cuda", dtype=torch.int32)
+        for odd in (0, 1):
+            k, v = base_k[odd:odd + n].clone() if not odd else base_k[1:], base_v[odd:odd + n].clone() if not odd else base_v[1:]
+            if odd:
+                assert k.data_ptr() % 16 == 8
+            k0, v0 = k.clone(), v.clone()
+            ka, va = torch.empty(n + 1, dtype=torch.int64, device="cuda")[odd:odd + n], torch.empty(n + 1, dtype=torch.int32, device="cuda")[odd:odd + n]
+            torch.cuda.synchronize()
+            in_alt = ctypes.c_int(-1)
+            rc = L.csa_sort_pairs_static(ctypes.c_void_p(stream.cuda_stream), k.data_ptr(), ka.data_ptr(), v.data_ptr(), va.data_ptr(), n, 0, 64, ctypes.byref(in_alt))
+            assert rc == 0, (n, odd, rc)
+            gk, gv = (ka, va) if in_alt.value else (k, v)
+            order = torch.sort(k0 ^ (-(1 << 63)), stable=True).indices
+            assert torch.equal(gk, k0[order]) and torch.equal(gv, v0[order]), (n, odd)
+
+
 def test_static_sort_refuses_more_than_its_fixed_scratch_holds():
     from cascade_b200._lib import lib
     L = lib()
