@@ -34,9 +34,10 @@ C2_PARTITIONS = 64
 C2_MEAN_DOC = 1024
 C3_TOKENS = 1_000_000_000
 C5_QUERIES = 4_000_000
-# DRAM read + write of one launch of the digit-pass kernel over 31.25 M records (the partition size of config 2), taken from
-# an ncu capture of that launch, not measured by the run that prints it; the algorithmic bytes of that launch are 750e6.
-ONESWEEP_TRAFFIC_FROM_PROFILE = 707.9e6
+# DRAM read + write per record of one launch of the digit-pass kernel (24 B algorithmic), from an ncu capture of a launch over
+# 1e8 records (a 1e8-token build); traffic grows with the records of a launch, so the benchmark scales it to its own launch
+# (generation 0 moves all n records per launch). It is a figure from that capture, not measured by the run that prints it.
+ONESWEEP_TRAFFIC_PER_RECORD_FROM_PROFILE = 23.71
 
 
 def measured_peak_gbs():
@@ -226,11 +227,13 @@ def pass_roofline(ctx, peak, peak_kind, step_ms_total, traffic):
     # algorithmic bytes: one read and one write of every record of every pass (12-byte key + position records; 8-byte
     # records in the keys-only passes that order rank updates by address)
     achieved = pb.value / (pm.value * 1e-3) / 1e9 if pm.value > 0 else 0.0
-    r = {"bound": "hbm", "kernel": "onesweep_pass_kernel (one 8-bit digit pass of the LSD radix sort)", "achieved": achieved, "peak": peak,
+    r = {"bound": "hbm", "kernel": "one 8-bit digit pass of the LSD radix sort (onesweep_seg_pass_kernel over all partitions in generation 0, onesweep_pass_kernel "
+                                   "over the tied suffixes later: the same tile code)", "achieved": achieved, "peak": peak,
          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
          "passes": pc.value, "records": pr.value, "pass_ms_total": pm.value}
     if traffic is not None:
-        r["traffic_note"] = "bytes per launch over 31.25 M records (algorithmic: 750e6), from an earlier ncu capture of that launch, not measured by this run"
+        r["traffic_note"] = ("DRAM bytes of one generation-0 launch (all records of the build; algorithmic: 24 B per record), scaled by the records from an ncu "
+                             "capture of the same kernel over 1e8 records (23.71 B per record); not measured by this run")
     if step_ms_total:
         r["share_of_step"] = pm.value / step_ms_total
     return r
@@ -352,7 +355,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         wall_ms = 1e3 * (time.perf_counter() - t0) / args.steps
     ms = sum(step_ms) / len(step_ms)
-    roofline = pass_roofline(ctx, peak, peak_kind, ms * args.steps, ONESWEEP_TRAFFIC_FROM_PROFILE)
+    roofline = pass_roofline(ctx, peak, peak_kind, ms * args.steps, ONESWEEP_TRAFFIC_PER_RECORD_FROM_PROFILE * n)
     validation = api.validate_sa(ctx, T, n, out)         # the whole array, outside the timed region
 
     # ---- end to end through the host-buffer entry point --------------------------------------------------------------
