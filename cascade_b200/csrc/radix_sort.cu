@@ -436,8 +436,8 @@ __device__ __forceinline__ u32 segment_of_tile(const u32* __restrict__ seg_tile0
 
 // One digit pass over MANY segments of one array in one launch: every segment is sorted on its own (its tiles look back no
 // further than its first tile, its records stay inside its range). digit_base: [segments][RADIX] offsets in the whole array;
-// skip: [segments], non-zero where the digit is the same for all of a segment's records: its tiles then copy their records
-// over unchanged, so that all segments change buffers together.
+// skip: [segments], what the segment does in this pass (see seg_plan_kernel): 0 sort; 1 copy its records over unchanged (the
+// digit is the same for all of them), so that all segments change buffers together; 2 nothing.
 template <int BLOCK, int ITEMS, typename V, int MATCH_BITS>
 __global__ void __launch_bounds__(BLOCK) onesweep_seg_pass_kernel(const u64* __restrict__ keys_in, u64* __restrict__ keys_out, const V* __restrict__ vals_in,
                                                                  V* __restrict__ vals_out, const u64* __restrict__ seg_off, const u32* __restrict__ seg_tile0,
@@ -466,7 +466,9 @@ __global__ void __launch_bounds__(BLOCK) onesweep_seg_pass_kernel(const u64* __r
     const u64 tile_base = seg_first + u64(tile - first_tile) * TILE;
     if(tile_base >= seg_end) return;
     const u32 valid = seg_end - tile_base >= u64(TILE) ? u32(TILE) : u32(seg_end - tile_base);
-    if(__ldg(skip + s))
+    const u32 mode = __ldg(skip + s);
+    if(mode == 2) return;
+    if(mode == 1)
     {
         for(u32 i = threadIdx.x; i < valid; i += BLOCK)
         {
@@ -482,6 +484,29 @@ __global__ void __launch_bounds__(BLOCK) onesweep_seg_pass_kernel(const u64* __r
     else
         onesweep_tile<BLOCK, ITEMS, V, MATCH_BITS, false>(keys_in, keys_out, vals_in, vals_out, seg_end, shift, dmask, db, nullptr, status, dev_status, tile, valid,
                                                           first_tile, tile_base);
+}
+
+// What a segment does in each pass of a segmented sort. skip: [passes][segments], 1 where the pass's digit is constant inside
+// the segment; it is rewritten in place as 0 = sort, 1 = copy the records over unchanged, 2 = nothing at all. Two passes
+// in a row that a segment would copy through leave its records in the buffer where they were, so both can do nothing; of a
+// run of such passes only the last one of an odd run copies. first_sorts: pass 0 sorts every segment whatever its flag says
+// (the unordered first pass has no copy-through form).
+__global__ void seg_plan_kernel(u32* __restrict__ skip, const u32 segs, const int passes, const int first_sorts)
+{
+    const u32 s = blockIdx.x * blockDim.x + threadIdx.x;
+    if(s >= segs) return;
+    int p = 0;
+    if(first_sorts && passes > 0) { skip[s] = 0; p = 1; }
+    while(p < passes)
+    {
+        if(skip[u64(p) * segs + s] == 0) { ++p; continue; }
+        int e = p;
+        while(e < passes && skip[u64(e) * segs + s] != 0) ++e;        // the run [p, e) is skipped
+        const int pairs = (e - p) / 2;
+        for(int k = p; k < p + 2 * pairs; ++k) skip[u64(k) * segs + s] = 2;
+        if((e - p) & 1) skip[u64(e - 1) * segs + s] = 1;
+        p = e;
+    }
 }
 
 // Digit offsets and skip flags of a segmented sort. hist: [passes][segments][RADIX]; base likewise, offsets in the whole array;
@@ -964,8 +989,24 @@ int sort_segments(csa_ctx* ctx, u64* keys, u64* keys_alt, u32* vals, u32* vals_a
     CSA_LAUNCH_CHECK(ctx);
     seg_digit_base_kernel<<<dim3(passes, segs), RADIX, 0, ctx->stream>>>(hist, seg_off, segs, base, skip);
     CSA_LAUNCH_CHECK(ctx);
+    seg_plan_kernel<<<unsigned(div_up(segs, 256)), 256, 0, ctx->stream>>>(skip, segs, passes, ctx->ties_in_any_order ? 1 : 0);
+    CSA_LAUNCH_CHECK(ctx);
 
     Pass_Timer& timer = timer_of(ctx);
+    // With pass timing on (the benchmark), the records that each pass really moves are counted: the plan comes back once, which
+    // drains the stream; an untimed sort reads nothing back.
+    std::vector<u64> moved(passes, n);
+    if(timer.on)
+    {
+        std::vector<u32> modes(size_t(passes) * segs);
+        CSA_CUDA(ctx, cudaMemcpyAsync(modes.data(), skip, modes.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        for(int p = 0; p < passes; ++p)
+        {
+            moved[p] = 0;
+            for(u32 sg = 0; sg < segs; ++sg) if(modes[size_t(p) * segs + sg] != 2) moved[p] += seg_off_host[sg + 1] - seg_off_host[sg];
+        }
+    }
     u64* kin = keys; u64* kout = keys_alt;
     u32* vin = vals; u32* vout = vals_alt;
     for(int p = 0; p < passes; ++p)
@@ -995,11 +1036,11 @@ int sort_segments(csa_ctx* ctx, u64* keys, u64* keys_alt, u32* vals, u32* vals_a
             {
                 CSA_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
                 timer.ev.push_back(e0); timer.ev.push_back(e1);
-                timer.passes++; timer.records += n; timer.bytes += 2 * n * (8 + (vin ? 4 : 0));
+                timer.passes++; timer.records += moved[p]; timer.bytes += 2 * moved[p] * (8 + (vin ? 4 : 0));
             }
         }
         ctx->counters[1]++;
-        ctx->counters[2] += n;
+        ctx->counters[2] += moved[p];
         u64* tk = kin; kin = kout; kout = tk;
         u32* tv = vin; vin = vout; vout = tv;
     }
