@@ -1,7 +1,7 @@
 """Writes the golden vectors under tests/golden/ by running the reference's own CPU code (oracle/_ref/libcascade_ref.so,
 compiled from the reference's sources by oracle/Makefile). Run in a container that has the reference tree:
 
-    make -C oracle && python tests/golden/make_golden.py
+    make -C oracle REF=<reference tree> && python tests/golden/make_golden.py
 
 Outputs:
   known_answers.json   the reference's known-answer table of (text, pattern, count) (its test_edge_cases), each with the
