@@ -73,7 +73,7 @@ def _worker(rank, world, port, n, p, kind, policy, q):
 
 
 @pytest.mark.parametrize("world,n,p,kind,policy", [(2, 3_000_000, 16, "zipf", 1), (2, 400_000, 8, "repeat", 1), (3, 1_000_003, 5, "zipf", 1),
-                                                    (2, 1_500_000, 16, "zipf", 0)])
+                                                    (2, 1_500_000, 16, "zipf", 0), (2, 1_200_000, 300, "zipf", 1)])
 def test_sharded_build_equals_the_single_gpu_build(world, n, p, kind, policy):
     port = _free_port()
     ctx = mp.get_context("spawn")
