@@ -507,6 +507,7 @@ def run_ours_multi(args):
             step_ms.append(_max_over_ranks(st.ms_total, dev))
             launches += st.kernel_launches
             peer += st.peer_bytes
+            per_gen = [int(x) for x in st.peer_bytes_per_gen[:st.generations + 1]]
         dist.barrier()
         torch.cuda.synchronize()
     ms = sum(step_ms) / len(step_ms)
@@ -584,13 +585,20 @@ def run_ours_multi(args):
                  "queries": q, "counts_hash": f"{api.counts_hash(itv.cpu().numpy().view(np.uint64)):016x}", "positions": int(cnt.sum().item())}
     launches_all = _sum_over_ranks(launches, dev)
     peer_all = _sum_over_ranks(peer, dev)
+    pg = torch.zeros(49, dtype=torch.float64, device=dev)
+    pg[:len(per_gen)] = torch.tensor(per_gen, dtype=torch.float64, device=dev)
+    dist.all_reduce(pg)
+    per_gen_all = [int(x) for x in pg[:st.generations + 1].cpu()]
     if rank == 0:
         line = {"metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
                 "config": workload_config(args, world), "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches_all),
                 "roofline": roofline,
                 "nvlink": {"peer_bytes_per_step_all_ranks": peer_all / args.steps, "generations": st.generations,
-                           "note": "positions to partition owners + ranks to and from position owners, 4 bytes each, (G-1)/G of them remote"},
+                           "peer_bytes_per_generation_all_ranks": per_gen_all,
+                           "note": "bytes written into other GPUs' memory; [0] = positions and generation-0 keys to the partitions' owners (12 B) and the first "
+                                   "ranks to the positions' owners (8 B), [t] = doubling generation t: rank requests and responses (4 B each) and rank updates "
+                                   "(8 B); (G-1)/G of the records are remote"},
                 "phases_ms_rank0": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output},
                 "query": query, "validated": bool(validation["ok"] and total == n), "validation": validation}
         print(json.dumps(line))

@@ -18,7 +18,7 @@ class BuildStats(ctypes.Structure):
         ("peer_bytes", c_u64),
         ("ms_partition", ctypes.c_double), ("ms_gen0", ctypes.c_double), ("ms_doubling", ctypes.c_double),
         ("ms_output", ctypes.c_double), ("ms_total", ctypes.c_double), ("ms_sort_passes", ctypes.c_double),
-        ("active_per_gen", c_u64 * 48),
+        ("active_per_gen", c_u64 * 48), ("peer_bytes_per_gen", c_u64 * 49),
     ]
 
 
@@ -71,6 +71,8 @@ _SIGS = {
     "csa_build_device_bytes": (ctypes.c_size_t, [c_u64, c_u32]),
     "csa_build_sa": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
     "csa_build_sa_host": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(BuildStats)]),
+    "csa_text_from_u8": (c_int, [c_vp, c_vp, c_u64, c_vp]),
+    "csa_text_from_u32": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, ctypes.POINTER(c_u32)]),
     "csa_store_create": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, c_u32, c_vp, ctypes.POINTER(c_vp)]),
     "csa_store_use_outbox": (c_int, [c_vp, c_vp, c_vp, c_vp, c_u64]),
     "csa_store_outbox_count": (c_u64, [c_vp]),

@@ -579,6 +579,7 @@ int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const
     }
     lap("generation 0 sorts + ranks");
     if(G > 1) CSA_TRY(route_updates(upd, n_local, keysA));      // generation 0's ranks go to the owners of their positions
+    st.peer_bytes_per_gen[0] = peer_bytes + route_bytes;
     lap("generation 0 rank exchange");
     CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars, act_count, 8, cudaMemcpyDeviceToHost, ctx->stream));
     CSA_CUDA(ctx, cudaEventRecord(ev[2], ctx->stream));
@@ -625,6 +626,12 @@ int build_multi_body(csa_ctx* ctx, const csa_comm* comm, Gather_State& gs, const
         for(u32 g = 0; g < G; ++g) { next_total += all2[2 * g]; any_status |= all2[2 * g + 1]; }
         if(any_status != 0) { u64 b = 0; csa_sync(ctx, reinterpret_cast<uint64_t*>(&b)); return csa_fail(ctx, CSA_E_DEVICE, "multi-GPU build: a rank reported a device status"); }
         if(debug) std::fprintf(stderr, "[csa %u/%u] generation %u: h=%llu active %llu -> %llu (all ranks %llu)\n", me, G, gen + 1, h, active, mine2[0], next_total);
+        if(gen + 1 < 49)
+        {
+            u64 before = 0;
+            for(u32 g2 = 0; g2 <= gen && g2 < 49; ++g2) before += st.peer_bytes_per_gen[g2];
+            st.peer_bytes_per_gen[gen + 1] = peer_bytes + route_bytes - before;
+        }
         active = mine2[0];
         total_active = next_total;
         pos_cur = pn; pos_other = ps;

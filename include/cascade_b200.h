@@ -158,6 +158,9 @@ typedef struct csa_build_stats
     double ms_total;
     double ms_sort_passes;      /* total of the digit passes, when pass timing is on */
     uint64_t active_per_gen[48];
+    uint64_t peer_bytes_per_gen[49];    /* multi-GPU builds: bytes this GPU wrote into other GPUs' memory; [0] = partition phase and
+                                         * generation 0 (positions, keys, first ranks), [t] = doubling generation t (rank requests,
+                                         * responses and updates) */
 } csa_build_stats;
 
 /* Device bytes that csa_build_sa allocates for a text of n symbols in p partitions (beyond text and output). */
@@ -174,6 +177,20 @@ int csa_build_sa(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint32_t p,
  * stands for `cascade <text> <sa>` (src/main.cu:12-46) once the files are in memory. */
 int csa_build_sa_host(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
                       csa_build_stats* stats);
+
+/* ---- texts of other symbol widths ---------------------------------------------------------------------------------------- */
+
+/* The reference instantiates its builder and its query engine for 1-, 2- and 4-byte symbols (src/GPU_SACA.cu:2400-2402,
+ * src/Query_Engine.cu:1684-1686). This library's kernels take 16-bit symbols; a text of another width is first mapped onto
+ * them in a way that keeps the numeric order of the symbols, hence the order of the suffixes, hence the suffix array (which
+ * holds positions, not symbols): out_dev receives n symbols and CSA_TEXT_PAD zeros, ready for the builds above.
+ * csa_text_from_u8: bytes widen as they are; patterns of a query widen the same way.
+ * csa_text_from_u32: every symbol is replaced by its rank among the distinct symbols of the text; alphabet_dev (65536 words)
+ * receives the distinct symbols in ascending order and *distinct their number; more than 65536 are refused with CSA_E_LIMIT
+ * (8-byte lanes and wider keys, include/lane.hpp's IDX_LANE_BYTES = 8, are not built). A pattern maps through the same
+ * alphabet; a pattern symbol that the text does not contain cannot be mapped, and such a pattern does not occur. */
+int csa_text_from_u8(csa_ctx* ctx, const uint8_t* text_dev, uint64_t n, uint16_t* out_dev);
+int csa_text_from_u32(csa_ctx* ctx, const uint32_t* text_dev, uint64_t n, uint16_t* out_dev, uint32_t* alphabet_dev, uint32_t* distinct);
 
 /* ---- build, one part at a time (suffix lists in host memory, positions up to 2^40) ---------------------------------- */
 
