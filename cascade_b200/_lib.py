@@ -19,7 +19,12 @@ class BuildStats(ctypes.Structure):
         ("ms_partition", ctypes.c_double), ("ms_gen0", ctypes.c_double), ("ms_doubling", ctypes.c_double),
         ("ms_output", ctypes.c_double), ("ms_total", ctypes.c_double), ("ms_sort_passes", ctypes.c_double),
         ("active_per_gen", c_u64 * 48), ("peer_bytes_per_gen", c_u64 * 49),
+        ("host_parts", c_u32), ("file_parts", c_u32), ("file_bytes_read", c_u64), ("file_bytes_written", c_u64),
     ]
+
+
+class TierOptions(ctypes.Structure):
+    _fields_ = [("part_suffixes", c_u64), ("host_list_bytes", c_u64), ("scratch_dir", ctypes.c_char_p), ("output_path", ctypes.c_char_p)]
 
 
 ALLGATHER_FN = ctypes.CFUNCTYPE(c_int, c_vp, c_vp, c_vp, c_u64)
@@ -89,6 +94,7 @@ _SIGS = {
     "csa_exchange_messages": (c_int, [c_vp, c_vp, ctypes.POINTER(c_u64)]),
     "csa_rank_order": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),
     "csa_build_sa_streamed": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, ctypes.POINTER(BuildStats)]),
+    "csa_build_sa_tiered": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, ctypes.POINTER(TierOptions), ctypes.POINTER(BuildStats)]),
     "csa_validate_workspace_bytes": (ctypes.c_size_t, [c_u64]),
     "csa_validate_sa": (c_int, [c_vp, c_vp, c_u64, c_vp, c_vp, ctypes.c_size_t, c_vp]),
     "csa_comm_open_shm": (c_int, [ctypes.c_char_p, c_u32, c_u32, c_u32, c_vp]),

@@ -2,6 +2,7 @@
 pointers. torch is used for device memory only; every computation happens in the library's own kernels.
 """
 import ctypes
+import os
 
 import numpy as np
 import torch
@@ -212,6 +213,20 @@ def build_sa_streamed(ctx, text_host, n, p=64, seed=0, out=None, part_suffixes=0
     st = BuildStats()
     ctx.check(ctx.L.csa_build_sa_streamed(ctx.h, _ptr(text_host), n, p, seed, _ptr(out), part_suffixes, ctypes.byref(st)))
     return out, st
+
+
+def build_sa_tiered(ctx, text_host, n, p=64, seed=0, out=None, part_suffixes=0, host_list_bytes=None, scratch_dir=None, output_path=None):
+    """The part-by-part build with the lists in tiers (csa_build_sa_tiered): lists of the first parts in host memory up to
+    host_list_bytes (None: no bound), the others in files below scratch_dir; output_path names a file that receives the
+    array, and with out=False no array is kept in memory at all. Returns (sa40 or None, stats)."""
+    from ._lib import TierOptions
+    if out is None:
+        out = np.zeros(5 * n + SA_PAD_BYTES, dtype=np.uint8)
+    opts = TierOptions(part_suffixes, 2**64 - 1 if host_list_bytes is None else host_list_bytes,
+                       None if scratch_dir is None else os.fsencode(scratch_dir), None if output_path is None else os.fsencode(output_path))
+    st = BuildStats()
+    ctx.check(ctx.L.csa_build_sa_tiered(ctx.h, _ptr(text_host), n, p, seed, None if out is False else _ptr(out), ctypes.byref(opts), ctypes.byref(st)))
+    return (None if out is False else out), st
 
 
 def validate_sa(ctx, text_dev, n, sa40_dev):

@@ -10,8 +10,9 @@
 //                         part by part with its lists in host memory (the reference forces its lower tier the same way,
 //                         src/Residency_Plan.cpp:44-45). Without it that build is chosen when the resident one does not fit the device
 //   GPU_SACA_CHUNK_CAP    most suffixes of a part of that build (the reference's test knob for small slabs, src/GPU_SACA.cu:660)
-//   GPU_SACA_SCRATCH      spill directories of the reference (src/GPU_SACA.cu:718-731). Accepted; no tier below host memory is
-//                         built here, so nothing is written there (said once on stderr)
+//   GPU_SACA_SCRATCH      colon-separated scratch directories (src/GPU_SACA.cu:718-731): when the part-by-part build's lists
+//                         do not fit GPU_SACA_RAM_BUDGET, the parts beyond it keep their lists in files there, striped over the
+//                         directories; without it such a build is refused
 //   CASCADE_DEVICE        CUDA device (default 0)
 //   CASCADE_GPUS          GPUs to shard the build over (default 1): one host thread per GPU, devices CASCADE_DEVICE + i modulo
 //                         the number of devices present
@@ -88,24 +89,33 @@ int main(int argc, char** argv)
     std::fprintf(stderr, "Loaded the text of %llu symbols. Time taken: %.3f s.\n", (unsigned long long)n, since());
 
     const uint32_t gpus = uint32_t(env_u64("CASCADE_GPUS", 1));
-    if(std::getenv("GPU_SACA_SCRATCH")) std::fprintf(stderr, "note: GPU_SACA_SCRATCH is accepted, but no tier below host memory is built: nothing is written there.\n");
     // Which build: the resident one keeps every list on the device; the part-by-part one keeps them in host memory.
     size_t dev_free = 0, dev_total = 0;
     cudaMemGetInfo(&dev_free, &dev_total);
     const uint64_t resident_need = csa_build_device_bytes(n, p) + (n + CSA_TEXT_PAD) * 2 + 5 * n + CSA_SA_PAD_BYTES;
     const bool forced = env_u64("GPU_SACA_FORCE_SPILL", 0) != 0;
     const bool by_parts = gpus <= 1 && (forced || resident_need > dev_free || n >= (1ull << 32) - (1ull << 26));
+    csa_tier_options tiers{};
+    tiers.part_suffixes = env_u64("GPU_SACA_CHUNK_CAP", 0);
+    tiers.host_list_bytes = ~uint64_t(0);
     if(by_parts)
     {
-        // host memory of that build: the text and the output (held already) and 4 bytes per suffix of ranks
+        // Host memory of that build beyond the text and the output, which are held already: 4 bytes per suffix of ranks (the
+        // lanes live in the output array). Past the budget, the parts beyond it keep their lists in files if there is a
+        // scratch directory; the build is refused if there is none, as the reference refuses (Host_Budget_Refusal).
         uint64_t budget = env_u64("GPU_SACA_RAM_BUDGET", 0);
         if(budget == 0) budget = uint64_t(0.9 * double(available_host_bytes()));
         const uint64_t need = 4 * n;
         if(budget != 0 && need > budget)
         {
-            std::fprintf(stderr, "error: the build would take %.1f GB more of host memory, past the budget of %.1f GB (GPU_SACA_RAM_BUDGET)\n", double(need) / 1e9,
-                         double(budget) / 1e9);
-            return EXIT_FAILURE;
+            tiers.scratch_dir = std::getenv("GPU_SACA_SCRATCH");
+            if(!tiers.scratch_dir)
+            {
+                std::fprintf(stderr, "error: the build would take %.1f GB more of host memory, past the budget of %.1f GB (GPU_SACA_RAM_BUDGET), "
+                             "and GPU_SACA_SCRATCH names no directory for the lists\n", double(need) / 1e9, double(budget) / 1e9);
+                return EXIT_FAILURE;
+            }
+            tiers.host_list_bytes = budget / 4 * 9;     // the bound counts 9 bytes a suffix, of which 5 are in the output array here
         }
     }
     csa_ctx* ctx = nullptr;
@@ -114,9 +124,11 @@ int main(int argc, char** argv)
     {
         if(csa_ctx_create(device, &ctx) != CSA_OK) { std::fprintf(stderr, "error: cannot create a device context\n"); return EXIT_FAILURE; }
         csa_build_stats st{};
-        const int rc = by_parts ? csa_build_sa_streamed(ctx, T, n, p, 0, SA, env_u64("GPU_SACA_CHUNK_CAP", 0), &st) : csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
+        const int rc = by_parts ? csa_build_sa_tiered(ctx, T, n, p, 0, SA, &tiers, &st) : csa_build_sa_host(ctx, T, n, p, 0, SA, &st);
         if(rc != CSA_OK) { std::fprintf(stderr, "error: build failed (%d): %s\n", rc, csa_last_error(ctx)); return EXIT_FAILURE; }
-        if(by_parts) std::fprintf(stderr, "Built part by part with the suffix lists in host memory (%s).\n", forced ? "GPU_SACA_FORCE_SPILL" : "the resident build does not fit the device");
+        if(by_parts) std::fprintf(stderr, "Built part by part (%s): the lists of %u parts in host memory, of %u parts in files (%.2f GB read, %.2f GB written).\n",
+                                  forced ? "GPU_SACA_FORCE_SPILL" : "the resident build does not fit the device", st.host_parts, st.file_parts,
+                                  double(st.file_bytes_read) / 1e9, double(st.file_bytes_written) / 1e9);
         std::fprintf(stderr, "Built the suffix array: %u partitions (largest %llu), %u doubling generations, %llu digit passes.\n", st.partitions,
                      (unsigned long long)st.max_partition, st.generations, (unsigned long long)st.sort_passes);
         std::fprintf(stderr, "Device time: partition %.1f ms, initial ranking %.1f ms, doubling %.1f ms, output %.1f ms.\n", st.ms_partition, st.ms_gen0,

@@ -28,11 +28,18 @@
 #include "sort.cuh"
 
 #include <atomic>
+#include <cerrno>
 #include <chrono>
 #include <cstdlib>
+#include <cstring>
 #include <new>
+#include <string>
 #include <thread>
 #include <vector>
+
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 struct csa_store
 {
@@ -611,10 +618,91 @@ double ms_since(const std::chrono::steady_clock::time_point& t0)
 
 }   // namespace
 
-extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
-                                     uint64_t part_suffixes, csa_build_stats* stats)
+namespace
 {
-    if(!ctx || !text_host || !sa40_host) return csa_fail(ctx, CSA_E_INVALID, "streamed build: null argument");
+bool write_all(int fd, const void* from, size_t bytes, u64 at)
+{
+    const u8* p = static_cast<const u8*>(from);
+    while(bytes > 0)
+    {
+        const ssize_t w = ::pwrite(fd, p, bytes < (size_t(1) << 30) ? bytes : (size_t(1) << 30), off_t(at));
+        if(w <= 0) { if(w < 0 && errno == EINTR) continue; return false; }
+        p += w; at += u64(w); bytes -= size_t(w);
+    }
+    return true;
+}
+
+bool read_all(int fd, void* to, size_t bytes, u64 at)
+{
+    u8* p = static_cast<u8*>(to);
+    while(bytes > 0)
+    {
+        const ssize_t r = ::pread(fd, p, bytes < (size_t(1) << 30) ? bytes : (size_t(1) << 30), off_t(at));
+        if(r <= 0) { if(r < 0 && errno == EINTR) continue; return false; }
+        p += r; at += u64(r); bytes -= size_t(r);
+    }
+    return true;
+}
+
+// The files of the parts whose lists do not fit the host bound: per part one file of lanes and one of ranks, in a directory
+// of this build's own below the scratch directory (the reference stripes such files over its scratch roots,
+// include/GPU_SACA.cuh:95-118). Everything is removed when the build ends, however it ends.
+struct Part_Files
+{
+    std::vector<std::string> dirs;
+    std::vector<int> lanes_fd, ranks_fd;
+    std::vector<std::string> names;
+    std::atomic<u64> bytes_read{0}, bytes_written{0};
+
+    // scratch: one directory, or several separated by colons; part u's files go to directory u modulo their number.
+    bool open_parts(const char* scratch, u32 first, u32 parts)
+    {
+        static std::atomic<unsigned> serial{0};
+        const std::string own = "/cascade_b200_" + std::to_string(long(::getpid())) + "_" + std::to_string(serial.fetch_add(1));
+        const std::string all(scratch);
+        for(size_t at = 0; at <= all.size();)
+        {
+            size_t end = all.find(':', at);
+            if(end == std::string::npos) end = all.size();
+            if(end > at)
+            {
+                const std::string dir = all.substr(at, end - at) + own;
+                if(::mkdir(dir.c_str(), 0700) != 0) return false;
+                dirs.push_back(dir);
+            }
+            at = end + 1;
+        }
+        if(dirs.empty()) return false;
+        lanes_fd.assign(parts, -1);
+        ranks_fd.assign(parts, -1);
+        for(u32 u = first; u < parts; ++u)
+            for(int kind = 0; kind < 2; ++kind)
+            {
+                names.push_back(dirs[u % dirs.size()] + "/part_" + std::to_string(u) + (kind ? ".ranks" : ".lanes"));
+                const int fd = ::open(names.back().c_str(), O_RDWR | O_CREAT | O_EXCL, 0600);
+                if(fd < 0) return false;
+                (kind ? ranks_fd : lanes_fd)[u] = fd;
+            }
+        return true;
+    }
+    bool read(int fd, void* to, size_t bytes, u64 at) { bytes_read += bytes; return read_all(fd, to, bytes, at); }
+    bool write(int fd, const void* from, size_t bytes, u64 at) { bytes_written += bytes; return write_all(fd, from, bytes, at); }
+    ~Part_Files()
+    {
+        for(int fd : lanes_fd) if(fd >= 0) ::close(fd);
+        for(int fd : ranks_fd) if(fd >= 0) ::close(fd);
+        for(const std::string& f : names) ::unlink(f.c_str());
+        for(const std::string& d : dirs) ::rmdir(d.c_str());
+    }
+};
+}
+
+extern "C" int csa_build_sa_tiered(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
+                                   const csa_tier_options* options, csa_build_stats* stats)
+{
+    if(!ctx || !text_host || !options) return csa_fail(ctx, CSA_E_INVALID, "streamed build: null argument");
+    if(!sa40_host && !options->output_path) return csa_fail(ctx, CSA_E_INVALID, "streamed build: neither an output array nor an output file");
+    uint64_t part_suffixes = options->part_suffixes;
     if(n == 0) return csa_fail(ctx, CSA_E_INVALID, "streamed build: empty text");
     if(p == 0 || p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_LIMIT, "streamed build: partition count out of range");
     if(n + g_position_offset >= (u64(1) << 40)) return csa_fail(ctx, CSA_E_LIMIT, "streamed build: positions must fit 40 bits");
@@ -698,17 +786,49 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     CSA_TRY(csa_store_create(ctx, T, n, pid, part_of_pid.data(), p_eff, nullptr, &st));
     struct Store_Guard { csa_store* s; ~Store_Guard() { csa_store_destroy(s); } } store_guard{st};
 
-    // ---- the parts' lanes go to the host: part u owns the bytes from 5 part_off[u] on of the output array ------------------
-    void* ranks_p = nullptr;
-    CSA_TRY(csa_host_aux(ctx, n * 4 + 64, &ranks_p));      // kept by the context: a second build of this size pins nothing
-    u32* ranks_host = static_cast<u32*>(ranks_p);
+    // ---- tiers: the first parts keep their lists in host memory while the bound allows, the others keep them in files --------
+    u32 first_file_part = parts;
+    if(options->host_list_bytes != ~uint64_t(0))
+        for(u32 u = 0; u < parts; ++u)
+            if(9 * part_off[u + 1] > options->host_list_bytes) { first_file_part = u; break; }
+    const bool files_in_use = first_file_part < parts;
+    if(files_in_use && !options->scratch_dir)
+        return csa_fail(ctx, CSA_E_NOMEM, "streamed build: the lists pass the host bound and no scratch directory is given");
+    Part_Files files;
+    if(files_in_use && !files.open_parts(options->scratch_dir, first_file_part, parts))
+        return csa_fail(ctx, CSA_E_INVALID, "streamed build: cannot create the part files in the scratch directory");
+    struct Fd_Guard { int fd = -1; ~Fd_Guard() { if(fd >= 0) ::close(fd); } } out_file;
+    if(options->output_path)
+    {
+        out_file.fd = ::open(options->output_path, O_WRONLY | O_CREAT | O_TRUNC, 0644);
+        if(out_file.fd < 0 || ::ftruncate(out_file.fd, off_t(5 * n)) != 0) return csa_fail(ctx, CSA_E_INVALID, "streamed build: cannot create the output file");
+    }
+    u64 largest_file_part = 0;
+    for(u32 u = first_file_part; u < parts; ++u) if(part_off[u + 1] - part_off[u] > largest_file_part) largest_file_part = part_off[u + 1] - part_off[u];
+    const u64 host_suffixes = part_off[first_file_part];
+    constexpr u64 CHUNK = u64(1) << 27;
+    const u64 chunk_cap = n < CHUNK ? n : CHUNK;
+    // One pinned array of the context (a second build of this size pins nothing): the ranks of the host parts, their lanes when
+    // there is no output array to keep them in, two buffers through which the lanes of the file parts reach their files, and
+    // this thread's buffers for a file part (lanes, ranks, ordered lanes).
+    const size_t bounce_bytes = files_in_use ? align_up256(5 * largest_file_part + 64) * 2 + align_up256(4 * largest_file_part + 64) : 0;
+    const size_t ranks_bytes = align_up256(host_suffixes * 4 + 64);
+    const size_t own_lanes_bytes = sa40_host ? 0 : align_up256(host_suffixes * 5 + 64);
+    const size_t to_files_bytes = files_in_use ? 2 * align_up256(5 * chunk_cap + 256) : 0;
+    void* pinned_p = nullptr;
+    CSA_TRY(csa_host_aux(ctx, ranks_bytes + own_lanes_bytes + to_files_bytes + bounce_bytes + 256, &pinned_p));
+    u8* const pinned = static_cast<u8*>(pinned_p);
+    u32* const ranks_host = reinterpret_cast<u32*>(pinned);
+    u8* const host_lanes = sa40_host ? sa40_host : pinned + ranks_bytes;
+    u8* const to_files[2] = {pinned + ranks_bytes + own_lanes_bytes, pinned + ranks_bytes + own_lanes_bytes + to_files_bytes / 2};
+    // Where the lists of host part u lie.
+    auto lanes_of = [&](u32 u) { return host_lanes + 5 * part_off[u]; };
+    auto ranks_of = [&](u32 u) { return ranks_host + part_off[u]; };
     const double ms_pinned = ms_since(t_start);
     {
         // Stretch by stretch: count the stretch's positions by part, scatter them into per-part runs of a staging buffer, and
         // copy every run to its part's place on the host. Two staging buffers and a second stream let the copies of one
         // stretch run under the scatter of the next.
-        constexpr u64 CHUNK = u64(1) << 27;
-        const u64 chunk_cap = n < CHUNK ? n : CHUNK;
         CSA_TRY(stage_b.alloc(ctx, 2 * align_up256(5 * chunk_cap + 256)));
         u8* const staging[2] = {static_cast<u8*>(stage_b.p), static_cast<u8*>(stage_b.p) + align_up256(5 * chunk_cap + 256)};
         CSA_TRY(csa_lanes(ctx));
@@ -735,13 +855,30 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
             CSA_CUDA(ctx, cudaEventRecord(scattered, ctx->stream));
             CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // chunk_first is a host array that the next stretch rewrites
             CSA_CUDA(ctx, cudaStreamWaitEvent(copy_stream, scattered, 0));
-            for(u32 u = 0; u < parts; ++u)
+            for(u32 u = 0; u < first_file_part; ++u)
             {
                 if(chunk_hist[u] == 0) continue;
-                CSA_CUDA(ctx, cudaMemcpyAsync(sa40_host + 5 * (part_off[u] + filled[u]), stage + 5 * chunk_first[u], 5 * chunk_hist[u], cudaMemcpyDeviceToHost, copy_stream));
+                CSA_CUDA(ctx, cudaMemcpyAsync(lanes_of(u) + 5 * filled[u], stage + 5 * chunk_first[u], 5 * chunk_hist[u], cudaMemcpyDeviceToHost, copy_stream));
                 filled[u] += chunk_hist[u];
             }
-            CSA_CUDA(ctx, cudaEventRecord(copied[k & 1], copy_stream));
+            if(files_in_use)
+            {
+                // The runs of the file parts follow one another in the staging buffer: one copy to the host, then one write per part.
+                const u64 from = chunk_first[first_file_part], bytes = 5 * (c - from);
+                u8* const via = to_files[k & 1];
+                if(bytes) CSA_CUDA(ctx, cudaMemcpyAsync(via, stage + 5 * from, bytes, cudaMemcpyDeviceToHost, copy_stream));
+                CSA_CUDA(ctx, cudaEventRecord(copied[k & 1], copy_stream));
+                CSA_CUDA(ctx, cudaStreamSynchronize(copy_stream));
+                for(u32 u = first_file_part; u < parts; ++u)
+                {
+                    if(chunk_hist[u] == 0) continue;
+                    if(!files.write(files.lanes_fd[u], via + 5 * (chunk_first[u] - from), 5 * chunk_hist[u], 5 * filled[u]))
+                        return csa_fail(ctx, CSA_E_INVALID, "streamed build: writing a part file failed");
+                    filled[u] += chunk_hist[u];
+                }
+            }
+            else
+                CSA_CUDA(ctx, cudaEventRecord(copied[k & 1], copy_stream));
         }
         CSA_CUDA(ctx, cudaStreamSynchronize(copy_stream));
         for(u32 u = 0; u < parts; ++u) if(filled[u] != part_off[u + 1] - part_off[u]) return csa_fail(ctx, CSA_E_DEVICE, "streamed build: a part's lanes do not add up");
@@ -756,6 +893,24 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     const int workers = parts < u32(WORKERS) ? int(parts) : WORKERS;
     for(int w = 1; w < workers; ++w)
         if(csa_ctx_create(ctx->device, &wctx[w]) != CSA_OK) return csa_fail(ctx, CSA_E_CUDA, "streamed build: cannot create a worker context");
+    // A worker's buffers for a file part: its lanes, its ranks, and the lanes in their final order.
+    struct Bounce { u8* lanes; u32* ranks; u8* ordered; } bounce[WORKERS] = {};
+    if(files_in_use)
+        for(int w = 0; w < workers; ++w)
+        {
+            u8* base = pinned + ranks_bytes + own_lanes_bytes + to_files_bytes;
+            if(w > 0)
+            {
+                void* own = nullptr;
+                if(csa_host_aux(wctx[w], bounce_bytes + 256, &own) != CSA_OK) return csa_fail(ctx, CSA_E_NOMEM, "streamed build: cannot pin a worker's buffers");
+                base = static_cast<u8*>(own);
+            }
+            bounce[w].lanes = base;
+            bounce[w].ordered = base + align_up256(5 * largest_file_part + 64);
+            bounce[w].ranks = reinterpret_cast<u32*>(base + 2 * align_up256(5 * largest_file_part + 64));
+        }
+    auto worker_of = [&](csa_ctx* c) { for(int w = 0; w < workers; ++w) if(wctx[w] == c) return w; return 0; };
+    auto io_failed = [&](csa_ctx* c) { return csa_fail(c, CSA_E_INVALID, "streamed build: reading or writing a part file failed"); };
     std::vector<u64> active(parts);
     // Runs job(context, part) over all parts on the workers; returns the first error.
     auto over_parts = [&](auto job) -> int
@@ -788,11 +943,24 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     CSA_TRY(over_parts([&](csa_ctx* c, u32 u) -> int
     {
         const u64 S = part_off[u + 1] - part_off[u];
-        csa_part in{sa40_host + 5 * part_off[u], nullptr, S, u};
-        csa_part_result out{sa40_host + 5 * part_off[u], ranks_host + part_off[u], 0, 0};
-        const int rc = csa_rank_gen0(c, st, &in, &out);
+        if(u < first_file_part)
+        {
+            csa_part in{lanes_of(u), nullptr, S, u};
+            csa_part_result out{lanes_of(u), ranks_of(u), 0, 0};
+            const int rc = csa_rank_gen0(c, st, &in, &out);
+            active[u] = out.active;
+            return rc;
+        }
+        const Bounce& b = bounce[worker_of(c)];
+        if(!files.read(files.lanes_fd[u], b.lanes, 5 * S, 0)) return io_failed(c);
+        csa_part in{b.lanes, nullptr, S, u};
+        csa_part_result out{b.lanes, b.ranks, 0, 0};
+        CSA_TRY(csa_rank_gen0(c, st, &in, &out));
         active[u] = out.active;
-        return rc;
+        u64 status = 0;
+        CSA_TRY(csa_sync(c, reinterpret_cast<uint64_t*>(&status)));
+        if(!files.write(files.lanes_fd[u], b.lanes, 5 * S, 0) || !files.write(files.ranks_fd[u], b.ranks, 4 * S, 0)) return io_failed(c);
+        return CSA_OK;
     }));
     csa_store_drop_partition_ids(st);
     cudaFree(pid_b.p); pid_b.p = nullptr;
@@ -816,11 +984,26 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
         CSA_TRY(over_parts([&](csa_ctx* c, u32 u) -> int
         {
             if(active[u] == 0) return CSA_OK;
-            csa_part in{sa40_host + 5 * part_off[u], ranks_host + part_off[u], active[u], u};
-            csa_part_result out{sa40_host + 5 * part_off[u], ranks_host + part_off[u], 0, 0};
-            const int rc = csa_rank_gen(c, st, &in, h, &out);
+            if(u < first_file_part)
+            {
+                csa_part in{lanes_of(u), ranks_of(u), active[u], u};
+                csa_part_result out{lanes_of(u), ranks_of(u), 0, 0};
+                const int rc = csa_rank_gen(c, st, &in, h, &out);
+                active[u] = out.active;
+                return rc;
+            }
+            // Only the tied suffixes, which lead the part's lists, travel.
+            const Bounce& b = bounce[worker_of(c)];
+            const u64 tied = active[u];
+            if(!files.read(files.lanes_fd[u], b.lanes, 5 * tied, 0) || !files.read(files.ranks_fd[u], b.ranks, 4 * tied, 0)) return io_failed(c);
+            csa_part in{b.lanes, b.ranks, tied, u};
+            csa_part_result out{b.lanes, b.ranks, 0, 0};
+            CSA_TRY(csa_rank_gen(c, st, &in, h, &out));
             active[u] = out.active;
-            return rc;
+            u64 status = 0;
+            CSA_TRY(csa_sync(c, reinterpret_cast<uint64_t*>(&status)));
+            if(!files.write(files.lanes_fd[u], b.lanes, 5 * tied, 0) || !files.write(files.ranks_fd[u], b.ranks, 4 * tied, 0)) return io_failed(c);
+            return CSA_OK;
         }));
         uint64_t applied = 0;
         CSA_TRY(csa_exchange_messages(ctx, st, &applied));
@@ -841,8 +1024,26 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
     CSA_TRY(over_parts([&](csa_ctx* c, u32 u) -> int
     {
         const u64 S = part_off[u + 1] - part_off[u];
-        return csa_rank_order(c, sa40_host + 5 * part_off[u], ranks_host + part_off[u], S, sa40_host + 5 * part_off[u]);
+        u64 status = 0;
+        if(u < first_file_part)
+        {
+            CSA_TRY(csa_rank_order(c, lanes_of(u), ranks_of(u), S, lanes_of(u)));
+            if(out_file.fd < 0) return CSA_OK;
+            CSA_TRY(csa_sync(c, reinterpret_cast<uint64_t*>(&status)));
+            return write_all(out_file.fd, lanes_of(u), 5 * S, 5 * part_off[u]) ? CSA_OK : io_failed(c);
+        }
+        const Bounce& b = bounce[worker_of(c)];
+        if(!files.read(files.lanes_fd[u], b.lanes, 5 * S, 0) || !files.read(files.ranks_fd[u], b.ranks, 4 * S, 0)) return io_failed(c);
+        CSA_TRY(csa_rank_order(c, b.lanes, b.ranks, S, b.ordered));
+        CSA_TRY(csa_sync(c, reinterpret_cast<uint64_t*>(&status)));
+        if(sa40_host) std::memcpy(sa40_host + 5 * part_off[u], b.ordered, 5 * S);
+        if(out_file.fd >= 0 && !write_all(out_file.fd, b.ordered, 5 * S, 5 * part_off[u])) return io_failed(c);
+        return CSA_OK;
     }));
+    bs.host_parts = first_file_part;
+    bs.file_parts = parts - first_file_part;
+    bs.file_bytes_read = files.bytes_read.load();
+    bs.file_bytes_written = files.bytes_written.load();
     bs.ms_output = ms_since(t_out);
     bs.ms_total = ms_since(t_start);
     for(int w = 0; w < workers; ++w)
@@ -852,4 +1053,14 @@ extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, ui
         bs.sort_records += wctx[w]->counters[2] - (w == 0 ? records_before : 0);
     }
     return CSA_OK;
+}
+
+extern "C" int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
+                                     uint64_t part_suffixes, csa_build_stats* stats)
+{
+    if(!sa40_host) return csa_fail(ctx, CSA_E_INVALID, "streamed build: null argument");
+    csa_tier_options options{};
+    options.part_suffixes = part_suffixes;
+    options.host_list_bytes = ~uint64_t(0);
+    return csa_build_sa_tiered(ctx, text_host, n, p, seed, sa40_host, &options, stats);
 }

@@ -161,6 +161,10 @@ typedef struct csa_build_stats
     uint64_t peer_bytes_per_gen[49];    /* multi-GPU builds: bytes this GPU wrote into other GPUs' memory; [0] = partition phase and
                                          * generation 0 (positions, keys, first ranks), [t] = doubling generation t (rank requests,
                                          * responses and updates) */
+    uint32_t host_parts;        /* csa_build_sa_tiered: parts whose lists stayed in host memory */
+    uint32_t file_parts;        /*   and parts whose lists went through files */
+    uint64_t file_bytes_read;   /*   bytes read from and written to those files */
+    uint64_t file_bytes_written;
 } csa_build_stats;
 
 /* Device bytes that csa_build_sa allocates for a text of n symbols in p partitions (beyond text and output). */
@@ -274,6 +278,26 @@ int csa_rank_order(csa_ctx* ctx, const uint8_t* lanes, const uint32_t* ranks, ui
  * the ranks besides the caller's buffers. part_suffixes bounds a part's size (0: 2^27). */
 int csa_build_sa_streamed(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
                           uint64_t part_suffixes, csa_build_stats* stats);
+/* Where the lists of csa_build_sa_tiered live. The reference plans three tiers for a partition's lists: device memory,
+ * pinned host memory, files (src/GPU_SACA.cu:38-121, chosen from GPU_SACA_RAM_BUDGET and GPU_SACA_SCRATCH, include/GPU_SACA.cuh:95-118). */
+typedef struct csa_tier_options
+{
+    uint64_t part_suffixes;     /* bound on a part's size, as in csa_build_sa_streamed (0: 2^27) */
+    uint64_t host_list_bytes;   /* host memory that the parts' lists may take, 9 bytes a suffix: the parts are taken in order
+                                 * while their lists fit below it, all later parts keep theirs in files. All ones: no bound */
+    const char* scratch_dir;    /* an existing directory for those files, or several separated by colons (part u's files go to
+                                 * directory u modulo their number); the build makes a directory of its own in each and removes
+                                 * it at the end. May be null if the bound is never passed (CSA_E_NOMEM if it then is) */
+    const char* output_path;    /* if not null, the suffix array is also written to this file (5 n bytes), part by part */
+} csa_tier_options;
+/* csa_build_sa_streamed with the lists in tiers: host memory up to a bound, files beyond it. A file part's lists are read into
+ * pinned buffers of the worker that takes the part (only the tied suffixes after generation 0), processed and written
+ * back, so host memory holds the host parts' lists (4 bytes a suffix for ranks, 5 more if sa40_host is null), 14 bytes per
+ * suffix of the largest file part for each of the three workers, and two buffers of 5 * 2^27 bytes. sa40_host may be null
+ * when output_path is given: the array then exists only in the file, as with the reference's Output_File
+ * (src/GPU_SACA.cu:1404-1409). Stands where the reference's Residency_Plan and Spill_Store stand. */
+int csa_build_sa_tiered(csa_ctx* ctx, const uint16_t* text_host, uint64_t n, uint32_t p, uint64_t seed, uint8_t* sa40_host,
+                        const csa_tier_options* options, csa_build_stats* stats);
 
 /* ---- validation -------------------------------------------------------------------------------------------- */
 

@@ -142,15 +142,25 @@ def test_cascade_and_query_find_against_the_oracle(tmp_path, oracle):
         assert np.array_equal(np.fromfile(out2, dtype=np.uint8), want[:5 * n]), gpus
 
     # the reference's knobs: the lower tier forced (the build then runs part by part with its lists in host memory, parts capped
-    # as the reference's test knob caps its slabs), and a host budget that the build would pass, which refuses it before it starts
+    # as the reference's test knob caps its slabs); a host budget that the build would pass refuses it before it starts, unless
+    # there are scratch directories, over which the lists of the parts beyond the budget are then striped as files
     out3 = os.path.join(tmp, "text.parts.sa40")
     r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), out3], capture_output=True, text=True,
-                       env=dict(env, GPU_SACA_FORCE_SPILL="1", GPU_SACA_CHUNK_CAP="70000", GPU_SACA_SCRATCH="/tmp"))
-    assert r.returncode == 0 and "part by part" in r.stderr and "GPU_SACA_SCRATCH" in r.stderr, r.stderr
+                       env=dict(env, GPU_SACA_FORCE_SPILL="1", GPU_SACA_CHUNK_CAP="70000"))
+    assert r.returncode == 0 and "part by part" in r.stderr and "of 0 parts in files" in r.stderr, r.stderr
     assert np.array_equal(np.fromfile(out3, dtype=np.uint8), want[:5 * n])
+    os.remove(out3)
     r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), out3], capture_output=True, text=True,
                        env=dict(env, GPU_SACA_FORCE_SPILL="1", GPU_SACA_RAM_BUDGET="100000"))
-    assert r.returncode != 0 and "GPU_SACA_RAM_BUDGET" in r.stderr
+    assert r.returncode != 0 and "GPU_SACA_RAM_BUDGET" in r.stderr and "GPU_SACA_SCRATCH" in r.stderr
+    roots = [os.path.join(tmp, "scratch_a"), os.path.join(tmp, "scratch_b")]
+    for d in roots:
+        os.mkdir(d)
+    r = subprocess.run([os.path.join(BIN, "cascade"), os.path.join(tmp, "text.u16"), out3], capture_output=True, text=True,
+                       env=dict(env, GPU_SACA_FORCE_SPILL="1", GPU_SACA_CHUNK_CAP="70000", GPU_SACA_RAM_BUDGET="500000", GPU_SACA_SCRATCH=":".join(roots)))
+    assert r.returncode == 0 and "parts in files" in r.stderr and "of 0 parts in files" not in r.stderr, r.stderr
+    assert np.array_equal(np.fromfile(out3, dtype=np.uint8), want[:5 * n])
+    assert all(os.listdir(d) == [] for d in roots)
 
     q = os.path.join(tmp, "a.qry")
     assert subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", q, "--kind", "substring", "--q", "5000", "--len", "1,2,4,8,16",

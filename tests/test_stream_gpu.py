@@ -177,3 +177,47 @@ def test_part_jobs_called_one_by_one(ctx, oracle):
         L.csa_store_destroy(store)
     assert gens >= 1
     assert np.array_equal(out[:5 * n], oracle.build_sa40(T)[:5 * n])
+
+
+@pytest.mark.parametrize("bound_fraction,keep_array", [(0.0, True), (0.4, True), (0.4, False), (None, False)])
+def test_lists_in_files_give_the_same_array(ctx, oracle, tmp_path, bound_fraction, keep_array):
+    """Tiers of the part-by-part build: with a host bound of nothing every part's lists go through files, with 40 % of the
+    lists' size the first parts stay in host memory; the array must be the oracle's, in memory and in the output file, and
+    the scratch directory must be empty again afterwards."""
+    from cascade_b200 import api
+    n = 700_000
+    Th = api.gen_corpus_host(n, 5, 384)
+    scratch = tmp_path / "scratch"
+    scratch.mkdir()
+    out_path = tmp_path / "sa.bin"
+    bound = None if bound_fraction is None else int(9 * n * bound_fraction)
+    sa, st = api.build_sa_tiered(ctx, Th, n, 32, part_suffixes=60_000, host_list_bytes=bound, scratch_dir=scratch, output_path=out_path,
+                                 out=None if keep_array else False)
+    want = oracle.build_sa40(Th[:n])[:5 * n]
+    assert np.array_equal(np.fromfile(out_path, dtype=np.uint8), want)
+    if keep_array:
+        assert np.array_equal(sa[:5 * n], want)
+    assert list(scratch.iterdir()) == []
+    assert st.host_parts + st.file_parts >= 10
+    if bound_fraction == 0.0:
+        assert st.host_parts == 0 and st.file_bytes_written >= 9 * n and st.file_bytes_read >= 9 * n
+    elif bound_fraction is None:
+        assert st.file_parts == 0 and st.file_bytes_written == 0
+    else:
+        assert st.host_parts > 0 and st.file_parts > 0
+
+
+def test_tiered_build_refusals(ctx, tmp_path):
+    from cascade_b200 import api
+    n = 100_000
+    Th = api.gen_corpus_host(n, 1, 256)
+    with pytest.raises(api.CascadeError) as e:      # the bound is passed and there is nowhere to put the lists
+        api.build_sa_tiered(ctx, Th, n, 8, part_suffixes=20_000, host_list_bytes=1000)
+    assert e.value.code == 3 and "scratch" in str(e.value)
+    with pytest.raises(api.CascadeError) as e:      # a scratch directory that does not exist
+        api.build_sa_tiered(ctx, Th, n, 8, part_suffixes=20_000, host_list_bytes=1000, scratch_dir=tmp_path / "nowhere")
+    assert e.value.code == 1
+    with pytest.raises(api.CascadeError):           # no array and no file
+        api.build_sa_tiered(ctx, Th, n, 8, out=False)
+    sa, st = api.build_sa_streamed(ctx, Th, n, 8)    # the context still works
+    assert st.n == n
