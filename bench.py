@@ -709,6 +709,25 @@ def run_c4(args):
             ts.append(time.perf_counter() - t0)
         c_driver = {"value": n / ts[-1], "unit": UNIT, "ms_per_step": 1e3 * ts[-1], "api": "csa_build_sa_streamed (pinned host text in, sa40 out in pinned host memory)",
                     "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output}}
+    file_tier = None
+    if world == 1 and args.scratch:
+        # the same again with the lists of the parts beyond --host-list-gb in files below --scratch (page cache included: the
+        # files are written and read back within seconds, so this times the file path, not a drive)
+        if c_driver is None:
+            th = torch.empty(n + api.TEXT_PAD, dtype=torch.uint16).pin_memory()
+            th.copy_(T)
+            oh = host["lanes"]
+        oh.zero_()
+        t0 = time.perf_counter()
+        _, st = api.build_sa_tiered(ctx, th, n, p, out=oh, part_suffixes=ps, host_list_bytes=int(args.host_list_gb * 1e9), scratch_dir=args.scratch)
+        dt = time.perf_counter() - t0
+        full = oh[:5 * n + api.SA_PAD_BYTES].to(dev)
+        vf = api.validate_sa(ctx, T, n, full)
+        del full
+        file_tier = {"value": n / dt, "unit": UNIT, "ms_per_step": 1e3 * dt, "api": "csa_build_sa_tiered", "host_list_gb": args.host_list_gb,
+                     "host_parts": st.host_parts, "file_parts": st.file_parts, "file_gb_read": st.file_bytes_read / 1e9,
+                     "file_gb_written": st.file_bytes_written / 1e9, "validated": bool(vf["ok"]),
+                     "phases_ms": {"partition": st.ms_partition, "gen0": st.ms_gen0, "doubling": st.ms_doubling, "output": st.ms_output}}
     own_active = info["active_per_generation"]
     if rank == 0:
         print(json.dumps({"metric": METRIC, "value": n / sec, "unit": UNIT, "n_gpus": world, "steps": len(times), "warmup": 1, "ms_per_step": 1e3 * sec,
@@ -725,7 +744,7 @@ def run_c4(args):
                           "nvlink_bytes_received_rank0": info["nvlink_bytes_received"],
                           "pcie_bytes_rank0": {"h2d": 5 * info["own_suffixes"] + 9 * info["own_suffixes"] + 9 * sum(own_active) // world,
                                                "d2h": 5 * info["own_suffixes"] + 9 * info["own_suffixes"] + 9 * sum(own_active) // world + 5 * info["own_suffixes"]},
-                          "validated": bool(v["ok"]), "validation": v, "one_call_entry_point": c_driver}))
+                          "validated": bool(v["ok"]), "validation": v, "one_call_entry_point": c_driver, "lists_in_files": file_tier}))
     if world > 1:
         dist.barrier()
     ctx.close()
@@ -765,6 +784,8 @@ def main():
     ap.add_argument("--part-suffixes", type=int, default=0, help="c4: most suffixes of a part (0 = the library's default, 2^27)")
     ap.add_argument("--list-budget-gb", type=float, default=-1.0,
                     help="c4: device memory (GB) that may hold parts' suffix lists; 0 keeps every list in pinned host memory, -1 (default) takes what is free")
+    ap.add_argument("--scratch", default=None, help="c4: a directory; the build is then also run with lists in files there (csa_build_sa_tiered)")
+    ap.add_argument("--host-list-gb", type=float, default=0.0, help="c4 with --scratch: host memory for lists, 9 bytes a suffix; parts beyond it use files")
     ap.add_argument("--micro", default=None, choices=["sort"], help="time one kernel family alone instead of the build")
     ap.add_argument("--records", type=int, default=31_250_000)
     ap.add_argument("--bits", type=int, default=64)
