@@ -91,6 +91,10 @@ _SIGS = {
     "csa_part_workspace_bytes": (ctypes.c_size_t, [c_u64]),
     "csa_rank_gen0": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), ctypes.POINTER(PartResult)]),
     "csa_rank_gen": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_u64, ctypes.POINTER(PartResult)]),
+    "csa_scatter_lanes_keys": (c_int, [c_vp, c_vp, c_vp, c_vp, c_u64, c_u64, c_vp, c_vp, c_vp, c_vp]),
+    "csa_rank_gen0_keys": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_vp, ctypes.POINTER(PartResult)]),
+    "csa_part_positions": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u64, c_vp]),
+    "csa_rank_gen_ranks": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_vp, ctypes.POINTER(PartResult)]),
     "csa_exchange_messages": (c_int, [c_vp, c_vp, ctypes.POINTER(c_u64)]),
     "csa_rank_order": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),
     "csa_build_sa_streamed": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, ctypes.POINTER(BuildStats)]),

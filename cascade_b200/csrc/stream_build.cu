@@ -107,6 +107,30 @@ __global__ void stream_keys_kernel(const u32* __restrict__ R, const u64 n, const
     idx[i] = u32(i);
 }
 
+// Generation 0 from keys that the caller made, and generation t from second ranks that the caller fetched (a rank store
+// sharded over several GPUs answers them): the list's own order.
+__global__ void given_keys0_kernel(const u64* __restrict__ given, const u64 count, u64* __restrict__ keys, u32* __restrict__ idx)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= count) return;
+    keys[i] = given[i];
+    idx[i] = u32(i);
+}
+
+__global__ void given_second_kernel(const u32* __restrict__ second, const u32* __restrict__ ranks, const u64 count, u64* __restrict__ keys, u32* __restrict__ idx)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i >= count) return;
+    keys[i] = (u64(ranks[i]) << 32) | second[i];
+    idx[i] = u32(i);
+}
+
+__global__ void lane_positions_kernel(const u8* __restrict__ lanes, const u64 count, const u64 offset, const u64 add, u64* __restrict__ out)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) out[i] = sa40_load(lanes, i) - offset + add;
+}
+
 __device__ __forceinline__ u32 sr_warp_max(u32 v)
 {
     #pragma unroll
@@ -329,6 +353,29 @@ __global__ void scatter_parts_kernel(const u16* __restrict__ pid, const u64 firs
     if(live) lane_store(staging, part_first[part] + base + __popc(peers & lanemask_lt()), first + i + offset);
 }
 
+// The same scatter from a window of a text that is sharded by position, with the generation-0 key beside every lane: the GPU
+// that holds a position's symbols makes its key. T[i] is the symbol at position first + i, pid[i] its partition; both are
+// readable 3 entries past `count` wherever those positions exist (the neighbour's first entries), T is zero past the text's end.
+__global__ void scatter_parts_keys_kernel(const u16* __restrict__ T, const u16* __restrict__ pid, const u64 first, const u64 count, const u64 n, const u64 offset,
+                                          const u16* __restrict__ part_of_pid, const u64* __restrict__ part_first, u64* __restrict__ cursor,
+                                          u8* __restrict__ lanes, u64* __restrict__ keys)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    u32 part = i < count ? u32(part_of_pid[pid[i]]) : 0xFFFFFFFFu;
+    if(part != 0xFFFFFFFFu && part_first[part] == ~0ull) part = 0xFFFFFFFFu;
+    const bool live = part != 0xFFFFFFFFu;
+    const u32 peers = __match_any_sync(0xFFFFFFFFu, part);
+    u64 base = 0;
+    if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + part), (unsigned long long)__popc(peers));
+    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(peers) - 1);
+    if(!live) return;
+    const u64 slot = part_first[part] + base + __popc(peers & lanemask_lt());
+    const u64 x = first + i, next = x + 3;
+    const u64 tag = next < n ? u64(part_of_pid[pid[i + 3]]) + 3 : (n + 2 - next);
+    lane_store(lanes, slot, x + offset);
+    keys[slot] = (u64(T[i]) << 48) | (u64(T[i + 1]) << 32) | (u64(T[i + 2]) << 16) | tag;
+}
+
 size_t part_workspace_bytes(u64 count)
 {
     const u64 c = count ? count : 1;
@@ -345,7 +392,10 @@ bool is_host_pointer(const void* p)
 }
 
 // The common body of csa_rank_gen0 (h = 0) and csa_rank_gen.
-int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_result* out)
+// given_keys: generation 0 with the caller's keys (device memory, in the order of in->lanes); given_second: generation t
+// with the caller's second ranks. With either, the store's text, partition ids and rank array are not read, and every new
+// rank leaves as a message.
+int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_result* out, const u64* given_keys = nullptr, const u32* given_second = nullptr)
 {
     if(!ctx || !st || !in || !out) return csa_fail(ctx, CSA_E_INVALID, "part job: null argument");
     out->active = 0; out->messages = 0;
@@ -353,7 +403,7 @@ int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_r
     if(S == 0) return CSA_OK;
     if(S >= (u64(1) << 31)) return csa_fail(ctx, CSA_E_LIMIT, "part job: a part holds fewer than 2^31 suffixes");
     if(!in->lanes || !out->lanes || !out->ranks || (h > 0 && !in->ranks)) return csa_fail(ctx, CSA_E_INVALID, "part job: null buffer");
-    if(h == 0 && !st->pid) return csa_fail(ctx, CSA_E_INVALID, "part job: generation 0 needs the store's partition ids");
+    if(h == 0 && !given_keys && !st->pid) return csa_fail(ctx, CSA_E_INVALID, "part job: generation 0 needs the store's partition ids");
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t need = part_workspace_bytes(S);
     void* ws = nullptr;
@@ -382,11 +432,14 @@ int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_r
     unpack_lanes_kernel<<<blocks, 256, 0, ctx->stream>>>(lanes_in, S, st->position_offset, pos);
     CSA_LAUNCH_CHECK(ctx);
     int bits = 64, prim_shift = 64;
-    if(h == 0)
+    if(given_keys)
+        given_keys0_kernel<<<blocks, 256, 0, ctx->stream>>>(given_keys, S, keysA, idxA);
+    else if(h == 0)
         stream_keys0_kernel<<<blocks, 256, 0, ctx->stream>>>(st->text, st->n, st->pid, st->part_of_pid, pos, S, keysA, idxA, ctx->d_status);
     else
     {
-        stream_keys_kernel<<<blocks, 256, 0, ctx->stream>>>(st->rank, st->n, h, pos, ranks_in, S, keysA, idxA, ctx->d_status);
+        if(given_second) given_second_kernel<<<blocks, 256, 0, ctx->stream>>>(given_second, ranks_in, S, keysA, idxA);
+        else stream_keys_kernel<<<blocks, 256, 0, ctx->stream>>>(st->rank, st->n, h, pos, ranks_in, S, keysA, idxA, ctx->d_status);
         bits = 64; prim_shift = 32;
     }
     CSA_LAUNCH_CHECK(ctx);
@@ -400,7 +453,7 @@ int rank_part(csa_ctx* ctx, csa_store* st, const csa_part* in, u64 h, csa_part_r
 
     // messages: generation 0 writes R itself (nothing reads R before generation 1); later generations fill the outbox
     u64 box_first = 0;
-    const bool boxed = h > 0;
+    const bool boxed = h > 0 || given_keys != nullptr;
     if(boxed)
     {
         box_first = st->box_count.fetch_add(S);
@@ -556,6 +609,47 @@ extern "C" int csa_rank_gen(csa_ctx* ctx, csa_store* st, const csa_part* in, uin
 {
     if(h == 0) return csa_fail(ctx, CSA_E_INVALID, "csa_rank_gen: h must be positive");
     return rank_part(ctx, st, in, h, out);
+}
+
+extern "C" int csa_rank_gen0_keys(csa_ctx* ctx, csa_store* st, const csa_part* in, const uint64_t* keys_dev, csa_part_result* out)
+{
+    if(!keys_dev) return csa_fail(ctx, CSA_E_INVALID, "csa_rank_gen0_keys: null keys");
+    return rank_part(ctx, st, in, 0, out, reinterpret_cast<const u64*>(keys_dev), nullptr);
+}
+
+extern "C" int csa_rank_gen_ranks(csa_ctx* ctx, csa_store* st, const csa_part* in, const uint32_t* second_ranks_dev, csa_part_result* out)
+{
+    if(!second_ranks_dev) return csa_fail(ctx, CSA_E_INVALID, "csa_rank_gen_ranks: null second ranks");
+    return rank_part(ctx, st, in, 1, out, nullptr, second_ranks_dev);
+}
+
+extern "C" int csa_part_positions(csa_ctx* ctx, csa_store* st, const uint8_t* lanes, uint64_t count, uint64_t add, uint64_t* positions_dev)
+{
+    if(!ctx || !st || (count && (!lanes || !positions_dev))) return csa_fail(ctx, CSA_E_INVALID, "csa_part_positions: null argument");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* ws = nullptr;
+    CSA_TRY(csa_arena(ctx, align_up256(5 * count + 64), &ws));
+    u8* lanes_in = static_cast<u8*>(ws);
+    CSA_CUDA(ctx, cudaMemcpyAsync(lanes_in, lanes, 5 * count, cudaMemcpyDefault, ctx->stream));
+    CSA_CUDA(ctx, cudaMemsetAsync(lanes_in + 5 * count, 0, 8, ctx->stream));
+    lane_positions_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(lanes_in, count, st->position_offset, add, reinterpret_cast<u64*>(positions_dev));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_scatter_lanes_keys(csa_ctx* ctx, csa_store* st, const uint16_t* text_window_dev, const uint16_t* pid_window_dev, uint64_t first, uint64_t count,
+                                      const uint64_t* part_first_dev, uint64_t* cursor_dev, uint8_t* lanes_dev, uint64_t* keys_dev)
+{
+    if(!ctx || !st || !text_window_dev || !pid_window_dev || !part_first_dev || !cursor_dev || !lanes_dev || !keys_dev || first + count > st->n)
+        return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_lanes_keys: bad argument");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    scatter_parts_keys_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(text_window_dev, pid_window_dev, first, count, st->n, st->position_offset,
+                                                                                     st->part_of_pid, reinterpret_cast<const u64*>(part_first_dev),
+                                                                                     reinterpret_cast<u64*>(cursor_dev), lanes_dev, reinterpret_cast<u64*>(keys_dev));
+    CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
 }
 
 extern "C" int csa_exchange_messages(csa_ctx* ctx, csa_store* st, uint64_t* applied)

@@ -462,3 +462,372 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
                  "launches": sum(c.launches for c in ctxs[:1])})
     segments = [(part_off[u], size[u], lanes_h[5 * own_first[u]:5 * (own_first[u] + size[u])]) for u in own]
     return segments, info
+
+
+# ---- the part-at-a-time build with nothing replicated: text, partition ids and rank store sharded by position ------------------
+
+def shard_bounds(n, world, rank):
+    """Equal stretches of whole 64 positions: (stretch, first position, end) of `rank`'s share of a text of n symbols."""
+    stretch = (-(-n // world) + 63) // 64 * 64
+    lo = min(n, rank * stretch)
+    return stretch, lo, min(n, lo + stretch)
+
+
+def _exchange(send, send_counts, recv_counts, width=1):
+    """All-to-all of one tensor cut into per-rank runs (counts in units of `width` elements). The collective library does it
+    between GPUs; a process group without device all-to-all (several test ranks on one GPU) goes through host memory."""
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if world == 1:
+        return send[:send_counts[0] * width].clone()
+    recv = torch.empty(sum(recv_counts) * width, dtype=send.dtype, device=send.device)
+    ss, rs = [c * width for c in send_counts], [c * width for c in recv_counts]
+    if dist.get_backend() == "nccl":
+        dist.all_to_all_single(recv, send[:sum(ss)].contiguous(), rs, ss)
+    else:
+        r_host = torch.empty(sum(rs), dtype=send.dtype)
+        dist.all_to_all_single(r_host, send[:sum(ss)].cpu().contiguous(), rs, ss)
+        recv.copy_(r_host)
+    return recv
+
+
+def _gather_small(t):
+    """All ranks' copies of a small host-side integer array (numpy int64), as one array [world, len]."""
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if world == 1:
+        return t[None, :].copy()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    mine = torch.from_numpy(np.ascontiguousarray(t, dtype=np.int64)).to(dev)
+    out = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(out, mine)
+    return torch.stack(out).cpu().numpy()
+
+
+def _halo_from_next(local, valid, k):
+    """The k entries that follow this rank's stretch of a position-sharded array: the first entries of the next ranks' stretches
+    (zero past the end of the array). local: device tensor whose first `valid` entries are this rank's."""
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    out = torch.zeros(k, dtype=local.dtype, device=local.device)
+    if world == 1:
+        return out
+    head = torch.zeros(k, dtype=torch.int32, device=local.device)
+    m = min(k, valid)
+    head[:m] = local[:m].to(torch.int32)
+    heads = [torch.empty_like(head) for _ in range(world)]
+    dist.all_gather(heads, head)
+    valids = _gather_small(np.array([m], np.int64))[:, 0]
+    at = 0
+    for g in range(rank + 1, world):
+        take = min(int(valids[g]), k - at)
+        if take > 0:
+            out[at:at + take] = heads[g][:take].to(local.dtype)
+            at += take
+        if at == k:
+            break
+    return out
+
+
+def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=1 << 28, lists_on_device=None):
+    """The part-at-a-time build with NOTHING replicated: rank r of the process group holds the symbols of its stretch of
+    positions only (shard_bounds), and the same stretch of the partition ids and of the rank store; parts are owned as in
+    build_sa_streamed_multi (u mod world). The GPU that holds a stretch of the text makes the generation-0 keys of its positions
+    and sends (lane, key) to the parts' owners; in a later generation the owner of a part asks the owners of the positions
+    h further on for their ranks, and new ranks travel back to the positions' owners as messages. Device memory per GPU:
+    8 n / world bytes (2 text + 2 partition ids until generation 0 is over + 4 ranks) plus the lists of its parts (9 bytes per
+    suffix, on the device while they fit, else in pinned host memory) plus one part's workspace and the windows in flight.
+    text_shard: device uint16 tensor with this rank's symbols first. Returns (segments, info) as build_sa_streamed_multi."""
+    import time
+    from ._lib import Part, PartResult, c_vp
+    L = ctx.L
+    dev = text_shard.device
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    stretch, lo, hi = shard_bounds(n, world, rank)
+    cnt = hi - lo
+    HALO = 64
+    info = {"ms": {}, "nvlink_bytes_sent": 0}
+
+    def mark(name, t0):
+        ctx.sync()
+        torch.cuda.synchronize(dev)
+        info["ms"][name] = info["ms"].get(name, 0.0) + 1e3 * (time.perf_counter() - t0)
+
+    def total_over_ranks(x):
+        if world == 1:
+            return int(x)
+        t = torch.tensor([int(x)], dtype=torch.int64, device=dev)
+        dist.all_reduce(t)
+        return int(t.item())
+
+    def sent(counts, bytes_each):
+        info["nvlink_bytes_sent"] += bytes_each * sum(int(c) for g, c in enumerate(counts) if g != rank)
+
+    t_all = time.perf_counter()
+    t0 = time.perf_counter()
+    # ---- this rank's stretch of the text with the symbols that follow it -------------------------------------------------------
+    T = torch.zeros(cnt + HALO + api.TEXT_PAD, dtype=torch.uint16, device=dev)
+    T[:cnt] = text_shard[:cnt]
+    T[cnt:cnt + HALO] = _halo_from_next(T.view(torch.int16), cnt, HALO).view(torch.uint16)
+    known = min(cnt + HALO, n - lo)                      # symbols of the text in T; zeros follow
+
+    # ---- splitters from samples of every stretch ----------------------------------------------------------------------------------
+    pe, piv = 1, None
+    if p > 1:
+        ns_all = min(1 << 19, max(1024, 32 * p * max(1, int(n).bit_length())))
+        ns = max(64, ns_all // world)
+        samples = torch.zeros(2 * ns, dtype=torch.int64, device=dev)
+        torch.cuda.synchronize(dev)
+        if cnt > 0:
+            ctx.check(L.csa_sample_kgrams(ctx.h, T.data_ptr(), cnt, ns, seed + rank, samples.data_ptr()))
+            ctx.sync()
+        if world > 1:
+            every = [torch.empty_like(samples) for _ in range(world)]
+            dist.all_gather(every, samples)
+            have = _gather_small(np.array([cnt > 0], np.int64))[:, 0]
+            samples = torch.cat([e for e, ok in zip(every, have) if ok])
+        sh = np.ascontiguousarray(samples.cpu().numpy().view(np.uint64))
+        piv = np.zeros(2 * (p - 1), np.uint64)
+        p_out = ctypes.c_uint32(0)
+        rc = L.csa_select_pivots(sh.ctypes.data, len(sh) // 2, p, piv.ctypes.data, ctypes.byref(p_out))
+        if rc != 0:
+            raise api.CascadeError(rc, "csa_select_pivots")
+        pe = p_out.value
+        del samples
+    pivd = torch.from_numpy(piv.view(np.int64)).to(dev) if pe > 1 else None
+
+    # ---- partition ids of this stretch, with the 3 ids that follow it -------------------------------------------------------------
+    pid = torch.zeros(cnt + 64, dtype=torch.int16, device=dev)
+    hist = torch.zeros(max(pe, 1), dtype=torch.int64, device=dev)
+    torch.cuda.synchronize(dev)
+    if pe > 1:
+        ctx.check(L.csa_install_pivots(ctx.h, piv.ctypes.data, pe))
+    try:
+        step = 1 << 28
+        for first in range(0, cnt, step):
+            ctx.check(L.csa_partition_ids(ctx.h, T.data_ptr(), known, first, min(step, cnt - first), pivd.data_ptr() if pivd is not None else None, pe,
+                                          pid.data_ptr() + 2 * first, hist.data_ptr()))
+        ctx.sync()
+    finally:
+        L.csa_install_pivots(ctx.h, None, 0)
+    pid[cnt:cnt + 3] = _halo_from_next(pid, cnt, 3)
+    if world > 1:
+        dist.all_reduce(hist)
+    sizes = hist.cpu().numpy()
+    part_of_pid, part_off = group_partitions_into_parts(sizes, part_suffixes)
+    parts = len(part_off) - 1
+    if part_off[-1] != n:
+        raise api.CascadeError(5, "partition sizes do not add up to n")
+    size = [int(part_off[u + 1] - part_off[u]) for u in range(parts)]
+    owner = [u % world for u in range(parts)]
+    own = [u for u in range(parts) if owner[u] == rank]
+    mark("partition_ids", t0)
+
+    t0 = time.perf_counter()
+    R = torch.zeros(cnt + 16, dtype=torch.int32, device=dev)              # this stretch of the rank store
+    unused = torch.zeros(16, dtype=torch.int32, device=dev)               # the store object keeps no rank array of its own here
+    store = c_vp()
+    torch.cuda.synchronize(dev)
+    ctx.check(L.csa_store_create(ctx.h, T.data_ptr(), n, pid.data_ptr(), part_of_pid.ctypes.data, pe, unused.data_ptr(), ctypes.byref(store)))
+    try:
+        # how many positions of every part each rank holds
+        local_d = torch.zeros(parts, dtype=torch.int64, device=dev)
+        if cnt > 0:
+            ctx.check(L.csa_part_sizes(ctx.h, store, 0, cnt, parts, local_d.data_ptr()))
+            ctx.sync()
+        held = _gather_small(local_d.cpu().numpy())                       # [world, parts]
+        if not np.array_equal(held.sum(axis=0), np.array(size)):
+            raise api.CascadeError(5, "the ranks' counts of a part do not add up to its size")
+
+        # where this rank's lists live
+        own_first, at = {}, 0
+        for u in own:
+            own_first[u] = at
+            at += size[u]
+        own_total = at
+        largest = max(size) if size else 1
+        if lists_on_device is None:
+            torch.cuda.empty_cache()
+            free_b, _ = torch.cuda.mem_get_info(dev)
+            lists_on_device = 9 * own_total + 26 * window_suffixes + int(L.csa_part_workspace_bytes(largest)) + 40 * largest + (4 << 30) < free_b
+        if lists_on_device:
+            lanes_all = torch.empty(5 * own_total + 64, dtype=torch.uint8, device=dev)
+            ranks_all = torch.empty(own_total + 16, dtype=torch.int32, device=dev)
+        else:
+            lanes_all = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+            ranks_all = torch.empty(own_total + 16, dtype=torch.int32).pin_memory()
+        out_lanes = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+        info["lists_on_device"] = bool(lists_on_device)
+
+        def lists(u):
+            return lanes_all.data_ptr() + 5 * own_first[u], ranks_all.data_ptr() + 4 * own_first[u]
+
+        def route_messages(pos, ranks):
+            """(position, rank) messages to the owners of the positions, applied to their stretch of the rank store."""
+            dest = torch.div(pos, stretch, rounding_mode="floor")
+            order = torch.argsort(dest, stable=True)
+            counts = torch.bincount(dest, minlength=world).cpu().numpy()[:world]
+            incoming = _gather_small(counts)[:, rank] if world > 1 else counts
+            sent(counts, 12)
+            got_pos = _exchange(pos[order], [int(c) for c in counts], [int(c) for c in incoming])
+            got_rank = _exchange(ranks[order], [int(c) for c in counts], [int(c) for c in incoming])
+            if got_pos.numel():
+                at_ = got_pos - lo
+                if int(at_.min()) < 0 or int(at_.max()) >= cnt:
+                    raise api.CascadeError(5, "a rank message for a position outside this stretch")
+                R[at_] = got_rank
+            return int(got_pos.numel())
+
+        def outbox_tensors(capacity):
+            box_l = torch.empty(capacity + 16, dtype=torch.int32, device=dev)
+            box_h = torch.empty(capacity + 16, dtype=torch.uint8, device=dev)
+            box_r = torch.empty(capacity + 16, dtype=torch.int32, device=dev)
+            torch.cuda.synchronize(dev)
+            ctx.check(L.csa_store_use_outbox(store, box_l.data_ptr(), box_h.data_ptr(), box_r.data_ptr(), capacity))
+            return box_l, box_h, box_r
+
+        def flush_outbox(box):
+            box_l, box_h, box_r = box
+            m = int(L.csa_store_outbox_count(store))
+            ctx.sync()
+            pos = (box_h[:m].to(torch.int64) << 32) | (box_l[:m].to(torch.int64) & 0xFFFFFFFF)
+            applied = route_messages(pos, box_r[:m])
+            ctx.check(L.csa_store_use_outbox(store, None, None, None, 0))
+            return m, applied
+        mark("setup", t0)
+
+        # ---- generation 0, a window of parts at a time ---------------------------------------------------------------------------------
+        # Every rank picks the window's positions out of its stretch with their keys, the runs travel to the parts' owners, and
+        # an owner ranks a part once its pieces from all ranks lie one after another.
+        t0 = time.perf_counter()
+        active = {u: 0 for u in own}
+        windows, cur, cur_n = [], [], 0
+        for u in range(parts):
+            if cur and cur_n + size[u] > window_suffixes * world:
+                windows.append(cur)
+                cur, cur_n = [], 0
+            cur.append(u)
+            cur_n += size[u]
+        if cur:
+            windows.append(cur)
+        first_d = torch.empty(parts, dtype=torch.int64, device=dev)
+        cursor_d = torch.zeros(parts, dtype=torch.int64, device=dev)
+        for wparts in windows:
+            by_owner = sorted(wparts, key=lambda u: (owner[u], u))
+            pf = np.full(parts, -1, np.int64)
+            at = 0
+            for u in by_owner:
+                pf[u] = at
+                at += int(held[rank, u])
+            mine_n = at
+            send_counts = [sum(int(held[rank, u]) for u in wparts if owner[u] == g) for g in range(world)]
+            my_parts = [u for u in wparts if owner[u] == rank]
+            recv_counts = [sum(int(held[g, u]) for u in my_parts) for g in range(world)]
+            st_lanes = torch.empty(5 * mine_n + 64, dtype=torch.uint8, device=dev)
+            st_keys = torch.empty(mine_n + 8, dtype=torch.int64, device=dev)
+            first_d.copy_(torch.from_numpy(pf))
+            cursor_d.zero_()
+            torch.cuda.synchronize(dev)
+            sweep = 1 << 30
+            for first in range(0, cnt, sweep):
+                ctx.check(L.csa_scatter_lanes_keys(ctx.h, store, T.data_ptr() + 2 * first, pid.data_ptr() + 2 * first, lo + first, min(sweep, cnt - first),
+                                                   first_d.data_ptr(), cursor_d.data_ptr(), st_lanes.data_ptr(), st_keys.data_ptr()))
+            ctx.sync()
+            sent(send_counts, 13)
+            got_lanes = _exchange(st_lanes, send_counts, recv_counts, width=5)
+            got_keys = _exchange(st_keys, send_counts, recv_counts)
+            del st_lanes, st_keys
+            box = outbox_tensors(sum(size[u] for u in my_parts))
+            src_at = np.concatenate([[0], np.cumsum(recv_counts)])[:world].astype(np.int64)      # where each rank's block starts
+            for u in my_parts:
+                pieces_l, pieces_k = [], []
+                for g in range(world):
+                    a = int(src_at[g]) + sum(int(held[g, v]) for v in my_parts if v < u)
+                    c = int(held[g, u])
+                    pieces_l.append(got_lanes[5 * a:5 * (a + c)])
+                    pieces_k.append(got_keys[a:a + c])
+                pl = torch.cat(pieces_l + [torch.zeros(64, dtype=torch.uint8, device=dev)])
+                pk = torch.cat(pieces_k + [torch.zeros(8, dtype=torch.int64, device=dev)])
+                torch.cuda.synchronize(dev)
+                lp, rp = lists(u)
+                pin, pout = Part(pl.data_ptr(), None, size[u], u), PartResult(lp, rp, 0, 0)
+                ctx.check(L.csa_rank_gen0_keys(ctx.h, store, ctypes.byref(pin), pk.data_ptr(), ctypes.byref(pout)))
+                ctx.sync()
+                active[u] = int(pout.active)
+                del pl, pk
+            del got_lanes, got_keys
+            flush_outbox(box)
+            del box
+        L.csa_store_drop_partition_ids(store)
+        del pid
+        total_active = total_over_ranks(sum(active.values()))
+        info["active_after_gen0"] = total_active
+        mark("gen0", t0)
+
+        # ---- doubling generations: the ranks go through their parts in step, one part each per round -----------------------------
+        t0 = time.perf_counter()
+        h, gens = 3, 0
+        info["active_per_generation"] = []
+        rounds = -(-parts // world)
+        while total_active > 0:
+            info["active_per_generation"].append(total_active)
+            box = outbox_tensors(sum(active.values()))
+            for k in range(rounds):
+                u = own[k] if k < len(own) else None
+                a = active[u] if u is not None else 0
+                ask = torch.empty(a + 8, dtype=torch.int64, device=dev)
+                if a:
+                    torch.cuda.synchronize(dev)
+                    ctx.check(L.csa_part_positions(ctx.h, store, lists(u)[0], a, h, ask.data_ptr()))
+                    ctx.sync()
+                ask = ask[:a]
+                dest = torch.div(ask, stretch, rounding_mode="floor")
+                order = torch.argsort(dest, stable=True)
+                counts = torch.bincount(dest, minlength=world).cpu().numpy()[:world] if a else np.zeros(world, np.int64)
+                incoming = _gather_small(counts)[:, rank] if world > 1 else counts
+                sc, rc_ = [int(c) for c in counts], [int(c) for c in incoming]
+                sent(sc, 8)
+                asked = _exchange(ask[order], sc, rc_)
+                if asked.numel():
+                    at_ = asked - lo
+                    if int(at_.min()) < 0 or int(at_.max()) >= cnt:
+                        raise api.CascadeError(5, "a rank was asked for a position outside this stretch")
+                    answers = R[at_]
+                else:
+                    answers = torch.empty(0, dtype=torch.int32, device=dev)
+                sent(rc_, 4)
+                back = _exchange(answers, rc_, sc)
+                if a:
+                    second = torch.empty(a + 8, dtype=torch.int32, device=dev)
+                    second[order] = back
+                    torch.cuda.synchronize(dev)
+                    lp, rp = lists(u)
+                    pin, pout = Part(lp, rp, a, u), PartResult(lp, rp, 0, 0)
+                    ctx.check(L.csa_rank_gen_ranks(ctx.h, store, ctypes.byref(pin), second.data_ptr(), ctypes.byref(pout)))
+                    ctx.sync()
+                    active[u] = int(pout.active)
+                    del second
+            flush_outbox(box)
+            del box
+            total_active = total_over_ranks(sum(active.values()))
+            h *= 2
+            gens += 1
+            if gens > 45:
+                raise api.CascadeError(5, "doubling did not terminate")
+        info["generations"] = gens
+        mark("doubling", t0)
+
+        # ---- every part into its final order -------------------------------------------------------------------------------------------
+        t0 = time.perf_counter()
+        for u in own:
+            lp, rp = lists(u)
+            ctx.check(L.csa_rank_order(ctx.h, lp, rp, size[u], out_lanes.data_ptr() + 5 * own_first[u]))
+        ctx.sync()
+        mark("output", t0)
+        del lanes_all, ranks_all
+    finally:
+        L.csa_store_destroy(store)
+    info["ms"]["total"] = 1e3 * (time.perf_counter() - t_all)
+    info.update({"partitions": pe, "parts": parts, "own_parts": len(own), "own_suffixes": own_total, "launches": ctx.launches,
+                 "device_bytes_per_position": 8.0 / world})
+    segments = [(int(part_off[u]), size[u], out_lanes[5 * own_first[u]:5 * (own_first[u] + size[u])]) for u in own]
+    return segments, info

@@ -262,6 +262,25 @@ int csa_rank_gen0(csa_ctx* ctx, csa_store* store, const csa_part* in, csa_part_r
  * so every part of a generation reads the ranks of the generation before. Replaces sort_and_re_rank_and_filter
  * (src/GPU_SACA.cu:1714-1995) with its message emission (include/GPU_SACA.cuh:291-353). */
 int csa_rank_gen(csa_ctx* ctx, csa_store* store, const csa_part* in, uint64_t h, csa_part_result* out);
+/* The same jobs for a text and a rank store that are sharded by position over several GPUs (no replica of either): the GPU
+ * that holds a stretch of the text makes the generation-0 keys of its positions, and second ranks are fetched from the GPUs
+ * that own them, before the job runs. The reference keeps every partition's positions and inboxes apart in the same way and
+ * joins them by messages (src/Partition_Backend.cpp:516-553); here the caller's collective carries them between the GPUs.
+ * csa_scatter_lanes_keys: as csa_scatter_lanes over the window [first, first + count) of the text, writing beside every lane
+ *   its generation-0 key (3 symbols, then the tag of the suffix 3 symbols on). text_window_dev[i] is the symbol at position
+ *   first + i and pid_window_dev[i] its partition id; both must be readable 3 entries past `count` where those positions
+ *   exist, and the text must read as zero past its end. The store's own text and partition ids are not read.
+ * csa_rank_gen0_keys: generation 0 of a part from such keys (device memory, in the order of in->lanes). Every suffix's first
+ *   rank leaves as a message in the outbox (csa_store_use_outbox); the store's rank array is not written.
+ * csa_part_positions: positions_dev[i] = position of lanes[i] + add, as 64-bit words: the addresses whose ranks generation t
+ *   needs (add = h). lanes may be host or device memory.
+ * csa_rank_gen_ranks: generation t of a part with second_ranks_dev[i] = the stored rank of the suffix h symbols after
+ *   in->lanes[i] (device memory), however the caller got it. Messages as in csa_rank_gen. */
+int csa_scatter_lanes_keys(csa_ctx* ctx, csa_store* store, const uint16_t* text_window_dev, const uint16_t* pid_window_dev, uint64_t first,
+                           uint64_t count, const uint64_t* part_first_dev, uint64_t* cursor_dev, uint8_t* lanes_dev, uint64_t* keys_dev);
+int csa_rank_gen0_keys(csa_ctx* ctx, csa_store* store, const csa_part* in, const uint64_t* keys_dev, csa_part_result* out);
+int csa_part_positions(csa_ctx* ctx, csa_store* store, const uint8_t* lanes, uint64_t count, uint64_t add, uint64_t* positions_dev);
+int csa_rank_gen_ranks(csa_ctx* ctx, csa_store* store, const csa_part* in, const uint32_t* second_ranks_dev, csa_part_result* out);
 /* After the last part of a generation: applies the outbox to the rank store and empties it; *applied = messages applied.
  * Stands where the reference routes messages to the inboxes of their target partitions between two generations
  * (src/Partition_Backend.cpp:516-553, include/message.hpp:22-61). */

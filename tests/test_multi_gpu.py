@@ -226,3 +226,65 @@ def test_part_at_a_time_build_over_several_ranks(world):
             assert np.array_equal(lanes, ref[5 * first:5 * (first + count)]), f"rank {rank}'s part at {first} differs"
             covered[first:first + count] += 1
     assert np.all(covered == 1)
+
+
+def _sharded_worker(rank, world, port, n, p, part_suffixes, window, on_device, offset, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from cascade_b200 import api, multi
+    from cascade_b200._lib import lib
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    ctx = api.Context(dev)
+    T = api.gen_corpus_device(ctx, n, 11, 256)
+    _, lo, hi = multi.shard_bounds(n, world, rank)
+    mine = T[lo:hi].clone()                      # all that this rank gives the build
+    if offset:
+        assert lib().csa_debug_set(4, offset) == 0
+    try:
+        segs, info = multi.build_sa_sharded(ctx, mine, n, p, part_suffixes=part_suffixes, window_suffixes=window, lists_on_device=on_device)
+    finally:
+        lib().csa_debug_set(4, 0)
+    ref = None
+    if rank == 0:
+        r, _ = api.build_sa(ctx, T, n, 16)
+        ref = r[:5 * n].cpu().numpy()
+    q.put((rank, [(f, c, t.numpy().copy()) for f, c, t in segs], ref, info["generations"], info["parts"]))
+    dist.barrier()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n,p,part_suffixes,window,on_device,offset", [
+    (1, 300_001, 64, 40_000, 100_000, True, 0),
+    (2, 700_001, 64, 50_000, 120_000, False, 0),
+    (3, 700_001, 300, 50_000, 1 << 28, True, 0),
+    (3, 1_000, 8, 100, 300, None, 0),                        # stretches of a few hundred positions
+    (2, 400_000, 32, 60_000, 1 << 28, True, (1 << 33) + 5),   # every lane above 2^32
+])
+def test_build_with_text_and_rank_store_sharded_by_position(world, n, p, part_suffixes, window, on_device, offset):
+    """Nothing is replicated: a rank holds its stretch of the text, of the partition ids and of the rank store only; keys and
+    ranks travel between the ranks. The parts, put together, are the resident build's array (shifted by the test offset)."""
+    from conftest import sa40_to_u64
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_sharded_worker, args=(r, world, port, n, p, part_suffixes, window, on_device, offset, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted((q.get(timeout=240) for _ in range(world)), key=lambda x: x[0])
+    for pr in procs:
+        pr.join(timeout=120)
+        assert pr.exitcode == 0
+    ref = res[0][2]
+    want = sa40_to_u64(ref, n) + np.uint64(offset)
+    covered = np.zeros(n, np.uint8)
+    for rank, segs, _, gens, parts in res:
+        assert gens >= 1
+        for first, count, lanes in segs:
+            assert np.array_equal(sa40_to_u64(lanes, count), want[first:first + count]), f"rank {rank}'s part at {first} differs"
+            covered[first:first + count] += 1
+    assert np.all(covered == 1)
