@@ -752,6 +752,86 @@ def run_c4(args):
         dist.destroy_process_group()
 
 
+def run_c4_sharded(args):
+    """The part-at-a-time build with nothing replicated (cascade_b200/multi.py: build_sa_sharded): every rank makes and holds its
+    own stretch of the corpus only, and the same stretch of the partition ids and the rank store; keys and ranks travel between
+    the GPUs. Strong scaling on a corpus beyond 2^32 tokens; wall time of the whole build, max over ranks. Where the whole
+    text, the whole array and the checker's workspace fit one device, the array is put together and checked in full on rank 0."""
+    import torch
+    import torch.distributed as dist
+    from cascade_b200 import api, multi
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n = args.tokens if args.tokens != C2_TOKENS else 4_500_000_000
+    p = 4096
+    ps = args.part_suffixes or (1 << 27)
+    ctx = api.Context(local)
+    _, lo, hi = multi.shard_bounds(n, world, rank)
+    mine = api.gen_corpus_device_window(ctx, lo, hi - lo, 0, C2_MEAN_DOC)
+    host, times, infos = {}, [], []
+    with ClockSampler(local) as clocks:
+        for it in range(1 + max(1, min(args.steps, 2))):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            segs, info = multi.build_sa_sharded(ctx, mine, n, p, part_suffixes=ps, host=host)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            if world > 1:
+                dt = _max_over_ranks(dt, dev)
+            if it > 0:
+                times.append(dt)
+                infos.append(info)
+    info = infos[-1]
+    sec = sum(times) / len(times)
+    del mine
+    torch.cuda.empty_cache()
+    v = None
+    need = 2 * n + 5 * n + int(ctx.L.csa_validate_workspace_bytes(n)) + (2 << 30)
+    free_b, _ = torch.cuda.mem_get_info(dev)
+    if need < free_b:
+        full = torch.zeros(5 * n + api.SA_PAD_BYTES, dtype=torch.uint8, device=dev)
+        for first, count, lanes in segs:
+            full[5 * first:5 * (first + count)].copy_(lanes, non_blocking=True)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.all_reduce(full)
+        if rank == 0:
+            T = api.gen_corpus_device(ctx, n, 0, C2_MEAN_DOC)
+            v = api.validate_sa(ctx, T, n, full)
+            del T
+        del full
+    sent_all = info["nvlink_bytes_sent"]
+    if world > 1:
+        t = torch.tensor([sent_all], dtype=torch.int64, device=dev)
+        dist.all_reduce(t)
+        sent_all = int(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": n / sec, "unit": UNIT, "n_gpus": world, "steps": len(times), "warmup": 1, "ms_per_step": 1e3 * sec,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                          "config": {"workload": "part-at-a-time build with text, partition ids and rank store sharded by position (nothing replicated): "
+                                                 "a scaled-down stand-in for BASELINE config 4", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
+                                     "partitions_asked": p, "part_suffixes": ps, "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0, "gpus": world,
+                                     "device_bytes_per_position_per_gpu": 8.0 / world, "lists_on_device": info["lists_on_device"]},
+                          "timed": "wall clock of the whole build from each rank's stretch of the text in its HBM to the parts in final order in pinned host "
+                                   "memory; max over ranks",
+                          "clocks": clocks.summary(), "partitions": info["partitions"], "parts": info["parts"], "generations": info["generations"],
+                          "active_per_generation": info["active_per_generation"], "phases_ms_rank0": info["ms"], "gpu_launches": info["launches"],
+                          "nvlink_bytes_sent_all_ranks": sent_all,
+                          "validated": None if v is None else bool(v["ok"]), "validation": v if v is not None else "the whole text and array do not fit one device"}))
+    if world > 1:
+        dist.barrier()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_repeat(args):
     """BASELINE config 3 alone (it is also a key of the default line)."""
     from cascade_b200 import api
@@ -778,7 +858,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sort-baseline", action="store_true")
-    ap.add_argument("--workload", default="zipf", choices=["zipf", "repeat", "c4"],
+    ap.add_argument("--workload", default="zipf", choices=["zipf", "repeat", "c4", "c4-sharded"],
                     help="zipf: BASELINE config 2; repeat: config 3 alone (1e9 tokens of near-duplicate documents, build only); "
                          "c4: the part-at-a-time build on more than 2^32 tokens (one-GPU stand-in for config 4)")
     ap.add_argument("--part-suffixes", type=int, default=0, help="c4: most suffixes of a part (0 = the library's default, 2^27)")
@@ -797,6 +877,8 @@ def main():
         return run_micro_sort(args)
     if args.workload == "c4":
         return run_c4(args)
+    if args.workload == "c4-sharded":
+        return run_c4_sharded(args)
     if args.workload == "repeat":
         return run_repeat(args)
     run_ours(args)

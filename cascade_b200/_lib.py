@@ -95,6 +95,11 @@ _SIGS = {
     "csa_rank_gen0_keys": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_vp, ctypes.POINTER(PartResult)]),
     "csa_part_positions": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u64, c_vp]),
     "csa_rank_gen_ranks": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_vp, ctypes.POINTER(PartResult)]),
+    "csa_bucket_by_owner": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u64, c_u32, c_vp, c_vp, c_vp, c_vp]),
+    "csa_rank_shard_read": (c_int, [c_vp, c_vp, c_u64, c_u64, c_vp, c_u64, c_vp]),
+    "csa_rank_shard_apply": (c_int, [c_vp, c_vp, c_u64, c_u64, c_vp, c_vp, c_u64]),
+    "csa_unbucket": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),
+    "csa_outbox_positions": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),
     "csa_exchange_messages": (c_int, [c_vp, c_vp, ctypes.POINTER(c_u64)]),
     "csa_rank_order": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),
     "csa_build_sa_streamed": (c_int, [c_vp, c_vp, c_u64, c_u32, c_u64, c_vp, c_u64, ctypes.POINTER(BuildStats)]),
@@ -116,6 +121,7 @@ _SIGS = {
     "csa_query_host": (c_int, [c_vp, ctypes.POINTER(Index), c_vp, c_vp, c_u64, c_u32, c_vp, c_vp, c_vp, c_vp, c_u64, ctypes.POINTER(c_u64)]),
     "csa_query_plan": (c_int, [c_u64, c_u64, c_u64, c_u64, c_int, ctypes.POINTER(QueryPlacement)]),
     "csa_gen_corpus_dev": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u32, c_vp, c_u32]),
+    "csa_gen_corpus_dev_window": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u64, c_u32, c_vp, c_u32]),
     "csa_gen_queries_host": (c_int, [c_int, c_vp, c_u64, c_u64, c_vp, c_u32, c_u64, c_u64, c_vp, c_vp, c_u64]),
     "csa_counts_hash": (c_u64, [c_vp, c_u64]),
     "csa_gen_corpus_host": (c_int, [c_vp, c_u64, c_u64, c_u64, c_u32, c_vp, c_u32]),

@@ -112,6 +112,18 @@ def gen_corpus_device(ctx, n, seed=0, mean_doc=512, cdf=None):
     return T
 
 
+def gen_corpus_device_window(ctx, first, count, seed=0, mean_doc=512, cdf=None):
+    """The symbols first .. first + count - 1 of the same corpus, followed by TEXT_PAD zeros: one GPU's stretch of a sharded text."""
+    cdf = zipf_cdf() if cdf is None else cdf
+    dev = torch.device("cuda", ctx.device)
+    cdf_t = torch.from_numpy(cdf.view(np.int64)).to(dev)
+    T = torch.zeros(count + TEXT_PAD, dtype=torch.uint16, device=dev)
+    torch.cuda.synchronize(dev)
+    ctx.check(ctx.L.csa_gen_corpus_dev_window(ctx.h, T.data_ptr(), first, count, seed, mean_doc, cdf_t.data_ptr(), len(cdf)))
+    ctx.sync()
+    return T
+
+
 def gen_repeat_corpus_host(n, seed=0, base_docs=4096, mean_doc=2048, mutate=0.001, vocab=50257, cdf=None):
     """The repetitive corpus: `base_docs` Zipf documents, then copies of random base documents with a fraction
     `mutate` of their tokens replaced by uniform ids, each preceded by 0xFFFF, cut at n symbols (numpy, host)."""

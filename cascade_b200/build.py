@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcascade_b200.so")
-SOURCES = ["ctx.cu", "radix_sort.cu", "partition.cu", "doubling.cu", "build_sa.cu", "build_multi.cu", "exchange.cu", "comm_shm.cu", "query.cu", "corpus.cu", "host_tools.cu", "validate.cu", "stream_build.cu", "symbols.cu"]
+SOURCES = ["ctx.cu", "radix_sort.cu", "partition.cu", "doubling.cu", "build_sa.cu", "build_multi.cu", "exchange.cu", "comm_shm.cu", "query.cu", "corpus.cu", "host_tools.cu", "validate.cu", "stream_build.cu", "symbols.cu", "rank_shards.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-O3,-fopenmp", "--expt-relaxed-constexpr",

@@ -51,10 +51,10 @@ __host__ __device__ __forceinline__ u16 symbol_at(u64 seed, u64 i, u32 mean_doc,
     return is_separator(seed, i, mean_doc) ? u16(0xFFFF) : token_at(seed, i, cdf, vocab);
 }
 
-__global__ void gen_corpus_kernel(u16* __restrict__ T, const u64 n, const u64 seed, const u32 mean_doc, const u64* __restrict__ cdf, const u32 vocab)
+__global__ void gen_corpus_kernel(u16* __restrict__ T, const u64 first, const u64 n, const u64 seed, const u32 mean_doc, const u64* __restrict__ cdf, const u32 vocab)
 {
     const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    if(i < n) T[i] = symbol_at(seed, i, mean_doc, cdf, vocab);
+    if(i < n) T[i] = symbol_at(seed, first + i, mean_doc, cdf, vocab);
 }
 
 }   // namespace
@@ -64,8 +64,22 @@ extern "C" int csa_gen_corpus_dev(csa_ctx* ctx, uint16_t* text, uint64_t n, uint
     if(!ctx || !text || !cdf || mean_doc == 0 || vocab == 0 || vocab > 65535) return csa_fail(ctx, CSA_E_INVALID, "csa_gen_corpus_dev: bad argument");
     if(n == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    gen_corpus_kernel<<<unsigned(div_up(n, 256)), 256, 0, ctx->stream>>>(text, n, seed, mean_doc, reinterpret_cast<const u64*>(cdf), vocab);
+    gen_corpus_kernel<<<unsigned(div_up(n, 256)), 256, 0, ctx->stream>>>(text, 0, n, seed, mean_doc, reinterpret_cast<const u64*>(cdf), vocab);
     CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_gen_corpus_dev_window(csa_ctx* ctx, uint16_t* text, uint64_t first, uint64_t count, uint64_t seed, uint32_t mean_doc, const uint64_t* cdf, uint32_t vocab)
+{
+    if(!ctx || !text || !cdf || mean_doc == 0 || vocab == 0 || vocab > 65535) return csa_fail(ctx, CSA_E_INVALID, "csa_gen_corpus_dev_window: bad argument");
+    if(count == 0) return CSA_OK;
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    for(u64 at = 0; at < count; at += u64(1) << 30)
+    {
+        const u64 c = count - at < (u64(1) << 30) ? count - at : (u64(1) << 30);
+        gen_corpus_kernel<<<unsigned(div_up(c, 256)), 256, 0, ctx->stream>>>(text + at, first + at, c, seed, mean_doc, reinterpret_cast<const u64*>(cdf), vocab);
+        CSA_LAUNCH_CHECK(ctx);
+    }
     return CSA_OK;
 }
 

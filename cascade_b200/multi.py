@@ -527,7 +527,7 @@ def _halo_from_next(local, valid, k):
     return out
 
 
-def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=1 << 28, lists_on_device=None):
+def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=1 << 28, lists_on_device=None, host=None):
     """The part-at-a-time build with NOTHING replicated: rank r of the process group holds the symbols of its stretch of
     positions only (shard_bounds), and the same stretch of the partition ids and of the rank store; parts are owned as in
     build_sa_streamed_multi (u mod world). The GPU that holds a stretch of the text makes the generation-0 keys of its positions
@@ -535,7 +535,8 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
     h further on for their ranks, and new ranks travel back to the positions' owners as messages. Device memory per GPU:
     8 n / world bytes (2 text + 2 partition ids until generation 0 is over + 4 ranks) plus the lists of its parts (9 bytes per
     suffix, on the device while they fit, else in pinned host memory) plus one part's workspace and the windows in flight.
-    text_shard: device uint16 tensor with this rank's symbols first. Returns (segments, info) as build_sa_streamed_multi."""
+    text_shard: device uint16 tensor with this rank's symbols first. `host` may be a dict that keeps the pinned buffers between
+    calls. Returns (segments, info) as build_sa_streamed_multi."""
     import time
     from ._lib import Part, PartResult, c_vp
     L = ctx.L
@@ -645,6 +646,7 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             at += size[u]
         own_total = at
         largest = max(size) if size else 1
+        host = host if host is not None else {}
         if lists_on_device is None:
             torch.cuda.empty_cache()
             free_b, _ = torch.cuda.mem_get_info(dev)
@@ -653,29 +655,56 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             lanes_all = torch.empty(5 * own_total + 64, dtype=torch.uint8, device=dev)
             ranks_all = torch.empty(own_total + 16, dtype=torch.int32, device=dev)
         else:
-            lanes_all = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
-            ranks_all = torch.empty(own_total + 16, dtype=torch.int32).pin_memory()
-        out_lanes = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+            if host.get("lanes") is None or host["lanes"].numel() < 5 * own_total + 64:
+                host["lanes"] = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+                host["ranks"] = torch.empty(own_total + 16, dtype=torch.int32).pin_memory()
+            lanes_all, ranks_all = host["lanes"], host["ranks"]
+        if host.get("out") is None or host["out"].numel() < 5 * own_total + 64:
+            host["out"] = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+        out_lanes = host["out"]
         info["lists_on_device"] = bool(lists_on_device)
 
         def lists(u):
             return lanes_all.data_ptr() + 5 * own_first[u], ranks_all.data_ptr() + 4 * own_first[u]
 
+        def bucket(pos, payload, want_order):
+            """pos (and payload) sorted into one run per owner; returns (counts, pos runs, payload runs, order)."""
+            m = int(pos.numel())
+            counts = np.zeros(world, np.uint64)
+            pos_b = torch.empty(m + 8, dtype=torch.int64, device=dev)
+            pay_b = torch.empty(m + 8, dtype=torch.int32, device=dev) if payload is not None else None
+            order = torch.empty(m + 8, dtype=torch.int32, device=dev) if want_order else None
+            torch.cuda.synchronize(dev)
+            ctx.check(L.csa_bucket_by_owner(ctx.h, pos.data_ptr() if m else None, payload.data_ptr() if payload is not None and m else None, m, stretch, world,
+                                            counts.ctypes.data, pos_b.data_ptr(), pay_b.data_ptr() if pay_b is not None else None,
+                                            order.data_ptr() if order is not None else None))
+            ctx.sync()
+            return [int(c) for c in counts], pos_b, pay_b, order
+
         def route_messages(pos, ranks):
-            """(position, rank) messages to the owners of the positions, applied to their stretch of the rank store."""
-            dest = torch.div(pos, stretch, rounding_mode="floor")
-            order = torch.argsort(dest, stable=True)
-            counts = torch.bincount(dest, minlength=world).cpu().numpy()[:world]
-            incoming = _gather_small(counts)[:, rank] if world > 1 else counts
-            sent(counts, 12)
-            got_pos = _exchange(pos[order], [int(c) for c in counts], [int(c) for c in incoming])
-            got_rank = _exchange(ranks[order], [int(c) for c in counts], [int(c) for c in incoming])
-            if got_pos.numel():
-                at_ = got_pos - lo
-                if int(at_.min()) < 0 or int(at_.max()) >= cnt:
-                    raise api.CascadeError(5, "a rank message for a position outside this stretch")
-                R[at_] = got_rank
-            return int(got_pos.numel())
+            """(position, rank) messages to the owners of the positions, applied to their stretch of the rank store; in runs of
+            2^27 messages, as many runs on every rank as the rank with the most messages needs."""
+            run = 1 << 27
+            runs = -(-int(pos.numel()) // run)
+            if world > 1:
+                runs = int(_gather_small(np.array([runs], np.int64)).max())
+            applied = 0
+            for k in range(runs):
+                ps_, rs_ = pos[k * run:(k + 1) * run], ranks[k * run:(k + 1) * run]
+                counts, pos_b, rank_b, _ = bucket(ps_, rs_, False)
+                incoming = [int(c) for c in _gather_small(np.array(counts, np.int64))[:, rank]] if world > 1 else counts
+                sent(counts, 12)
+                got_pos = _exchange(pos_b, counts, incoming)
+                got_rank = _exchange(rank_b, counts, incoming)
+                del pos_b, rank_b
+                m = int(got_pos.numel())
+                if m:
+                    torch.cuda.synchronize(dev)
+                    ctx.check(L.csa_rank_shard_apply(ctx.h, R.data_ptr(), lo, cnt, got_pos.data_ptr(), got_rank.data_ptr(), m))
+                    ctx.sync()
+                    applied += m
+                del got_pos, got_rank
+            return applied
 
         def outbox_tensors(capacity):
             box_l = torch.empty(capacity + 16, dtype=torch.int32, device=dev)
@@ -689,8 +718,18 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             box_l, box_h, box_r = box
             m = int(L.csa_store_outbox_count(store))
             ctx.sync()
-            pos = (box_h[:m].to(torch.int64) << 32) | (box_l[:m].to(torch.int64) & 0xFFFFFFFF)
-            applied = route_messages(pos, box_r[:m])
+            applied, run = 0, 1 << 29                                  # positions as 64-bit words, a run at a time
+            runs = -(-m // run)
+            if world > 1:
+                runs = int(_gather_small(np.array([runs], np.int64)).max())
+            for k in range(runs):
+                a, b = min(m, k * run), min(m, (k + 1) * run)
+                pos = torch.empty(b - a + 8, dtype=torch.int64, device=dev)
+                torch.cuda.synchronize(dev)
+                ctx.check(L.csa_outbox_positions(ctx.h, box_l.data_ptr() + 4 * a, box_h.data_ptr() + a, b - a, pos.data_ptr()))
+                ctx.sync()
+                applied += route_messages(pos[:b - a], box_r[a:b])
+                del pos
             ctx.check(L.csa_store_use_outbox(store, None, None, None, 0))
             return m, applied
         mark("setup", t0)
@@ -779,33 +818,31 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                     torch.cuda.synchronize(dev)
                     ctx.check(L.csa_part_positions(ctx.h, store, lists(u)[0], a, h, ask.data_ptr()))
                     ctx.sync()
-                ask = ask[:a]
-                dest = torch.div(ask, stretch, rounding_mode="floor")
-                order = torch.argsort(dest, stable=True)
-                counts = torch.bincount(dest, minlength=world).cpu().numpy()[:world] if a else np.zeros(world, np.int64)
-                incoming = _gather_small(counts)[:, rank] if world > 1 else counts
-                sc, rc_ = [int(c) for c in counts], [int(c) for c in incoming]
+                sc, ask_b, _, order = bucket(ask[:a], None, True)
+                rc_ = [int(c) for c in _gather_small(np.array(sc, np.int64))[:, rank]] if world > 1 else sc
                 sent(sc, 8)
-                asked = _exchange(ask[order], sc, rc_)
-                if asked.numel():
-                    at_ = asked - lo
-                    if int(at_.min()) < 0 or int(at_.max()) >= cnt:
-                        raise api.CascadeError(5, "a rank was asked for a position outside this stretch")
-                    answers = R[at_]
-                else:
-                    answers = torch.empty(0, dtype=torch.int32, device=dev)
+                asked = _exchange(ask_b, sc, rc_)
+                del ask_b
+                m = int(asked.numel())
+                answers = torch.empty(m + 8, dtype=torch.int32, device=dev)
+                if m:
+                    torch.cuda.synchronize(dev)
+                    ctx.check(L.csa_rank_shard_read(ctx.h, R.data_ptr(), lo, cnt, asked.data_ptr(), m, answers.data_ptr()))
+                    ctx.sync()
                 sent(rc_, 4)
                 back = _exchange(answers, rc_, sc)
+                del asked, answers
                 if a:
                     second = torch.empty(a + 8, dtype=torch.int32, device=dev)
-                    second[order] = back
                     torch.cuda.synchronize(dev)
+                    ctx.check(L.csa_unbucket(ctx.h, order.data_ptr(), back.data_ptr(), a, second.data_ptr()))
                     lp, rp = lists(u)
                     pin, pout = Part(lp, rp, a, u), PartResult(lp, rp, 0, 0)
                     ctx.check(L.csa_rank_gen_ranks(ctx.h, store, ctypes.byref(pin), second.data_ptr(), ctypes.byref(pout)))
                     ctx.sync()
                     active[u] = int(pout.active)
                     del second
+                del back, order
             flush_outbox(box)
             del box
             total_active = total_over_ranks(sum(active.values()))

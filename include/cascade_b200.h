@@ -281,6 +281,23 @@ int csa_scatter_lanes_keys(csa_ctx* ctx, csa_store* store, const uint16_t* text_
 int csa_rank_gen0_keys(csa_ctx* ctx, csa_store* store, const csa_part* in, const uint64_t* keys_dev, csa_part_result* out);
 int csa_part_positions(csa_ctx* ctx, csa_store* store, const uint8_t* lanes, uint64_t count, uint64_t add, uint64_t* positions_dev);
 int csa_rank_gen_ranks(csa_ctx* ctx, csa_store* store, const csa_part* in, const uint32_t* second_ranks_dev, csa_part_result* out);
+/* The rank store sharded by position, one stretch of `stretch` positions per GPU (owner = position / stretch), seen from one GPU:
+ * csa_bucket_by_owner: sorts count (< 2^32) positions into one run per owner, in owner order; counts_host[g] = length of owner
+ *   g's run (valid on return: the call waits for the counts). payload (32-bit words that travel with the positions) and order
+ *   (order_dev[j] = index in the input of the j-th entry of the runs) are optional. The order inside a run is arbitrary.
+ * csa_rank_shard_read: answers_dev[i] = shard_dev[asked_dev[i] - first] for requests that arrived for this GPU's stretch
+ *   [first, first + positions); a request outside it sets the range bit of the status word and reads as 0.
+ * csa_rank_shard_apply: shard_dev[positions_dev[i] - first] = ranks_dev[i] for the messages that arrived for this stretch.
+ * csa_unbucket: out_dev[order_dev[j]] = values_dev[j]: answers back into the order in which the requests were made.
+ * csa_outbox_positions: the outbox's positions (csa_store_use_outbox keeps them as low 32 and high 8 bits) as 64-bit words. */
+int csa_bucket_by_owner(csa_ctx* ctx, const uint64_t* positions_dev, const uint32_t* payload_dev, uint64_t count, uint64_t stretch, uint32_t owners,
+                        uint64_t* counts_host, uint64_t* positions_out_dev, uint32_t* payload_out_dev, uint32_t* order_dev);
+int csa_rank_shard_read(csa_ctx* ctx, const uint32_t* shard_dev, uint64_t first, uint64_t positions, const uint64_t* asked_dev, uint64_t count,
+                        uint32_t* answers_dev);
+int csa_rank_shard_apply(csa_ctx* ctx, uint32_t* shard_dev, uint64_t first, uint64_t positions, const uint64_t* positions_dev, const uint32_t* ranks_dev,
+                         uint64_t count);
+int csa_unbucket(csa_ctx* ctx, const uint32_t* order_dev, const uint32_t* values_dev, uint64_t count, uint32_t* out_dev);
+int csa_outbox_positions(csa_ctx* ctx, const uint32_t* pos_lo_dev, const uint8_t* pos_hi_dev, uint64_t count, uint64_t* positions_dev);
 /* After the last part of a generation: applies the outbox to the rank store and empties it; *applied = messages applied.
  * Stands where the reference routes messages to the inboxes of their target partitions between two generations
  * (src/Partition_Backend.cpp:516-553, include/message.hpp:22-61). */
@@ -456,6 +473,9 @@ int csa_query_plan(uint64_t n, uint64_t device_budget, uint64_t host_budget, uin
  * tokens drawn by inverse CDF from cdf[vocab] (64-bit thresholds). The device and host forms give the same symbols. */
 int csa_gen_corpus_dev(csa_ctx* ctx, uint16_t* text_dev, uint64_t n, uint64_t seed, uint32_t mean_doc,
                        const uint64_t* cdf_dev, uint32_t vocab);
+/* The symbols first .. first + count - 1 of the same corpus into text_dev[0, count): one GPU's stretch of a sharded text. */
+int csa_gen_corpus_dev_window(csa_ctx* ctx, uint16_t* text_dev, uint64_t first, uint64_t count, uint64_t seed, uint32_t mean_doc,
+                              const uint64_t* cdf_dev, uint32_t vocab);
 int csa_gen_corpus_host(uint16_t* text_host, uint64_t first, uint64_t count, uint64_t seed, uint32_t mean_doc,
                         const uint64_t* cdf_host, uint32_t vocab);
 
