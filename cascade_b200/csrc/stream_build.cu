@@ -338,42 +338,59 @@ __global__ void count_parts_kernel(const u16* __restrict__ pid, const u64 count,
     for(u32 i = threadIdx.x; i < parts; i += blockDim.x) if(s_cnt[i]) atomicAdd(reinterpret_cast<unsigned long long*>(hist + i), (unsigned long long)s_cnt[i]);
 }
 
-__global__ void scatter_parts_kernel(const u16* __restrict__ pid, const u64 first, const u64 count, const u64 offset, const u16* __restrict__ part_of_pid,
-                                     const u64* __restrict__ part_first, u64* __restrict__ cursor, u8* __restrict__ staging)
-{
-    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    u32 part = i < count ? u32(part_of_pid[pid[i]]) : 0xFFFFFFFFu;
-    if(part != 0xFFFFFFFFu && part_first[part] == ~0ull) part = 0xFFFFFFFFu;       // a part that the caller does not want now
-    const bool live = part != 0xFFFFFFFFu;
-    // the lanes of a warp that go to one part take their places with one atomic
-    const u32 peers = __match_any_sync(0xFFFFFFFFu, part);
-    u64 base = 0;
-    if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + part), (unsigned long long)__popc(peers));
-    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(peers) - 1);
-    if(live) lane_store(staging, part_first[part] + base + __popc(peers & lanemask_lt()), first + i + offset);
-}
+// A thread takes SP_ITEMS consecutive positions (one 16-byte load of partition ids where the window is aligned), so that the
+// chain of dependent loads (id -> part -> is the part wanted) is paid once per 8 positions, and a warp-item in which no lane
+// has a wanted position costs one ballot. The lanes of a warp that go to one part take their places with one atomic.
+// KEYS: also write the generation-0 key beside every lane (3 symbols, then the tag of the suffix 3 symbols on), for a text
+// that is sharded by position: T[i] is the symbol at position first + i and pid[i] its partition; both are readable 3 entries
+// past `count` wherever those positions exist (the neighbour's first entries), and T is zero past the text's end.
+constexpr int SP_ITEMS = 8;
 
-// The same scatter from a window of a text that is sharded by position, with the generation-0 key beside every lane: the GPU
-// that holds a position's symbols makes its key. T[i] is the symbol at position first + i, pid[i] its partition; both are
-// readable 3 entries past `count` wherever those positions exist (the neighbour's first entries), T is zero past the text's end.
-__global__ void scatter_parts_keys_kernel(const u16* __restrict__ T, const u16* __restrict__ pid, const u64 first, const u64 count, const u64 n, const u64 offset,
-                                          const u16* __restrict__ part_of_pid, const u64* __restrict__ part_first, u64* __restrict__ cursor,
-                                          u8* __restrict__ lanes, u64* __restrict__ keys)
+template <bool KEYS>
+__global__ void __launch_bounds__(256) scatter_parts_kernel(const u16* __restrict__ T, const u16* __restrict__ pid, const u64 first, const u64 count, const u64 n,
+                                                            const u64 offset, const u16* __restrict__ part_of_pid, const u64* __restrict__ part_first,
+                                                            u64* __restrict__ cursor, u8* __restrict__ lanes, u64* __restrict__ keys)
 {
-    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
-    u32 part = i < count ? u32(part_of_pid[pid[i]]) : 0xFFFFFFFFu;
-    if(part != 0xFFFFFFFFu && part_first[part] == ~0ull) part = 0xFFFFFFFFu;
-    const bool live = part != 0xFFFFFFFFu;
-    const u32 peers = __match_any_sync(0xFFFFFFFFu, part);
-    u64 base = 0;
-    if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + part), (unsigned long long)__popc(peers));
-    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(peers) - 1);
-    if(!live) return;
-    const u64 slot = part_first[part] + base + __popc(peers & lanemask_lt());
-    const u64 x = first + i, next = x + 3;
-    const u64 tag = next < n ? u64(part_of_pid[pid[i + 3]]) + 3 : (n + 2 - next);
-    lane_store(lanes, slot, x + offset);
-    keys[slot] = (u64(T[i]) << 48) | (u64(T[i + 1]) << 32) | (u64(T[i + 2]) << 16) | tag;
+    const u64 i0 = (u64(blockIdx.x) * blockDim.x + threadIdx.x) * SP_ITEMS;
+    u16 id[SP_ITEMS];
+    if(i0 + SP_ITEMS <= count && (reinterpret_cast<uintptr_t>(pid + i0) & 15) == 0)
+    {
+        const uint4 v = *reinterpret_cast<const uint4*>(pid + i0);
+        id[0] = u16(v.x); id[1] = u16(v.x >> 16); id[2] = u16(v.y); id[3] = u16(v.y >> 16);
+        id[4] = u16(v.z); id[5] = u16(v.z >> 16); id[6] = u16(v.w); id[7] = u16(v.w >> 16);
+    }
+    else
+    {
+        #pragma unroll
+        for(int j = 0; j < SP_ITEMS; ++j) id[j] = i0 + j < count ? pid[i0 + j] : u16(0);
+    }
+    u32 part[SP_ITEMS];
+    #pragma unroll
+    for(int j = 0; j < SP_ITEMS; ++j) part[j] = i0 + j < count ? u32(part_of_pid[id[j]]) : 0xFFFFFFFFu;
+    u64 run_first[SP_ITEMS];
+    #pragma unroll
+    for(int j = 0; j < SP_ITEMS; ++j) run_first[j] = part[j] != 0xFFFFFFFFu ? part_first[part[j]] : ~0ull;
+    #pragma unroll
+    for(int j = 0; j < SP_ITEMS; ++j)
+    {
+        const bool live = run_first[j] != ~0ull;         // ~0: a part that the caller does not want now
+        if(__ballot_sync(0xFFFFFFFFu, live) == 0) continue;
+        const u32 key_part = live ? part[j] : 0xFFFFFFFFu;
+        const u32 peers = __match_any_sync(0xFFFFFFFFu, key_part);
+        u64 base = 0;
+        if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + key_part), (unsigned long long)__popc(peers));
+        base = __shfl_sync(0xFFFFFFFFu, base, __ffs(peers) - 1);
+        if(!live) continue;
+        const u64 slot = run_first[j] + base + __popc(peers & lanemask_lt());
+        const u64 i = i0 + j, x = first + i;
+        lane_store(lanes, slot, x + offset);
+        if(KEYS)
+        {
+            const u64 next = x + 3;
+            const u64 tag = next < n ? u64(part_of_pid[pid[i + 3]]) + 3 : (n + 2 - next);
+            keys[slot] = (u64(T[i]) << 48) | (u64(T[i + 1]) << 32) | (u64(T[i + 2]) << 16) | tag;
+        }
+    }
 }
 
 size_t part_workspace_bytes(u64 count)
@@ -597,8 +614,8 @@ extern "C" int csa_scatter_lanes(csa_ctx* ctx, csa_store* st, uint64_t first, ui
     if(!ctx || !st || !st->pid || !part_first_dev || !cursor_dev || !lanes_dev || first + count > st->n) return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_lanes: bad argument");
     if(count == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    scatter_parts_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(st->pid + first, first, count, st->position_offset, st->part_of_pid,
-                                                                                reinterpret_cast<const u64*>(part_first_dev), reinterpret_cast<u64*>(cursor_dev), lanes_dev);
+    scatter_parts_kernel<false><<<unsigned(div_up(count, 256 * SP_ITEMS)), 256, 0, ctx->stream>>>(nullptr, st->pid + first, first, count, st->n, st->position_offset, st->part_of_pid,
+                                                                                                reinterpret_cast<const u64*>(part_first_dev), reinterpret_cast<u64*>(cursor_dev), lanes_dev, nullptr);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
@@ -645,9 +662,9 @@ extern "C" int csa_scatter_lanes_keys(csa_ctx* ctx, csa_store* st, const uint16_
         return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_lanes_keys: bad argument");
     if(count == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    scatter_parts_keys_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(text_window_dev, pid_window_dev, first, count, st->n, st->position_offset,
-                                                                                     st->part_of_pid, reinterpret_cast<const u64*>(part_first_dev),
-                                                                                     reinterpret_cast<u64*>(cursor_dev), lanes_dev, reinterpret_cast<u64*>(keys_dev));
+    scatter_parts_kernel<true><<<unsigned(div_up(count, 256 * SP_ITEMS)), 256, 0, ctx->stream>>>(text_window_dev, pid_window_dev, first, count, st->n, st->position_offset,
+                                                                                               st->part_of_pid, reinterpret_cast<const u64*>(part_first_dev),
+                                                                                               reinterpret_cast<u64*>(cursor_dev), lanes_dev, reinterpret_cast<u64*>(keys_dev));
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
@@ -944,7 +961,7 @@ extern "C" int csa_build_sa_tiered(csa_ctx* ctx, const uint16_t* text_host, uint
             CSA_CUDA(ctx, cudaMemcpyAsync(part_first_dev, chunk_first.data(), size_t(parts) * 8, cudaMemcpyHostToDevice, ctx->stream));
             CSA_CUDA(ctx, cudaMemsetAsync(cursor_dev, 0, size_t(parts) * 8, ctx->stream));
             if(k >= 2) CSA_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, copied[k & 1], 0));       // the copies out of this staging buffer, two stretches ago
-            scatter_parts_kernel<<<unsigned(div_up(c, 256)), 256, 0, ctx->stream>>>(pid + first, first, c, offset, st->part_of_pid, part_first_dev, cursor_dev, stage);
+            scatter_parts_kernel<false><<<unsigned(div_up(c, 256 * SP_ITEMS)), 256, 0, ctx->stream>>>(nullptr, pid + first, first, c, n, offset, st->part_of_pid, part_first_dev, cursor_dev, stage, nullptr);
             CSA_LAUNCH_CHECK(ctx);
             CSA_CUDA(ctx, cudaEventRecord(scattered, ctx->stream));
             CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // chunk_first is a host array that the next stretch rewrites

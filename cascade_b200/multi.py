@@ -527,14 +527,15 @@ def _halo_from_next(local, valid, k):
     return out
 
 
-def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=1 << 28, lists_on_device=None, host=None):
+def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=None, lists_on_device=None, host=None):
     """The part-at-a-time build with NOTHING replicated: rank r of the process group holds the symbols of its stretch of
     positions only (shard_bounds), and the same stretch of the partition ids and of the rank store; parts are owned as in
     build_sa_streamed_multi (u mod world). The GPU that holds a stretch of the text makes the generation-0 keys of its positions
     and sends (lane, key) to the parts' owners; in a later generation the owner of a part asks the owners of the positions
     h further on for their ranks, and new ranks travel back to the positions' owners as messages. Device memory per GPU:
     8 n / world bytes (2 text + 2 partition ids until generation 0 is over + 4 ranks) plus the lists of its parts (9 bytes per
-    suffix, on the device while they fit, else in pinned host memory) plus one part's workspace and the windows in flight.
+    suffix, on the device while they fit, else in pinned host memory) plus one part's workspace and the windows in flight
+    (window_suffixes per rank and window of generation 0, 52 bytes each; None: what the free memory allows).
     text_shard: device uint16 tensor with this rank's symbols first. `host` may be a dict that keeps the pinned buffers between
     calls. Returns (segments, info) as build_sa_streamed_multi."""
     import time
@@ -647,10 +648,25 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
         own_total = at
         largest = max(size) if size else 1
         host = host if host is not None else {}
+        if window_suffixes is None:
+            window_suffixes = host.get("window_suffixes")
         if lists_on_device is None:
-            torch.cuda.empty_cache()
+            lists_on_device = host.get("lists_on_device")
+        free_b = None
+        if lists_on_device is None or window_suffixes is None:
+            torch.cuda.empty_cache()                # what an earlier build left in the allocator's cache counts as free
             free_b, _ = torch.cuda.mem_get_info(dev)
-            lists_on_device = 9 * own_total + 26 * window_suffixes + int(L.csa_part_workspace_bytes(largest)) + 40 * largest + (4 << 30) < free_b
+            free_b -= int(L.csa_part_workspace_bytes(largest)) + 40 * largest + (6 << 30)      # a job's workspace, a part's pieces put together
+        if lists_on_device is None:
+            lists_on_device = 9 * own_total + 52 * (1 << 26) < free_b
+            host["lists_on_device"] = lists_on_device
+        if window_suffixes is None:
+            # a window's lanes and keys lie twice on a GPU: as picked out of its stretch, and as received for its parts
+            room = free_b - (9 * own_total if lists_on_device else 0)
+            window_suffixes = max(1 << 24, min(1 << 31, room // 2 // 52))
+            if world > 1:
+                window_suffixes = int(_gather_small(np.array([window_suffixes], np.int64)).min())
+            host["window_suffixes"] = window_suffixes
         if lists_on_device:
             lanes_all = torch.empty(5 * own_total + 64, dtype=torch.uint8, device=dev)
             ranks_all = torch.empty(own_total + 16, dtype=torch.int32, device=dev)
@@ -767,14 +783,18 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             cursor_d.zero_()
             torch.cuda.synchronize(dev)
             sweep = 1 << 30
+            t1 = time.perf_counter()
             for first in range(0, cnt, sweep):
                 ctx.check(L.csa_scatter_lanes_keys(ctx.h, store, T.data_ptr() + 2 * first, pid.data_ptr() + 2 * first, lo + first, min(sweep, cnt - first),
                                                    first_d.data_ptr(), cursor_d.data_ptr(), st_lanes.data_ptr(), st_keys.data_ptr()))
-            ctx.sync()
+            mark("gen0_scan", t1)
+            t1 = time.perf_counter()
             sent(send_counts, 13)
             got_lanes = _exchange(st_lanes, send_counts, recv_counts, width=5)
             got_keys = _exchange(st_keys, send_counts, recv_counts)
             del st_lanes, st_keys
+            mark("gen0_keys_to_owners", t1)
+            t1 = time.perf_counter()
             box = outbox_tensors(sum(size[u] for u in my_parts))
             src_at = np.concatenate([[0], np.cumsum(recv_counts)])[:world].astype(np.int64)      # where each rank's block starts
             for u in my_parts:
@@ -794,8 +814,11 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                 active[u] = int(pout.active)
                 del pl, pk
             del got_lanes, got_keys
+            mark("gen0_rank", t1)
+            t1 = time.perf_counter()
             flush_outbox(box)
             del box
+            mark("gen0_ranks_to_owners", t1)
         L.csa_store_drop_partition_ids(store)
         del pid
         total_active = total_over_ranks(sum(active.values()))
@@ -813,6 +836,7 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             for k in range(rounds):
                 u = own[k] if k < len(own) else None
                 a = active[u] if u is not None else 0
+                t1 = time.perf_counter()
                 ask = torch.empty(a + 8, dtype=torch.int64, device=dev)
                 if a:
                     torch.cuda.synchronize(dev)
@@ -832,6 +856,8 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                 sent(rc_, 4)
                 back = _exchange(answers, rc_, sc)
                 del asked, answers
+                mark("doubling_fetch", t1)
+                t1 = time.perf_counter()
                 if a:
                     second = torch.empty(a + 8, dtype=torch.int32, device=dev)
                     torch.cuda.synchronize(dev)
@@ -843,8 +869,11 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                     active[u] = int(pout.active)
                     del second
                 del back, order
+                mark("doubling_rank", t1)
+            t1 = time.perf_counter()
             flush_outbox(box)
             del box
+            mark("doubling_ranks_to_owners", t1)
             total_active = total_over_ranks(sum(active.values()))
             h *= 2
             gens += 1
