@@ -50,6 +50,7 @@ struct csa_store
     const u16* pid = nullptr;       // borrowed: partition id of every position (generation 0 only)
     u16* part_of_pid = nullptr;     // owned: p entries
     u32 p = 0;
+    u32 parts = 0;                  // 1 + the largest entry of part_of_pid
     u64 position_offset = 0;        // test hook: lanes carry position + offset
     // the outbox of one generation: positions (low 32 bits and high 8 bits apart, so that every store is aligned) and ranks
     u32* box_lo = nullptr;
@@ -338,9 +339,11 @@ __global__ void count_parts_kernel(const u16* __restrict__ pid, const u64 count,
     for(u32 i = threadIdx.x; i < parts; i += blockDim.x) if(s_cnt[i]) atomicAdd(reinterpret_cast<unsigned long long*>(hist + i), (unsigned long long)s_cnt[i]);
 }
 
-// A thread takes SP_ITEMS consecutive positions (one 16-byte load of partition ids where the window is aligned), so that the
-// chain of dependent loads (id -> part -> is the part wanted) is paid once per 8 positions, and a warp-item in which no lane
-// has a wanted position costs one ballot. The lanes of a warp that go to one part take their places with one atomic.
+// A block takes 256 * SP_ITEMS consecutive positions, a thread SP_ITEMS of them (one 16-byte load of partition ids where the
+// window is aligned), so that the chain of dependent loads (id -> part -> is the part wanted) is paid once per 8 positions. The
+// block counts its positions per part in shared memory (a warp's lanes with one part share one atomic), takes its places in the
+// parts' runs with ONE global atomic per part that it holds, and then writes: the global cursors see a few dozen atomics per
+// block instead of one per warp and part.
 // KEYS: also write the generation-0 key beside every lane (3 symbols, then the tag of the suffix 3 symbols on), for a text
 // that is sharded by position: T[i] is the symbol at position first + i and pid[i] its partition; both are readable 3 entries
 // past `count` wherever those positions exist (the neighbour's first entries), and T is zero past the text's end.
@@ -348,9 +351,15 @@ constexpr int SP_ITEMS = 8;
 
 template <bool KEYS>
 __global__ void __launch_bounds__(256) scatter_parts_kernel(const u16* __restrict__ T, const u16* __restrict__ pid, const u64 first, const u64 count, const u64 n,
-                                                            const u64 offset, const u16* __restrict__ part_of_pid, const u64* __restrict__ part_first,
-                                                            u64* __restrict__ cursor, u8* __restrict__ lanes, u64* __restrict__ keys)
+                                                            const u64 offset, const u16* __restrict__ part_of_pid, const u32 parts,
+                                                            const u64* __restrict__ part_first, u64* __restrict__ cursor, u8* __restrict__ lanes,
+                                                            u64* __restrict__ keys)
 {
+    extern __shared__ __align__(8) unsigned char sp_smem[];
+    u64* const s_base = reinterpret_cast<u64*>(sp_smem);                   // [parts] where the block's records of a part start in the part's run
+    u32* const s_cnt = reinterpret_cast<u32*>(sp_smem + size_t(parts) * 8); // [parts]
+    for(u32 t = threadIdx.x; t < parts; t += blockDim.x) s_cnt[t] = 0;
+    __syncthreads();
     const u64 i0 = (u64(blockIdx.x) * blockDim.x + threadIdx.x) * SP_ITEMS;
     u16 id[SP_ITEMS];
     if(i0 + SP_ITEMS <= count && (reinterpret_cast<uintptr_t>(pid + i0) & 15) == 0)
@@ -369,19 +378,30 @@ __global__ void __launch_bounds__(256) scatter_parts_kernel(const u16* __restric
     for(int j = 0; j < SP_ITEMS; ++j) part[j] = i0 + j < count ? u32(part_of_pid[id[j]]) : 0xFFFFFFFFu;
     u64 run_first[SP_ITEMS];
     #pragma unroll
-    for(int j = 0; j < SP_ITEMS; ++j) run_first[j] = part[j] != 0xFFFFFFFFu ? part_first[part[j]] : ~0ull;
+    for(int j = 0; j < SP_ITEMS; ++j) run_first[j] = (part[j] != 0xFFFFFFFFu && part[j] < parts) ? part_first[part[j]] : ~0ull;     // ~0: not wanted now
+    u32 place[SP_ITEMS];
     #pragma unroll
     for(int j = 0; j < SP_ITEMS; ++j)
     {
-        const bool live = run_first[j] != ~0ull;         // ~0: a part that the caller does not want now
+        const bool live = run_first[j] != ~0ull;
+        place[j] = 0;
         if(__ballot_sync(0xFFFFFFFFu, live) == 0) continue;
         const u32 key_part = live ? part[j] : 0xFFFFFFFFu;
         const u32 peers = __match_any_sync(0xFFFFFFFFu, key_part);
-        u64 base = 0;
-        if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + key_part), (unsigned long long)__popc(peers));
+        u32 base = 0;
+        if(live && (peers & lanemask_lt()) == 0) base = atomicAdd(&s_cnt[key_part], u32(__popc(peers)));
         base = __shfl_sync(0xFFFFFFFFu, base, __ffs(peers) - 1);
-        if(!live) continue;
-        const u64 slot = run_first[j] + base + __popc(peers & lanemask_lt());
+        place[j] = base + __popc(peers & lanemask_lt());
+    }
+    __syncthreads();
+    for(u32 t = threadIdx.x; t < parts; t += blockDim.x)
+        if(s_cnt[t]) s_base[t] = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + t), (unsigned long long)s_cnt[t]);
+    __syncthreads();
+    #pragma unroll
+    for(int j = 0; j < SP_ITEMS; ++j)
+    {
+        if(run_first[j] == ~0ull) continue;
+        const u64 slot = run_first[j] + s_base[part[j]] + place[j];
         const u64 i = i0 + j, x = first + i;
         lane_store(lanes, slot, x + offset);
         if(KEYS)
@@ -523,6 +543,7 @@ extern "C" int csa_store_create(csa_ctx* ctx, const uint16_t* text_dev, uint64_t
         delete st;
         return csa_fail(ctx, CSA_E_NOMEM, "csa_store_create: no device memory for the rank store");
     }
+    for(u32 q = 0; q < p; ++q) if(u32(part_of_pid_host[q]) + 1 > st->parts) st->parts = u32(part_of_pid_host[q]) + 1;
     CSA_CUDA(ctx, cudaMemcpyAsync(st->part_of_pid, part_of_pid_host, size_t(p) * 2, cudaMemcpyHostToDevice, ctx->stream));
     CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     *out = st;
@@ -614,8 +635,9 @@ extern "C" int csa_scatter_lanes(csa_ctx* ctx, csa_store* st, uint64_t first, ui
     if(!ctx || !st || !st->pid || !part_first_dev || !cursor_dev || !lanes_dev || first + count > st->n) return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_lanes: bad argument");
     if(count == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    scatter_parts_kernel<false><<<unsigned(div_up(count, 256 * SP_ITEMS)), 256, 0, ctx->stream>>>(nullptr, st->pid + first, first, count, st->n, st->position_offset, st->part_of_pid,
-                                                                                                reinterpret_cast<const u64*>(part_first_dev), reinterpret_cast<u64*>(cursor_dev), lanes_dev, nullptr);
+    scatter_parts_kernel<false><<<unsigned(div_up(count, 256 * SP_ITEMS)), 256, size_t(st->parts) * 12, ctx->stream>>>(nullptr, st->pid + first, first, count, st->n, st->position_offset,
+                                                                                                                      st->part_of_pid, st->parts, reinterpret_cast<const u64*>(part_first_dev),
+                                                                                                                      reinterpret_cast<u64*>(cursor_dev), lanes_dev, nullptr);
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
 }
@@ -662,8 +684,8 @@ extern "C" int csa_scatter_lanes_keys(csa_ctx* ctx, csa_store* st, const uint16_
         return csa_fail(ctx, CSA_E_INVALID, "csa_scatter_lanes_keys: bad argument");
     if(count == 0) return CSA_OK;
     CSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    scatter_parts_kernel<true><<<unsigned(div_up(count, 256 * SP_ITEMS)), 256, 0, ctx->stream>>>(text_window_dev, pid_window_dev, first, count, st->n, st->position_offset,
-                                                                                               st->part_of_pid, reinterpret_cast<const u64*>(part_first_dev),
+    scatter_parts_kernel<true><<<unsigned(div_up(count, 256 * SP_ITEMS)), 256, size_t(st->parts) * 12, ctx->stream>>>(text_window_dev, pid_window_dev, first, count, st->n, st->position_offset,
+                                                                                               st->part_of_pid, st->parts, reinterpret_cast<const u64*>(part_first_dev),
                                                                                                reinterpret_cast<u64*>(cursor_dev), lanes_dev, reinterpret_cast<u64*>(keys_dev));
     CSA_LAUNCH_CHECK(ctx);
     return CSA_OK;
@@ -961,7 +983,8 @@ extern "C" int csa_build_sa_tiered(csa_ctx* ctx, const uint16_t* text_host, uint
             CSA_CUDA(ctx, cudaMemcpyAsync(part_first_dev, chunk_first.data(), size_t(parts) * 8, cudaMemcpyHostToDevice, ctx->stream));
             CSA_CUDA(ctx, cudaMemsetAsync(cursor_dev, 0, size_t(parts) * 8, ctx->stream));
             if(k >= 2) CSA_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, copied[k & 1], 0));       // the copies out of this staging buffer, two stretches ago
-            scatter_parts_kernel<false><<<unsigned(div_up(c, 256 * SP_ITEMS)), 256, 0, ctx->stream>>>(nullptr, pid + first, first, c, n, offset, st->part_of_pid, part_first_dev, cursor_dev, stage, nullptr);
+            scatter_parts_kernel<false><<<unsigned(div_up(c, 256 * SP_ITEMS)), 256, size_t(parts) * 12, ctx->stream>>>(nullptr, pid + first, first, c, n, offset, st->part_of_pid, parts, part_first_dev,
+                                                                                                                     cursor_dev, stage, nullptr);
             CSA_LAUNCH_CHECK(ctx);
             CSA_CUDA(ctx, cudaEventRecord(scattered, ctx->stream));
             CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // chunk_first is a host array that the next stretch rewrites
