@@ -96,6 +96,7 @@ _SIGS = {
     "csa_part_positions": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u64, c_vp]),
     "csa_rank_gen_ranks": (c_int, [c_vp, c_vp, ctypes.POINTER(Part), c_vp, ctypes.POINTER(PartResult)]),
     "csa_bucket_by_owner": (c_int, [c_vp, c_vp, c_vp, c_u64, c_u64, c_u32, c_vp, c_vp, c_vp, c_vp]),
+    "csa_order_by_address": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_u64, c_int, c_int, c_u64, c_u32, c_int, c_vp, c_vp, ctypes.c_size_t, ctypes.POINTER(c_int)]),
     "csa_rank_shard_read": (c_int, [c_vp, c_vp, c_u64, c_u64, c_vp, c_u64, c_vp]),
     "csa_rank_shard_apply": (c_int, [c_vp, c_vp, c_u64, c_u64, c_vp, c_vp, c_u64]),
     "csa_unbucket": (c_int, [c_vp, c_vp, c_vp, c_u64, c_vp]),

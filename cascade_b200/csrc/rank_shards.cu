@@ -4,6 +4,7 @@
 // on the host and fills it with messages (include/message.hpp:22-61, src/Partition_Backend.cpp:516-553); here the owner of a
 // position is position / stretch and the runs cross NVLink.
 #include "common.cuh"
+#include "sort.cuh"
 
 namespace
 {
@@ -13,15 +14,33 @@ __global__ void owner_count_kernel(const u64* __restrict__ pos, const u64 count,
     __shared__ u32 s_cnt[CSA_MAX_GPUS];
     if(threadIdx.x < CSA_MAX_GPUS) s_cnt[threadIdx.x] = 0;
     __syncthreads();
+    u32 mine[CSA_MAX_GPUS];
+    #pragma unroll
+    for(int g = 0; g < CSA_MAX_GPUS; ++g) mine[g] = 0;
     const u64 stride = u64(gridDim.x) * blockDim.x;
     for(u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
     {
-        const u64 g = pos[i] / stretch;
-        if(g < owners) atomicAdd(&s_cnt[g], 1u);
-        else atomicOr(dev_status, (u64)CSA_ST_RANGE);
+        const u64 o = pos[i] / stretch;
+        if(o >= owners) { atomicOr(dev_status, (u64)CSA_ST_RANGE); continue; }
+        #pragma unroll
+        for(int g = 0; g < CSA_MAX_GPUS; ++g) mine[g] += (o == u64(g));
+    }
+    #pragma unroll
+    for(int g = 0; g < CSA_MAX_GPUS; ++g)
+    {
+        u32 v = mine[g];
+        #pragma unroll
+        for(int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        if(lane_id() == 0 && v) atomicAdd(&s_cnt[g], v);
     }
     __syncthreads();
     if(threadIdx.x < owners && s_cnt[threadIdx.x]) atomicAdd(reinterpret_cast<unsigned long long*>(counts + threadIdx.x), (unsigned long long)s_cnt[threadIdx.x]);
+}
+
+__global__ void iota_kernel(u32* __restrict__ out, const u64 count)
+{
+    const u64 i = u64(blockIdx.x) * blockDim.x + threadIdx.x;
+    if(i < count) out[i] = u32(i);
 }
 
 // cursor[g]: where owner g's run starts, advanced as the run fills. The lanes of a warp with one owner take their places with
@@ -102,6 +121,39 @@ extern "C" int csa_bucket_by_owner(csa_ctx* ctx, const uint64_t* positions_dev, 
     owner_scatter_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(reinterpret_cast<const u64*>(positions_dev), payload_dev, count, stretch, owners, cursor_dev,
                                                                                 reinterpret_cast<u64*>(positions_out_dev), payload_out_dev, order_dev);
     CSA_LAUNCH_CHECK(ctx);
+    return CSA_OK;
+}
+
+extern "C" int csa_order_by_address(csa_ctx* ctx, uint64_t* positions_dev, uint64_t* positions_alt_dev, uint32_t* payload_dev, uint32_t* payload_alt_dev, uint64_t count,
+                                    int begin_bit, int end_bit, uint64_t stretch, uint32_t owners, int payload_is_index, uint64_t* counts_host, void* workspace_dev,
+                                    size_t workspace_bytes, int* in_alt)
+{
+    if(!ctx || !counts_host || !in_alt || owners == 0 || owners > CSA_MAX_GPUS || stretch == 0 || begin_bit < 0 || end_bit > 64 || begin_bit >= end_bit)
+        return csa_fail(ctx, CSA_E_INVALID, "csa_order_by_address: bad argument");
+    if(begin_bit < 63 && stretch % (u64(1) << begin_bit) != 0) return csa_fail(ctx, CSA_E_INVALID, "csa_order_by_address: a stretch must be whole address buckets");
+    *in_alt = 0;
+    for(u32 g = 0; g < owners; ++g) counts_host[g] = 0;
+    if(count == 0) return CSA_OK;
+    if(!positions_dev || !positions_alt_dev || !payload_dev || !payload_alt_dev) return csa_fail(ctx, CSA_E_INVALID, "csa_order_by_address: null buffer");
+    if(count >= (u64(1) << 32)) return csa_fail(ctx, CSA_E_LIMIT, "csa_order_by_address: at most 2^32 - 1 entries a call");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    u64* counts_dev = ctx->d_scalars + 40;            // CSA_MAX_GPUS words
+    CSA_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, sizeof(u64) * CSA_MAX_GPUS, ctx->stream));
+    const unsigned blocks = unsigned(div_up(count, 256) < 148 * 8 ? div_up(count, 256) : 148 * 8);
+    owner_count_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const u64*>(positions_dev), count, stretch, owners, counts_dev, ctx->d_status);
+    CSA_LAUNCH_CHECK(ctx);
+    if(payload_is_index)
+    {
+        iota_kernel<<<unsigned(div_up(count, 256)), 256, 0, ctx->stream>>>(payload_dev, count);
+        CSA_LAUNCH_CHECK(ctx);
+    }
+    CSA_CUDA(ctx, cudaMemcpyAsync(ctx->h_scalars + 40, counts_dev, sizeof(u64) * CSA_MAX_GPUS, cudaMemcpyDeviceToHost, ctx->stream));
+    // one or two digit passes on the address bits from begin_bit up: owners' runs follow one another, addresses inside a run sweep upwards
+    CSA_TRY(csa_sort_pairs(ctx, positions_dev, positions_alt_dev, payload_dev, payload_alt_dev, 4, count, begin_bit, end_bit, workspace_dev, workspace_bytes, in_alt));
+    CSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    u64 total = 0;
+    for(u32 g = 0; g < owners; ++g) { counts_host[g] = ctx->h_scalars[40 + g]; total += counts_host[g]; }
+    if(total != count) { u64 bits = 0; const int rc = csa_sync(ctx, reinterpret_cast<uint64_t*>(&bits)); return rc != CSA_OK ? rc : csa_fail(ctx, CSA_E_DEVICE, "csa_order_by_address: a position beyond the last owner"); }
     return CSA_OK;
 }
 

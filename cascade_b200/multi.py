@@ -466,9 +466,22 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
 
 # ---- the part-at-a-time build with nothing replicated: text, partition ids and rank store sharded by position ------------------
 
+def address_bits(n):
+    """(begin_bit, end_bit) of the address bits by which requests and messages are ordered on their way to the owners: the top
+    8 bits of a position while a bucket of the rank store then stays within 128 MB, about the L2 (one digit pass), else the top
+    16 (two passes; at 4.5e9 positions the second pass cost what the better locality of the writes saved)."""
+    end = max(1, int(n - 1).bit_length())
+    begin = max(0, end - 8)
+    if begin > 25:
+        begin = end - 16
+    return begin, end
+
+
 def shard_bounds(n, world, rank):
-    """Equal stretches of whole 64 positions: (stretch, first position, end) of `rank`'s share of a text of n symbols."""
-    stretch = (-(-n // world) + 63) // 64 * 64
+    """Equal stretches of whole address buckets (and whole 64 positions): (stretch, first position, end) of `rank`'s share of a
+    text of n symbols."""
+    unit = max(64, 1 << address_bits(n)[0])
+    stretch = (-(-n // world) + unit - 1) // unit * unit
     lo = min(n, rank * stretch)
     return stretch, lo, min(n, lo + stretch)
 
@@ -683,44 +696,49 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
         def lists(u):
             return lanes_all.data_ptr() + 5 * own_first[u], ranks_all.data_ptr() + 4 * own_first[u]
 
+        addr_begin, addr_end = address_bits(n)
+
         def bucket(pos, payload, want_order):
-            """pos (and payload) sorted into one run per owner; returns (counts, pos runs, payload runs, order)."""
+            """pos (and payload, or the entries' indexes) ordered by address: one run per owner, ascending buckets inside.
+            Returns (counts, positions, payload or order)."""
             m = int(pos.numel())
             counts = np.zeros(world, np.uint64)
-            pos_b = torch.empty(m + 8, dtype=torch.int64, device=dev)
-            pay_b = torch.empty(m + 8, dtype=torch.int32, device=dev) if payload is not None else None
-            order = torch.empty(m + 8, dtype=torch.int32, device=dev) if want_order else None
+            if m == 0:
+                return [0] * world, pos, torch.empty(0, dtype=torch.int32, device=dev)
+            pos_alt = torch.empty(m + 8, dtype=torch.int64, device=dev)
+            pay = payload if payload is not None else torch.empty(m + 8, dtype=torch.int32, device=dev)
+            pay_alt = torch.empty(m + 8, dtype=torch.int32, device=dev)
+            wsb = int(L.csa_sort_workspace_bytes(m))
+            ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+            in_alt = ctypes.c_int(0)
             torch.cuda.synchronize(dev)
-            ctx.check(L.csa_bucket_by_owner(ctx.h, pos.data_ptr() if m else None, payload.data_ptr() if payload is not None and m else None, m, stretch, world,
-                                            counts.ctypes.data, pos_b.data_ptr(), pay_b.data_ptr() if pay_b is not None else None,
-                                            order.data_ptr() if order is not None else None))
+            ctx.check(L.csa_order_by_address(ctx.h, pos.data_ptr(), pos_alt.data_ptr(), pay.data_ptr(), pay_alt.data_ptr(), m, addr_begin, addr_end, stretch, world,
+                                             1 if want_order else 0, counts.ctypes.data, ws.data_ptr(), wsb, ctypes.byref(in_alt)))
             ctx.sync()
-            return [int(c) for c in counts], pos_b, pay_b, order
+            del ws
+            return [int(c) for c in counts], (pos_alt if in_alt.value else pos), (pay_alt if in_alt.value else pay)
 
         def route_messages(pos, ranks):
-            """(position, rank) messages to the owners of the positions, applied to their stretch of the rank store; in runs of
-            2^27 messages, as many runs on every rank as the rank with the most messages needs."""
-            run = 1 << 27
-            runs = -(-int(pos.numel()) // run)
-            if world > 1:
-                runs = int(_gather_small(np.array([runs], np.int64)).max())
-            applied = 0
-            for k in range(runs):
-                ps_, rs_ = pos[k * run:(k + 1) * run], ranks[k * run:(k + 1) * run]
-                counts, pos_b, rank_b, _ = bucket(ps_, rs_, False)
-                incoming = [int(c) for c in _gather_small(np.array(counts, np.int64))[:, rank]] if world > 1 else counts
-                sent(counts, 12)
-                got_pos = _exchange(pos_b, counts, incoming)
-                got_rank = _exchange(rank_b, counts, incoming)
-                del pos_b, rank_b
-                m = int(got_pos.numel())
-                if m:
-                    torch.cuda.synchronize(dev)
-                    ctx.check(L.csa_rank_shard_apply(ctx.h, R.data_ptr(), lo, cnt, got_pos.data_ptr(), got_rank.data_ptr(), m))
-                    ctx.sync()
-                    applied += m
-                del got_pos, got_rank
-            return applied
+            """(position, rank) messages to the owners of the positions, applied to their stretch of the rank store."""
+            t1 = time.perf_counter()
+            counts, pos_b, rank_b = bucket(pos, ranks, False)
+            incoming = [int(c) for c in _gather_small(np.array(counts, np.int64))[:, rank]] if world > 1 else counts
+            mark("route_bucket", t1)
+            t1 = time.perf_counter()
+            sent(counts, 12)
+            got_pos = _exchange(pos_b, counts, incoming)
+            got_rank = _exchange(rank_b, counts, incoming)
+            del pos_b, rank_b
+            mark("route_exchange", t1)
+            t1 = time.perf_counter()
+            m = int(got_pos.numel())
+            if m:
+                torch.cuda.synchronize(dev)
+                ctx.check(L.csa_rank_shard_apply(ctx.h, R.data_ptr(), lo, cnt, got_pos.data_ptr(), got_rank.data_ptr(), m))
+                ctx.sync()
+            del got_pos, got_rank
+            mark("route_apply", t1)
+            return m
 
         def outbox_tensors(capacity):
             box_l = torch.empty(capacity + 16, dtype=torch.int32, device=dev)
@@ -731,10 +749,11 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             return box_l, box_h, box_r
 
         def flush_outbox(box):
+            """The outbox, in runs of 2^29 messages (as many runs on every rank as the rank with the most messages needs)."""
             box_l, box_h, box_r = box
             m = int(L.csa_store_outbox_count(store))
             ctx.sync()
-            applied, run = 0, 1 << 29                                  # positions as 64-bit words, a run at a time
+            applied, run = 0, 1 << 29
             runs = -(-m // run)
             if world > 1:
                 runs = int(_gather_small(np.array([runs], np.int64)).max())
@@ -842,7 +861,7 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                     torch.cuda.synchronize(dev)
                     ctx.check(L.csa_part_positions(ctx.h, store, lists(u)[0], a, h, ask.data_ptr()))
                     ctx.sync()
-                sc, ask_b, _, order = bucket(ask[:a], None, True)
+                sc, ask_b, order = bucket(ask[:a], None, True)
                 rc_ = [int(c) for c in _gather_small(np.array(sc, np.int64))[:, rank]] if world > 1 else sc
                 sent(sc, 8)
                 asked = _exchange(ask_b, sc, rc_)

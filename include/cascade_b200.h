@@ -292,6 +292,15 @@ int csa_rank_gen_ranks(csa_ctx* ctx, csa_store* store, const csa_part* in, const
  * csa_outbox_positions: the outbox's positions (csa_store_use_outbox keeps them as low 32 and high 8 bits) as 64-bit words. */
 int csa_bucket_by_owner(csa_ctx* ctx, const uint64_t* positions_dev, const uint32_t* payload_dev, uint64_t count, uint64_t stretch, uint32_t owners,
                         uint64_t* counts_host, uint64_t* positions_out_dev, uint32_t* payload_out_dev, uint32_t* order_dev);
+/* csa_order_by_address: the same runs per owner, with the addresses inside a run in ascending order of their bits
+ * [begin_bit, end_bit): one digit pass of the radix sort per 8 bits. A stretch must be whole address buckets (a multiple of
+ * 2^begin_bit), and end_bit must cover the highest position. The owner then reads or writes its stretch of the rank store in
+ * address order, bucket by bucket, instead of at random. Positions and payload are sorted between the two buffers given for
+ * each (*in_alt = 1: the result is in the alt buffers); payload_is_index fills the payload with 0, 1, 2, ... first, which
+ * makes it the `order` of csa_unbucket. workspace: csa_sort_workspace_bytes(count). */
+int csa_order_by_address(csa_ctx* ctx, uint64_t* positions_dev, uint64_t* positions_alt_dev, uint32_t* payload_dev, uint32_t* payload_alt_dev,
+                         uint64_t count, int begin_bit, int end_bit, uint64_t stretch, uint32_t owners, int payload_is_index, uint64_t* counts_host,
+                         void* workspace_dev, size_t workspace_bytes, int* in_alt);
 int csa_rank_shard_read(csa_ctx* ctx, const uint32_t* shard_dev, uint64_t first, uint64_t positions, const uint64_t* asked_dev, uint64_t count,
                         uint32_t* answers_dev);
 int csa_rank_shard_apply(csa_ctx* ctx, uint32_t* shard_dev, uint64_t first, uint64_t positions, const uint64_t* positions_dev, const uint32_t* ranks_dev,
