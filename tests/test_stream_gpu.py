@@ -221,3 +221,83 @@ def test_tiered_build_refusals(ctx, tmp_path):
         api.build_sa_tiered(ctx, Th, n, 8, out=False)
     sa, st = api.build_sa_streamed(ctx, Th, n, 8)    # the context still works
     assert st.n == n
+
+
+def test_rank_shard_primitives(ctx):
+    """The pieces a sharded rank store is driven with, one by one against numpy: positions ordered into runs per owner (by
+    address or just by owner), a stretch answering requests and taking messages, answers put back into request order, and the
+    outbox's split positions joined; a request outside the stretch is reported, not served."""
+    L = ctx.L
+    rng = np.random.default_rng(3)
+    n, owners = 1_000_000, 3
+    end = int(n - 1).bit_length()
+    begin = end - 8
+    unit = max(64, 1 << begin)
+    stretch = (-(-n // owners) + unit - 1) // unit * unit
+    m = 300_001
+    pos = rng.integers(0, n, m).astype(np.uint64)
+    pay = rng.integers(0, 1 << 31, m).astype(np.uint32)
+    for by_address in (False, True):
+        pd = torch.from_numpy(pos.view(np.int64)).cuda()
+        yd = torch.from_numpy(pay.view(np.int32)).cuda()
+        counts = np.zeros(owners, np.uint64)
+        if by_address:
+            pa, ya = torch.empty_like(pd), torch.empty_like(yd)
+            wsb = L.csa_sort_workspace_bytes(m)
+            ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+            in_alt = ctypes.c_int(0)
+            torch.cuda.synchronize()
+            ctx.check(L.csa_order_by_address(ctx.h, pd.data_ptr(), pa.data_ptr(), yd.data_ptr(), ya.data_ptr(), m, begin, end, stretch, owners, 1,
+                                             counts.ctypes.data, ws.data_ptr(), wsb, ctypes.byref(in_alt)))
+            ctx.sync()
+            got_pos = (pa if in_alt.value else pd).cpu().numpy().view(np.uint64)
+            order = (ya if in_alt.value else yd).cpu().numpy().view(np.uint32)
+            assert np.all(np.diff((got_pos >> np.uint64(begin)).astype(np.int64)) >= 0), "buckets must ascend"
+        else:
+            po, yo, od = torch.empty_like(pd), torch.empty_like(yd), torch.empty(m, dtype=torch.int32, device="cuda")
+            torch.cuda.synchronize()
+            ctx.check(L.csa_bucket_by_owner(ctx.h, pd.data_ptr(), yd.data_ptr(), m, stretch, owners, counts.ctypes.data, po.data_ptr(), yo.data_ptr(), od.data_ptr()))
+            ctx.sync()
+            got_pos, order = po.cpu().numpy().view(np.uint64), od.cpu().numpy().view(np.uint32)
+            assert np.array_equal(yo.cpu().numpy().view(np.uint32), pay[order])
+        assert np.array_equal(counts, np.bincount((pos // np.uint64(stretch)).astype(np.int64), minlength=owners).astype(np.uint64))
+        assert np.array_equal(got_pos, pos[order]) and np.array_equal(np.sort(order), np.arange(m, dtype=np.uint32))
+        assert np.all(np.diff((got_pos // np.uint64(stretch)).astype(np.int64)) >= 0), "one run per owner, in owner order"
+    # owner 1's stretch: apply messages, read them back, put the answers into the order of the requests
+    lo, cnt = stretch, min(n, 2 * stretch) - stretch
+    shard = torch.zeros(cnt + 16, dtype=torch.int32, device="cuda")
+    mine = np.unique(pos[(pos >= lo) & (pos < lo + cnt)])
+    ranks = rng.integers(1, 1 << 31, len(mine)).astype(np.uint32)
+    md, rd = torch.from_numpy(mine.view(np.int64)).cuda(), torch.from_numpy(ranks.view(np.int32)).cuda()
+    torch.cuda.synchronize()
+    ctx.check(L.csa_rank_shard_apply(ctx.h, shard.data_ptr(), lo, cnt, md.data_ptr(), rd.data_ptr(), len(mine)))
+    perm = rng.permutation(len(mine)).astype(np.uint32)
+    asked = torch.from_numpy(mine[perm].view(np.int64)).cuda()
+    ans = torch.zeros(len(mine), dtype=torch.int32, device="cuda")
+    back = torch.zeros(len(mine), dtype=torch.int32, device="cuda")
+    order_d = torch.from_numpy(perm.view(np.int32)).cuda()
+    torch.cuda.synchronize()
+    ctx.check(L.csa_rank_shard_read(ctx.h, shard.data_ptr(), lo, cnt, asked.data_ptr(), len(mine), ans.data_ptr()))
+    ctx.check(L.csa_unbucket(ctx.h, order_d.data_ptr(), ans.data_ptr(), len(mine), back.data_ptr()))
+    ctx.sync()
+    assert np.array_equal(back.cpu().numpy().view(np.uint32), ranks)
+    # the outbox keeps positions as low 32 and high 8 bits
+    big = rng.integers(0, 1 << 40, 1000).astype(np.uint64)
+    lo32 = torch.from_numpy((big & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)).cuda()
+    hi8 = torch.from_numpy((big >> np.uint64(32)).astype(np.uint8)).cuda()
+    joined = torch.zeros(1000, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    ctx.check(L.csa_outbox_positions(ctx.h, lo32.data_ptr(), hi8.data_ptr(), 1000, joined.data_ptr()))
+    ctx.sync()
+    assert np.array_equal(joined.cpu().numpy().view(np.uint64), big)
+    # a request for a position of another stretch: answered with 0 and reported by the status word, no fault
+    from cascade_b200 import api
+    outside = torch.tensor([0], dtype=torch.int64, device="cuda")
+    one = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.check(L.csa_rank_shard_read(ctx.h, shard.data_ptr(), lo, cnt, outside.data_ptr(), 1, one.data_ptr()))
+    with pytest.raises(api.CascadeError):
+        ctx.sync()
+    assert int(one.item()) == 0
+    ctx.check(L.csa_rank_shard_read(ctx.h, shard.data_ptr(), lo, cnt, asked.data_ptr(), 1, one.data_ptr()))
+    ctx.sync()                                        # the context works on
