@@ -71,6 +71,7 @@ _SIGS = {
     "csa_get_pass_timing": (c_int, [c_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_u64), ctypes.POINTER(c_u64), ctypes.POINTER(c_u64)]),
     "csa_sample_kgrams": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u64, c_vp]),
     "csa_select_pivots": (c_int, [c_vp, c_u64, c_u32, c_vp, ctypes.POINTER(c_u32)]),
+    "csa_select_pivots_dev": (c_int, [c_vp, c_vp, c_u64, c_u32, c_vp, ctypes.POINTER(c_u32)]),
     "csa_partition_ids": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u64, c_vp, c_u32, c_vp, c_vp]),
     "csa_scatter_by_pid": (c_int, [c_vp, c_vp, c_u64, c_u64, c_u32, c_vp, c_vp]),
     "csa_build_device_bytes": (ctypes.c_size_t, [c_u64, c_u32]),

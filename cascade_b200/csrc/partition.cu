@@ -639,6 +639,11 @@ size_t pick_splitters_scratch_bytes(u64 n_samples)
     return align_up256(n_samples * 16) + 2 * align_up256(n_samples * 8) + 2 * align_up256(n_samples * 4) + align_up256(csa_sort_workspace_bytes(n_samples)) + 1024;
 }
 
+namespace
+{
+int order_samples_and_pick(csa_ctx* ctx, const u64* samples, u64 n_samples, u32 p, u64* hiA, u64* hiB, u32* ixA, u32* ixB, void* ws, size_t wsb, u64* pivots_host, u32* p_out);
+}
+
 int pick_splitters(csa_ctx* ctx, const u16* T, u64 n, u32 p, u64 seed, u64 n_samples, void* scratch, size_t scratch_bytes, u64* pivots_host, u32* p_out)
 {
     Carver cv(scratch, scratch_bytes);
@@ -651,6 +656,34 @@ int pick_splitters(csa_ctx* ctx, const u16* T, u64 n, u32 p, u64 seed, u64 n_sam
     void* ws = cv.take<u8>(wsb);
     if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "splitters: scratch too small");
     CSA_TRY(csa_sample_kgrams(ctx, T, n, n_samples, seed, reinterpret_cast<uint64_t*>(samples)));
+    return order_samples_and_pick(ctx, samples, n_samples, p, hiA, hiB, ixA, ixB, ws, wsb, pivots_host, p_out);
+}
+
+// The same from samples that lie in device memory already (a text sharded over several GPUs: every GPU samples its stretch
+// and the samples meet by the caller's all-gather). The scratch comes from the context's arena.
+extern "C" int csa_select_pivots_dev(csa_ctx* ctx, const uint64_t* samples_dev, uint64_t n_samples, uint32_t p, uint64_t* pivots_host, uint32_t* p_out)
+{
+    if(!ctx || !samples_dev || !pivots_host || !p_out || n_samples == 0 || p == 0 || p > CSA_MAX_PARTITIONS) return csa_fail(ctx, CSA_E_INVALID, "csa_select_pivots_dev: bad argument");
+    if(n_samples >= (u64(1) << 31)) return csa_fail(ctx, CSA_E_LIMIT, "csa_select_pivots_dev: too many samples");
+    CSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t wsb = csa_sort_workspace_bytes(n_samples);
+    const size_t need = 2 * align_up256(n_samples * 8) + 2 * align_up256(n_samples * 4) + align_up256(wsb) + 1024;
+    void* scratch = nullptr;
+    CSA_TRY(csa_arena(ctx, need, &scratch));
+    Carver cv(scratch, ctx->arena_bytes);
+    u64* hiA = cv.take<u64>(n_samples);
+    u64* hiB = cv.take<u64>(n_samples);
+    u32* ixA = cv.take<u32>(n_samples);
+    u32* ixB = cv.take<u32>(n_samples);
+    void* ws = cv.take<u8>(wsb);
+    if(!cv.ok) return csa_fail(ctx, CSA_E_NOMEM, "csa_select_pivots_dev: scratch too small");
+    return order_samples_and_pick(ctx, reinterpret_cast<const u64*>(samples_dev), n_samples, p, hiA, hiB, ixA, ixB, ws, wsb, reinterpret_cast<u64*>(pivots_host), p_out);
+}
+
+namespace
+{
+int order_samples_and_pick(csa_ctx* ctx, const u64* samples, u64 n_samples, u32 p, u64* hiA, u64* hiB, u32* ixA, u32* ixB, void* ws, size_t wsb, u64* pivots_host, u32* p_out)
+{
     split_samples_kernel<<<unsigned(div_up(n_samples, 256)), 256, 0, ctx->stream>>>(samples, n_samples, hiA, ixA);
     CSA_LAUNCH_CHECK(ctx);
     int in_alt = 0;
@@ -682,3 +715,4 @@ int pick_splitters(csa_ctx* ctx, const u16* T, u64 n, u32 p, u64 seed, u64 n_sam
     *p_out = made + 1;
     return CSA_OK;
 }
+}   // namespace

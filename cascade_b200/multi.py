@@ -227,13 +227,9 @@ def build_sa_streamed_multi(ctx, text_dev, n, p=4096, seed=0, part_suffixes=1 <<
         samples = torch.empty(2 * ns, dtype=torch.int64, device=dev)
         torch.cuda.synchronize(dev)
         ctx.check(L.csa_sample_kgrams(ctx.h, text_dev.data_ptr(), n, ns, seed, samples.data_ptr()))
-        ctx.sync()
-        sh = samples.cpu().numpy().view(np.uint64)
         piv = np.zeros(2 * (p - 1), np.uint64)
         p_out = ctypes.c_uint32(0)
-        rc = L.csa_select_pivots(sh.ctypes.data, ns, p, piv.ctypes.data, ctypes.byref(p_out))
-        if rc != 0:
-            raise api.CascadeError(rc, "csa_select_pivots")
+        ctx.check(L.csa_select_pivots_dev(ctx.h, samples.data_ptr(), ns, p, piv.ctypes.data, ctypes.byref(p_out)))
         pe = p_out.value
         del samples
     pivd = torch.from_numpy(piv.view(np.int64)).to(dev) if pe > 1 else None
@@ -600,12 +596,11 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             dist.all_gather(every, samples)
             have = _gather_small(np.array([cnt > 0], np.int64))[:, 0]
             samples = torch.cat([e for e, ok in zip(every, have) if ok])
-        sh = np.ascontiguousarray(samples.cpu().numpy().view(np.uint64))
+        samples = samples.contiguous()
         piv = np.zeros(2 * (p - 1), np.uint64)
         p_out = ctypes.c_uint32(0)
-        rc = L.csa_select_pivots(sh.ctypes.data, len(sh) // 2, p, piv.ctypes.data, ctypes.byref(p_out))
-        if rc != 0:
-            raise api.CascadeError(rc, "csa_select_pivots")
+        torch.cuda.synchronize(dev)
+        ctx.check(L.csa_select_pivots_dev(ctx.h, samples.data_ptr(), samples.numel() // 2, p, piv.ctypes.data, ctypes.byref(p_out)))
         pe = p_out.value
         del samples
     pivd = torch.from_numpy(piv.view(np.int64)).to(dev) if pe > 1 else None

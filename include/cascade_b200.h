@@ -122,6 +122,10 @@ int csa_sample_kgrams(csa_ctx* ctx, const uint16_t* text_dev, uint64_t n, uint64
  * (inclusive upper bounds) at equal strides, so that equal K-grams never split. pivots_host holds 2 (p-1)
  * words; *p_out receives the partition count actually formed (<= p). */
 int csa_select_pivots(const uint64_t* samples_host, uint64_t n_samples, uint32_t p, uint64_t* pivots_host, uint32_t* p_out);
+/* The same choice from samples in device memory, ordered by the device's radix sort (only runs of samples that tie on their
+ * first word are put in order on the host): for samples gathered from several GPUs, whose order on the host would cost tens of
+ * milliseconds at 2^19 samples. */
+int csa_select_pivots_dev(csa_ctx* ctx, const uint64_t* samples_dev, uint64_t n_samples, uint32_t p, uint64_t* pivots_host, uint32_t* p_out);
 /* For the positions [first, first + count) of the text: partition id = min{q : kgram(i) <= pivot[q]}, written to
  * pid_dev[i - first], and the partitions' sizes added into hist_dev[p]. Replaces compute_partition_IDs_kernel
  * (include/GPU_SACA.cuh:23-73, launched at src/GPU_SACA.cu:939). pivots_dev holds 2 (p-1) words. */
