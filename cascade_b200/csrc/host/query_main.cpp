@@ -13,6 +13,7 @@
 #include <cinttypes>
 #include <cstdlib>
 #include <map>
+#include <random>
 
 using namespace cascade_host;
 
@@ -25,7 +26,7 @@ const char* const USAGE =
     "  query plan --index DIR [--stride S|auto] [--sa-res device|pinned|auto] [--device-budget BYTES] [--host-budget BYTES]\n"
     "  query find --index DIR --queries Q1.qry[,Q2.qry,...] [--q N] [--stride S|auto] [--sa-res device|pinned|auto] [--reps K] [--locate M]\n"
     "             [--itv-out F] [--cnt-out F] [--pos-out F] [--cnt-dir D] [--validate] [--device D] [--device-budget BYTES] [--host-budget BYTES]\n"
-    "  query gen --index DIR --out Q.qry --kind substring|random [--q N --len L1[,L2,...]] [--source F] [--vocab V] [--seed S]\n";
+    "  query gen --index DIR --out Q.qry --kind substring|mutated|random|unigram [--q N --len L1[,L2,...]] [--source F] [--vocab V] [--seed S]\n";
 
 struct Args
 {
@@ -136,18 +137,23 @@ int run_gen(const Args& a)
 {
     Index_Meta m; std::string err;
     if(!read_index_meta(a.get("index"), m, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
+    // The reference's four kinds (src/query.cu:108-111): substrings of the text, substrings with one symbol replaced by another
+    // one ("mutated"), random symbols below the vocabulary, and every symbol of the vocabulary once ("unigram").
     const std::string kind = a.get("kind", "substring");
-    if(kind != "substring" && kind != "random")
+    if(kind != "substring" && kind != "random" && kind != "mutated" && kind != "unigram")
     {
-        std::fprintf(stderr, "error: --kind %s is not supported: this generator makes the kinds substring and random (the reference also has mutated and unigram)\n", kind.c_str());
+        std::fprintf(stderr, "error: --kind %s is not one of substring, mutated, random, unigram\n", kind.c_str());
         return 1;
     }
-    const uint64_t q = a.u64("q", 1000), seed = a.u64("seed", 1), vocab = a.u64("vocab", 65536);
+    uint64_t q = a.u64("q", 1000);
+    const uint64_t seed = a.u64("seed", 1), vocab = a.u64("vocab", 65536);
+    if(vocab == 0 || vocab > 65536) { std::fprintf(stderr, "error: --vocab must be between 1 and 65536\n"); return 1; }
     std::vector<uint32_t> lens;
     for(const auto& t : split(a.get("len", "8"), ',')) lens.push_back(uint32_t(std::strtoul(t.c_str(), nullptr, 10)));
+    const bool from_text = kind == "substring" || kind == "mutated";
     std::vector<uint16_t> T;
     uint64_t n = 0;
-    if(kind == "substring")
+    if(from_text)
     {
         const std::string src = a.get("source", m.text);
         uint64_t bytes = 0;
@@ -155,11 +161,36 @@ int run_gen(const Args& a)
         n = bytes / 2; T.resize(n);
         if(!read_file(src, T.data(), bytes, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
     }
-    const uint64_t cap = q * uint64_t(*std::max_element(lens.begin(), lens.end())) + 1;
-    std::vector<uint64_t> off(q + 1);
-    std::vector<uint16_t> sym(cap);
-    const int rc = csa_gen_queries_host(kind == "substring" ? 0 : 1, T.data(), n, q, lens.data(), uint32_t(lens.size()), vocab, seed, off.data(), sym.data(), cap);
-    if(rc != CSA_OK) { std::fprintf(stderr, "error: query generation failed (%d)\n", rc); return 1; }
+    std::vector<uint64_t> off;
+    std::vector<uint16_t> sym;
+    if(kind == "unigram")
+    {
+        q = vocab;
+        off.resize(q + 1);
+        sym.resize(q + 1);
+        for(uint64_t c = 0; c < q; ++c) { off[c] = c; sym[c] = uint16_t(c); }
+        off[q] = q;
+    }
+    else
+    {
+        const uint64_t cap = q * uint64_t(*std::max_element(lens.begin(), lens.end())) + 1;
+        off.resize(q + 1);
+        sym.resize(cap);
+        const int rc = csa_gen_queries_host(from_text ? 0 : 1, T.data(), n, q, lens.data(), uint32_t(lens.size()), vocab, seed, off.data(), sym.data(), cap);
+        if(rc != CSA_OK) { std::fprintf(stderr, "error: query generation failed (%d)\n", rc); return 1; }
+        if(kind == "mutated" && vocab > 1)
+        {
+            std::mt19937_64 rng(seed ^ 0x6D75746174656421ull);
+            for(uint64_t i = 0; i < q; ++i)
+            {
+                const uint64_t len = off[i + 1] - off[i];
+                if(len == 0) continue;
+                uint16_t& x = sym[off[i] + rng() % len];
+                const uint16_t old = x;
+                do x = uint16_t(rng() % vocab); while(x == old);
+            }
+        }
+    }
     if(!write_qry(a.get("out"), off, sym.data(), seed, err)) { std::fprintf(stderr, "error: %s\n", err.c_str()); return 1; }
     std::printf("out=%s\nq=%" PRIu64 "\nsym_c=%" PRIu64 "\nkind=%s\nvocab=%" PRIu64 "\nseed=%" PRIu64 "\n", a.get("out").c_str(), q, off[q], kind.c_str(), vocab, seed);
     return 0;

@@ -91,8 +91,8 @@ int csa_sort_segments(csa_ctx* ctx, uint64_t* keys_dev, uint64_t* keys_alt_dev, 
  * with a line on stderr). It calls no cudaMalloc, cudaFree or other allocating routine. Keys are 64-bit, values 32-bit;
  * every pass runs, so *in_alt = number of passes & 1. The work is queued on `stream` (a cudaStream_t, or null) of the
  * current device and the call returns after it has finished, with CSA_E_DEVICE if a bounded wait ran out.
- * The first call on each device looks up the array's device address and sizes the kernel's shared memory; make that
- * first call outside any stream capture. All calls share the one array: calls that overlap on the GPU (two streams, two
+ * The first call on each device also looks up the array's device address and sizes the kernel's shared memory. Every call
+ * synchronises `stream` before it returns. All calls share the one array: calls that overlap on the GPU (two streams, two
  * threads) race on it, so keep them one after another per device. */
 int csa_sort_pairs_static(void* stream, uint64_t* keys_dev, uint64_t* keys_alt_dev, uint32_t* vals_dev, uint32_t* vals_alt_dev,
                           uint64_t n, int begin_bit, int end_bit, int* in_alt);

@@ -47,6 +47,24 @@ def test_query_gen_and_info_without_a_gpu(tmp_path):
         off, sym, (mn, mx, sd) = _read_qry(out)
         woff, wsym = api.gen_queries(kind, T if kind == "substring" else None, 50000 if kind == "substring" else 0, 300, seed=seed)
         assert np.array_equal(off, woff) and np.array_equal(sym, wsym) and sd == seed and 1 <= mn <= mx <= 16
+    # mutated: the substrings of the same seed with exactly one symbol replaced; unigram: every symbol of the vocabulary once
+    out = os.path.join(tmp, "mutated.qry")
+    r = subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", out, "--kind", "mutated", "--q", "300", "--len",
+                        "1,2,3,4,5,6,7,8,9,10,11,12,13,14,15,16", "--seed", "1", "--vocab", "50257"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    off, sym, _ = _read_qry(out)
+    woff, wsym = api.gen_queries("substring", T, 50000, 300, seed=1)
+    assert np.array_equal(off, woff)
+    changed = np.add.reduceat((sym[:int(off[-1])] != wsym[:int(off[-1])]).astype(np.int64), off[:-1].astype(np.int64))
+    diff = sym[:int(off[-1])] != wsym[:int(off[-1])]
+    assert np.all(changed == 1) and sym[:int(off[-1])][diff].max() < 50257
+    out = os.path.join(tmp, "unigram.qry")
+    r = subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", out, "--kind", "unigram", "--vocab", "300"], capture_output=True, text=True)
+    assert r.returncode == 0 and _kv(r.stdout)["q"] == "300", r.stderr
+    off, sym, _ = _read_qry(out)
+    assert np.array_equal(off, np.arange(301)) and np.array_equal(sym[:300], np.arange(300))
+    r = subprocess.run([os.path.join(BIN, "query"), "gen", "--index", tmp, "--out", out, "--kind", "nonsense"], capture_output=True, text=True)
+    assert r.returncode != 0 and "substring, mutated, random, unigram" in r.stderr
     r = subprocess.run([os.path.join(BIN, "query"), "info", "--index", tmp], capture_output=True, text=True)
     assert r.returncode == 0 and _kv(r.stdout)["n"] == "50000"
     r = subprocess.run([os.path.join(BIN, "query"), "bogus"], capture_output=True, text=True)
