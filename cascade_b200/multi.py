@@ -693,9 +693,9 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
 
         addr_begin, addr_end = address_bits(n)
 
-        def bucket(pos, payload, want_order):
+        def bucket(pos, payload, want_order, c=ctx):
             """pos (and payload, or the entries' indexes) ordered by address: one run per owner, ascending buckets inside.
-            Returns (counts, positions, payload or order)."""
+            Returns (counts, positions, payload or order). c: the context (stream and scratch) that does the work."""
             m = int(pos.numel())
             counts = np.zeros(world, np.uint64)
             if m == 0:
@@ -706,10 +706,10 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             wsb = int(L.csa_sort_workspace_bytes(m))
             ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
             in_alt = ctypes.c_int(0)
-            torch.cuda.synchronize(dev)
-            ctx.check(L.csa_order_by_address(ctx.h, pos.data_ptr(), pos_alt.data_ptr(), pay.data_ptr(), pay_alt.data_ptr(), m, addr_begin, addr_end, stretch, world,
-                                             1 if want_order else 0, counts.ctypes.data, ws.data_ptr(), wsb, ctypes.byref(in_alt)))
-            ctx.sync()
+            torch.cuda.current_stream(dev).synchronize()
+            c.check(L.csa_order_by_address(c.h, pos.data_ptr(), pos_alt.data_ptr(), pay.data_ptr(), pay_alt.data_ptr(), m, addr_begin, addr_end, stretch, world,
+                                           1 if want_order else 0, counts.ctypes.data, ws.data_ptr(), wsb, ctypes.byref(in_alt)))
+            c.sync()
             del ws
             return [int(c) for c in counts], (pos_alt if in_alt.value else pos), (pay_alt if in_alt.value else pay)
 
@@ -840,59 +840,93 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
         mark("gen0", t0)
 
         # ---- doubling generations: the ranks go through their parts in step, one part each per round -----------------------------
+        # Fetching the second ranks of a round's part (requests out, answers back: this thread, a context of its own, the
+        # collective) runs while the part of the round before is ranked (a second thread, the main context). Nothing that the
+        # two touch is shared: a job reads and writes its own part's lists and appends to the outbox; the rank store changes only
+        # after the generation's last part.
+        import threading
         t0 = time.perf_counter()
         h, gens = 3, 0
         info["active_per_generation"] = []
         rounds = -(-parts // world)
-        while total_active > 0:
-            info["active_per_generation"].append(total_active)
-            box = outbox_tensors(sum(active.values()))
-            for k in range(rounds):
-                u = own[k] if k < len(own) else None
-                a = active[u] if u is not None else 0
+        fetch_ctx = api.Context(dev.index)
+        mine = torch.cuda.current_stream(dev)
+
+        def lap(name, t1):
+            info["ms"][name] = info["ms"].get(name, 0.0) + 1e3 * (time.perf_counter() - t1)
+
+        def rank_job(u, a, second, failures):
+            try:
+                torch.cuda.set_device(dev)
+                lp, rp = lists(u)
+                pin, pout = Part(lp, rp, a, u), PartResult(lp, rp, 0, 0)
+                ctx.check(L.csa_rank_gen_ranks(ctx.h, store, ctypes.byref(pin), second.data_ptr(), ctypes.byref(pout)))
+                ctx.sync()
+                active[u] = int(pout.active)
+            except Exception as e:        # noqa: BLE001 - raised on the main thread after the join
+                failures.append(e)
+
+        try:
+            while total_active > 0:
+                info["active_per_generation"].append(total_active)
+                box = outbox_tensors(sum(active.values()))
+                running, failures = None, []
+                for k in range(rounds):
+                    u = own[k] if k < len(own) else None
+                    a = active[u] if u is not None else 0
+                    t1 = time.perf_counter()
+                    ask = torch.empty(a + 8, dtype=torch.int64, device=dev)
+                    if a:
+                        mine.synchronize()
+                        fetch_ctx.check(L.csa_part_positions(fetch_ctx.h, store, lists(u)[0], a, h, ask.data_ptr()))
+                        fetch_ctx.sync()
+                    sc, ask_b, order = bucket(ask[:a], None, True, fetch_ctx)
+                    rc_ = [int(c) for c in _gather_small(np.array(sc, np.int64))[:, rank]] if world > 1 else sc
+                    sent(sc, 8)
+                    asked = _exchange(ask_b, sc, rc_)
+                    m = int(asked.numel())
+                    answers = torch.empty(m + 8, dtype=torch.int32, device=dev)
+                    if m:
+                        mine.synchronize()
+                        fetch_ctx.check(L.csa_rank_shard_read(fetch_ctx.h, R.data_ptr(), lo, cnt, asked.data_ptr(), m, answers.data_ptr()))
+                        fetch_ctx.sync()
+                    sent(rc_, 4)
+                    back = _exchange(answers, rc_, sc)
+                    second = None
+                    if a:
+                        second = torch.empty(a + 8, dtype=torch.int32, device=dev)
+                        mine.synchronize()
+                        fetch_ctx.check(L.csa_unbucket(fetch_ctx.h, order.data_ptr(), back.data_ptr(), a, second.data_ptr()))
+                        fetch_ctx.sync()
+                    del ask, ask_b, asked, answers, back, order
+                    lap("doubling_fetch", t1)
+                    t1 = time.perf_counter()
+                    if running is not None:
+                        running.join()
+                        if failures:
+                            raise failures[0]
+                    lap("doubling_wait_for_rank", t1)
+                    running = None
+                    if a:
+                        running = threading.Thread(target=rank_job, args=(u, a, second, failures))
+                        running.start()
                 t1 = time.perf_counter()
-                ask = torch.empty(a + 8, dtype=torch.int64, device=dev)
-                if a:
-                    torch.cuda.synchronize(dev)
-                    ctx.check(L.csa_part_positions(ctx.h, store, lists(u)[0], a, h, ask.data_ptr()))
-                    ctx.sync()
-                sc, ask_b, order = bucket(ask[:a], None, True)
-                rc_ = [int(c) for c in _gather_small(np.array(sc, np.int64))[:, rank]] if world > 1 else sc
-                sent(sc, 8)
-                asked = _exchange(ask_b, sc, rc_)
-                del ask_b
-                m = int(asked.numel())
-                answers = torch.empty(m + 8, dtype=torch.int32, device=dev)
-                if m:
-                    torch.cuda.synchronize(dev)
-                    ctx.check(L.csa_rank_shard_read(ctx.h, R.data_ptr(), lo, cnt, asked.data_ptr(), m, answers.data_ptr()))
-                    ctx.sync()
-                sent(rc_, 4)
-                back = _exchange(answers, rc_, sc)
-                del asked, answers
-                mark("doubling_fetch", t1)
+                if running is not None:
+                    running.join()
+                    if failures:
+                        raise failures[0]
+                lap("doubling_wait_for_rank", t1)
                 t1 = time.perf_counter()
-                if a:
-                    second = torch.empty(a + 8, dtype=torch.int32, device=dev)
-                    torch.cuda.synchronize(dev)
-                    ctx.check(L.csa_unbucket(ctx.h, order.data_ptr(), back.data_ptr(), a, second.data_ptr()))
-                    lp, rp = lists(u)
-                    pin, pout = Part(lp, rp, a, u), PartResult(lp, rp, 0, 0)
-                    ctx.check(L.csa_rank_gen_ranks(ctx.h, store, ctypes.byref(pin), second.data_ptr(), ctypes.byref(pout)))
-                    ctx.sync()
-                    active[u] = int(pout.active)
-                    del second
-                del back, order
-                mark("doubling_rank", t1)
-            t1 = time.perf_counter()
-            flush_outbox(box)
-            del box
-            mark("doubling_ranks_to_owners", t1)
-            total_active = total_over_ranks(sum(active.values()))
-            h *= 2
-            gens += 1
-            if gens > 45:
-                raise api.CascadeError(5, "doubling did not terminate")
+                flush_outbox(box)
+                del box
+                lap("doubling_ranks_to_owners", t1)
+                total_active = total_over_ranks(sum(active.values()))
+                h *= 2
+                gens += 1
+                if gens > 45:
+                    raise api.CascadeError(5, "doubling did not terminate")
+        finally:
+            fetch_ctx.close()
         info["generations"] = gens
         mark("doubling", t0)
 
