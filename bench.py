@@ -790,6 +790,25 @@ def run_c4_sharded(args):
                 infos.append(info)
     info = infos[-1]
     sec = sum(times) / len(times)
+    # once more with the parts left in the GPUs' memory (each rank one range of the array), as a sharded index wants them
+    resident = None
+    if info["lists_on_device"] or world > 1:
+        ok = torch.tensor([int(bool(info["lists_on_device"]))], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            dsegs, dinfo = multi.build_sa_sharded(ctx, mine, n, p, part_suffixes=ps, host=host, output="device")
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            if world > 1:
+                dt = _max_over_ranks(dt, dev)
+            same = all(torch.equal(d[2].cpu(), h_[2]) for d, h_ in zip(dsegs, segs))
+            resident = {"ms_per_step": 1e3 * dt, "value": n / dt, "unit": UNIT, "equal_to_the_host_copy_rank0": bool(same), "output_ms_rank0": dinfo["ms"]["output"]}
+            del dsegs
     del mine
     torch.cuda.empty_cache()
     v = None
@@ -879,7 +898,7 @@ def run_c4_sharded(args):
                                    "memory; max over ranks",
                           "clocks": clocks.summary(), "partitions": info["partitions"], "parts": info["parts"], "generations": info["generations"],
                           "active_per_generation": info["active_per_generation"], "phases_ms_rank0": info["ms"], "gpu_launches": info["launches"],
-                          "nvlink_bytes_sent_all_ranks": sent_all,
+                          "nvlink_bytes_sent_all_ranks": sent_all, "array_left_on_the_devices": resident,
                           "validated": bool(v["ok"]) if "out_of_order" in v else "in part: too large for one device to check in full", "validation": v}))
     if world > 1:
         dist.barrier()

@@ -536,17 +536,19 @@ def _halo_from_next(local, valid, k):
     return out
 
 
-def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=None, lists_on_device=None, host=None):
+def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, window_suffixes=None, lists_on_device=None, host=None, output="host"):
     """The part-at-a-time build with NOTHING replicated: rank r of the process group holds the symbols of its stretch of
-    positions only (shard_bounds), and the same stretch of the partition ids and of the rank store; parts are owned as in
-    build_sa_streamed_multi (u mod world). The GPU that holds a stretch of the text makes the generation-0 keys of its positions
+    positions only (shard_bounds), and the same stretch of the partition ids and of the rank store; a rank owns a run of
+    consecutive parts (part u belongs to rank u * world // parts), so its parts in final order are ONE range of the suffix array. The GPU that holds a stretch of the text makes the generation-0 keys of its positions
     and sends (lane, key) to the parts' owners; in a later generation the owner of a part asks the owners of the positions
     h further on for their ranks, and new ranks travel back to the positions' owners as messages. Device memory per GPU:
     8 n / world bytes (2 text + 2 partition ids until generation 0 is over + 4 ranks) plus the lists of its parts (9 bytes per
     suffix, on the device while they fit, else in pinned host memory) plus one part's workspace and the windows in flight
     (window_suffixes per rank and window of generation 0, 52 bytes each; None: what the free memory allows).
     text_shard: device uint16 tensor with this rank's symbols first. `host` may be a dict that keeps the pinned buffers between
-    calls. Returns (segments, info) as build_sa_streamed_multi."""
+    calls. output = "host": the parts end in pinned host memory; "device": they stay in this GPU's memory (the lists must be
+    resident), which is where a ShardedIndex over the same ranks wants its slice of the array.
+    Returns (segments, info) as build_sa_streamed_multi."""
     import time
     from ._lib import Part, PartResult, c_vp
     L = ctx.L
@@ -628,7 +630,7 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
     if part_off[-1] != n:
         raise api.CascadeError(5, "partition sizes do not add up to n")
     size = [int(part_off[u + 1] - part_off[u]) for u in range(parts)]
-    owner = [u % world for u in range(parts)]
+    owner = [u * world // parts for u in range(parts)]
     own = [u for u in range(parts) if owner[u] == rank]
     mark("partition_ids", t0)
 
@@ -641,6 +643,7 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
     try:
         # how many positions of every part each rank holds
         local_d = torch.zeros(parts, dtype=torch.int64, device=dev)
+        torch.cuda.synchronize(dev)             # the zeros are written on torch's stream, the counts on the context's
         if cnt > 0:
             ctx.check(L.csa_part_sizes(ctx.h, store, 0, cnt, parts, local_d.data_ptr()))
             ctx.sync()
@@ -683,9 +686,14 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                 host["lanes"] = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
                 host["ranks"] = torch.empty(own_total + 16, dtype=torch.int32).pin_memory()
             lanes_all, ranks_all = host["lanes"], host["ranks"]
-        if host.get("out") is None or host["out"].numel() < 5 * own_total + 64:
-            host["out"] = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
-        out_lanes = host["out"]
+        if output == "device":
+            if not lists_on_device:
+                raise api.CascadeError(3, "the array can stay on the device only where the parts' lists are resident there")
+            out_lanes = lanes_all                   # every part is put into its final order in place
+        else:
+            if host.get("out") is None or host["out"].numel() < 5 * own_total + 64:
+                host["out"] = torch.empty(5 * own_total + 64, dtype=torch.uint8).pin_memory()
+            out_lanes = host["out"]
         info["lists_on_device"] = bool(lists_on_device)
 
         def lists(u):
@@ -937,7 +945,9 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
             ctx.check(L.csa_rank_order(ctx.h, lp, rp, size[u], out_lanes.data_ptr() + 5 * own_first[u]))
         ctx.sync()
         mark("output", t0)
-        del lanes_all, ranks_all
+        del ranks_all
+        if output != "device":
+            del lanes_all
     finally:
         L.csa_store_destroy(store)
     info["ms"]["total"] = 1e3 * (time.perf_counter() - t_all)

@@ -81,7 +81,7 @@ def test_sharded_build_equals_the_single_gpu_build(world, n, p, kind, policy):
     procs = [ctx.Process(target=_worker, args=(r, world, port, n, p, kind, policy, q)) for r in range(world)]
     for pr in procs:
         pr.start()
-    res = sorted((q.get(timeout=240) for _ in range(world)), key=lambda x: x[0])
+    res = sorted(_collect(procs, q, world), key=lambda x: x[0])
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
@@ -177,6 +177,25 @@ def test_a_rank_that_fails_alone_takes_every_rank_out_of_the_build():
     assert all(r[2] < 30 and r[3] for r in res), res
 
 
+def _collect(procs, q, world, limit=240):
+    """One result per rank from the queue. A rank that fails leaves the others waiting in a collective: they are ended at once
+    instead of after their timeouts."""
+    import queue as queue_module
+    import time as time_module
+    res, deadline = [], time_module.time() + limit
+    while len(res) < world:
+        try:
+            res.append(q.get(timeout=1))
+        except queue_module.Empty:
+            failed = [pr for pr in procs if pr.exitcode not in (None, 0)]
+            if failed or time_module.time() > deadline:
+                for pr in procs:
+                    if pr.is_alive():
+                        pr.terminate()
+                pytest.fail("a rank failed" if failed else "the ranks did not finish in time")
+    return res
+
+
 def _streamed_worker(rank, world, port, n, p, part_suffixes, q):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
@@ -214,7 +233,7 @@ def test_part_at_a_time_build_over_several_ranks(world):
     procs = [ctx.Process(target=_streamed_worker, args=(r, world, port, n, p, part_suffixes, q)) for r in range(world)]
     for pr in procs:
         pr.start()
-    res = sorted((q.get(timeout=240) for _ in range(world)), key=lambda x: x[0])
+    res = sorted(_collect(procs, q, world), key=lambda x: x[0])
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
@@ -246,6 +265,13 @@ def _sharded_worker(rank, world, port, n, p, part_suffixes, window, on_device, o
         assert lib().csa_debug_set(4, offset) == 0
     try:
         segs, info = multi.build_sa_sharded(ctx, mine, n, p, part_suffixes=part_suffixes, window_suffixes=window, lists_on_device=on_device)
+        if on_device:
+            # the same build with the parts left in device memory: the same bytes, and one range of the array per rank
+            dsegs, _ = multi.build_sa_sharded(ctx, mine, n, p, part_suffixes=part_suffixes, window_suffixes=window, lists_on_device=True, output="device")
+            assert len(dsegs) == len(segs)
+            for (f, c, t), (df, dc, dt) in zip(segs, dsegs):
+                assert (f, c) == (df, dc) and dt.is_cuda and torch.equal(dt.cpu(), t)
+            assert all(a[0] + a[1] == b[0] for a, b in zip(dsegs[:-1], dsegs[1:])), "a rank's parts are consecutive ranges"
     finally:
         lib().csa_debug_set(4, 0)
     ref = None
@@ -277,7 +303,7 @@ def test_build_with_text_and_rank_store_sharded_by_position(world, n, p, part_su
     procs = [ctx.Process(target=_sharded_worker, args=(r, world, port, n, p, part_suffixes, window, on_device, offset, q)) for r in range(world)]
     for pr in procs:
         pr.start()
-    res = sorted((q.get(timeout=240) for _ in range(world)), key=lambda x: x[0])
+    res = sorted(_collect(procs, q, world), key=lambda x: x[0])
     for pr in procs:
         pr.join(timeout=120)
         assert pr.exitcode == 0
