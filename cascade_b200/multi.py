@@ -826,8 +826,12 @@ def build_sa_sharded(ctx, text_shard, n, p=4096, seed=0, part_suffixes=1 << 27, 
                     c = int(held[g, u])
                     pieces_l.append(got_lanes[5 * a:5 * (a + c)])
                     pieces_k.append(got_keys[a:a + c])
-                pl = torch.cat(pieces_l + [torch.zeros(64, dtype=torch.uint8, device=dev)])
-                pk = torch.cat(pieces_k + [torch.zeros(8, dtype=torch.int64, device=dev)])
+                filled = [g for g in range(world) if int(held[g, u]) > 0]
+                if len(filled) == 1:                   # the part's records came from one rank: they lie in one piece already
+                    pl, pk = pieces_l[filled[0]], pieces_k[filled[0]]
+                else:
+                    pl = torch.cat(pieces_l + [torch.zeros(64, dtype=torch.uint8, device=dev)])
+                    pk = torch.cat(pieces_k + [torch.zeros(8, dtype=torch.int64, device=dev)])
                 torch.cuda.synchronize(dev)
                 lp, rp = lists(u)
                 pin, pout = Part(pl.data_ptr(), None, size[u], u), PartResult(lp, rp, 0, 0)
