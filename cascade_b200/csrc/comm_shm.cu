@@ -141,7 +141,7 @@ void* attach_object(const char* name, size_t bytes, uint32_t rank, uint32_t worl
             {
                 Shm_Header* h = static_cast<Shm_Header*>(p);
                 Shm_Slot* slots = reinterpret_cast<Shm_Slot*>(h + 1);
-                // A job that has not finished its first all-gather: nobody is past round 1 and this rank has not published.
+                // A job that has not finished its first all-gather: nobody is past the first exchange and this rank has not published.
                 bool fresh = h->magic.load(std::memory_order_acquire) == SHM_LIVE && h->world == world && slots[rank].seq.load(std::memory_order_acquire) == 0;
                 for(uint32_t g = 0; fresh && g < world; ++g) fresh = slots[g].seq.load(std::memory_order_acquire) <= 1;
                 if(fresh) return p;
