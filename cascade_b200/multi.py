@@ -504,7 +504,7 @@ def _gather_small(t):
     world = dist.get_world_size() if dist.is_initialized() else 1
     if world == 1:
         return t[None, :].copy()
-    dev = torch.device("cuda", torch.cuda.current_device())
+    dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
     mine = torch.from_numpy(np.ascontiguousarray(t, dtype=np.int64)).to(dev)
     out = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(out, mine)

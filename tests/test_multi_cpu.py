@@ -253,3 +253,70 @@ def test_a_missing_rank_makes_the_others_fail_within_the_limit():
         assert rc == 6 and time.perf_counter() - t0 < 10.0
     finally:
         del os.environ["CASCADE_COMM_TIMEOUT_S"]
+
+
+def test_stretches_are_whole_address_buckets_and_cover_the_text():
+    from cascade_b200 import multi
+    for n in (1, 63, 64, 65, 1000, 700_001, 2_000_000_000, 4_500_000_000, 16_000_000_000, (1 << 40) - 1):
+        begin, end = multi.address_bits(n)
+        assert 0 <= begin < end and (n - 1) >> end == 0 and end - begin <= 16
+        assert end - begin <= 8 or begin > 9, "two digit passes only for texts whose one-pass buckets would pass the L2"
+        for world in (1, 2, 3, 4, 8):
+            bounds = [multi.shard_bounds(n, world, r) for r in range(world)]
+            stretch = bounds[0][0]
+            assert stretch % 64 == 0 and stretch % (1 << begin) == 0 and stretch * world >= n
+            at = 0
+            for s, lo, hi in bounds:
+                assert s == stretch and lo == min(n, at) and lo <= hi <= n and hi - lo <= stretch
+                at += stretch
+            assert bounds[-1][2] == n and sum(hi - lo for _, lo, hi in bounds) == n
+
+
+def _sharded_host_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from cascade_b200 import multi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # every rank's view of small per-rank arrays
+    seen = multi._gather_small(np.array([rank, 10 * rank + 1], np.int64))
+    # the entries that follow a rank's stretch: rank 0 holds 5 entries, rank 1 two, rank 2 none, rank 3 four
+    valid = [5, 2, 0, 4][rank]
+    local = torch.arange(100 * rank, 100 * rank + 8, dtype=torch.int16)
+    halo = multi._halo_from_next(local, valid, 4)
+    # runs per destination: rank r sends (d + 1) entries worth r * 1000 + d to rank d, twice as many bytes when width is 2
+    counts = [d + 1 for d in range(world)]
+    incoming = [rank + 1] * world
+    send = torch.cat([torch.full((d + 1,), rank * 1000 + d, dtype=torch.int64) for d in range(world)])
+    got = multi._exchange(send, counts, incoming)
+    send2 = torch.cat([torch.full((2 * (d + 1),), rank * 1000 + d, dtype=torch.int32) for d in range(world)])
+    got2 = multi._exchange(send2, counts, incoming, width=2)
+    q.put((rank, seen.tolist(), halo.tolist(), got.tolist(), got2.tolist()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_halo_exchange_and_runs_between_four_gloo_ranks():
+    """The host-side pieces of the build with text and rank store sharded by position: what every rank learns of the others'
+    counts, the entries that follow a stretch (taken from as many following ranks as it needs, zeros past the end), and the
+    all-to-all of per-destination runs."""
+    world, port = 4, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_sharded_host_worker, args=(r, world, port, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    for rank, seen, halo, got, got2 in res:
+        assert seen == [[r, 10 * r + 1] for r in range(world)]
+        want = [s * 1000 + rank for s in range(world) for _ in range(rank + 1)]
+        assert got == want and got2 == [x for x in want for _ in range(2)]
+    assert res[0][2] == [100, 101, 300, 301]           # two entries of rank 1, none of rank 2, then rank 3's
+    assert res[1][2] == [300, 301, 302, 303]
+    assert res[2][2] == [300, 301, 302, 303]
+    assert res[3][2] == [0, 0, 0, 0]                   # nothing follows the last stretch
