@@ -733,7 +733,7 @@ def run_c4(args):
         print(json.dumps({"metric": METRIC, "value": n / sec, "unit": UNIT, "n_gpus": world, "steps": len(times), "warmup": 1, "ms_per_step": 1e3 * sec,
                           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
                           "config": {"workload": "part-at-a-time build with the suffix lists in pinned host memory: a scaled-down stand-in for BASELINE config 4 "
-                                                 "(64e9 tokens with NVMe spill, which is not built)", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
+                                                 "(64e9 tokens on 1-8 GPUs under a 512 GB host cap); text and rank store on every GPU (--workload c4-sharded shards them)", "tokens": n, "beyond_2_32_positions": n > (1 << 32),
                                      "partitions_asked": p, "part_suffixes": ps, "mean_doc": C2_MEAN_DOC, "vocab": 50257, "seed": 0, "gpus": world,
                                      "lists_on_device_rank0": info["lists_on_device"], "lists_on_host_rank0": info["lists_on_host"],
                                      "list_budget_gb": "what is free" if args.list_budget_gb < 0 else args.list_budget_gb},
