@@ -320,3 +320,27 @@ def test_halo_exchange_and_runs_between_four_gloo_ranks():
     assert res[1][2] == [300, 301, 302, 303]
     assert res[2][2] == [300, 301, 302, 303]
     assert res[3][2] == [0, 0, 0, 0]                   # nothing follows the last stretch
+
+
+def test_partitions_are_grouped_into_parts_in_order():
+    """Parts are runs of whole partitions in partition order, each within the bound unless one partition alone passes it; the
+    ranks of a sharded build own runs of consecutive parts whose sizes differ by at most one part."""
+    import pytest
+    from cascade_b200 import api, multi
+    rng = np.random.default_rng(5)
+    for p, bound in ((1, 100), (64, 1000), (300, 50), (4096, 1 << 20)):
+        sizes = rng.integers(0, 400, p).astype(np.uint64)
+        part_of_pid, part_off = multi.group_partitions_into_parts(sizes, bound)
+        parts = len(part_off) - 1
+        assert part_off[0] == 0 and part_off[-1] == int(sizes.sum()) and np.all(np.diff(part_of_pid.astype(np.int64)) >= 0)
+        assert int(part_of_pid[-1]) == parts - 1 and np.all(np.diff(part_of_pid.astype(np.int64)) <= 1)
+        for u in range(parts):
+            inside = sizes[part_of_pid == u]
+            assert int(inside.sum()) == part_off[u + 1] - part_off[u]
+            assert int(inside.sum()) <= bound or int(np.count_nonzero(inside)) == 1
+        for world in (1, 2, 3, 8):
+            owner = [u * world // parts for u in range(parts)]
+            held = np.bincount(owner, minlength=world)
+            assert owner == sorted(owner) and held.max() - held.min() <= 1
+    with pytest.raises(api.CascadeError):
+        multi.group_partitions_into_parts(np.array([1 << 31], np.uint64), 1 << 27)
